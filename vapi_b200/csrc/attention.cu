@@ -1,0 +1,315 @@
+// Paged grouped-query attention over the block table, for prompt portions and decode
+// tokens in one launch.  This is the general kernel: any head_dim that is a multiple of
+// 16 up to 256, any number of heads and groups, an optional sliding window, float or
+// bfloat16 storage, all arithmetic in float.  It is the attention of the true 32-bit
+// path, and of the serving path wherever no faster specialisation applies.
+//
+// Semantics of the reference's paged attention
+// (crates/vapi-backend-candle/src/attention.rs:90-163): a sequence brings len_q queries
+// over len_k keys; query j sits at position p = len_k - len_q + j and sees keys i <= p
+// (and i > p - window when a window is set); scores are scale * q.k in float, softmax in
+// float, q head h reads kv head h / (nh / nkv).
+//
+// Work decomposition.  For one (sequence, kv head) the rows are the pairs (query token,
+// q head of the group), row = token * n_rep + rep, cut into tiles of 16; a block of four
+// warps takes one tile and walks the keys in tiles of 32 that all its rows share.  Warp w
+// owns rows w, w+4, w+8, w+12 of the tile entirely (scores, running max and sum, output),
+// so the only block-wide synchronisation is around the key/value tile in shared memory.
+// With `splits` > 1 the key tiles of a row tile are divided among `splits` blocks that
+// write unnormalised partial results to scratch memory, and a second kernel combines them
+// in a fixed order.
+#include "common.cuh"
+
+using namespace vapi;
+
+constexpr int ATT_ROWS = 16;
+constexpr int ATT_BK = 32;
+constexpr int ATT_WARPS = 4;
+constexpr int ATT_RPW = ATT_ROWS / ATT_WARPS;  // rows per warp
+
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    using type = float4;
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    using type = uint2;
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+        const float2 fa = __bfloat1622float2(a), fb = __bfloat1622float2(b);
+        return make_float4(fa.x, fa.y, fb.x, fb.y);
+    }
+};
+
+template <typename T, int DMAX>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+paged_attention_kernel(const T* __restrict__ q, long long q_row_stride,
+                       const T* __restrict__ cache, const int* __restrict__ block_table,
+                       int table_stride, const int* __restrict__ cu_q,
+                       const int* __restrict__ seqlens_k, T* __restrict__ out,
+                       float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv,
+                       int d, int page_size, int num_pages, float scale, int window, int splits,
+                       int* __restrict__ status) {
+    constexpr int DPL = DMAX / 32;
+    extern __shared__ __align__(16) float smem[];
+    const int ld = d + 4;  // row pitch in floats: keeps float4 alignment, spreads banks
+    float* Qs = smem;                     // [ATT_ROWS][ld]
+    float* Ks = Qs + ATT_ROWS * ld;       // [ATT_BK][ld]
+    float* Vs = Ks + ATT_BK * ld;         // [ATT_BK][ld]
+    float* Ps = Vs + ATT_BK * ld;         // [ATT_WARPS][ATT_RPW][ATT_BK]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int s = blockIdx.z / splits, sp = blockIdx.z - s * splits;
+    const int g = blockIdx.y;
+    const int q0 = cu_q[s], qlen = cu_q[s + 1] - q0, klen = seqlens_k[s];
+    const int n_rep = nh / nkv;
+    const int rows_total = qlen * n_rep;
+    const int tile_start = blockIdx.x * ATT_ROWS;
+    if (tile_start >= rows_total) return;
+    const int last_row = min(rows_total, tile_start + ATT_ROWS) - 1;
+    const int base_pos = klen - qlen;
+    const int p_min = base_pos + tile_start / n_rep;
+    const int p_max = base_pos + last_row / n_rep;
+    const int key_lo = window > 0 ? max(0, p_min - window + 1) : 0;
+    const int kt_lo = key_lo / ATT_BK, kt_hi = p_max / ATT_BK;
+    const int nt = kt_hi - kt_lo + 1;
+    const int chunk = (nt + splits - 1) / splits;
+    const int kt_begin = kt_lo + sp * chunk;
+    const int kt_end = min(kt_hi + 1, kt_begin + chunk);
+
+    // queries of the tile, scaled, as float
+    for (int idx = threadIdx.x; idx < ATT_ROWS * (d / 4); idx += blockDim.x) {
+        const int lr = idx / (d / 4), c4 = idx - lr * (d / 4);
+        const int rr = tile_start + lr;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (rr < rows_total) {
+            const int tok = rr / n_rep, h = g * n_rep + (rr - tok * n_rep);
+            v = Vec4<T>::load(q + (size_t)(q0 + tok) * q_row_stride + (size_t)h * d + c4 * 4);
+            v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+        }
+        *reinterpret_cast<float4*>(Qs + lr * ld + c4 * 4) = v;
+    }
+
+    int row_pos[ATT_RPW];
+    bool row_ok[ATT_RPW];
+    float m[ATT_RPW], l[ATT_RPW], acc[ATT_RPW][DPL];
+#pragma unroll
+    for (int a = 0; a < ATT_RPW; ++a) {
+        const int rr = tile_start + warp + ATT_WARPS * a;
+        row_ok[a] = rr < rows_total;
+        row_pos[a] = base_pos + (row_ok[a] ? rr / n_rep : 0);
+        m[a] = -INFINITY;
+        l[a] = 0.f;
+#pragma unroll
+        for (int c = 0; c < DPL; ++c) acc[a][c] = 0.f;
+    }
+
+    const int* bt = block_table + (size_t)s * table_stride;
+    for (int kt = kt_begin; kt < kt_end; ++kt) {
+        __syncthreads();  // the previous tile is no longer read (and Qs is written)
+        for (int idx = threadIdx.x; idx < ATT_BK * (d / 4); idx += blockDim.x) {
+            const int jj = idx / (d / 4), c4 = idx - jj * (d / 4);
+            const int j = kt * ATT_BK + jj;
+            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+            if (j >= key_lo && j <= p_max && j < klen) {  // keys no row of the tile can see stay zero
+                const int page = bt[j / page_size];
+                if (page < 0 || page >= num_pages) {
+                    if (status) atomicExch(status, 4);
+                } else {
+                    const size_t base = (((size_t)page * 2) * nkv + g) * page_size * (size_t)d +
+                                        (size_t)(j % page_size) * d + c4 * 4;
+                    kv = Vec4<T>::load(cache + base);
+                    vv = Vec4<T>::load(cache + base + (size_t)nkv * page_size * d);
+                }
+            }
+            *reinterpret_cast<float4*>(Ks + jj * ld + c4 * 4) = kv;
+            *reinterpret_cast<float4*>(Vs + jj * ld + c4 * 4) = vv;
+        }
+        __syncthreads();
+
+        // scores of this warp's rows against key `lane` of the tile
+        float sc[ATT_RPW];
+#pragma unroll
+        for (int a = 0; a < ATT_RPW; ++a) sc[a] = 0.f;
+        const float4* k4 = reinterpret_cast<const float4*>(Ks + lane * ld);
+        for (int c4 = 0; c4 < d / 4; ++c4) {
+            const float4 kv = k4[c4];
+#pragma unroll
+            for (int a = 0; a < ATT_RPW; ++a) {
+                if (!row_ok[a]) continue;
+                const float4 qv = *reinterpret_cast<const float4*>(Qs + (warp + ATT_WARPS * a) * ld + c4 * 4);
+                sc[a] = fmaf(qv.x, kv.x, sc[a]);
+                sc[a] = fmaf(qv.y, kv.y, sc[a]);
+                sc[a] = fmaf(qv.z, kv.z, sc[a]);
+                sc[a] = fmaf(qv.w, kv.w, sc[a]);
+            }
+        }
+        const int j = kt * ATT_BK + lane;
+        float* pw = Ps + (warp * ATT_RPW) * ATT_BK;
+#pragma unroll
+        for (int a = 0; a < ATT_RPW; ++a) {
+            if (!row_ok[a]) continue;  // uniform across the warp
+            const bool vis = j <= row_pos[a] && j < klen && (window <= 0 || j > row_pos[a] - window);
+            const float sv = vis ? sc[a] : -INFINITY;
+            const float m_new = fmaxf(m[a], warp_max(sv));
+            float p = 0.f, alpha = 1.f;
+            if (m_new != -INFINITY) {
+                alpha = expf(m[a] - m_new);  // m[a] = -inf gives 0
+                p = vis ? expf(sv - m_new) : 0.f;
+            }
+            l[a] = l[a] * alpha + warp_sum(p);
+            m[a] = m_new;
+#pragma unroll
+            for (int c = 0; c < DPL; ++c) acc[a][c] *= alpha;
+            pw[a * ATT_BK + lane] = p;
+        }
+        __syncwarp();
+        for (int jj = 0; jj < ATT_BK; ++jj) {
+            float vcol[DPL];
+#pragma unroll
+            for (int c = 0; c < DPL; ++c) {
+                const int col = lane + 32 * c;
+                vcol[c] = col < d ? Vs[jj * ld + col] : 0.f;
+            }
+#pragma unroll
+            for (int a = 0; a < ATT_RPW; ++a) {
+                if (!row_ok[a]) continue;
+                const float p = pw[a * ATT_BK + jj];
+#pragma unroll
+                for (int c = 0; c < DPL; ++c) acc[a][c] = fmaf(p, vcol[c], acc[a][c]);
+            }
+        }
+        __syncwarp();
+    }
+
+#pragma unroll
+    for (int a = 0; a < ATT_RPW; ++a) {
+        if (!row_ok[a]) continue;
+        const int rr = tile_start + warp + ATT_WARPS * a;
+        const int tok = rr / n_rep, h = g * n_rep + (rr - tok * n_rep);
+        const size_t grow = (size_t)(q0 + tok) * nh + h;
+        if (splits == 1) {
+            const float inv = l[a] > 0.f ? 1.f / l[a] : 0.f;
+#pragma unroll
+            for (int c = 0; c < DPL; ++c) {
+                const int col = lane + 32 * c;
+                if (col < d) out[grow * d + col] = from_f32<T>(acc[a][c] * inv);
+            }
+        } else {
+            float* po = part_o + (grow * splits + sp) * (size_t)d;
+#pragma unroll
+            for (int c = 0; c < DPL; ++c) {
+                const int col = lane + 32 * c;
+                if (col < d) po[col] = acc[a][c];
+            }
+            if (lane == 0) {
+                part_ml[(grow * splits + sp) * 2] = m[a];
+                part_ml[(grow * splits + sp) * 2 + 1] = l[a];
+            }
+        }
+    }
+}
+
+// Combine the partial results of `splits` blocks: one warp per (token, head).
+template <typename T>
+__global__ void attention_combine_kernel(const float* __restrict__ part_o,
+                                         const float* __restrict__ part_ml, T* __restrict__ out,
+                                         long long rows, int d, int splits) {
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    float mx = -INFINITY;
+    for (int sp = 0; sp < splits; ++sp) mx = fmaxf(mx, part_ml[(row * splits + sp) * 2]);
+    float lsum = 0.f;
+    for (int sp = 0; sp < splits; ++sp) {
+        const float ms = part_ml[(row * splits + sp) * 2];
+        if (ms != -INFINITY) lsum += part_ml[(row * splits + sp) * 2 + 1] * expf(ms - mx);
+    }
+    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+    for (int col = lane; col < d; col += 32) {
+        float o = 0.f;
+        for (int sp = 0; sp < splits; ++sp) {
+            const float ms = part_ml[(row * splits + sp) * 2];
+            if (ms != -INFINITY) o += part_o[(row * splits + sp) * (size_t)d + col] * expf(ms - mx);
+        }
+        out[row * d + col] = from_f32<T>(o * inv);
+    }
+}
+
+template <typename T, int DMAX>
+static int launch_attention(const void* q, long long q_row_stride, const void* cache,
+                            const int* block_table, int table_stride, const int* cu_q,
+                            const int* seqlens_k, void* out, float* part_o, float* part_ml,
+                            int num_seqs, int max_q, int nh, int nkv, int d, int page_size,
+                            int num_pages, float scale, int window, int splits, int* status,
+                            cudaStream_t stream) {
+    const int n_rep = nh / nkv;
+    const long long max_rows = (long long)max_q * n_rep;
+    const long long tiles = (max_rows + ATT_ROWS - 1) / ATT_ROWS;
+    if (tiles > 0x7fffffffLL) return fail(-1, "paged_attention: too many query rows");
+    if (nkv > 65535 || (long long)num_seqs * splits > 65535)
+        return fail(-1, "paged_attention: %d kv heads or %d sequences x %d splits exceed the grid",
+                    nkv, num_seqs, splits);
+    const size_t smem = ((size_t)(ATT_ROWS + 2 * ATT_BK) * (d + 4) + ATT_WARPS * ATT_RPW * ATT_BK) * sizeof(float);
+    auto kern = paged_attention_kernel<T, DMAX>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(-101, "paged_attention: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    }
+    dim3 grid((unsigned)tiles, nkv, num_seqs * splits);
+    kern<<<grid, ATT_WARPS * 32, smem, stream>>>(
+        (const T*)q, q_row_stride, (const T*)cache, block_table, table_stride, cu_q, seqlens_k,
+        (T*)out, part_o, part_ml, nh, nkv, d, page_size, num_pages, scale, window, splits, status);
+    return check_launch("paged_attention");
+}
+
+// q: [n, *] with `q_row_stride` elements between tokens, head h at h*d.
+// cache: one layer, [num_pages, 2, nkv, page_size, d].  out: [n, nh*d].
+// splits > 1 needs part_o [n*nh*splits*d] and part_ml [n*nh*splits*2] floats of scratch.
+VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, const void* cache,
+                                     int dtype, const int* block_table, int table_stride,
+                                     const int* cu_q, const int* seqlens_k, void* out,
+                                     float* part_o, float* part_ml, int n, int num_seqs,
+                                     int max_q, int nh, int nkv, int d, int page_size,
+                                     int num_pages, float scale, int window, int splits,
+                                     int* status, cudaStream_t stream) {
+    if (n <= 0 || num_seqs <= 0 || max_q <= 0) return 0;
+    if (d < 16 || d > 256 || d % 16 != 0)
+        return fail(-1, "paged_attention: head_dim %d is not a multiple of 16 in 16..256", d);
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0)
+        return fail(-1, "paged_attention: %d heads are not a multiple of %d kv heads", nh, nkv);
+    if (page_size <= 0 || num_pages <= 0) return fail(-1, "paged_attention: no pages");
+    if (q_row_stride % 4 != 0) return fail(-1, "paged_attention: q row stride %lld is not a multiple of 4", q_row_stride);
+    if (splits < 1) splits = 1;
+    if (splits > 1 && (!part_o || !part_ml))
+        return fail(-1, "paged_attention: %d splits need scratch buffers", splits);
+    int rc;
+#define VAPI_ATT(T, DM)                                                                         \
+    rc = launch_attention<T, DM>(q, q_row_stride, cache, block_table, table_stride, cu_q,       \
+                                 seqlens_k, out, part_o, part_ml, num_seqs, max_q, nh, nkv, d,  \
+                                 page_size, num_pages, scale, window, splits, status, stream)
+    if (dtype == VAPI_F32) {
+        if (d <= 64) VAPI_ATT(float, 64); else if (d <= 128) VAPI_ATT(float, 128); else VAPI_ATT(float, 256);
+    } else if (dtype == VAPI_BF16) {
+        if (d <= 64) VAPI_ATT(__nv_bfloat16, 64); else if (d <= 128) VAPI_ATT(__nv_bfloat16, 128); else VAPI_ATT(__nv_bfloat16, 256);
+    } else {
+        return fail(-2, "paged_attention: unsupported dtype %d", dtype);
+    }
+#undef VAPI_ATT
+    if (rc != 0) return rc;
+    if (splits > 1) {
+        const long long rows = (long long)n * nh;
+        const int wpb = 4;
+        const long long blocks = (rows + wpb - 1) / wpb;
+        if (dtype == VAPI_F32)
+            attention_combine_kernel<float><<<(unsigned)blocks, wpb * 32, 0, stream>>>(part_o, part_ml, (float*)out, rows, d, splits);
+        else
+            attention_combine_kernel<__nv_bfloat16><<<(unsigned)blocks, wpb * 32, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, rows, d, splits);
+        return check_launch("attention_combine");
+    }
+    return 0;
+}
+
+VAPI_EXPORT const char* vapi_last_error() { return error_buffer(); }

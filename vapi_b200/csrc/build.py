@@ -1,0 +1,180 @@
+"""Builds the CUDA sources of this package for sm_100a, one shared library per source.
+
+Each ``<name>.cu`` becomes ``_build/lib<name>-<hash>.so`` next to it, where the hash covers
+the source, the shared headers and the compiler flags, so a stale library is never picked
+up.  A library is built the first time something asks for it, which means a program only
+compiles what the model it runs needs.  While nvcc runs, a line is printed to stderr now and
+then so that a first call does not look hung.
+
+The build needs nothing but ``nvcc``: the libraries export plain C functions that take raw
+device pointers, and they are loaded with ``ctypes``.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from typing import Dict, List, Optional
+
+CSRC_DIR = os.path.dirname(os.path.abspath(__file__))
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC",
+                "-Xcompiler", "-fvisibility=hidden"]
+#: extra nvcc flags and libraries per source
+EXTRA: Dict[str, List[str]] = {}
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def sources() -> List[str]:
+    """Names (without .cu) of every kernel source of the package."""
+    return sorted(f[:-3] for f in os.listdir(CSRC_DIR) if f.endswith(".cu"))
+
+
+def find_nvcc() -> str:
+    cands = [os.environ.get("VAPI_NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"]
+    home = os.environ.get("CUDA_HOME") or os.environ.get("CUDA_PATH")
+    if home:
+        cands.insert(1, os.path.join(home, "bin", "nvcc"))
+    for c in cands:
+        if c and os.path.isfile(c) and os.access(c, os.X_OK):
+            return c
+    raise BuildError("nvcc was not found (set VAPI_NVCC or CUDA_HOME); the CUDA kernels of "
+                     "vapi_b200 cannot be built and there is no fallback")
+
+
+def _headers() -> List[str]:
+    return sorted(os.path.join(CSRC_DIR, f) for f in os.listdir(CSRC_DIR)
+                  if f.endswith((".cuh", ".h")))
+
+
+def _digest(name: str) -> str:
+    h = hashlib.sha256()
+    for path in [os.path.join(CSRC_DIR, name + ".cu")] + _headers():
+        with open(path, "rb") as f:
+            h.update(f.read())
+        h.update(b"\0")
+    h.update(" ".join(ARCH_FLAGS + COMMON_FLAGS + EXTRA.get(name, [])).encode())
+    return h.hexdigest()[:12]
+
+
+def _build_dirs() -> List[str]:
+    """Where a library may live: in the tree first, else a per-user temporary folder."""
+    dirs = []
+    env = os.environ.get("VAPI_BUILD_DIR")
+    if env:
+        dirs.append(env)
+    dirs.append(os.path.join(CSRC_DIR, "_build"))
+    dirs.append(os.path.join(tempfile.gettempdir(), f"vapi_b200-build-{os.getuid()}"))
+    return dirs
+
+
+def library_path(name: str) -> Optional[str]:
+    """Path of an up-to-date built library for ``name`` or None."""
+    fname = f"lib{name}-{_digest(name)}.so"
+    for d in _build_dirs():
+        p = os.path.join(d, fname)
+        if os.path.isfile(p):
+            return p
+    return None
+
+
+def _writable_dir() -> str:
+    last = None
+    for d in _build_dirs():
+        try:
+            os.makedirs(d, exist_ok=True)
+            probe = os.path.join(d, f".probe-{os.getpid()}-{threading.get_ident()}")
+            with open(probe, "w"):
+                pass
+            os.remove(probe)
+            return d
+        except OSError as e:  # read-only checkout: try the next place
+            last = e
+    raise BuildError(f"no writable folder for built kernels (tried {_build_dirs()}): {last}")
+
+
+def build(name: str, verbose: bool = True) -> str:
+    """Build one source if needed and return the library path."""
+    src = os.path.join(CSRC_DIR, name + ".cu")
+    if not os.path.isfile(src):
+        raise BuildError(f"no kernel source {src}")
+    have = library_path(name)
+    if have:
+        return have
+    nvcc = find_nvcc()
+    out_dir = _writable_dir()
+    out = os.path.join(out_dir, f"lib{name}-{_digest(name)}.so")
+    tmp = out + f".tmp{os.getpid()}"
+    cmd = [nvcc] + ARCH_FLAGS + COMMON_FLAGS + ["-I", CSRC_DIR] + EXTRA.get(name, []) + ["-o", tmp, src]
+    env = dict(os.environ)
+    env.setdefault("TMPDIR", tempfile.gettempdir())
+    if verbose:
+        print(f"[vapi_b200] compiling {name}.cu for sm_100a ...", file=sys.stderr, flush=True)
+    t0 = time.time()
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, env=env, cwd=out_dir)
+    done = threading.Event()
+
+    def ticker() -> None:
+        while not done.wait(10.0):
+            if verbose:
+                print(f"[vapi_b200] still compiling {name}.cu ({time.time() - t0:.0f} s)",
+                      file=sys.stderr, flush=True)
+
+    th = threading.Thread(target=ticker, daemon=True)
+    th.start()
+    try:
+        log, _ = proc.communicate()
+    finally:
+        done.set()
+    if proc.returncode != 0:
+        try:
+            os.remove(tmp)
+        except OSError:
+            pass
+        raise BuildError(f"nvcc failed on {name}.cu:\n{' '.join(cmd)}\n{log.decode(errors='replace')}")
+    os.replace(tmp, out)
+    if verbose:
+        print(f"[vapi_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s",
+              file=sys.stderr, flush=True)
+    return out
+
+
+def build_all(verbose: bool = True, jobs: int = 4) -> Dict[str, str]:
+    """Build every source (in parallel) and return name -> path."""
+    names = sources()
+    out: Dict[str, str] = {}
+    errs: List[str] = []
+    lock = threading.Lock()
+    sem = threading.Semaphore(max(1, jobs))
+
+    def one(n: str) -> None:
+        with sem:
+            try:
+                p = build(n, verbose)
+                with lock:
+                    out[n] = p
+            except BuildError as e:
+                with lock:
+                    errs.append(str(e))
+
+    ths = [threading.Thread(target=one, args=(n,)) for n in names]
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join()
+    if errs:
+        raise BuildError("\n".join(errs))
+    return out
+
+
+if __name__ == "__main__":
+    for k, v in build_all().items():
+        print(k, v)

@@ -1,0 +1,89 @@
+// Shared device helpers for the sm_100a kernels of this package.
+//
+// Conventions used by every kernel file:
+//  * the residual stream is float; "activation" tensors are T = float (the true
+//    32-bit path) or __nv_bfloat16 (the serving path); all arithmetic that the
+//    exactness rules name (softmax, norms, rotation angles, the residual sum)
+//    is done in float, with one rounding to T when a value is stored;
+//  * small parameter vectors (norm weights, biases, conv taps) are always float;
+//  * every exported function is extern "C", takes raw device pointers and a
+//    cudaStream_t, validates its sizes on the host, and returns 0 or a negative
+//    error code after recording a message that vapi_last_error() returns.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+#define VAPI_EXPORT extern "C" __attribute__((visibility("default")))
+
+// dtype codes shared with the Python side
+#define VAPI_F32 0
+#define VAPI_BF16 1
+
+namespace vapi {
+
+// ---- error reporting (host) ------------------------------------------------
+inline char* error_buffer() {
+    static thread_local char buf[512] = {0};
+    return buf;
+}
+inline int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(error_buffer(), 512, fmt, ap);
+    va_end(ap);
+    return code;
+}
+inline int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(-100, "%s: launch failed: %s", what, cudaGetErrorString(e));
+    return 0;
+}
+
+// ---- element conversion ------------------------------------------------------
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+// round a float to T's precision and come back (what a store followed by a load gives)
+template <typename T> __device__ __forceinline__ float round_to(float v) {
+    return to_f32(from_f32<T>(v));
+}
+
+// ---- warp / block reductions -----------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` is 33 floats of shared memory.  The order of the additions depends
+// only on blockDim, never on the data or on the rest of the batch.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+}  // namespace vapi

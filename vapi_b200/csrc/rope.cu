@@ -1,0 +1,134 @@
+// Rotary position tables for a step, and the fused per-head q/k RMSNorm + RoPE +
+// paged K/V write that follows the q/k/v projection.
+//
+// Reference behaviour: inv_freq_i = 1 / theta^(2i/d) and angle = p * inv_freq_i in
+// float (crates/vapi-backend-candle/src/models/lfm2.rs:163-183); per-head RMSNorm of
+// q and k, then rotate-half RoPE (pairs (i, i + d/2)), then the roped-normed k and
+// the raw v go to the token's cache slot (lfm2.rs:343-375).  Here the angles, the
+// norm and the rotation are float end to end with one rounding at the store.
+#include "common.cuh"
+
+using namespace vapi;
+
+// cos/sin rows for the step's tokens: [n, half] each, float.
+__global__ void rope_cos_sin_kernel(const int* __restrict__ positions,
+                                    const float* __restrict__ inv_freq,
+                                    float* __restrict__ cosr, float* __restrict__ sinr,
+                                    int n, int half) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n * half) return;
+    const int t = i / half, j = i - t * half;
+    const float a = (float)positions[t] * inv_freq[j];
+    cosr[i] = cosf(a);
+    sinr[i] = sinf(a);
+}
+
+VAPI_EXPORT int vapi_rope_cos_sin(const int* positions, const float* inv_freq, float* cosr,
+                                  float* sinr, int n, int half, cudaStream_t stream) {
+    if (n <= 0 || half <= 0) return 0;
+    const int total = n * half;
+    rope_cos_sin_kernel<<<(total + 255) / 256, 256, 0, stream>>>(positions, inv_freq, cosr, sinr, n, half);
+    return check_launch("rope_cos_sin");
+}
+
+// One warp per (token, head).  Heads are laid out in a qkv row as
+// [q heads | k heads | v heads], each head_dim wide.
+//   q: norm (if qw) -> rope (if cosr) -> written back in place
+//   k: norm (if kw) -> rope (if cosr) -> written to the cache slot (if cache)
+//   v: copied to the cache slot (if cache)
+// Cache layer layout: [num_pages, 2 (k,v), n_kv, page_size, head_dim].
+constexpr int QK_WARPS = 4;
+constexpr int QK_MAX_D = 256;
+
+template <typename T>
+__global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ qw,
+                                          const float* __restrict__ kw, float eps,
+                                          const float* __restrict__ cosr,
+                                          const float* __restrict__ sinr, int rot,
+                                          T* __restrict__ cache,
+                                          const int* __restrict__ slot_mapping, int n, int nh,
+                                          int nkv, int d, int page_size, int num_pages,
+                                          int* __restrict__ status) {
+    __shared__ float sh[QK_WARPS][QK_MAX_D];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = nh + 2 * nkv;
+    const long long item = (long long)blockIdx.x * QK_WARPS + warp;
+    if (item >= (long long)n * heads) return;
+    const int t = (int)(item / heads), h = (int)(item - (long long)t * heads);
+    T* src = qkv + (size_t)t * heads * d + (size_t)h * d;
+    const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
+    const float* w = is_q ? qw : (is_k ? kw : nullptr);
+    const bool rope = (is_q || is_k) && cosr != nullptr;
+    float* s = sh[warp];
+
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) {
+        const float v = to_f32(src[i]);
+        s[i] = v;
+        ss += v * v;
+    }
+    float inv = 1.f;
+    if (w) {
+        ss = warp_sum(ss);
+        inv = rsqrtf(ss / (float)d + eps);
+    }
+    __syncwarp();
+
+    T* dst = nullptr;
+    if (is_q) {
+        dst = src;
+    } else if (cache) {
+        const int slot = slot_mapping[t];
+        const int page = slot / page_size, off = slot - page * page_size;
+        if (slot < 0 || page >= num_pages) {
+            if (lane == 0 && status) atomicExch(status, 2);
+            return;
+        }
+        const int g = is_k ? h - nh : h - nh - nkv;
+        dst = cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * nkv + g) * page_size + off) * d;
+    }
+    if (!dst) return;
+
+    const int half = rot >> 1;
+    for (int i = lane; i < d; i += 32) {
+        float v = w ? s[i] * inv * w[i] : s[i];
+        if (rope && i < rot) {
+            const int j = i < half ? i : i - half;
+            const int pi = i < half ? i + half : i - half;
+            const float pv = w ? s[pi] * inv * w[pi] : s[pi];
+            const float c = cosr[(size_t)t * half + j], sn = sinr[(size_t)t * half + j];
+            v = i < half ? v * c - pv * sn : v * c + pv * sn;
+        }
+        dst[i] = from_f32<T>(v);
+    }
+}
+
+VAPI_EXPORT int vapi_qk_norm_rope_write(void* qkv, int dtype, const float* qw, const float* kw,
+                                        float eps, const float* cosr, const float* sinr, int rot,
+                                        void* cache, const int* slot_mapping, int n, int nh,
+                                        int nkv, int d, int page_size, int num_pages,
+                                        int* status, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (d <= 0 || d > QK_MAX_D || (d % 2) != 0)
+        return fail(-1, "qk_norm_rope_write: head_dim %d is not an even size up to %d", d, QK_MAX_D);
+    if (cosr && (rot <= 0 || rot > d || (rot % 2) != 0))
+        return fail(-1, "qk_norm_rope_write: rotary width %d does not fit head_dim %d", rot, d);
+    if (nh <= 0 || nkv < 0) return fail(-1, "qk_norm_rope_write: bad head counts %d/%d", nh, nkv);
+    if (cache && (page_size <= 0 || num_pages <= 0 || !slot_mapping))
+        return fail(-1, "qk_norm_rope_write: cache given without pages or slot mapping");
+    const long long items = (long long)n * (nh + 2 * nkv);
+    const int blocks = (int)((items + QK_WARPS - 1) / QK_WARPS);
+    if (dtype == VAPI_F32)
+        qk_norm_rope_write_kernel<float><<<blocks, QK_WARPS * 32, 0, stream>>>(
+            (float*)qkv, qw, kw, eps, cosr, sinr, rot, (float*)cache, slot_mapping, n, nh, nkv, d,
+            page_size, num_pages, status);
+    else if (dtype == VAPI_BF16)
+        qk_norm_rope_write_kernel<__nv_bfloat16><<<blocks, QK_WARPS * 32, 0, stream>>>(
+            (__nv_bfloat16*)qkv, qw, kw, eps, cosr, sinr, rot, (__nv_bfloat16*)cache,
+            slot_mapping, n, nh, nkv, d, page_size, num_pages, status);
+    else
+        return fail(-2, "qk_norm_rope_write: unsupported dtype %d", dtype);
+    return check_launch("qk_norm_rope_write");
+}
+
+VAPI_EXPORT const char* vapi_last_error() { return error_buffer(); }

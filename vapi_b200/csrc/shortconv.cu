@@ -1,0 +1,150 @@
+// The gated short convolution between in_proj and out_proj, with its rolling state.
+//
+// Math of the reference (crates/vapi-backend-candle/src/models/lfm2.rs:509-565 and the
+// conv_write / conv_apply kernels, crates/vapi-backend-candle/src/fused.rs:167-233):
+//   h3 = [B | C | x] (+ in_proj bias);  g[t] = B[t] * x[t], rounded to the storage type;
+//   conv[t][c] = sum_k w[k][c] * g[t - (L-1-k)][c] (+ conv bias), g before the start of
+//   the sequence = 0;  y[t] = C[t] * conv[t], one rounding.
+//
+// The reference keeps g per token in paged rows and gathers L-1 predecessors through the
+// block table.  Here each request owns one fixed-size state per conv layer, the last L-1
+// rows of g, [L-1, H] in the storage type.  One kernel serves prompt portions of any
+// length (down to one token, shorter than the state) and decode tokens:
+//   * a token at index i >= L-1 of its portion needs only rows of this step;
+//   * the tokens i < L-1 need the old state.  They are all handled, one after the other,
+//     by the thread of token i == 0, which reads the old state into registers before it
+//     writes the new one: no other thread reads or writes that request's state, so there
+//     is no ordering to arrange between blocks;
+//   * rows of the state that stand for positions before 0 are never read (taken as zero),
+//     so a slot needs no clearing when another request takes it over.
+#include "common.cuh"
+
+using namespace vapi;
+
+constexpr int CONV_LMAX = 8;
+
+template <typename T>
+__device__ __forceinline__ float gate_row(const T* __restrict__ h3, const float* __restrict__ in_bias,
+                                          size_t row, int c, int hidden) {
+    const T* r = h3 + row * 3 * (size_t)hidden;
+    float b = to_f32(r[c]), x = to_f32(r[2 * hidden + c]);
+    if (in_bias) {
+        b += in_bias[c];
+        x += in_bias[2 * hidden + c];
+    }
+    return round_to<T>(b * x);
+}
+
+template <typename T>
+__device__ __forceinline__ void emit(const T* __restrict__ h3, const float* __restrict__ in_bias,
+                                     const float* __restrict__ conv_bias, T* __restrict__ out,
+                                     size_t row, int c, int hidden, float acc) {
+    float cc = to_f32(h3[row * 3 * (size_t)hidden + hidden + c]);
+    if (in_bias) cc += in_bias[hidden + c];
+    if (conv_bias) acc += conv_bias[c];
+    out[row * (size_t)hidden + c] = from_f32<T>(cc * acc);
+}
+
+template <typename T>
+__global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restrict__ in_bias,
+                                 const float* __restrict__ taps,  // [L, H], k = 0 oldest
+                                 const float* __restrict__ conv_bias, T* __restrict__ state,
+                                 long long slot_stride, const int* __restrict__ state_slots,
+                                 const int* __restrict__ tok_seq, const int* __restrict__ cu_q,
+                                 const int* __restrict__ positions, T* __restrict__ out, int n,
+                                 int hidden, int L, int num_slots, int* __restrict__ status) {
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int r = blockIdx.x;
+    if (c >= hidden || r >= n) return;
+    const int s = tok_seq[r];
+    const int r0 = cu_q[s], q = cu_q[s + 1] - r0;
+    const int i = r - r0;
+    float w[CONV_LMAX];
+#pragma unroll
+    for (int k = 0; k < CONV_LMAX; ++k) w[k] = k < L ? taps[(size_t)k * hidden + c] : 0.f;
+
+    if (i >= L - 1) {
+        // every tap lies inside this step's rows
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < CONV_LMAX; ++k)
+            if (k < L) acc += w[k] * gate_row(h3, in_bias, (size_t)(r - (L - 1 - k)), c, hidden);
+        emit(h3, in_bias, conv_bias, out, (size_t)r, c, hidden, acc);
+        return;
+    }
+    if (i != 0) return;  // tokens 1 .. L-2 of a portion belong to the thread of token 0
+
+    const int slot = state_slots[s];
+    if (slot < 0 || slot >= num_slots) {
+        if (status) atomicExch(status, 3);
+        return;
+    }
+    T* st = state + (size_t)slot * slot_stride;
+    const int p0 = positions[r];
+    // hist[0 .. L-2] = g at positions p0-(L-1) .. p0-1; hist[L-1] = the current token
+    float hist[CONV_LMAX];
+#pragma unroll
+    for (int j = 0; j < CONV_LMAX; ++j) {
+        hist[j] = 0.f;
+        if (j < L - 1 && p0 - (L - 1) + j >= 0) hist[j] = to_f32(st[(size_t)j * hidden + c]);
+    }
+    const int m = q < L - 1 ? q : L - 1;
+    for (int ii = 0; ii < m; ++ii) {
+        const float g = gate_row(h3, in_bias, (size_t)(r + ii), c, hidden);
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < CONV_LMAX; ++k) {
+            if (k < L - 1) acc += w[k] * hist[k];
+            if (k == L - 1) acc += w[k] * g;
+        }
+        emit(h3, in_bias, conv_bias, out, (size_t)(r + ii), c, hidden, acc);
+        // slide: drop the oldest row, the current one becomes the newest of the history
+#pragma unroll
+        for (int k = 0; k < CONV_LMAX - 1; ++k)
+            if (k < L - 2) hist[k] = hist[k + 1];
+#pragma unroll
+        for (int k = 0; k < CONV_LMAX; ++k)
+            if (k == L - 2) hist[k] = g;
+    }
+    // the new state: the last L-1 rows of g up to position p0 + q - 1
+    if (q <= L - 1) {
+#pragma unroll
+        for (int j = 0; j < CONV_LMAX; ++j)
+            if (j < L - 1) st[(size_t)j * hidden + c] = from_f32<T>(hist[j]);
+    } else {
+        for (int j = 0; j < L - 1; ++j) {
+            const float g = gate_row(h3, in_bias, (size_t)(r + q - (L - 1) + j), c, hidden);
+            st[(size_t)j * hidden + c] = from_f32<T>(g);
+        }
+    }
+}
+
+VAPI_EXPORT int vapi_shortconv(const void* h3, int dtype, const float* in_bias, const float* taps,
+                               const float* conv_bias, void* state, long long slot_stride,
+                               const int* state_slots, const int* tok_seq, const int* cu_q,
+                               const int* positions, void* out, int n, int hidden, int L,
+                               int num_slots, int* status, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (L < 1 || L > CONV_LMAX)
+        return fail(-1, "shortconv: kernel length %d is outside 1..%d", L, CONV_LMAX);
+    if (hidden <= 0) return fail(-1, "shortconv: hidden=%d", hidden);
+    if (L > 1 && (!state || num_slots <= 0)) return fail(-1, "shortconv: no state buffer");
+    const int threads = 128;
+    const int cblocks = (hidden + threads - 1) / threads;
+    if (cblocks > 65535) return fail(-1, "shortconv: hidden=%d is too wide for the grid", hidden);
+    dim3 grid(n, cblocks);
+    if (dtype == VAPI_F32)
+        shortconv_kernel<float><<<grid, threads, 0, stream>>>(
+            (const float*)h3, in_bias, taps, conv_bias, (float*)state, slot_stride, state_slots,
+            tok_seq, cu_q, positions, (float*)out, n, hidden, L, num_slots, status);
+    else if (dtype == VAPI_BF16)
+        shortconv_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+            (const __nv_bfloat16*)h3, in_bias, taps, conv_bias, (__nv_bfloat16*)state, slot_stride,
+            state_slots, tok_seq, cu_q, positions, (__nv_bfloat16*)out, n, hidden, L, num_slots,
+            status);
+    else
+        return fail(-2, "shortconv: unsupported dtype %d", dtype);
+    return check_launch("shortconv");
+}
+
+VAPI_EXPORT const char* vapi_last_error() { return error_buffer(); }

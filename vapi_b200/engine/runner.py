@@ -1,0 +1,179 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+``ModelRunner`` owns the bound model, the cache manager and the step packer.  ``step``
+takes any mix of prompt portions and single decode tokens, runs exactly the tokens it is
+given as one batch against the cache that earlier steps left, writes their keys, values and
+states, and returns float32 logits at the wanted places.  It is the only forward pass of the
+package: generation, the scheduler, trace replay and the benchmark all go through it.
+
+It corresponds to the reference's ``ExecutionBackend::forward`` over
+``PagedLfm2::prepare`` + ``forward_prepared``
+(crates/vapi-engine/src/backend.rs:303-336, crates/vapi-backend-candle/src/models/lfm2.rs:718-818).
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..cache.manager import CacheManager, RequestCache
+from ..config.model import eos_token_ids, load_config_json, resolve_architecture
+from ..models.plan import ModelPlan
+from ..parts.base import CacheView
+from ..weights.loader import load_tensors
+from ..weights.random import random_tensors
+from .step import StepContext, StepEntry, StepError, StepPacker, validate_step
+
+DTYPES = {"float32": torch.float32, "fp32": torch.float32, "f32": torch.float32,
+          "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"dtype {name} is not supported (float32, bfloat16)")
+        return name
+    try:
+        return DTYPES[str(name).lower()]
+    except KeyError:
+        raise ValueError(f"dtype `{name}` is not one of {sorted(DTYPES)}")
+
+
+class ModelRunner:
+    #: tokens per cache page (the reference's block is 32 tokens, crates/vapi-core/src/config.rs:15;
+    #: 64 keeps a page of one kv head at 8 KB for head_dim 64 in bfloat16)
+    default_page_size = 64
+
+    def __init__(self, plan: ModelPlan, tensors: Dict[str, torch.Tensor], *, dtype, device="cuda",
+                 page_size: int = default_page_size, num_pages: Optional[int] = None, max_requests: int = 64,
+                 max_batched_tokens: int = 8192, max_context: Optional[int] = None,
+                 watermark: float = 0.0, kv_cache_fraction: float = 0.85, validate: bool = True):
+        self.plan, self.dtype, self.device = plan, parse_dtype(dtype), torch.device(device)
+        if self.device.type == "cuda":
+            ops.strict_fp32()
+        plan.bind(tensors, self.dtype)
+        self.vocab_size = plan.vocab_size
+        self.max_context = min(int(max_context or plan.max_positions), plan.max_positions)
+        self.max_batched_tokens = int(max_batched_tokens)
+        self.validate = validate
+        sites = plan.cache_sites()
+        if num_pages is None:
+            num_pages = self._pages_from_memory(sites, page_size, max_requests, kv_cache_fraction)
+        self.cache = CacheManager(sites, page_size=page_size, num_pages=num_pages, max_requests=max_requests,
+                                  dtype=self.dtype, device=self.device, watermark=watermark)
+        width = -(-self.max_context // page_size)
+        width = -(-width // 4) * 4
+        self.packer = StepPacker(self.cache, self.device, self.max_batched_tokens,
+                                 max(max_requests, 1) , width)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # one CacheView skeleton per run-order entry
+        self._site_of: List[Optional[int]] = []
+        for i, call in enumerate(plan.order):
+            owner = call.cache_of if call.cache_of is not None else i
+            self._site_of.append(owner if self.cache.site_tensor(owner) is not None else None)
+        self.steps_run = 0
+
+    # ---- construction -------------------------------------------------------------
+    @classmethod
+    def from_dir(cls, model_dir: str, *, dtype="bfloat16", device="cuda", **kw) -> "ModelRunner":
+        """Load a model folder (config.json + safetensors); the architecture is chosen by
+        config.json through the registry."""
+        cfg_json = load_config_json(model_dir)
+        arch = resolve_architecture(cfg_json)
+        plan = arch.plan(arch.parse(cfg_json))
+        eos = eos_token_ids(model_dir, cfg_json)
+        if eos:
+            plan.eos_token_ids = eos
+        tensors = load_tensors(model_dir, plan.tensor_specs(), parse_dtype(dtype), device)
+        return cls(plan, tensors, dtype=dtype, device=device, **kw)
+
+    @classmethod
+    def from_random(cls, config_json: Dict[str, Any], seed: int, *, dtype="bfloat16", device="cuda",
+                    std: float = 0.02, norm_init: str = "ones", **kw) -> "ModelRunner":
+        """Random weights drawn directly on the device, without a folder in between."""
+        arch = resolve_architecture(config_json)
+        plan = arch.plan(arch.parse(config_json))
+        dt = parse_dtype(dtype)
+        raw = random_tensors(plan, seed, std, norm_init, torch.float32, device=str(device))
+        specs = {s.name: s for s in plan.tensor_specs()}
+        tensors = {k: (v if specs[k].role != "matrix" else v.to(dt)) for k, v in raw.items()}
+        return cls(plan, tensors, dtype=dtype, device=device, **kw)
+
+    def _pages_from_memory(self, sites, page_size, max_requests, fraction) -> int:
+        """free memory x fraction / bytes per page, the reference's sizing rule
+        (crates/vapi-backend-candle/src/backend.rs:385-400) with the state slots taken off first."""
+        from ..parts.base import PagedSpec, StateSpec
+        esize = 4 if self.dtype == torch.float32 else 2
+        per_token = sum(s.elems_per_token() for _, s in sites if isinstance(s, PagedSpec)) * esize
+        per_req = 0
+        for _, s in sites:
+            if isinstance(s, StateSpec):
+                k = 1
+                for d in s.shape:
+                    k *= d
+                per_req += k * esize
+        if self.device.type != "cuda":
+            raise ValueError("num_pages must be given when the device is not CUDA")
+        free, _ = torch.cuda.mem_get_info(self.device)
+        budget = int(free * fraction) - per_req * (max_requests + 1)
+        pages = budget // max(per_token * page_size, 1) if per_token else max_requests
+        # never more than every request at full context could use
+        cap = max_requests * -(-self.max_context // page_size)
+        pages = min(int(pages), cap)
+        if pages <= 0:
+            raise ValueError("the cache budget leaves no room for a single page")
+        return pages
+
+    # ---- the step ------------------------------------------------------------------
+    def views(self, ctx: StepContext) -> List[CacheView]:
+        out = []
+        for i, call in enumerate(self.plan.order):
+            site = self._site_of[i]
+            if site is None:
+                out.append(CacheView("none"))
+                continue
+            kind, gi = self.cache.site_kind(site)
+            out.append(CacheView(kind, self.cache.site_tensor(site),
+                                 ctx.groups[gi] if kind == "paged" else None,
+                                 write=call.cache_of is None))
+        return out
+
+    def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        """Device work of a step for a prepared context; returns float32 logits [rows, vocab]
+        or None when no logits are wanted (the caches are written either way)."""
+        plan = self.plan
+        x = plan.embedding.forward(ctx)
+        for pe in plan.position_encodings:
+            ctx.pos[pe.name] = pe.prepare(ctx)
+        views = self.views(ctx)
+        delta = None
+        for i, call in enumerate(plan.order):
+            delta = plan.layers[call.layer].forward(x, delta, ctx, views[i])
+        if ctx.logits_rows is None:
+            return None
+        xn = plan.final_norm.apply(x, delta, ctx.dtype, rows=ctx.logits_rows)
+        return plan.head.forward(xn)
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch.  Pages must have been reserved by the caller
+        (``cache.reserve(rc, rc.num_tokens + len(tokens))``): what happens when they run out
+        is the scheduler's decision, not the step function's."""
+        if self.validate:
+            validate_step(entries, self.cache, self.vocab_size, self.max_context)
+        ctx = self.packer.pack(entries, self.dtype, status=self.status)
+        logits = self.forward(ctx)
+        for e in entries:
+            self.cache.commit(e.cache, e.start + len(e.tokens))
+        self.steps_run += 1
+        return logits
+
+    def check_status(self) -> None:
+        """Raise if a kernel met an index it refused to follow (a bad token id, slot or
+        page): the host validation should have caught it first."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            names = {1: "token id outside the vocabulary", 2: "cache slot outside the pool",
+                     3: "state slot outside the pool", 4: "page id outside the pool"}
+            raise RuntimeError(f"a kernel refused an index: {names.get(code, code)}")

@@ -1,0 +1,352 @@
+"""The kernels of the package as Python functions over torch tensors.
+
+Every function here launches hand-written CUDA for sm_100a from ``vapi_b200/csrc`` on the
+current torch stream (``linear`` alone is a library matrix product, as in the reference,
+which calls cuBLAS through candle for every projection).  There is no CPU path: a tensor
+that is not on a CUDA device is refused, and a missing or unbuildable extension raises.
+
+Activation tensors are float32 (the true 32-bit path) or bfloat16 (the serving path); the
+residual stream is always float32; small parameter vectors (norm weights, biases, conv
+taps) are always float32.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..csrc import build as _build
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+_libs: Dict[str, ctypes.CDLL] = {}
+_lock = threading.Lock()
+loaded_libraries: Dict[str, str] = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _lib(name: str) -> ctypes.CDLL:
+    lib = _libs.get(name)
+    if lib is not None:
+        return lib
+    with _lock:
+        lib = _libs.get(name)
+        if lib is None:
+            path = _build.build(name)
+            lib = ctypes.CDLL(path)
+            lib.vapi_last_error.restype = ctypes.c_char_p
+            _libs[name] = lib
+            loaded_libraries[name] = path
+    return lib
+
+
+def _check(lib: ctypes.CDLL, rc: int) -> None:
+    if rc != 0:
+        raise KernelError(lib.vapi_last_error().decode(errors="replace") + f" (code {rc})")
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} is not supported by the kernels (float32, bfloat16)")
+
+
+def _cuda(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("vapi_b200 kernels run on CUDA tensors only; there is no CPU fallback")
+
+
+def _p(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _contig(t: torch.Tensor, what: str) -> None:
+    if not t.is_contiguous():
+        raise KernelError(f"{what} must be contiguous")
+
+
+def _i32(t: Optional[torch.Tensor], what: str) -> None:
+    if t is not None and t.dtype != torch.int32:
+        raise KernelError(f"{what} must be int32")
+
+
+def _f32(t: Optional[torch.Tensor], what: str) -> None:
+    if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+        raise KernelError(f"{what} must be contiguous float32")
+
+
+# ---------------------------------------------------------------------------------------
+def embed(table: torch.Tensor, tokens: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rows of ``table`` [V, H] for ``tokens`` [n] as the float32 residual stream [n, H]."""
+    _cuda(table, tokens)
+    _contig(table, "embedding table")
+    _i32(tokens, "tokens")
+    n, (vocab, hidden) = tokens.numel(), table.shape
+    out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    lib = _lib("elementwise")
+    _check(lib, lib.vapi_embed(_p(table), _dt(table), _p(tokens), _p(out), n, hidden, vocab, _p(status), _stream()))
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x += delta`` (when given) and ``out = rmsnorm(x) * weight``; x is the float32 stream.
+
+    With ``rows`` the output has one row per entry of ``rows`` and ``x`` is left untouched
+    (the sum is formed on the fly): that is the form the final norm uses for the rows whose
+    logits are wanted.
+    """
+    _cuda(x, delta, weight, rows)
+    _f32(x, "residual stream")
+    _f32(weight, "norm weight")
+    _i32(rows, "rows")
+    hidden = x.shape[-1]
+    if weight.numel() != hidden:
+        raise KernelError(f"norm weight has {weight.numel()} elements for rows of {hidden}")
+    if delta is not None:
+        _contig(delta, "delta")
+        if delta.shape != x.shape or delta.dtype != out_dtype:
+            raise KernelError("delta must have the stream's shape and the activation dtype")
+    n_out = rows.numel() if rows is not None else x.shape[0]
+    out = torch.empty((n_out, hidden), dtype=out_dtype, device=x.device)
+    lib = _lib("elementwise")
+    _check(lib, lib.vapi_add_rmsnorm(_p(x), _p(delta), _p(weight), ctypes.c_float(eps), _p(rows), _p(out),
+                                     _dt(out), n_out, hidden, _stream()))
+    return out
+
+
+def add_residual(x: torch.Tensor, delta: torch.Tensor) -> None:
+    """``x += delta`` on the float32 stream."""
+    _cuda(x, delta)
+    _f32(x, "residual stream")
+    _contig(delta, "delta")
+    lib = _lib("elementwise")
+    _check(lib, lib.vapi_add_residual(_p(x), _p(delta), _dt(delta), ctypes.c_longlong(x.numel()), _stream()))
+
+
+def swiglu(g: torch.Tensor) -> torch.Tensor:
+    """``silu(g[:, :F]) * g[:, F:]`` for a stacked gate/up product [n, 2F]."""
+    _cuda(g)
+    _contig(g, "gate/up product")
+    rows, two_f = g.shape
+    if two_f % 2:
+        raise KernelError("swiglu needs an even number of columns")
+    out = torch.empty((rows, two_f // 2), dtype=g.dtype, device=g.device)
+    lib = _lib("elementwise")
+    _check(lib, lib.vapi_swiglu(_p(g), _p(out), _dt(g), rows, two_f // 2, _stream()))
+    return out
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``x @ weight.T (+ bias)``: the library matrix product.
+
+    float32 runs without any reduced-precision mode (see :func:`strict_fp32`).  A weight kept
+    in float32 beside bfloat16 activations is multiplied in float32.
+    """
+    _cuda(x, weight)
+    if weight.dtype != x.dtype:
+        y = torch.mm(x.to(torch.float32), weight.to(torch.float32).t())
+        if bias is not None:
+            y = y + bias
+        return y.to(out_dtype or x.dtype)
+    if out_dtype is not None and out_dtype != x.dtype:
+        if bias is not None:
+            return (torch.mm(x, weight.t(), out_dtype=out_dtype) + bias.to(out_dtype))
+        return torch.mm(x, weight.t(), out_dtype=out_dtype)
+    if bias is not None:
+        return torch.addmm(bias.to(x.dtype), x, weight.t())
+    return torch.mm(x, weight.t())
+
+
+def strict_fp32() -> None:
+    """Switch off every reduced-precision matrix mode of the library products."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
+    try:
+        torch.set_float32_matmul_precision("highest")
+    except Exception:  # pragma: no cover
+        pass
+
+
+def rope_cos_sin(positions: torch.Tensor, inv_freq: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos and sin of ``position * inv_freq`` in float32: two [n, len(inv_freq)] tensors."""
+    _cuda(positions, inv_freq)
+    _i32(positions, "positions")
+    _f32(inv_freq, "inv_freq")
+    n, half = positions.numel(), inv_freq.numel()
+    cos = torch.empty((n, half), dtype=torch.float32, device=positions.device)
+    sin = torch.empty_like(cos)
+    lib = _lib("rope")
+    _check(lib, lib.vapi_rope_cos_sin(_p(positions), _p(inv_freq), _p(cos), _p(sin), n, half, _stream()))
+    return cos, sin
+
+
+def qk_norm_rope_write(qkv: torch.Tensor, nh: int, nkv: int, d: int,
+                       q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                       cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot: int,
+                       cache_layer: Optional[torch.Tensor], slot_mapping: Optional[torch.Tensor],
+                       status: Optional[torch.Tensor] = None) -> None:
+    """Per-head RMSNorm and rotate-half RoPE of q and k in a fused ``qkv`` [n, (nh+2nkv)*d];
+    q is rewritten in place, k (normed, roped) and v go to ``cache_layer``
+    [pages, 2, nkv, page_size, d] at ``slot_mapping``.  ``cache_layer=None`` leaves the
+    cache alone (a layer that reads another layer's cache)."""
+    _cuda(qkv, q_weight, k_weight, cos, sin, cache_layer, slot_mapping)
+    _contig(qkv, "qkv")
+    _f32(q_weight, "q norm weight")
+    _f32(k_weight, "k norm weight")
+    _f32(cos, "cos")
+    _f32(sin, "sin")
+    _i32(slot_mapping, "slot mapping")
+    n = qkv.shape[0]
+    if qkv.shape[1] != (nh + 2 * nkv) * d:
+        raise KernelError(f"qkv has {qkv.shape[1]} columns, expected {(nh + 2 * nkv) * d}")
+    page_size = num_pages = 0
+    if cache_layer is not None:
+        _contig(cache_layer, "cache layer")
+        if cache_layer.dtype != qkv.dtype or tuple(cache_layer.shape[1:3]) != (2, nkv) or cache_layer.shape[4] != d:
+            raise KernelError(f"cache layer {tuple(cache_layer.shape)} / {cache_layer.dtype} does not fit "
+                              f"nkv={nkv} d={d} {qkv.dtype}")
+        num_pages, page_size = cache_layer.shape[0], cache_layer.shape[3]
+    if cos is not None and (cos.shape != (n, rot // 2) or sin is None or sin.shape != cos.shape):
+        raise KernelError("cos/sin must be [n, rot/2]")
+    lib = _lib("rope")
+    _check(lib, lib.vapi_qk_norm_rope_write(
+        _p(qkv), _dt(qkv), _p(q_weight), _p(k_weight), ctypes.c_float(eps), _p(cos), _p(sin), rot,
+        _p(cache_layer), _p(slot_mapping), n, nh, nkv, d, page_size, num_pages, _p(status), _stream()))
+
+
+def attention_splits(num_seqs: int, max_q: int, max_k: int, nh: int, nkv: int) -> int:
+    """How many blocks share the keys of one row tile: 1 unless the step is so small that
+    the device would sit idle (decode of few sequences over long contexts)."""
+    n_rep = nh // nkv
+    tiles = -(-(max_q * n_rep) // 16)
+    blocks = max(1, num_seqs * nkv * tiles)
+    if max_q > 1 and blocks >= 148:
+        return 1
+    want = -(-296 // blocks)
+    by_len = max(1, max_k // 256)
+    return max(1, min(want, by_len, 32))
+
+
+def paged_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tensor,
+                    block_table: torch.Tensor, cu_q: torch.Tensor, seqlens_k: torch.Tensor,
+                    n: int, num_seqs: int, max_q: int, max_k: int, nh: int, nkv: int, d: int,
+                    scale: float, window: int = 0, splits: Optional[int] = None,
+                    status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal GQA attention of a mixed batch over the paged cache; returns [n, nh*d].
+
+    ``q`` may be a view into a fused qkv tensor: head h of token t is at
+    ``t*q_row_stride + h*d``.  ``window`` > 0 limits each query to the last ``window`` keys.
+    """
+    _cuda(q, cache_layer, block_table, cu_q, seqlens_k)
+    _i32(block_table, "block table")
+    _i32(cu_q, "cu_q")
+    _i32(seqlens_k, "seqlens_k")
+    _contig(cache_layer, "cache layer")
+    if cache_layer.dtype != q.dtype:
+        raise KernelError("q and the cache must have one dtype")
+    if block_table.dim() != 2 or block_table.stride(1) != 1:
+        raise KernelError("block table must be [S, width] with unit inner stride")
+    num_pages, page_size = cache_layer.shape[0], cache_layer.shape[3]
+    if splits is None:
+        splits = attention_splits(num_seqs, max_q, max_k, nh, nkv)
+    out = torch.empty((n, nh * d), dtype=q.dtype, device=q.device)
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty((n * nh * splits * d,), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n * nh * splits * 2,), dtype=torch.float32, device=q.device)
+    lib = _lib("attention")
+    _check(lib, lib.vapi_paged_attention(
+        _p(q), ctypes.c_longlong(q_row_stride), _p(cache_layer), _dt(q), _p(block_table),
+        block_table.stride(0), _p(cu_q), _p(seqlens_k), _p(out), _p(part_o), _p(part_ml), n, num_seqs,
+        max_q, nh, nkv, d, page_size, num_pages, ctypes.c_float(scale), window, splits, _p(status),
+        _stream()))
+    return out
+
+
+def shortconv(h3: torch.Tensor, in_bias: Optional[torch.Tensor], taps: torch.Tensor,
+              conv_bias: Optional[torch.Tensor], state_layer: Optional[torch.Tensor],
+              state_slots: torch.Tensor, tok_seq: torch.Tensor, cu_q: torch.Tensor,
+              positions: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gating, causal depthwise convolution and state update of the short-conv mixer.
+
+    ``h3`` [n, 3H] = B | C | x; ``taps`` [L, H] oldest first; ``state_layer`` is a view
+    [slots, L-1, H] of the per-request state (any slot stride).  Returns y [n, H].
+    """
+    _cuda(h3, in_bias, taps, conv_bias, state_layer, state_slots, tok_seq, cu_q, positions)
+    _contig(h3, "h3")
+    _f32(in_bias, "in_proj bias")
+    _f32(taps, "conv taps")
+    _f32(conv_bias, "conv bias")
+    for t, w in ((state_slots, "state slots"), (tok_seq, "tok_seq"), (cu_q, "cu_q"), (positions, "positions")):
+        _i32(t, w)
+    n, three_h = h3.shape
+    hidden = three_h // 3
+    L = taps.shape[0]
+    if three_h != 3 * hidden or taps.shape[1] != hidden:
+        raise KernelError("h3 must be [n, 3H] and taps [L, H]")
+    slot_stride = num_slots = 0
+    if L > 1:
+        if state_layer is None or state_layer.dtype != h3.dtype or tuple(state_layer.shape[1:]) != (L - 1, hidden):
+            raise KernelError(f"state must be [slots, {L - 1}, {hidden}] of {h3.dtype}")
+        if state_layer.stride(2) != 1 or state_layer.stride(1) != hidden:
+            raise KernelError("state rows must be contiguous")
+        slot_stride, num_slots = state_layer.stride(0), state_layer.shape[0]
+    out = torch.empty((n, hidden), dtype=h3.dtype, device=h3.device)
+    lib = _lib("shortconv")
+    _check(lib, lib.vapi_shortconv(
+        _p(h3), _dt(h3), _p(in_bias), _p(taps), _p(conv_bias), _p(state_layer if L > 1 else None),
+        ctypes.c_longlong(slot_stride), _p(state_slots), _p(tok_seq), _p(cu_q), _p(positions), _p(out),
+        n, hidden, L, num_slots, _p(status), _stream()))
+    return out
+
+
+def sample_rows(logits: torch.Tensor, mode: Optional[torch.Tensor] = None,
+                inv_t: Optional[torch.Tensor] = None, seeds: Optional[torch.Tensor] = None,
+                draws: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of float32 ``logits`` [R, V]: greedy argmax (lowest id wins ties),
+    or, where ``mode`` is 2, Gumbel-max temperature sampling keyed by (seed, draw)."""
+    _cuda(logits, mode, inv_t, seeds, draws)
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("logits must be float32 with unit inner stride")
+    _i32(mode, "mode")
+    _f32(inv_t, "inverse temperatures")
+    for t in (seeds, draws):
+        if t is not None and t.dtype != torch.int64:
+            raise KernelError("seeds and draw counters must be int64")
+    rows, vocab = logits.shape
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    lib = _lib("sampling")
+    _check(lib, lib.vapi_sample_rows(_p(logits), rows, vocab, ctypes.c_longlong(logits.stride(0)), _p(mode),
+                                     _p(inv_t), _p(seeds), _p(draws), _p(out), _stream()))
+    return out
+
+
+def apply_penalties(logits: torch.Tensor, rows: torch.Tensor, toks: torch.Tensor, counts: torch.Tensor,
+                    rep: torch.Tensor, freq: torch.Tensor, pres: torch.Tensor) -> None:
+    """Repetition / frequency / presence penalties on (row, token) pairs, in place."""
+    _cuda(logits, rows, toks, counts, rep, freq, pres)
+    _i32(rows, "rows")
+    _i32(toks, "tokens")
+    for t, w in ((counts, "counts"), (rep, "repetition"), (freq, "frequency"), (pres, "presence")):
+        _f32(t, w)
+    lib = _lib("sampling")
+    _check(lib, lib.vapi_apply_penalties(_p(logits), logits.shape[1], ctypes.c_longlong(logits.stride(0)),
+                                         _p(rows), _p(toks), _p(counts), _p(rep), _p(freq), _p(pres),
+                                         rows.numel(), _stream()))

@@ -1,0 +1,95 @@
+"""Grouped-query attention over the paged cache."""
+from __future__ import annotations
+
+import math
+from typing import Any, Dict, List, Optional
+
+import torch
+
+from .. import ops
+from .base import CacheView, Mixer, PagedSpec, TensorSpec, register_mixer
+
+
+class GQAttention(Mixer):
+    """q/k/v projection, optional per-head RMSNorm of q and k, optional rotary encoding,
+    cache write, causal attention over the block table (optionally windowed), out
+    projection (crates/vapi-backend-candle/src/models/lfm2.rs:343-406; attention semantics
+    crates/vapi-backend-candle/src/attention.rs:90-163).
+
+    The three projections are fused into one matrix at bind time.  ``names`` maps the roles
+    ``q k v o q_norm k_norm`` to checkpoint sub-names, so another architecture's naming is a
+    parameter, not a subclass.  ``pos`` names the position encoding whose ``(cos, sin)`` to
+    apply (None: no rotation).
+    """
+
+    def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, *,
+                 qk_norm_eps: Optional[float] = None, pos: Optional[str] = "rope",
+                 rot_dim: Optional[int] = None, window: int = 0, bias: bool = False,
+                 scale: Optional[float] = None, names: Optional[Dict[str, str]] = None):
+        if n_heads <= 0 or n_kv_heads <= 0 or n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} kv heads")
+        if head_dim % 16 or not 16 <= head_dim <= 256:
+            raise ValueError(f"head_dim {head_dim} must be a multiple of 16 in 16..256")
+        self.hidden, self.nh, self.nkv, self.d = int(hidden), int(n_heads), int(n_kv_heads), int(head_dim)
+        self.qk_norm_eps = qk_norm_eps
+        self.pos = pos
+        self.rot_dim = int(rot_dim) if rot_dim is not None else self.d
+        self.window = int(window)
+        self.bias = bool(bias)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.d)
+        self.names = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "out_proj",
+                      "q_norm": "q_layernorm", "k_norm": "k_layernorm"}
+        if names:
+            self.names.update(names)
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_w = self.k_w = None
+
+    def cache_spec(self):
+        return PagedSpec(self.nkv, self.d, self.window)
+
+    def tensor_specs(self, prefix: str) -> List[TensorSpec]:
+        n, (h, nh, nkv, d) = self.names, (self.hidden, self.nh, self.nkv, self.d)
+        specs = [TensorSpec(f"{prefix}{n['q']}.weight", (nh * d, h)),
+                 TensorSpec(f"{prefix}{n['k']}.weight", (nkv * d, h)),
+                 TensorSpec(f"{prefix}{n['v']}.weight", (nkv * d, h)),
+                 TensorSpec(f"{prefix}{n['o']}.weight", (h, nh * d))]
+        if self.bias:
+            specs += [TensorSpec(f"{prefix}{n['q']}.bias", (nh * d,), role="vector"),
+                      TensorSpec(f"{prefix}{n['k']}.bias", (nkv * d,), role="vector"),
+                      TensorSpec(f"{prefix}{n['v']}.bias", (nkv * d,), role="vector"),
+                      TensorSpec(f"{prefix}{n['o']}.bias", (h,), role="vector")]
+        if self.qk_norm_eps is not None:
+            specs += [TensorSpec(f"{prefix}{n['q_norm']}.weight", (d,), role="vector", init="ones"),
+                      TensorSpec(f"{prefix}{n['k_norm']}.weight", (d,), role="vector", init="ones")]
+        return specs
+
+    def bind(self, tensors, prefix, dtype):
+        n = self.names
+        parts = [tensors[f"{prefix}{n[r]}.weight"] for r in ("q", "k", "v")]
+        wd = parts[0].dtype if all(p.dtype == parts[0].dtype for p in parts) else torch.float32
+        self.w_qkv = torch.cat([p.to(wd) for p in parts], 0).contiguous()
+        self.w_o = tensors[f"{prefix}{n['o']}.weight"].contiguous()
+        if self.bias:
+            self.b_qkv = torch.cat([tensors[f"{prefix}{n[r]}.bias"] for r in ("q", "k", "v")], 0).contiguous()
+            self.b_o = tensors[f"{prefix}{n['o']}.bias"].contiguous()
+        if self.qk_norm_eps is not None:
+            self.q_w = tensors[f"{prefix}{n['q_norm']}.weight"].contiguous()
+            self.k_w = tensors[f"{prefix}{n['k_norm']}.weight"].contiguous()
+
+    def forward(self, a: torch.Tensor, ctx: Any, cache: CacheView) -> torch.Tensor:
+        nh, nkv, d = self.nh, self.nkv, self.d
+        qkv = ops.linear(a, self.w_qkv, self.b_qkv)
+        cos = sin = None
+        if self.pos is not None:
+            cos, sin = ctx.pos[self.pos]
+        grp = cache.group
+        ops.qk_norm_rope_write(qkv, nh, nkv, d, self.q_w, self.k_w,
+                               self.qk_norm_eps if self.qk_norm_eps is not None else 0.0,
+                               cos, sin, self.rot_dim,
+                               cache.tensor if cache.write else None, grp.slot_mapping, ctx.status)
+        y = ops.paged_attention(qkv, qkv.stride(0), cache.tensor, grp.block_table, ctx.cu_q,
+                                ctx.seqlens_k, ctx.n, ctx.num_seqs, ctx.max_q, ctx.max_k, nh, nkv, d,
+                                self.scale, self.window, ctx.attention_splits, ctx.status)
+        return ops.linear(y, self.w_o, self.b_o)
+
+
+register_mixer("gqa_attention", GQAttention)

@@ -1,0 +1,183 @@
+"""Interfaces of the parts a model is put together from.
+
+A model is a list of blocks; a block arranges a *mixer* (attention, short convolution, or
+anything else that moves information between tokens), a *feed-forward*, and *norms*; a
+*position encoding* prepares per-step tensors that mixers may use.  Each part
+
+* is constructed from plain sizes and constants (never from a model configuration object),
+* names the checkpoint tensors it wants (:class:`TensorSpec`) under a prefix it is given,
+* says what kind of cache it needs (:class:`PagedSpec`, :class:`StateSpec` or ``None``),
+* binds its loaded tensors once (``bind``) and then runs on a step (``forward``).
+
+No part knows which model it is in.  Parts are looked up by name in small registries so a
+test (or a new architecture) can add one without touching this package's files.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+# --------------------------------------------------------------------------------------
+# what a part asks of the checkpoint
+
+
+@dataclass(frozen=True)
+class TensorSpec:
+    """One checkpoint tensor a part needs.
+
+    ``role`` decides the run-time dtype: a ``matrix`` is an operand of a matrix product or
+    an embedding table and is kept in the compute dtype (bfloat16 when serving), except
+    that a tensor the checkpoint stores in 32-bit stays 32-bit; a ``vector`` (norm weight,
+    bias, conv tap) is always handed to kernels as float32; a ``table`` is integer data and
+    becomes int32.  ``init`` is how the random-weights writer fills it.
+    """
+
+    name: str
+    shape: Tuple[int, ...]
+    role: str = "matrix"      # matrix | vector | table
+    init: str = "normal"      # normal | ones | zeros
+    optional: bool = False
+
+
+# --------------------------------------------------------------------------------------
+# what a part asks of the cache manager
+
+
+@dataclass(frozen=True)
+class PagedSpec:
+    """Per-token cache in pages: keys and values of ``n_kv`` heads of ``head_dim``.
+
+    ``window`` = 0 keeps every position; ``window`` = W > 0 means positions more than W
+    behind the newest are never read again, so the manager may give their pages back.
+    Layers with equal specs share one group: one pool of pages, one block table a request.
+    """
+
+    n_kv: int
+    head_dim: int
+    window: int = 0
+
+    def elems_per_token(self) -> int:
+        return 2 * self.n_kv * self.head_dim
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Per-request state of fixed size (``shape`` elements per layer), kept in a slot.
+
+    ``kind`` only serves to keep unlike states in separate tensors; ``dtype`` None means the
+    compute dtype.  The state of a fresh request is *undefined memory*: a mixer must derive
+    "nothing before position 0" from the positions it is given, never from zeroed memory.
+    """
+
+    kind: str
+    shape: Tuple[int, ...]
+    dtype: Optional[torch.dtype] = None
+
+
+@dataclass
+class CacheView:
+    """What a mixer sees of the cache at one call site of one step.
+
+    ``paged``: ``tensor`` is this layer's [pages, 2, n_kv, page_size, head_dim]; ``group`` has
+    the step's ``slot_mapping`` [n] and ``block_table`` [S, width] for the layer's group.
+    ``state``: ``tensor`` is this layer's view [slots, *shape]; ``ctx.state_slots`` [S] names
+    each sequence's slot.  ``write`` False: the call site reads a cache another layer owns.
+    """
+
+    kind: str                 # "paged" | "state" | "none"
+    tensor: Optional[torch.Tensor] = None
+    group: Any = None
+    write: bool = True
+
+
+# --------------------------------------------------------------------------------------
+# the parts
+
+
+class Part:
+    """Base of every part: tensor specs and binding."""
+
+    def tensor_specs(self, prefix: str) -> List[TensorSpec]:
+        return []
+
+    def bind(self, tensors: Dict[str, torch.Tensor], prefix: str, dtype: torch.dtype) -> None:
+        """Take the loaded tensors (by full checkpoint name); fuse or reshape them once."""
+
+
+class Norm(Part):
+    """A norm over the last dimension that also folds in the pending residual add."""
+
+    def apply(self, x: torch.Tensor, delta: Optional[torch.Tensor], dtype: torch.dtype,
+              rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``x`` is the float32 residual stream [n, H].  Adds ``delta`` (a layer's output in
+        the activation dtype) into it when given, and returns the normed rows in ``dtype``.
+        With ``rows`` only those rows are produced and ``x`` is left unchanged."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Prepares, once per step, what mixers need to place tokens (e.g. cos/sin rows)."""
+
+    name: str = "pos"
+
+    def prepare(self, ctx: "Any") -> Any:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    """Moves information between the tokens of a sequence."""
+
+    def cache_spec(self) -> Optional[object]:
+        """A :class:`PagedSpec`, a :class:`StateSpec` or None."""
+        return None
+
+    def forward(self, a: torch.Tensor, ctx: "Any", cache: CacheView) -> torch.Tensor:
+        """``a`` [n, H] normed activations of every token of the step; returns the layer's
+        contribution to the residual stream, [n, H] in the activation dtype."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, f: torch.Tensor, ctx: "Any") -> torch.Tensor:
+        raise NotImplementedError
+
+
+# --------------------------------------------------------------------------------------
+# registries: name -> constructor.  A new kind of part is one register_* call.
+
+MIXERS: Dict[str, Callable[..., Mixer]] = {}
+FEED_FORWARDS: Dict[str, Callable[..., FeedForward]] = {}
+NORMS: Dict[str, Callable[..., Norm]] = {}
+POSITION_ENCODINGS: Dict[str, Callable[..., PositionEncoding]] = {}
+
+
+def _register(table: Dict[str, Callable], name: str, ctor: Callable, replace: bool) -> None:
+    if name in table and not replace and table[name] is not ctor:
+        raise ValueError(f"part `{name}` is already registered")
+    table[name] = ctor
+
+
+def register_mixer(name: str, ctor: Callable[..., Mixer], *, replace: bool = False) -> None:
+    _register(MIXERS, name, ctor, replace)
+
+
+def register_feed_forward(name: str, ctor: Callable[..., FeedForward], *, replace: bool = False) -> None:
+    _register(FEED_FORWARDS, name, ctor, replace)
+
+
+def register_norm(name: str, ctor: Callable[..., Norm], *, replace: bool = False) -> None:
+    _register(NORMS, name, ctor, replace)
+
+
+def register_position_encoding(name: str, ctor: Callable[..., PositionEncoding], *, replace: bool = False) -> None:
+    _register(POSITION_ENCODINGS, name, ctor, replace)
+
+
+def make_part(table: Dict[str, Callable], kind: str, **params: Any) -> Any:
+    try:
+        ctor = table[kind]
+    except KeyError:
+        raise KeyError(f"no part named `{kind}`; registered: {sorted(table)}")
+    return ctor(**params)
