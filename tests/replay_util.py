@@ -1,0 +1,150 @@
+"""Traces for bin/trace_run and the means to run them and check the logits they give."""
+from __future__ import annotations
+
+import json
+import os
+import random
+import subprocess
+import sys
+from typing import Dict, List, Sequence, Tuple
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
+PAGE = 64
+
+
+def round_up(x: int, m: int = PAGE) -> int:
+    return -(-x // m) * m
+
+
+class Trace:
+    """Steps plus, for each step, which (request, position) each wanted row is."""
+
+    def __init__(self):
+        self.steps: List[dict] = []
+        self.rows: Dict[int, List[Tuple[str, int]]] = {}
+        self._len: Dict[str, int] = {}
+        self.peak_tokens = 0
+
+    def add(self, entries: Sequence[Tuple[str, Sequence[int], Sequence[int]]], end: Sequence[str] = ()) -> None:
+        step = len(self.steps)
+        rec = {"step": step, "entries": [], "end": list(end)}
+        rows = []
+        for rid, toks, want in entries:
+            start = self._len.get(rid, 0)
+            rec["entries"].append({"id": rid, "tokens": [int(t) for t in toks], "want": [int(w) for w in want]})
+            rows += [(rid, start + int(w)) for w in want]
+            self._len[rid] = start + len(toks)
+        self.peak_tokens = max(self.peak_tokens, sum(round_up(v) for v in self._len.values()))
+        for rid in end:
+            self._len.pop(rid, None)
+        self.steps.append(rec)
+        if rows:
+            self.rows[step] = rows
+
+
+def whole(tr: Trace, rid: str, toks: Sequence[int]) -> None:
+    tr.add([(rid, toks, range(len(toks)))], end=[rid])
+
+
+def tail_decode(tr: Trace, rid: str, toks: Sequence[int], tail: int = 32) -> None:
+    """Most of it in one step, the last `tail` tokens one by one."""
+    head = max(1, len(toks) - tail)
+    tr.add([(rid, toks[:head], [head - 1])])
+    for i in range(head, len(toks)):
+        tr.add([(rid, toks[i:i + 1], [0])], end=[rid] if i == len(toks) - 1 else [])
+    if head == len(toks):
+        tr.add([], end=[rid])
+
+
+def portions(tr: Trace, rid: str, toks: Sequence[int], sizes: Sequence[int]) -> None:
+    """Portions of changing size (cycled), down to two tokens; logits wanted everywhere."""
+    pos, i = 0, 0
+    while pos < len(toks):
+        q = min(sizes[i % len(sizes)], len(toks) - pos)
+        last = pos + q >= len(toks)
+        tr.add([(rid, toks[pos:pos + q], range(q))], end=[rid] if last else [])
+        pos += q
+        i += 1
+
+
+def mixed(tr: Trace, requests: Dict[str, Sequence[int]], seed: int, max_live: int = 4,
+          decode_tail: int = 12) -> None:
+    """Up to `max_live` requests at a time: portions of some beside single tokens of others,
+    some requests sitting a step out, starts and ends interleaved."""
+    rng = random.Random(seed)
+    waiting = list(requests.items())
+    live: Dict[str, int] = {}
+    while waiting or live:
+        while waiting and len(live) < max_live and (not live or rng.random() < 0.6):
+            rid, _ = waiting.pop(0)
+            live[rid] = 0
+        entries, ends = [], []
+        for rid in list(live):
+            toks, pos = requests[rid], live[rid]
+            if len(live) > 1 and rng.random() < 0.2:
+                continue                                   # left out of this step
+            remaining = len(toks) - pos
+            if remaining <= decode_tail:
+                q = 1
+            else:
+                q = min(remaining - decode_tail, rng.choice([2, 3, 5, 16, 31, 64, 65, 100]))
+            want = [q - 1] if rng.random() < 0.7 else list(range(q))
+            entries.append((rid, toks[pos:pos + q], want))
+            live[rid] = pos + q
+            if live[rid] >= len(toks):
+                ends.append(rid)
+        if not entries:
+            continue
+        tr.add(entries, end=ends)
+        for rid in ends:
+            del live[rid]
+
+
+def run_trace(model_dir: str, dtype: str, tr: Trace, out_dir: str, max_tokens: int = None,
+              extra_env: Dict[str, str] = None, timeout: int = 900) -> Dict[int, np.ndarray]:
+    """Run bin/trace_run as a user would; return step -> [wanted, vocab] float32."""
+    os.makedirs(out_dir, exist_ok=True)
+    cmd = [sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", out_dir,
+           "--max-tokens", str(max_tokens if max_tokens is not None else tr.peak_tokens)]
+    env = dict(os.environ)
+    env.update(extra_env or {})
+    inp = "".join(json.dumps(s) + "\n" for s in tr.steps)
+    proc = subprocess.run(cmd, input=inp, capture_output=True, text=True, env=env, timeout=timeout)
+    if proc.returncode != 0:
+        raise RuntimeError(f"trace_run exited {proc.returncode}\nstdout:\n{proc.stdout[-2000:]}\nstderr:\n{proc.stderr[-4000:]}")
+    done = [int(l.split()[1]) for l in proc.stdout.splitlines() if l.startswith("done ")]
+    assert done == [s["step"] for s in tr.steps], "every step must be acknowledged in order"
+    with open(os.path.join(model_dir, "config.json")) as f:
+        vocab = json.load(f)["vocab_size"]
+    out = {}
+    for step, rows in tr.rows.items():
+        arr = np.fromfile(os.path.join(out_dir, f"{step}.f32"), dtype="<f4")
+        assert arr.size == len(rows) * vocab, f"step {step}: {arr.size} values for {len(rows)} rows"
+        out[step] = arr.reshape(len(rows), vocab)
+    return out
+
+
+def compare(tr: Trace, got: Dict[int, np.ndarray], ref: Dict[str, torch.Tensor], dtype: str):
+    """Worst difference over all wanted rows, with where it is.  Returns (ok, message)."""
+    worst = (0.0, None)
+    span = max(float(r.max() - r.min()) for r in ref.values())
+    for step, rows in tr.rows.items():
+        for i, (rid, pos) in enumerate(rows):
+            d = float(np.abs(got[step][i] - ref[rid][pos].numpy()).max())
+            if not np.isfinite(got[step][i]).all():
+                return False, f"step {step} row {i} ({rid} @ {pos}) is not finite"
+            if d > worst[0]:
+                worst = (d, (step, rid, pos))
+    limit = limit_for(dtype, span)
+    return worst[0] <= limit, f"worst |diff| {worst[0]:.3e} at (step, request, position) {worst[1]}; limit {limit:.3e}, logit range {span:.2f}"
+
+
+def limit_for(dtype: str, span: float) -> float:
+    """float32: 1e-4 absolute on logits of order 10 (the reference's model tests use 1e-4,
+    crates/vapi-backend-candle/src/models/lfm2.rs:924-953); bfloat16: 5 % of the logit range
+    (lfm2.rs:1017-1024)."""
+    return 1e-4 * max(1.0, span / 10.0) if dtype == "float32" else 0.05 * span

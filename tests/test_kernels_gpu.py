@@ -1,0 +1,289 @@
+"""Each CUDA kernel alone against its plain float32 restatement, at sizes other than the
+engine tests' (sizes that are no power of two, head sizes from 16 to 256, odd group counts)."""
+import itertools
+import math
+
+import pytest
+import torch
+
+import plain_ops
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+def dev(t):
+    return t.cuda() if t is not None else None
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from vapi_b200 import ops as o
+    return o
+
+
+def test_cpu_tensors_are_refused(ops):
+    with pytest.raises(ops.KernelError):
+        ops.swiglu(torch.zeros(2, 8))
+
+
+@pytest.mark.parametrize("wdt", DTYPES)
+def test_embed(ops, wdt):
+    torch.manual_seed(0)
+    table = torch.randn(301, 72).to(wdt)
+    toks = torch.randint(0, 301, (19,), dtype=torch.int32)
+    got = ops.embed(dev(table), dev(toks))
+    assert got.dtype == torch.float32
+    torch.testing.assert_close(got.cpu(), plain_ops.embed(table, toks), atol=0, rtol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [72, 2048, 1000])
+def test_add_rmsnorm(ops, dtype, hidden):
+    torch.manual_seed(1)
+    n = 13
+    x = torch.randn(n, hidden) * 3
+    delta = torch.randn(n, hidden).to(dtype)
+    w = 1 + 0.1 * torch.randn(hidden)
+    x_ref = x.clone()
+    want = plain_ops.add_rmsnorm(x_ref, delta, w, 1e-6, dtype)
+    xg = dev(x.clone())
+    got = ops.add_rmsnorm(xg, dev(delta), dev(w), 1e-6, dtype)
+    torch.testing.assert_close(xg.cpu(), x_ref, atol=1e-6, rtol=1e-6)       # the stream got the add
+    torch.testing.assert_close(got.cpu().float(), want.float(), **tol(dtype))
+    # rows form: x untouched, rows gathered (with a repeat)
+    rows = torch.tensor([3, 0, 3, 12], dtype=torch.int32)
+    x2 = dev(x.clone())
+    got2 = ops.add_rmsnorm(x2, dev(delta), dev(w), 1e-6, dtype, dev(rows))
+    want2 = plain_ops.add_rmsnorm(x.clone(), delta, w, 1e-6, dtype, rows)
+    torch.testing.assert_close(x2.cpu(), x, atol=0, rtol=0)
+    torch.testing.assert_close(got2.cpu().float(), want2.float(), **tol(dtype))
+    # no delta
+    got3 = ops.add_rmsnorm(dev(x.clone()), None, dev(w), 1e-5, dtype)
+    want3 = plain_ops.add_rmsnorm(x.clone(), None, w, 1e-5, dtype)
+    torch.testing.assert_close(got3.cpu().float(), want3.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(ops, dtype):
+    torch.manual_seed(2)
+    for rows, ff in ((1, 8), (7, 24), (33, 1000)):
+        g = (torch.randn(rows, 2 * ff) * 4).to(dtype)
+        torch.testing.assert_close(ops.swiglu(dev(g)).cpu().float(), plain_ops.swiglu(g).float(), **tol(dtype))
+
+
+def test_rope_cos_sin(ops):
+    pos = torch.tensor([0, 1, 2, 63, 64, 1000, 4095, 100000], dtype=torch.int32)
+    inv = 1.0 / torch.pow(torch.tensor(1e6), torch.arange(0, 48, 2, dtype=torch.float32) / 48.0)
+    c, s = ops.rope_cos_sin(dev(pos), dev(inv))
+    cr, sr = plain_ops.rope_cos_sin(pos, inv)
+    torch.testing.assert_close(c.cpu(), cr, atol=2e-6, rtol=0)
+    torch.testing.assert_close(s.cpu(), sr, atol=2e-6, rtol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,rot", [(4, 2, 16, 16), (6, 1, 32, 32), (3, 3, 48, 32), (5, 5, 256, 256), (8, 2, 64, 64)])
+def test_qk_norm_rope_write(ops, dtype, nh, nkv, d, rot):
+    torch.manual_seed(3)
+    n, page, pages = 11, 16, 7
+    qkv = torch.randn(n, (nh + 2 * nkv) * d).to(dtype)
+    qw, kw = 1 + 0.1 * torch.randn(d), 1 + 0.1 * torch.randn(d)
+    pos = torch.randint(0, 500, (n,), dtype=torch.int32)
+    inv = 1.0 / torch.pow(torch.tensor(1e4), torch.arange(0, rot, 2, dtype=torch.float32) / rot)
+    cos, sin = plain_ops.rope_cos_sin(pos, inv)
+    slots = torch.randperm(page * pages)[:n].to(torch.int32)
+    cache = torch.full((pages, 2, nkv, page, d), 7.0).to(dtype)
+    cache_ref, qkv_ref = cache.clone(), qkv.clone()
+    plain_ops.qk_norm_rope_write(qkv_ref, nh, nkv, d, qw, kw, 1e-5, cos, sin, rot, cache_ref, slots)
+    qg, cg = dev(qkv.clone()), dev(cache.clone())
+    ops.qk_norm_rope_write(qg, nh, nkv, d, dev(qw), dev(kw), 1e-5, dev(cos), dev(sin), rot, cg, dev(slots))
+    torch.testing.assert_close(qg.cpu().float()[:, :nh * d], qkv_ref.float()[:, :nh * d], **tol(dtype))
+    torch.testing.assert_close(cg.cpu().float(), cache_ref.float(), **tol(dtype))   # untouched slots keep 7.0
+    # no norm, no rope, no cache: q is left as it was
+    q2 = dev(qkv.clone())
+    ops.qk_norm_rope_write(q2, nh, nkv, d, None, None, 0.0, None, None, rot, None, None)
+    torch.testing.assert_close(q2.cpu(), qkv, atol=0, rtol=0)
+
+
+def _attention_case(ops, dtype, nh, nkv, d, page, lens, window=0, splits=None, planted=False, seed=4):
+    """lens: list of (len_q, len_k) per sequence; pages are handed out in a shuffled order."""
+    torch.manual_seed(seed)
+    S = len(lens)
+    n = sum(q for q, _ in lens)
+    need = [-(-k // page) for _, k in lens]
+    num_pages = sum(need) + 3
+    perm = torch.randperm(num_pages).tolist()
+    width = max(need) + 1
+    table = torch.zeros((S, width), dtype=torch.int32)
+    it = iter(perm)
+    for s in range(S):
+        for j in range(need[s]):
+            table[s, j] = next(it)
+    cache = torch.randn(num_pages, 2, nkv, page, d).to(dtype)
+    q = torch.randn(n, nh * d).to(dtype)
+    if planted:
+        # one far key per sequence gets a score that stands out; its value is marked so that
+        # losing the key (a page edge, a split boundary) changes the output a lot
+        r = 0
+        for s, (ql, kl) in enumerate(lens):
+            far = min(kl - ql, 3) if kl - ql > 0 else 0
+            pg, off = int(table[s, far // page]), far % page
+            cache[pg, 0, :, off] = 0
+            cache[pg, 0, :, off, 0] = 6.0
+            cache[pg, 1, :, off] = 50.0
+            q[r:r + ql] = 0
+            q.view(n, nh, d)[r:r + ql, :, 0] = 2.0 * math.sqrt(d)   # score 12 for the planted key
+            r += ql
+    cu_q = torch.tensor([0] + list(itertools.accumulate(a for a, _ in lens)), dtype=torch.int32)
+    kl = torch.tensor([b for _, b in lens], dtype=torch.int32)
+    max_q, max_k = max(a for a, _ in lens), max(b for _, b in lens)
+    scale = 1.0 / math.sqrt(d)
+    want = plain_ops.paged_attention(q, nh * d, cache, table, cu_q, kl, n, S, max_q, max_k, nh, nkv, d, scale, window)
+    got = ops.paged_attention(dev(q), nh * d, dev(cache), dev(table), dev(cu_q), dev(kl), n, S, max_q, max_k,
+                              nh, nkv, d, scale, window, splits)
+    t = dict(atol=3e-5, rtol=3e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(got.cpu().float(), want.float(), **t)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d", [(4, 2, 16), (6, 1, 32), (3, 1, 48), (8, 2, 64), (2, 2, 128), (40, 1, 16), (2, 1, 256)])
+def test_paged_attention_mixed_batch(ops, dtype, nh, nkv, d):
+    # a whole prompt, a portion over a cached prefix, decode tokens, a 2-token portion at a page edge
+    _attention_case(ops, dtype, nh, nkv, d, 16, [(37, 37), (9, 50), (1, 81), (1, 1), (2, 33), (1, 16), (1, 17)])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_far_key_stands_out(ops, dtype):
+    _attention_case(ops, dtype, 8, 2, 64, 64, [(1, 700), (5, 300), (1, 65)], planted=True)
+    _attention_case(ops, dtype, 8, 2, 64, 64, [(1, 700), (1, 640), (1, 65)], planted=True, splits=4)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("splits", [2, 3, 7])
+def test_paged_attention_split_keys(ops, dtype, splits):
+    _attention_case(ops, dtype, 8, 2, 64, 32, [(1, 1000), (1, 31), (1, 32), (1, 33), (3, 200)], splits=splits)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 5, 16, 40])
+def test_paged_attention_window(ops, dtype, window):
+    _attention_case(ops, dtype, 4, 2, 32, 16, [(20, 20), (7, 90), (1, 64), (1, 3)], window=window)
+    _attention_case(ops, dtype, 4, 2, 32, 16, [(1, 200), (1, 64)], window=window, splits=3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("L,bias,hidden", [(3, False, 72), (4, True, 96), (2, True, 40), (1, False, 64), (8, False, 130)])
+def test_shortconv_portions_and_state(ops, dtype, L, bias, hidden):
+    """Several steps over the same requests: portions shorter than the state, single tokens,
+    a fresh request in a slot another one used (stale state must not leak in)."""
+    torch.manual_seed(5)
+    slots_n = 5
+    state_ref = torch.full((slots_n, max(L - 1, 1), hidden), 9.0).to(dtype)[:, :L - 1]
+    state_gpu = dev(state_ref.clone())
+    taps = torch.randn(L, hidden)
+    in_b = torch.randn(3 * hidden) if bias else None
+    cv_b = torch.randn(hidden) if bias else None
+    # (slot, start position, portion length) per sequence and step
+    steps = [
+        [(2, 0, 1), (0, 0, 7), (4, 0, 2)],
+        [(2, 1, 1), (0, 7, 2), (4, 2, 1), (1, 0, 3)],
+        [(2, 2, 5), (0, 9, 1), (4, 3, 2)],
+        [(2, 0, 4), (3, 0, 1)],          # slot 2 starts over: a new request in a used slot
+        [(2, 4, 1), (3, 1, 1)],
+    ]
+    for step in steps:
+        n = sum(q for _, _, q in step)
+        h3 = torch.randn(n, 3 * hidden).to(dtype)
+        cu, pos, tseq = [0], [], []
+        for i, (_, p0, q) in enumerate(step):
+            cu.append(cu[-1] + q)
+            pos += list(range(p0, p0 + q))
+            tseq += [i] * q
+        ss = torch.tensor([s for s, _, _ in step], dtype=torch.int32)
+        cu_t, pos_t, ts_t = (torch.tensor(v, dtype=torch.int32) for v in (cu, pos, tseq))
+        want = plain_ops.shortconv(h3, in_b, taps, cv_b, state_ref, ss, ts_t, cu_t, pos_t)
+        got = ops.shortconv(dev(h3), dev(in_b), dev(taps), dev(cv_b), state_gpu if L > 1 else None, dev(ss),
+                            dev(ts_t), dev(cu_t), dev(pos_t))
+        torch.testing.assert_close(got.cpu().float(), want.float(), **tol(dtype))
+        if L > 1:
+            torch.testing.assert_close(state_gpu.cpu().float(), state_ref.float(), **tol(dtype))
+
+
+def test_sample_rows_greedy_ties_and_gumbel(ops):
+    torch.manual_seed(6)
+    V = 1000
+    logits = torch.randn(6, V)
+    logits[0, 17] = logits[0, 900] = 50.0                  # a tie: the lowest id wins
+    got = ops.sample_rows(dev(logits)).cpu()
+    assert got.tolist() == plain_ops.sample_rows(logits).tolist()
+    assert got[0] == 17
+    mode = torch.tensor([1, 2, 2, 0, 2, 2], dtype=torch.int32)
+    inv_t = torch.tensor([1.0, 1.25, 0.5, 1.0, 2.0, 1.0])
+    seeds = torch.tensor([0, 3, 3, 0, 2 ** 62 + 5, -7], dtype=torch.int64)
+    draws = torch.tensor([0, 0, 1, 0, 9, 4], dtype=torch.int64)
+    out = torch.full((6,), -1, dtype=torch.int32)
+    got = ops.sample_rows(dev(logits), dev(mode), dev(inv_t), dev(seeds), dev(draws), dev(out)).cpu()
+    want = plain_ops.sample_rows(logits, mode, inv_t, seeds, draws, torch.full((6,), -1, dtype=torch.int32))
+    assert got.tolist() == want.tolist()
+    assert got[3] == -1                                     # mode 0: untouched
+    # same (seed, draw) -> same token, whatever row it sits in
+    again = ops.sample_rows(dev(logits[[2, 1]].contiguous()), dev(mode[[2, 1]].contiguous()),
+                            dev(inv_t[[2, 1]].contiguous()), dev(seeds[[2, 1]].contiguous()),
+                            dev(draws[[2, 1]].contiguous())).cpu()
+    assert again.tolist() == [int(got[2]), int(got[1])]
+
+
+def test_gumbel_follows_the_tempered_softmax(ops):
+    """Frequencies of many draws against softmax(logits / T), within 4 sigma per token
+    (the reference's own check, crates/vapi-backend-candle/src/fused.rs:767-857)."""
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5, -3.0, 1.5, 0.0]])
+    T, N = 0.7, 4000
+    big = logits.repeat(N, 1).contiguous()
+    mode = torch.full((N,), 2, dtype=torch.int32)
+    inv_t = torch.full((N,), 1.0 / T)
+    seeds = torch.full((N,), 11, dtype=torch.int64)
+    draws = torch.arange(N, dtype=torch.int64)
+    toks = ops.sample_rows(dev(big), dev(mode), dev(inv_t), dev(seeds), dev(draws)).cpu()
+    p = torch.softmax(logits[0] / T, 0)
+    freq = torch.bincount(toks.long(), minlength=8).float() / N
+    sigma = torch.sqrt(p * (1 - p) / N)
+    assert torch.all((freq - p).abs() <= 4 * sigma + 1e-3), (freq, p)
+
+
+def test_apply_penalties(ops):
+    torch.manual_seed(7)
+    logits = torch.randn(3, 50)
+    rows = torch.tensor([0, 0, 2, 2], dtype=torch.int32)
+    toks = torch.tensor([4, 9, 4, 30], dtype=torch.int32)
+    counts = torch.tensor([1.0, 3.0, 2.0, 1.0])
+    rep, freq, pres = torch.tensor([1.3, 1.0, 0.8]), torch.tensor([0.1, 0.0, 0.5]), torch.tensor([0.2, 0.0, 0.0])
+    want = logits.clone()
+    plain_ops.apply_penalties(want, rows, toks, counts, rep, freq, pres)
+    got = dev(logits.clone())
+    ops.apply_penalties(got, dev(rows), dev(toks), dev(counts), dev(rep), dev(freq), dev(pres))
+    torch.testing.assert_close(got.cpu(), want, atol=1e-6, rtol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_linear_is_not_reduced_precision(ops, dtype):
+    torch.manual_seed(8)
+    ops.strict_fp32()
+    x = torch.randn(9, 300).to(dtype)
+    w = torch.randn(70, 300).to(dtype)
+    b = torch.randn(70)
+    got = ops.linear(dev(x), dev(w), dev(b.to(dtype)))
+    want = plain_ops.linear(x, w, b.to(dtype))
+    t = dict(atol=1e-4, rtol=1e-5) if dtype == torch.float32 else dict(atol=0.3, rtol=2e-2)
+    torch.testing.assert_close(got.cpu().float(), want.float(), **t)
+    if dtype == torch.bfloat16:
+        got32 = ops.linear(dev(x), dev(w), None, torch.float32)
+        assert got32.dtype == torch.float32
+        torch.testing.assert_close(got32.cpu(), plain_ops.linear(x, w, None, torch.float32), atol=2e-3, rtol=1e-4)
+        # a weight kept in float32 beside bfloat16 activations multiplies in float32
+        got_mixed = ops.linear(dev(x), dev(w.float()))
+        torch.testing.assert_close(got_mixed.cpu().float(), plain_ops.linear(x, w).float(), atol=0.3, rtol=2e-2)
