@@ -1,0 +1,328 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at LFM2-1.2B sizes with random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers N]
+
+One JSON line on stdout.  ``value`` is decoded tokens per second at the given batch, device-
+timed over exactly K decode steps with CUDA events (each step: the packed index data goes
+host->device, the captured decode graph replays, greedy tokens are chosen on the device).
+``e2e`` is the same metric through the engine loop a user drives (scheduler, step, sampler,
+host tokens in and out, wall clock).  ``prefill`` times one 2,048-token prompt in one step;
+``roofline`` relates the decode step to the bytes it must read.  Peaks come from
+MEASURED_PEAKS.json when the file is there, else from the fallback figures.
+
+The engine runs on one GPU: with --gpus above 1 it says so and exits with 2.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# LFM2-1.2B layer sizes: full_attention at layers 2, 5, 8, 10, 12, 14 of 16
+LFM2_1P2B = {
+    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
+    "vocab_size": 65536, "hidden_size": 2048, "intermediate_size": 12288,
+    "block_auto_adjust_ff_dim": True, "block_ffn_dim_multiplier": 1.0, "block_multiple_of": 256,
+    "num_hidden_layers": 16, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64,
+    "conv_L_cache": 3, "conv_bias": False, "rope_theta": 1000000.0, "norm_eps": 1e-5,
+    "tie_word_embeddings": True, "max_position_embeddings": 128000,
+    "layer_types": ["full_attention" if l in (2, 5, 8, 10, 12, 14) else "conv" for l in range(16)],
+}
+FULL_LAYERS = 16
+
+
+def peaks():
+    p = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                m = json.load(f)
+            for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+                if isinstance(m.get(k), (int, float)):
+                    p[k] = float(m[k])
+            p["source"] = "measured"
+        except (OSError, ValueError):
+            pass
+    return p
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm = sorted(int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def model_numbers(runner):
+    """Bytes of every weight a decode step reads once, and matrix-product flops per token."""
+    import torch
+    seen, wbytes, mm_params = set(), 0, 0
+    plan = runner.plan
+
+    def add(t, is_matrix):
+        nonlocal wbytes, mm_params
+        if t is None or t.data_ptr() in seen:
+            return
+        seen.add(t.data_ptr())
+        wbytes += t.numel() * t.element_size()
+        if is_matrix:
+            mm_params += t.numel()
+
+    for call in plan.order:
+        blk = plan.layers[call.layer]
+        for part in (blk.mixer, blk.ffn, blk.mixer_norm, blk.ffn_norm):
+            for v in vars(part).values():
+                if isinstance(v, torch.Tensor):
+                    add(v, v.dim() == 2 and v.shape[0] > 8)
+    add(plan.final_norm.weight, False)
+    add(plan.head.weight, True)        # tied: the embedding table, read once by the head
+    return wbytes, mm_params
+
+
+def run(args):
+    import torch
+    from vapi_b200 import ops
+    from vapi_b200.engine.engine import Engine
+    from vapi_b200.engine.runner import ModelRunner
+    from vapi_b200.engine.scheduler import SchedulerConfig
+    from vapi_b200.engine.step import StepEntry
+    from vapi_b200.sampling.params import SamplingParams
+
+    pk = peaks()
+    cfg = dict(LFM2_1P2B)
+    layers = args.layers or FULL_LAYERS
+    if layers != FULL_LAYERS:
+        cfg["num_hidden_layers"] = layers
+        cfg["layer_types"] = cfg["layer_types"][:layers]
+    ctx_len, B = args.context, args.batch
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    max_b = max(B, 64)
+    page = ModelRunner.default_page_size
+    pages = max_b * (-(-ctx_len // page)) + 8
+    runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", num_pages=pages,
+                                     max_requests=max_b, max_batched_tokens=8192, max_context=ctx_len + 64,
+                                     watermark=0.0, validate=True)
+    wbytes, mm_params = model_numbers(runner)
+    gen = torch.Generator().manual_seed(1)
+    vocab = cfg["vocab_size"]
+
+    def fill(batch, length):
+        """Open `batch` requests and prefill them to `length` tokens in portions (untimed)."""
+        rcs = []
+        for i in range(batch):
+            rc = runner.cache.open(("bench", batch, i))
+            toks = torch.randint(0, vocab, (length,), generator=gen).tolist()
+            pos = 0
+            while pos < length:
+                q = min(4096, length - pos)
+                assert runner.cache.reserve(rc, pos + q)
+                runner.step([StepEntry(rc, toks[pos:pos + q], [])])
+                pos += q
+            rcs.append(rc)
+        torch.cuda.synchronize()
+        return rcs
+
+    def decode_steps(rcs, count, timed):
+        """`count` decode steps on the stream; device time in ms when `timed`."""
+        toks = torch.randint(0, vocab, (count, len(rcs)), generator=gen).tolist()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for s in range(count):
+            entries = []
+            for j, rc in enumerate(rcs):
+                assert runner.cache.reserve(rc, rc.num_tokens + 1)
+                entries.append(StepEntry(rc, [toks[s][j]], [0]))
+            logits = runner.step_decode_graph(entries)
+            if logits is None:
+                logits = runner.step(entries)
+            ops.sample_rows(logits)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) if timed else 0.0
+
+    def decode_point(batch, steps, warmup, clocks=None):
+        start_len = ctx_len - (steps + warmup) - 1
+        rcs = fill(batch, start_len)
+        decode_steps(rcs, warmup, False)
+        if clocks:
+            clocks.start()
+        before = ops.launch_count
+        ms = decode_steps(rcs, steps, True)
+        launches = ops.launch_count - before
+        clk = clocks.stop() if clocks else None
+        kv_bytes = sum(rc.num_tokens for rc in rcs) * runner.cache.bytes_per_token() + \
+            batch * runner.cache.state_bytes_per_request()
+        for rc in rcs:
+            runner.cache.close(rc)
+        return ms, launches, clk, kv_bytes
+
+    # ---- headline: decode at the given batch -----------------------------------------
+    clocks = ClockSampler()
+    ms, launches, clk, kv_bytes = decode_point(B, args.steps, args.warmup, clocks)
+    ms_step = ms / args.steps
+    value = B * args.steps / (ms / 1e3)
+    step_bytes = wbytes + kv_bytes
+    achieved = step_bytes / (ms_step / 1e3) / 1e9
+
+    # ---- other batch sizes ----------------------------------------------------------
+    points = {}
+    for b in (1, 64):
+        st = max(16, args.steps // 2)
+        m, _, _, _ = decode_point(b, st, max(3, args.warmup // 2))
+        points[f"decode_b{b}"] = round(b * st / (m / 1e3), 1)
+
+    # ---- prefill of 2,048 tokens in one step ---------------------------------------
+    T = 2048
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    times = []
+    for it in range(3 + 5):
+        rc = runner.cache.open(("prefill", it))
+        toks = torch.randint(0, vocab, (T,), generator=gen).tolist()
+        assert runner.cache.reserve(rc, T)
+        flush.zero_()                                   # larger than L2: nothing of the last run stays cached
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        runner.step([StepEntry(rc, toks, [T - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= 3:
+            times.append(e0.elapsed_time(e1))
+        runner.cache.close(rc)
+    pre_ms = sorted(times)[len(times) // 2]
+    c = runner.plan.config
+    n_attn = sum(1 for t in c.layer_types if t == "full_attention")
+    head_params = runner.plan.head.weight.numel()
+    flops = 2.0 * (mm_params - head_params) * T + 2.0 * head_params * 1 + \
+        n_attn * 4.0 * c.num_attention_heads * c.head_dim * (T * (T + 1) / 2)
+    prefill = {"value": round(T / (pre_ms / 1e3), 1), "tokens": T, "ms": round(pre_ms, 3),
+               "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+               "tflops": round(flops / (pre_ms / 1e3) / 1e12, 1), "peak_tflops": pk["bf16_tflops"]}
+    del flush
+
+    # ---- end to end through the engine loop ----------------------------------------
+    eng = Engine(runner, SchedulerConfig(max_concurrent_seqs=max_b, max_batched_tokens=8192,
+                                         prefill_chunk_tokens=4096, max_context=ctx_len + 64), use_graphs=True)
+    start_len = ctx_len - (args.steps + args.warmup) - 2
+    for i in range(B):
+        prompt = torch.randint(0, vocab, (start_len,), generator=gen).tolist()
+        eng.admit(("e2e", i), prompt, SamplingParams(temperature=0.0, max_tokens=args.steps + args.warmup + 1,
+                                                     ignore_eos=True))
+    while any(s.needs_prefill() for s in eng.scheduler.seqs.values()) or eng.scheduler.num_waiting:
+        eng.step()
+    for _ in range(args.warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    h2d = d2h = 0
+    for _ in range(args.steps):
+        out = eng.step()
+        assert len(out.new_tokens) == B
+        h2d += runner.packer.h2d_bytes_last + eng.sampler.h2d_bytes_last
+        d2h += eng.sampler.d2h_bytes_last
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    e2e = {"value": round(B * args.steps / e2e_s, 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps,
+           "ms_per_step": round(e2e_s * 1e3 / args.steps, 4)}
+    runner.check_status()
+
+    line = {
+        "metric": "LFM2-1.2B decode tokens/s (batch %d, context %d), random weights" % (B, ctx_len),
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (seeded uniform-random token ids, random-init weights N(0, 0.02))",
+        "impl": "vapi_b200",
+        "config": {
+            "model": "LFM2-1.2B sizes", "global_batch": B, "seq_len": ctx_len, "parallelism": "single GPU",
+            "layers": layers, "layers_of_configuration": FULL_LAYERS, "attention_layers": n_attn,
+            "hidden_size": c.hidden_size, "intermediate_size": c.intermediate_size, "vocab_size": c.vocab_size,
+            "heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads, "head_dim": c.head_dim,
+            "conv_L_cache": c.conv_L_cache, "page_size": page, "cuda_graphs": True,
+            "l2": "inputs larger than L2 (weights %.2f GB per step)" % (wbytes / 1e9),
+            "peaks": pk["source"],
+        },
+        "e2e": e2e,
+        "gpu_launches": launches,
+        "clocks": clk,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
+        "points": points,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def reference_arm():
+    """The reference is a Rust workspace (Cargo, candle); it has no Python package to
+    install and no Rust toolchain exists here, so its arm cannot run."""
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "Heyo-Computer/vapi is a Rust/Cargo workspace with no Python packaging; "
+                                     "pip cannot install it offline and there is no cargo/rustc in the image"}),
+          flush=True)
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0 = all)")
+    ap.add_argument("--impl", default="vapi_b200", choices=["vapi_b200", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print("bench.py: this engine runs on one GPU; --gpus %d is not supported" % args.gpus, flush=True)
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    return run(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,276 @@
+"""On the GPU: greedy generation through the Python entry point against the plain model,
+captured decode steps against eager ones, temperature sampling, each part alone against the
+plain model's function for it, and a toy mixer with state of its own that is registered,
+built and stepped without touching the package's files."""
+import math
+
+import pytest
+import torch
+
+import plain_lfm2
+import plain_ops
+from conftest import TINY_A, TINY_B, TINY_C
+
+pytestmark = pytest.mark.gpu
+
+
+def _prompts(cfg, seed, lens):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(8, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+
+
+def _agrees_up_to_a_near_tie(plain, prompt, got, want, gap=0.5):
+    """bfloat16 may part from the float32 tokens only where the plain top-1/top-2 gap is small
+    (the reference's rule for real models, crates/vapi-backend-candle/tests/real_model.rs:336-341)."""
+    for i, (a, b) in enumerate(zip(got, want)):
+        if a != b:
+            top = torch.topk(plain.logits(list(prompt) + want[:i])[-1], 2).values
+            return float(top[0] - top[1]) < gap
+    return True
+
+
+@pytest.mark.parametrize("name,cfg", [("A", TINY_A), ("B", TINY_B), ("C", TINY_C)])
+def test_greedy_generation_float32(name, cfg, tiny_dirs):
+    from vapi_b200 import LLM, SamplingParams
+    plain = plain_lfm2.PlainLfm2(tiny_dirs[name])
+    prompts = _prompts(cfg, 1, [1, 7, 33, 70])
+    for graphs in (False, True):
+        llm = LLM(tiny_dirs[name], dtype="f32", num_blocks=24, max_concurrent_seqs=4, max_batched_tokens=64,
+                  max_context=256, prefill_chunk_tokens=16, cuda_graphs=graphs)
+        out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True))
+        llm.runner.check_status()
+        for p, c in zip(prompts, out):
+            want = plain.greedy(p, 16)
+            assert c.tokens == want or _agrees_up_to_a_near_tie(plain, p, c.tokens, want, gap=1e-3), (graphs, c.tokens, want)
+        llm.runner.cache.check_invariants()
+        if graphs:
+            assert llm.runner._graphs, "pure decode steps must have gone through a captured graph"
+
+
+def test_greedy_generation_bfloat16(tiny_dirs, tmp_path):
+    from vapi_b200 import LLM, SamplingParams
+    from vapi_b200.weights import write_random_model
+    d = write_random_model(str(tmp_path / "m"), TINY_B, 12, std=0.2, norm_init="perturbed", dtype=torch.bfloat16)
+    plain = plain_lfm2.PlainLfm2(d)
+    prompts = _prompts(TINY_B, 2, [5, 40, 97])
+    llm = LLM(d, dtype="bf16", num_blocks=24, max_concurrent_seqs=4, max_batched_tokens=64, max_context=256,
+              prefill_chunk_tokens=16)
+    out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    for p, c in zip(prompts, out):
+        assert _agrees_up_to_a_near_tie(plain, p, c.tokens, plain.greedy(p, 12)), (c.tokens,)
+
+
+def test_captured_decode_equals_eager_decode(tiny_dirs):
+    from vapi_b200.engine.runner import ModelRunner
+    from vapi_b200.engine.step import StepEntry
+    prompts = _prompts(TINY_B, 3, [20, 3, 64])
+    outs = {}
+    for graphs in (False, True):
+        r = ModelRunner.from_dir(tiny_dirs["B"], dtype="float32", num_pages=16, max_requests=4, max_batched_tokens=128,
+                                 max_context=256)
+        rcs = []
+        for i, p in enumerate(prompts):
+            rc = r.cache.open(i)
+            assert r.cache.reserve(rc, len(p))
+            r.step([StepEntry(rc, p, [])])
+            rcs.append(rc)
+        rows = []
+        for s in range(6):
+            entries = []
+            for j, rc in enumerate(rcs):
+                assert r.cache.reserve(rc, rc.num_tokens + 1)
+                entries.append(StepEntry(rc, [(7 * s + j) % 500], [0]))
+            lg = r.step_decode_graph(entries) if graphs else r.step(entries)
+            assert lg is not None
+            rows.append(lg.clone().cpu())
+        outs[graphs] = torch.stack(rows)
+        r.check_status()
+    assert (outs[True] - outs[False]).abs().max() < 1e-4
+
+
+def test_temperature_sampling_is_seeded_and_batch_independent(tiny_dirs):
+    from vapi_b200 import LLM, SamplingParams
+    prompts = _prompts(TINY_B, 4, [5, 40, 97])
+    sp = SamplingParams(temperature=0.8, max_tokens=10, seed=3, ignore_eos=True)
+
+    def run(which):
+        llm = LLM(tiny_dirs["B"], dtype="f32", num_blocks=24, max_concurrent_seqs=4, max_batched_tokens=64,
+                  max_context=256, prefill_chunk_tokens=16)
+        return {i: c.tokens for i, c in zip(which, llm.generate([prompts[i] for i in which], sp))}
+
+    together = run([0, 1, 2])
+    assert together == run([0, 1, 2])
+    assert together[1] == run([1])[1]
+    greedy = LLM(tiny_dirs["B"], dtype="f32", num_blocks=24, max_concurrent_seqs=4, max_batched_tokens=64,
+                 max_context=256).generate([prompts[1]], SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    assert together[1] != greedy[0].tokens, "temperature 0.8 on a flat tiny model should not reproduce greedy"
+    # truncating samplers run on the host from the row of logits
+    tk = LLM(tiny_dirs["B"], dtype="f32", num_blocks=24, max_concurrent_seqs=4, max_batched_tokens=64, max_context=256)
+    one = tk.generate([prompts[1]], SamplingParams(temperature=1.0, top_k=1, max_tokens=10, seed=1, ignore_eos=True))
+    assert one[0].tokens == greedy[0].tokens
+
+
+def test_penalties_change_what_is_generated(tiny_dirs):
+    from vapi_b200 import LLM, SamplingParams
+    p = _prompts(TINY_A, 6, [12])
+    llm = LLM(tiny_dirs["A"], dtype="f32", num_blocks=8, max_concurrent_seqs=2, max_batched_tokens=64, max_context=128)
+    base = llm.generate(p, SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True))[0].tokens
+    pen = llm.generate(p, SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True, presence_penalty=2.0,
+                                         frequency_penalty=1.0))[0].tokens
+    assert len(set(pen)) >= len(set(base)) and pen != base
+
+
+# ---- each part alone -----------------------------------------------------------------------
+def _ctx_for(n, S, cu, klens, positions, page_table=None, slots=None, state_slots=None, dtype=torch.float32):
+    from vapi_b200.engine.step import GroupMeta, StepContext
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    tok_seq = []
+    for s in range(S):
+        tok_seq += [s] * (cu[s + 1] - cu[s])
+    groups = [GroupMeta(i32(slots), i32(page_table))] if page_table is not None else []
+    return StepContext(n=n, num_seqs=S, num_rows=0, max_q=max(cu[s + 1] - cu[s] for s in range(S)), max_k=max(klens),
+                       tokens=i32([0] * n), positions=i32(positions), tok_seq=i32(tok_seq), cu_q=i32(cu),
+                       seqlens_k=i32(klens), state_slots=i32(state_slots or [0] * S), logits_rows=None,
+                       groups=groups, dtype=dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_parts_alone(dtype):
+    """Norm, position encoding, attention, short conv, feed-forward and the block, each built
+    from sizes alone (no model configuration), against the plain model's function."""
+    from vapi_b200.parts import (CacheView, GQAttention, PreNormBlock, RMSNorm, RotaryEncoding, ShortConv, SwiGLU)
+    torch.manual_seed(0)
+    H, nh, nkv, d, F, L, T, eps, theta = 80, 5, 1, 32, 112, 4, 23, 1e-6, 5e4
+    tol = dict(atol=2e-4, rtol=2e-4) if dtype == torch.float32 else dict(atol=6e-2, rtol=6e-2)
+    c = dict(hidden=H, heads=nh, kv_heads=nkv, head_dim=d, eps=eps, theta=theta, L=L, conv_bias=True)
+    w = {k: (torch.randn(s) * 0.2).to(dtype).float() for k, s in {
+        "a.q_proj.weight": (nh * d, H), "a.k_proj.weight": (nkv * d, H), "a.v_proj.weight": (nkv * d, H),
+        "a.out_proj.weight": (H, nh * d), "c.in_proj.weight": (3 * H, H), "c.out_proj.weight": (H, H),
+        "f.w1.weight": (F, H), "f.w3.weight": (F, H), "f.w2.weight": (H, F)}.items()}
+    w.update({"a.q_layernorm.weight": 1 + 0.1 * torch.randn(d), "a.k_layernorm.weight": 1 + 0.1 * torch.randn(d),
+              "c.in_proj.bias": 0.2 * torch.randn(3 * H), "c.conv.weight": 0.5 * torch.randn(H, 1, L),
+              "c.conv.bias": 0.2 * torch.randn(H), "c.out_proj.bias": 0.2 * torch.randn(H),
+              "n1.weight": 1 + 0.1 * torch.randn(H), "n2.weight": 1 + 0.1 * torch.randn(H)})
+    dev = {k: (v.cuda().to(dtype) if v.dim() == 2 and "conv" not in k else v.cuda()) for k, v in w.items()}
+    x = torch.randn(T, H)
+    a = x.to(dtype).float()
+
+    page, pages = 16, 4
+    ctx = _ctx_for(T, 1, [0, T], [T], list(range(T)), page_table=[[2, 0, 3, 1]],
+                   slots=[[2, 0, 3, 1][p // page] * page + p % page for p in range(T)], dtype=dtype)
+    rope = RotaryEncoding(d, theta, 4096)
+    ctx.pos["rope"] = rope.prepare(ctx)
+    cr, sr = plain_lfm2.rope_tables(torch.arange(T), d, theta, torch.float32)
+    torch.testing.assert_close(ctx.pos["rope"][0].cpu(), cr, atol=1e-5, rtol=0)
+
+    att = GQAttention(H, nh, nkv, d, qk_norm_eps=eps, pos="rope")
+    att.bind(dev, "a.", dtype)
+    kv = torch.zeros(pages, 2, nkv, page, d, dtype=dtype, device="cuda")
+    got = att.forward(a.cuda().to(dtype), ctx, CacheView("paged", kv, ctx.groups[0], True))
+    torch.testing.assert_close(got.float().cpu(), plain_lfm2.attention(a, w, "a.", c), **tol)
+
+    conv = ShortConv(H, L, bias=True)
+    conv.bind(dev, "c.", dtype)
+    state = torch.full((2, L - 1, H), 5.0, dtype=dtype, device="cuda")
+    got = conv.forward(a.cuda().to(dtype), ctx, CacheView("state", state, None, True))
+    torch.testing.assert_close(got.float().cpu(), plain_lfm2.shortconv(a, w, "c.", c), **tol)
+
+    ffn = SwiGLU(H, F)
+    ffn.bind(dev, "f.", dtype)
+    got = ffn.forward(a.cuda().to(dtype), ctx)
+    torch.testing.assert_close(got.float().cpu(), plain_lfm2.feed_forward(a, w, "f."), **tol)
+
+    norm = RMSNorm(H, eps)
+    norm.bind(dev, "n1.", dtype)
+    xs = x.clone().cuda()
+    got = norm.apply(xs, None, dtype)
+    torch.testing.assert_close(got.float().cpu(), plain_lfm2.rmsnorm(x, w["n1.weight"], eps), **tol)
+
+    # the block: conv mixer + feed-forward around the float32 stream, pending delta handed on
+    blk = PreNormBlock(RMSNorm(H, eps), ShortConv(H, L, bias=True), RMSNorm(H, eps), SwiGLU(H, F),
+                       {"mixer_norm": "n1.", "mixer": "c.", "ffn_norm": "n2.", "ffn": "f."})
+    blk.bind(dev, "", dtype)
+    xs = x.clone().cuda()
+    delta = blk.forward(xs, None, ctx, CacheView("state", torch.zeros_like(state), None, True))
+    x1 = x + plain_lfm2.shortconv(plain_lfm2.rmsnorm(x, w["n1.weight"], eps), w, "c.", c)
+    want = x1 + plain_lfm2.feed_forward(plain_lfm2.rmsnorm(x1, w["n2.weight"], eps), w, "f.")
+    torch.testing.assert_close((xs + delta.float()).cpu(), want, **(tol if dtype == torch.float32 else dict(atol=0.15, rtol=6e-2)))
+
+
+# ---- a toy mixer with state of its own --------------------------------------------------------
+def test_a_toy_mixer_with_its_own_state_can_be_registered_built_and_stepped(tmp_path):
+    """A running-mean mixer defined here: state = (sum of inputs so far) per request.  It gets
+    a state slot from the cache manager, a registry entry, an architecture of its own, and
+    runs through the package's step function, portions and decode tokens alike; the
+    package's files are not touched.  Its math is plain torch on the device, which is the
+    toy's own business; everything around it is the engine."""
+    import json
+    import os
+    from vapi_b200.config import Architecture, register_architecture, unregister_architecture
+    from vapi_b200.engine.runner import ModelRunner
+    from vapi_b200.engine.step import StepEntry
+    from vapi_b200.models.plan import LayerCall, ModelPlan
+    from vapi_b200.parts import (Mixer, OutputHead, PreNormBlock, RMSNorm, StateSpec, SwiGLU, TensorSpec,
+                                 TokenEmbedding, register_mixer, make_part, MIXERS)
+    from vapi_b200.weights import write_random_model
+
+    class RunningMean(Mixer):
+        def __init__(self, hidden):
+            self.hidden = hidden
+
+        def cache_spec(self):
+            return StateSpec("running_sum", (self.hidden,), torch.float32)
+
+        def tensor_specs(self, prefix):
+            return [TensorSpec(prefix + "gain", (self.hidden,), role="vector", init="ones")]
+
+        def bind(self, tensors, prefix, dtype):
+            self.gain = tensors[prefix + "gain"]
+
+        def forward(self, a, ctx, cache):
+            out = torch.empty_like(a)
+            cu, pos, slots = ctx.cu_q.tolist(), ctx.positions.tolist(), ctx.state_slots.tolist()
+            for s in range(ctx.num_seqs):
+                r0, r1 = cu[s], cu[s + 1]
+                st = cache.tensor[slots[s]]
+                base = st.clone() if pos[r0] > 0 else torch.zeros_like(st)     # position 0: nothing before
+                run = base + torch.cumsum(a[r0:r1].float(), 0)
+                cnt = torch.arange(pos[r0] + 1, pos[r0] + 1 + (r1 - r0), device=a.device).unsqueeze(1)
+                out[r0:r1] = (run / cnt * self.gain).to(a.dtype)
+                st.copy_(run[-1])
+            return out
+
+    register_mixer("toy_running_mean", RunningMean, replace=True)
+
+    def plan(cfg):
+        H, V = cfg["hidden_size"], cfg["vocab_size"]
+        emb = TokenEmbedding(V, H, "emb.weight")
+        layers = [PreNormBlock(RMSNorm(H, 1e-5), make_part(MIXERS, "toy_running_mean", hidden=H), RMSNorm(H, 1e-5),
+                               SwiGLU(H, cfg["ff"]), {"mixer_norm": "n1.", "mixer": "mix.", "ffn_norm": "n2.", "ffn": "ffn."})
+                  for _ in range(2)]
+        # the run order names layer 0 twice: shared weights, a state of its own at each call site
+        return ModelPlan("ToyForCausalLM", V, H, 512, emb, layers, ["l0.", "l1."],
+                         [LayerCall(0), LayerCall(1), LayerCall(0)], RMSNorm(H, 1e-5), "final.",
+                         OutputHead(V, H, True, emb))
+
+    register_architecture(Architecture("ToyForCausalLM", ("toy",), lambda v: v, plan), replace=True)
+    try:
+        cfg = {"architectures": ["ToyForCausalLM"], "vocab_size": 100, "hidden_size": 48, "ff": 64}
+        d = write_random_model(str(tmp_path / "toy"), cfg, 0, std=0.3, norm_init="perturbed")
+        r = ModelRunner.from_dir(d, dtype="float32", num_pages=4, max_requests=3, max_batched_tokens=64, max_context=128)
+        assert len(r.cache.state) == 1 and r.cache.state[0].tensor.shape == (4, 3, 48) and not r.cache.paged
+        toks = torch.randint(0, 100, (30,), generator=torch.Generator().manual_seed(0)).tolist()
+        a = r.cache.open("whole")
+        whole = r.step([StepEntry(a, toks, list(range(30)))]).cpu()
+        r.cache.close(a)
+        b, c2 = r.cache.open("cut"), r.cache.open("other")     # `cut` lands in the slot `whole` used
+        rows, pos = [], 0
+        for q in (2, 1, 9, 1, 1, 16):
+            other = StepEntry(c2, [5] * 3, [])                 # another request alongside, in its own slot
+            out = r.step([other, StepEntry(b, toks[pos:pos + q], list(range(q)))])
+            rows.append(out.cpu())
+            pos += q
+        assert (torch.cat(rows) - whole).abs().max() < 1e-4
+    finally:
+        unregister_architecture("ToyForCausalLM")
+        MIXERS.pop("toy_running_mean", None)

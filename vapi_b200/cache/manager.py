@@ -102,6 +102,7 @@ class CacheManager:
             for j, s in enumerate(ss):
                 self._site[s] = ("state", gi, j)
         self._live: Dict[object, RequestCache] = {}
+        self._set_aside: List[List[int]] = [[] for _ in self.paged]
 
     # ---- what the model sees -------------------------------------------------------
     @property
@@ -121,6 +122,19 @@ class CacheManager:
         if kind == "paged":
             return self.paged[gi].tensor[j]
         return self.state[gi].tensor[:, j]
+
+    def set_aside_pages(self) -> Optional[List[int]]:
+        """Take one page per paged group out of circulation (for the padding rows of a
+        fixed-shape decode step, like the reference's reserved blocks,
+        crates/vapi-backend-candle/src/backend.rs:426-438).  None if a group has no free page."""
+        if any(g.pool.num_free == 0 for g in self.paged):
+            return None
+        pages = []
+        for gi, g in enumerate(self.paged):
+            p = g.pool.allocate()
+            self._set_aside[gi].append(p)
+            pages.append(p)
+        return pages
 
     # ---- sizing -----------------------------------------------------------------------
     def pages_for(self, tokens: int) -> int:
@@ -143,9 +157,6 @@ class CacheManager:
 
     def live(self, request_id) -> Optional[RequestCache]:
         return self._live.get(request_id)
-
-    def _needed(self, g: PagedGroup, rc_table: List[int], total: int) -> int:
-        return max(0, self.pages_for(total) - len(rc_table))
 
     def pages_needed(self, rc: Optional[RequestCache], total: int) -> List[int]:
         """New pages each group would need so that positions < total are covered."""
@@ -216,7 +227,7 @@ class CacheManager:
         """No page lost, held twice or freed twice; the same for slots."""
         for gi, g in enumerate(self.paged):
             g.pool.check_invariants()
-            held = sorted(p for rc in self._live.values() for p in rc.tables[gi] if p >= 0)
+            held = sorted([p for rc in self._live.values() for p in rc.tables[gi] if p >= 0] + self._set_aside[gi])
             assert len(set(held)) == len(held), "a page is held by two requests"
             assert held == g.pool.held_pages(), "pool and requests disagree about held pages"
         self.slots.check_invariants()

@@ -210,6 +210,7 @@ def unregister_architecture(name: str) -> None:
 
 
 def registered_architectures() -> List[str]:
+    _ensure_builtin()
     return sorted({a.name for a in _REGISTRY.values()})
 
 

@@ -1,0 +1,1 @@
+"""Step function, scheduler and engine loop."""

@@ -73,6 +73,9 @@ class ModelRunner:
             owner = call.cache_of if call.cache_of is not None else i
             self._site_of.append(owner if self.cache.site_tensor(owner) is not None else None)
         self.steps_run = 0
+        self.graph_max_batch = min(64, max_requests)
+        self._graphs: Dict[int, Any] = {}
+        self._graphs_off = self.device.type != "cuda"
 
     # ---- construction -------------------------------------------------------------
     @classmethod
@@ -167,6 +170,87 @@ class ModelRunner:
             self.cache.commit(e.cache, e.start + len(e.tokens))
         self.steps_run += 1
         return logits
+
+    # ---- captured decode steps --------------------------------------------------------
+    def _bucket(self, S: int) -> int:
+        b = 1
+        while b < S:
+            b *= 2
+        return b
+
+    def _capture(self, B: int):
+        """Capture the device work of a pure decode step of B sequences into a CUDA graph
+        (the reference does the same per power-of-two bucket up to 64,
+        crates/vapi-backend-candle/src/backend.rs:1015-1019, 1124-1214).  Inputs live at fixed
+        offsets of the packer's device buffer; padding rows use pages and a state slot that
+        no request owns."""
+        if self.packer._pad_pages is None:
+            pages = self.cache.set_aside_pages()
+            if pages is None:
+                return None
+            self.packer.set_pad_pages(pages)
+        width = self.packer.max_width
+        ctx = self.packer.pack([], self.dtype, n_cap=B, s_cap=B, width=width, status=self.status)
+        ctx.max_k = self.max_context
+        ctx.attention_splits = self._decode_splits(B)
+        cur = torch.cuda.current_stream()
+        side = torch.cuda.Stream()
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                ctx.pos = {}
+                self.forward(ctx)
+        cur.wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        ctx.pos = {}
+        before = ops.launch_count
+        with torch.cuda.graph(graph):
+            logits = self.forward(ctx)
+        return graph, logits, ops.launch_count - before
+
+    def _decode_splits(self, B: int) -> int:
+        from ..parts.attention import GQAttention
+        best = 1
+        for blk in self.plan.layers:
+            m = getattr(blk, "mixer", None)
+            if isinstance(m, GQAttention):
+                best = max(best, ops.attention_splits(B, 1, self.max_context, m.nh, m.nkv))
+        return best
+
+    def step_decode_graph(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """A pure decode step (one token and one wanted row per request) through a captured
+        graph; None when the step is not of that shape or graphs are unavailable, in which
+        case the caller uses :meth:`step`."""
+        S = len(entries)
+        if self._graphs_off or S == 0 or S > self.graph_max_batch:
+            return None
+        for e in entries:
+            if len(e.tokens) != 1 or list(e.want) != [0]:
+                return None
+        if self.validate:
+            validate_step(entries, self.cache, self.vocab_size, self.max_context)
+        B = self._bucket(S)
+        if B not in self._graphs:
+            try:
+                self._graphs[B] = self._capture(B)
+            except Exception as exc:      # capture failed: run eagerly from now on
+                import warnings
+                warnings.warn(f"CUDA graph capture failed ({exc}); decoding eagerly")
+                self._graphs_off = True
+                torch.cuda.synchronize()
+                return None
+            if self._graphs[B] is None:
+                self._graphs_off = True
+                return None
+        graph, logits, kernels = self._graphs[B]
+        self.packer.pack(entries, self.dtype, n_cap=B, s_cap=B, width=self.packer.max_width, status=self.status)
+        graph.replay()
+        ops.launch_count += kernels
+        for e in entries:
+            self.cache.commit(e.cache, e.start + 1)
+        self.steps_run += 1
+        return logits[:S]
 
     def check_status(self) -> None:
         """Raise if a kernel met an index it refused to follow (a bad token id, slot or

@@ -162,7 +162,7 @@ class StepPacker:
         S = len(entries)
         n = sum(len(e.tokens) for e in entries)
         R = sum(len(e.want) for e in entries)
-        w_need = max(cache.pages_for(e.start + len(e.tokens)) for e in entries)
+        w_need = max([cache.pages_for(e.start + len(e.tokens)) for e in entries] or [1])
         pad = n_cap is not None
         n_c = n_cap if pad else n
         s_c = s_cap if pad else S
@@ -184,7 +184,7 @@ class StepPacker:
         cu_q, pos_n = [0], 0
         toks, poss, tseq, rows = [], [], [], []
         slots: List[List[int]] = [[] for _ in range(self.G)]
-        max_q = max_k = 0
+        max_q = max_k = 1 if pad else 0
         for si, e in enumerate(entries):
             q, st = len(e.tokens), e.start
             max_q, max_k = max(max_q, q), max(max_k, st + q)
@@ -207,6 +207,7 @@ class StepPacker:
             cu_q.append(cu_q[-1] + 1)
             hb[lay["seqlens_k"] + si] = 1
             hb[lay["state_slots"] + si] = cache.scratch_slot
+            rows.append(len(toks))
             tseq.append(si)
             toks.append(0)
             poss.append(0)
@@ -240,11 +241,11 @@ class StepPacker:
                             d[lay[f"table{g}"]:lay[f"table{g}"] + s_eff * w_c].view(s_eff, w_c))
                   for g in range(self.G)]
         return StepContext(
-            n=n_eff, num_seqs=s_eff, num_rows=R, max_q=max_q, max_k=max_k,
+            n=n_eff, num_seqs=s_eff, num_rows=len(rows), max_q=max_q, max_k=max_k,
             tokens=view("tokens", n_eff), positions=view("positions", n_eff), tok_seq=view("tok_seq", n_eff),
             cu_q=view("cu_q", s_eff + 1), seqlens_k=view("seqlens_k", s_eff),
             state_slots=view("state_slots", s_eff),
-            logits_rows=view("rows", R) if R > 0 else None,
+            logits_rows=view("rows", len(rows)) if rows else None,
             groups=groups, dtype=dtype, status=status)
 
     # a page per group that padding rows may scribble on; set by whoever captures graphs

@@ -46,9 +46,15 @@ def _lib(name: str) -> ctypes.CDLL:
     return lib
 
 
-def _check(lib: ctypes.CDLL, rc: int) -> None:
+#: how many of this package's own kernels have been launched (library products not counted)
+launch_count = 0
+
+
+def _check(lib: ctypes.CDLL, rc: int, launches: int = 1) -> None:
+    global launch_count
     if rc != 0:
         raise KernelError(lib.vapi_last_error().decode(errors="replace") + f" (code {rc})")
+    launch_count += launches
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -275,7 +281,7 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tenso
         _p(q), ctypes.c_longlong(q_row_stride), _p(cache_layer), _dt(q), _p(block_table),
         block_table.stride(0), _p(cu_q), _p(seqlens_k), _p(out), _p(part_o), _p(part_ml), n, num_seqs,
         max_q, nh, nkv, d, page_size, num_pages, ctypes.c_float(scale), window, splits, _p(status),
-        _stream()))
+        _stream()), 2 if splits > 1 else 1)
     return out
 
 
