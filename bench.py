@@ -139,7 +139,7 @@ def run(args):
     page = ModelRunner.default_page_size
     pages = max_b * (-(-ctx_len // page)) + 8
     runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", num_pages=pages,
-                                     max_requests=max_b, max_batched_tokens=8192, max_context=ctx_len + 64,
+                                     max_requests=max_b, max_batched_tokens=8192, max_context=ctx_len + 256,
                                      watermark=0.0, validate=True)
     wbytes, mm_params = model_numbers(runner)
     gen = torch.Generator().manual_seed(1)
@@ -196,57 +196,41 @@ def run(args):
             runner.cache.close(rc)
         return ms, launches, clk, kv_bytes
 
+    if args.only == "prefill":
+        return prefill_only(args, runner, mm_params, pk, gen, vocab, dev)
     # ---- headline: decode at the given batch -----------------------------------------
     clocks = ClockSampler()
     ms, launches, clk, kv_bytes = decode_point(B, args.steps, args.warmup, clocks)
     ms_step = ms / args.steps
     value = B * args.steps / (ms / 1e3)
+    print(f"[bench] decode b{B}: {value:.0f} tok/s, {ms_step:.3f} ms/step", file=sys.stderr, flush=True)
     step_bytes = wbytes + kv_bytes
     achieved = step_bytes / (ms_step / 1e3) / 1e9
 
+    if args.only == "decode":
+        print(json.dumps({"only": "decode", "value": round(value, 1), "ms_per_step": round(ms_step, 4),
+                          "gpu_launches": launches, "roofline_frac": round(achieved / pk["hbm_gbs"], 4)}), flush=True)
+        return 0
     # ---- other batch sizes ----------------------------------------------------------
     points = {}
     for b in (1, 64):
         st = max(16, args.steps // 2)
         m, _, _, _ = decode_point(b, st, max(3, args.warmup // 2))
         points[f"decode_b{b}"] = round(b * st / (m / 1e3), 1)
+        print(f"[bench] decode b{b}: {points[f'decode_b{b}']} tok/s", file=sys.stderr, flush=True)
 
-    # ---- prefill of 2,048 tokens in one step ---------------------------------------
-    T = 2048
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
-    times = []
-    for it in range(3 + 5):
-        rc = runner.cache.open(("prefill", it))
-        toks = torch.randint(0, vocab, (T,), generator=gen).tolist()
-        assert runner.cache.reserve(rc, T)
-        flush.zero_()                                   # larger than L2: nothing of the last run stays cached
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        e0.record()
-        runner.step([StepEntry(rc, toks, [T - 1])])
-        e1.record()
-        torch.cuda.synchronize()
-        if it >= 3:
-            times.append(e0.elapsed_time(e1))
-        runner.cache.close(rc)
-    pre_ms = sorted(times)[len(times) // 2]
+    prefill = measure_prefill(runner, mm_params, pk, gen, vocab, dev)
     c = runner.plan.config
     n_attn = sum(1 for t in c.layer_types if t == "full_attention")
-    head_params = runner.plan.head.weight.numel()
-    flops = 2.0 * (mm_params - head_params) * T + 2.0 * head_params * 1 + \
-        n_attn * 4.0 * c.num_attention_heads * c.head_dim * (T * (T + 1) / 2)
-    prefill = {"value": round(T / (pre_ms / 1e3), 1), "tokens": T, "ms": round(pre_ms, 3),
-               "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
-               "tflops": round(flops / (pre_ms / 1e3) / 1e12, 1), "peak_tflops": pk["bf16_tflops"]}
-    del flush
 
     # ---- end to end through the engine loop ----------------------------------------
     eng = Engine(runner, SchedulerConfig(max_concurrent_seqs=max_b, max_batched_tokens=8192,
-                                         prefill_chunk_tokens=4096, max_context=ctx_len + 64), use_graphs=True)
+                                         prefill_chunk_tokens=4096, max_context=ctx_len + 256), use_graphs=True)
+    # requests finish their prompts at different steps, so leave room for the early ones
     start_len = ctx_len - (args.steps + args.warmup) - 2
     for i in range(B):
         prompt = torch.randint(0, vocab, (start_len,), generator=gen).tolist()
-        eng.admit(("e2e", i), prompt, SamplingParams(temperature=0.0, max_tokens=args.steps + args.warmup + 1,
+        eng.admit(("e2e", i), prompt, SamplingParams(temperature=0.0, max_tokens=args.steps + args.warmup + 128,
                                                      ignore_eos=True))
     while any(s.needs_prefill() for s in eng.scheduler.seqs.values()) or eng.scheduler.num_waiting:
         eng.step()
@@ -257,7 +241,7 @@ def run(args):
     h2d = d2h = 0
     for _ in range(args.steps):
         out = eng.step()
-        assert len(out.new_tokens) == B
+        assert len(out.new_tokens) == B, (len(out.new_tokens), eng.stats, eng.last_error)
         h2d += runner.packer.h2d_bytes_last + eng.sampler.h2d_bytes_last
         d2h += eng.sampler.d2h_bytes_last
     torch.cuda.synchronize()
@@ -294,6 +278,46 @@ def run(args):
     return 0
 
 
+def measure_prefill(runner, mm_params, pk, gen, vocab, dev, warm=3, iters=5):
+    """One 2,048-token prompt in one step, L2 flushed before each timed run."""
+    import torch
+    from vapi_b200.engine.step import StepEntry
+    T = 2048
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    times = []
+    for it in range(warm + iters):
+        rc = runner.cache.open(("prefill", it))
+        toks = torch.randint(0, vocab, (T,), generator=gen).tolist()
+        assert runner.cache.reserve(rc, T)
+        flush.zero_()                                   # larger than L2: nothing of the last run stays cached
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        runner.step([StepEntry(rc, toks, [T - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= warm:
+            times.append(e0.elapsed_time(e1))
+        runner.cache.close(rc)
+    pre_ms = sorted(times)[len(times) // 2]
+    c = runner.plan.config
+    n_attn = sum(1 for t in c.layer_types if t == "full_attention")
+    head_params = runner.plan.head.weight.numel()
+    flops = 2.0 * (mm_params - head_params) * T + 2.0 * head_params * 1 + \
+        n_attn * 4.0 * c.num_attention_heads * c.head_dim * (T * (T + 1) / 2)
+    prefill = {"value": round(T / (pre_ms / 1e3), 1), "tokens": T, "ms": round(pre_ms, 3),
+               "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+               "tflops": round(flops / (pre_ms / 1e3) / 1e12, 1), "peak_tflops": pk["bf16_tflops"]}
+    print(f"[bench] prefill: {prefill}", file=sys.stderr, flush=True)
+    return prefill
+
+
+def prefill_only(args, runner, mm_params, pk, gen, vocab, dev):
+    p = measure_prefill(runner, mm_params, pk, gen, vocab, dev, warm=max(1, min(args.warmup, 3)), iters=max(1, min(args.steps, 5)))
+    print(json.dumps({"only": "prefill", "prefill": p}), flush=True)
+    return 0
+
+
 def reference_arm():
     """The reference is a Rust workspace (Cargo, candle); it has no Python package to
     install and no Rust toolchain exists here, so its arm cannot run."""
@@ -313,6 +337,8 @@ def main():
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0 = all)")
     ap.add_argument("--impl", default="vapi_b200", choices=["vapi_b200", "reference"])
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="profiling aid: run just the headline decode point, or just the prefill")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()

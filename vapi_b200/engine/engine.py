@@ -67,6 +67,7 @@ class Engine:
         self.stats = EngineStats()
         self.max_step_failures = int(max_step_failures)
         self._failures_in_a_row = 0
+        self.last_error: Optional[str] = None
         self.use_graphs = use_graphs
         #: replaceable in tests: the function that runs a planned batch and returns logits
         self.step_fn: Callable[[StepPlan], Optional[torch.Tensor]] = self._run
@@ -119,7 +120,8 @@ class Engine:
                 rows = [(self.scheduler.seqs[s].params, self.states[s]) for s in plan.sampled_seqs]
                 sampled = self.sampler.sample(logits, rows)
             t3 = time.perf_counter()
-        except Exception:
+        except Exception as exc:
+            self.last_error = f"{type(exc).__name__}: {exc}"
             self.stats.failed_steps += 1
             self._failures_in_a_row += 1
             self.scheduler.fail_all()
