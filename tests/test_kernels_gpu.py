@@ -110,7 +110,7 @@ def test_qk_norm_rope_write(ops, dtype, nh, nkv, d, rot):
     torch.testing.assert_close(q2.cpu(), qkv, atol=0, rtol=0)
 
 
-def _attention_case(ops, dtype, nh, nkv, d, page, lens, window=0, splits=None, planted=False, seed=4):
+def _attention_case(ops, dtype, nh, nkv, d, page, lens, window=0, splits=None, planted=False, seed=4, impl="auto"):
     """lens: list of (len_q, len_k) per sequence; pages are handed out in a shuffled order."""
     torch.manual_seed(seed)
     S = len(lens)
@@ -145,7 +145,7 @@ def _attention_case(ops, dtype, nh, nkv, d, page, lens, window=0, splits=None, p
     scale = 1.0 / math.sqrt(d)
     want = plain_ops.paged_attention(q, nh * d, cache, table, cu_q, kl, n, S, max_q, max_k, nh, nkv, d, scale, window)
     got = ops.paged_attention(dev(q), nh * d, dev(cache), dev(table), dev(cu_q), dev(kl), n, S, max_q, max_k,
-                              nh, nkv, d, scale, window, splits)
+                              nh, nkv, d, scale, window, splits, None, impl)
     t = dict(atol=3e-5, rtol=3e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
     torch.testing.assert_close(got.cpu().float(), want.float(), **t)
 
@@ -174,6 +174,65 @@ def test_paged_attention_split_keys(ops, dtype, splits):
 def test_paged_attention_window(ops, dtype, window):
     _attention_case(ops, dtype, 4, 2, 32, 16, [(20, 20), (7, 90), (1, 64), (1, 3)], window=window)
     _attention_case(ops, dtype, 4, 2, 32, 16, [(1, 200), (1, 64)], window=window, splits=3)
+
+
+# ---- the tensor-core kernel of the serving path (bfloat16, head_dim 64 / 128, pages of 64n) ----
+TC = dict(dtype=torch.bfloat16, impl="tensor_core")
+
+
+@pytest.mark.parametrize("nh,nkv,d,page", [(8, 2, 64, 64), (32, 8, 64, 64), (6, 1, 64, 128), (4, 4, 128, 64), (40, 1, 64, 64), (3, 1, 128, 128)])
+def test_tensor_core_attention_mixed_batch(ops, nh, nkv, d, page):
+    # whole prompts (one longer than a block's 16 tokens x 4 heads), a portion over a cached prefix,
+    # decode tokens at and beside page and tile edges, a 2-token portion
+    _attention_case(ops, nh=nh, nkv=nkv, d=d, page=page,
+                    lens=[(150, 150), (9, 200), (1, 64), (1, 65), (1, 1), (2, 129), (1, 128), (70, 70), (1, 63)], **TC)
+
+
+def test_tensor_core_attention_decode_only_and_splits(ops):
+    for splits in (1, 2, 5, 16):
+        _attention_case(ops, nh=32, nkv=8, d=64, page=64, lens=[(1, 1000), (1, 64), (1, 65), (1, 3), (1, 513)],
+                        splits=splits, **TC)
+    _attention_case(ops, nh=16, nkv=1, d=128, page=64, lens=[(1, 300), (1, 64)], splits=3, **TC)      # 16 rows exactly
+    _attention_case(ops, nh=34, nkv=2, d=64, page=64, lens=[(1, 300), (1, 64)], splits=3, **TC)       # 17 rows: 4-warp blocks
+
+
+def test_tensor_core_attention_far_key_stands_out(ops):
+    _attention_case(ops, nh=8, nkv=2, d=64, page=64, lens=[(1, 700), (5, 300), (1, 65), (100, 400)], planted=True, **TC)
+    _attention_case(ops, nh=8, nkv=2, d=64, page=64, lens=[(1, 700), (1, 640), (1, 65)], planted=True, splits=4, **TC)
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 100])
+def test_tensor_core_attention_window(ops, window):
+    _attention_case(ops, nh=4, nkv=2, d=64, page=64, lens=[(90, 90), (7, 300), (1, 64), (1, 3), (1, 129)], window=window, **TC)
+    _attention_case(ops, nh=4, nkv=2, d=64, page=64, lens=[(1, 500), (1, 64)], window=window, splits=3, **TC)
+
+
+def test_tensor_core_attention_ignores_garbage_beyond_the_sequence(ops):
+    """Cache memory past a sequence's last key (and pages nobody wrote) may hold anything,
+    NaN included; it must not reach the result."""
+    torch.manual_seed(11)
+    nh, nkv, d, page = 8, 2, 64, 64
+    cache = torch.full((6, 2, nkv, page, d), float("nan")).to(torch.bfloat16)
+    lens = [(1, 70), (3, 10)]
+    table = torch.tensor([[4, 1, 0, 0], [2, 0, 0, 0]], dtype=torch.int32)
+    cache[4] = torch.randn(2, nkv, page, d)
+    cache[1, :, :, :6] = torch.randn(2, nkv, 6, d).to(torch.bfloat16)
+    cache[2, :, :, :10] = torch.randn(2, nkv, 10, d).to(torch.bfloat16)
+    q = torch.randn(4, nh * d).to(torch.bfloat16)
+    cu, kl = torch.tensor([0, 1, 4], dtype=torch.int32), torch.tensor([70, 10], dtype=torch.int32)
+    want = plain_ops.paged_attention(q, nh * d, cache, table, cu, kl, 4, 2, 3, 70, nh, nkv, d, 0.125)
+    for impl in ("tensor_core", "general"):
+        got = ops.paged_attention(dev(q), nh * d, dev(cache), dev(table), dev(cu), dev(kl), 4, 2, 3, 70, nh, nkv, d,
+                                  0.125, 0, None, None, impl)
+        assert torch.isfinite(got.float()).all(), impl
+        torch.testing.assert_close(got.cpu().float(), want.float(), atol=3e-2, rtol=3e-2)
+
+
+def test_tensor_core_attention_is_refused_where_it_does_not_apply(ops):
+    with pytest.raises(ops.KernelError, match="tensor-core kernel needs"):
+        _attention_case(ops, nh=4, nkv=2, d=32, page=64, lens=[(1, 10)], **TC)
+    with pytest.raises(ops.KernelError, match="tensor-core kernel needs"):
+        _attention_case(ops, nh=4, nkv=2, d=64, page=16, lens=[(1, 10)], **TC)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -19,6 +19,7 @@
 // write unnormalised partial results to scratch memory, and a second kernel combines them
 // in a fixed order.
 #include "common.cuh"
+#include "attention_mma.cuh"
 
 using namespace vapi;
 
@@ -268,13 +269,16 @@ static int launch_attention(const void* q, long long q_row_stride, const void* c
 // q: [n, *] with `q_row_stride` elements between tokens, head h at h*d.
 // cache: one layer, [num_pages, 2, nkv, page_size, d].  out: [n, nh*d].
 // splits > 1 needs part_o [n*nh*splits*d] and part_ml [n*nh*splits*2] floats of scratch.
+// impl: 0 = the tensor-core kernel where it applies (bfloat16, head_dim 64 or 128, page size a
+// multiple of 64), else the general one; 1 = the general kernel; 2 = the tensor-core kernel or
+// an error.
 VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, const void* cache,
                                      int dtype, const int* block_table, int table_stride,
                                      const int* cu_q, const int* seqlens_k, void* out,
                                      float* part_o, float* part_ml, int n, int num_seqs,
                                      int max_q, int nh, int nkv, int d, int page_size,
                                      int num_pages, float scale, int window, int splits,
-                                     int* status, cudaStream_t stream) {
+                                     int impl, int* status, cudaStream_t stream) {
     if (n <= 0 || num_seqs <= 0 || max_q <= 0) return 0;
     if (d < 16 || d > 256 || d % 16 != 0)
         return fail(-1, "paged_attention: head_dim %d is not a multiple of 16 in 16..256", d);
@@ -286,11 +290,25 @@ VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, cons
     if (splits > 1 && (!part_o || !part_ml))
         return fail(-1, "paged_attention: %d splits need scratch buffers", splits);
     int rc;
+    const bool fast_ok = dtype == VAPI_BF16 && (d == 64 || d == 128) && page_size % FA_BK == 0 &&
+                         q_row_stride % 2 == 0;
+    if (impl == 2 && !fast_ok)
+        return fail(-3, "paged_attention: the tensor-core kernel needs bfloat16, head_dim 64 or 128 and a page "
+                        "size that is a multiple of 64 (got dtype %d, head_dim %d, page size %d)", dtype, d, page_size);
+    const bool fast = fast_ok && impl != 1;
+#define VAPI_FLASH(HD, NW, ST)                                                                   \
+    rc = launch_flash<HD, NW, ST>(q, q_row_stride, cache, block_table, table_stride, cu_q,       \
+                                  seqlens_k, out, part_o, part_ml, num_seqs, max_q, nh, nkv,     \
+                                  page_size, num_pages, scale, window, splits, status, stream)
 #define VAPI_ATT(T, DM)                                                                         \
     rc = launch_attention<T, DM>(q, q_row_stride, cache, block_table, table_stride, cu_q,       \
                                  seqlens_k, out, part_o, part_ml, num_seqs, max_q, nh, nkv, d,  \
                                  page_size, num_pages, scale, window, splits, status, stream)
-    if (dtype == VAPI_F32) {
+    if (fast) {
+        const bool few_rows = (long long)max_q * (nh / nkv) <= 16;
+        if (d == 64) { if (few_rows) VAPI_FLASH(64, 1, 4); else VAPI_FLASH(64, 4, 3); }
+        else         { if (few_rows) VAPI_FLASH(128, 1, 4); else VAPI_FLASH(128, 4, 3); }
+    } else if (dtype == VAPI_F32) {
         if (d <= 64) VAPI_ATT(float, 64); else if (d <= 128) VAPI_ATT(float, 128); else VAPI_ATT(float, 256);
     } else if (dtype == VAPI_BF16) {
         if (d <= 64) VAPI_ATT(__nv_bfloat16, 64); else if (d <= 128) VAPI_ATT(__nv_bfloat16, 128); else VAPI_ATT(__nv_bfloat16, 256);
@@ -298,6 +316,7 @@ VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, cons
         return fail(-2, "paged_attention: unsupported dtype %d", dtype);
     }
 #undef VAPI_ATT
+#undef VAPI_FLASH
     if (rc != 0) return rc;
     if (splits > 1) {
         const long long rows = (long long)n * nh;

@@ -50,14 +50,25 @@ def find_nvcc() -> str:
                      "vapi_b200 cannot be built and there is no fallback")
 
 
-def _headers() -> List[str]:
-    return sorted(os.path.join(CSRC_DIR, f) for f in os.listdir(CSRC_DIR)
-                  if f.endswith((".cuh", ".h")))
+def _headers(name: str) -> List[str]:
+    """The package's own headers that ``name``.cu includes, directly or through another."""
+    import re
+    seen: List[str] = []
+    todo = [os.path.join(CSRC_DIR, name + ".cu")]
+    while todo:
+        path = todo.pop()
+        with open(path, "r", encoding="utf-8") as f:
+            for inc in re.findall(r'^\s*#\s*include\s+"([^"]+)"', f.read(), flags=re.M):
+                ipath = os.path.join(CSRC_DIR, inc)
+                if os.path.isfile(ipath) and ipath not in seen:
+                    seen.append(ipath)
+                    todo.append(ipath)
+    return sorted(seen)
 
 
 def _digest(name: str) -> str:
     h = hashlib.sha256()
-    for path in [os.path.join(CSRC_DIR, name + ".cu")] + _headers():
+    for path in [os.path.join(CSRC_DIR, name + ".cu")] + _headers(name):
         with open(path, "rb") as f:
             h.update(f.read())
         h.update(b"\0")
@@ -141,6 +152,12 @@ def build(name: str, verbose: bool = True) -> str:
             pass
         raise BuildError(f"nvcc failed on {name}.cu:\n{' '.join(cmd)}\n{log.decode(errors='replace')}")
     os.replace(tmp, out)
+    for old in os.listdir(out_dir):          # earlier builds of this source are of no use any more
+        if old.startswith(f"lib{name}-") and old.endswith(".so") and os.path.join(out_dir, old) != out:
+            try:
+                os.remove(os.path.join(out_dir, old))
+            except OSError:
+                pass
     if verbose:
         print(f"[vapi_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s",
               file=sys.stderr, flush=True)

@@ -244,7 +244,7 @@ def attention_splits(num_seqs: int, max_q: int, max_k: int, nh: int, nkv: int) -
     blocks = max(1, num_seqs * nkv * tiles)
     if max_q > 1 and blocks >= 148:
         return 1
-    want = -(-296 // blocks)
+    want = -(-592 // blocks)
     by_len = max(1, max_k // 256)
     return max(1, min(want, by_len, 32))
 
@@ -253,11 +253,14 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tenso
                     block_table: torch.Tensor, cu_q: torch.Tensor, seqlens_k: torch.Tensor,
                     n: int, num_seqs: int, max_q: int, max_k: int, nh: int, nkv: int, d: int,
                     scale: float, window: int = 0, splits: Optional[int] = None,
-                    status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    status: Optional[torch.Tensor] = None, impl: str = "auto") -> torch.Tensor:
     """Causal GQA attention of a mixed batch over the paged cache; returns [n, nh*d].
 
     ``q`` may be a view into a fused qkv tensor: head h of token t is at
     ``t*q_row_stride + h*d``.  ``window`` > 0 limits each query to the last ``window`` keys.
+    ``impl``: "auto" picks the tensor-core kernel where it applies (bfloat16, head_dim 64 or
+    128, page size a multiple of 64) and the general kernel elsewhere; "general" and
+    "tensor_core" force one (the latter raises where it does not apply).
     """
     _cuda(q, cache_layer, block_table, cu_q, seqlens_k)
     _i32(block_table, "block table")
@@ -280,8 +283,8 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tenso
     _check(lib, lib.vapi_paged_attention(
         _p(q), ctypes.c_longlong(q_row_stride), _p(cache_layer), _dt(q), _p(block_table),
         block_table.stride(0), _p(cu_q), _p(seqlens_k), _p(out), _p(part_o), _p(part_ml), n, num_seqs,
-        max_q, nh, nkv, d, page_size, num_pages, ctypes.c_float(scale), window, splits, _p(status),
-        _stream()), 2 if splits > 1 else 1)
+        max_q, nh, nkv, d, page_size, num_pages, ctypes.c_float(scale), window, splits,
+        {"auto": 0, "general": 1, "tensor_core": 2}[impl], _p(status), _stream()), 2 if splits > 1 else 1)
     return out
 
 
