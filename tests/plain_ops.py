@@ -17,8 +17,18 @@ def _f(t):
     return t.to(torch.float32)
 
 
-def embed(table, tokens, status=None):
-    return _f(table[tokens.long()])
+def embed(table, tokens, status=None, want_ss=False):
+    out = _f(table[tokens.long()])
+    return (out, (out ** 2).sum(1)[None, :]) if want_ss else out
+
+
+def add_residual_ss(x, delta):
+    x += _f(delta)
+    return (x ** 2).sum(1)[None, :]
+
+
+def skinny_applies(rows, weight):
+    return False
 
 
 def add_rmsnorm(x, delta, weight, eps, out_dtype, rows=None):
@@ -211,6 +221,6 @@ def apply_penalties(logits, rows, toks, counts, rep, freq, pres):
         logits[r, t] = v
 
 
-ALL = ["embed", "add_rmsnorm", "add_residual", "swiglu", "linear", "strict_fp32", "rope_cos_sin",
+ALL = ["embed", "add_rmsnorm", "add_residual", "add_residual_ss", "skinny_applies", "swiglu", "linear", "strict_fp32", "rope_cos_sin",
        "qk_norm_rope_write", "attention_splits", "paged_attention", "shortconv", "sample_rows",
        "apply_penalties"]

@@ -346,3 +346,67 @@ def test_linear_is_not_reduced_precision(ops, dtype):
         # a weight kept in float32 beside bfloat16 activations multiplies in float32
         got_mixed = ops.linear(dev(x), dev(w.float()))
         torch.testing.assert_close(got_mixed.cpu().float(), plain_ops.linear(x, w).float(), atol=0.3, rtol=2e-2)
+
+
+# ---- the weight-streaming product of decode steps ---------------------------------------------
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(72, 96), (2048, 2048), (1000, 320), (6144, 1536)])
+def test_skinny_linear_plain_products(ops, M, N, K):
+    torch.manual_seed(20)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    b = torch.randn(N)
+    want = a.float() @ w.float().t()
+    for rpb in (8, 16):
+        got = ops.skinny_linear(dev(w), act=dev(a), epilogue="f32", rows_per_block=rpb)
+        torch.testing.assert_close(got.cpu(), want, atol=2e-3, rtol=1e-3)
+    got = ops.skinny_linear(dev(w), act=dev(a), epilogue="bf16", bias=dev(b))
+    torch.testing.assert_close(got.cpu().float(), (want + b).to(torch.bfloat16).float(), atol=2e-2, rtol=2e-2)
+    # and `linear` sends decode-sized bfloat16 products there
+    before = ops.launch_count
+    got = ops.linear(dev(a), dev(w), None, torch.float32)
+    assert ops.launch_count == before + 1
+    torch.testing.assert_close(got.cpu(), want, atol=2e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("M", [1, 8, 13])
+def test_skinny_linear_fusions(ops, M):
+    """Norm prologue from partial sums, SwiGLU epilogue, residual epilogue with new partial sums:
+    a feed-forward of a decode step as two launches."""
+    torch.manual_seed(21)
+    H, F, eps = 96, 200, 1e-6
+    x = torch.randn(M, H) * 2
+    nw = 1 + 0.1 * torch.randn(H)
+    w13 = (torch.randn(2 * F, H) * 0.2).to(torch.bfloat16)
+    w2 = (torch.randn(H, 224) * 0.2).to(torch.bfloat16)[:, :224]
+    # partial sums of squares of x as some producer with 5 blocks would leave them
+    parts = torch.stack([(x[:, i * 20:(i + 1) * 20] ** 2).sum(1) for i in range(4)] + [(x[:, 80:] ** 2).sum(1)])
+    s = ops.skinny_linear(dev(w13), x=dev(x), ss_in=dev(parts.contiguous()), norm_weight=dev(nw), eps=eps, epilogue="swiglu")
+    xn = (x * torch.rsqrt((x ** 2).mean(1, keepdim=True) + eps) * nw).to(torch.bfloat16).float()
+    gu = xn @ w13.float().t()
+    want_s = (gu[:, :F] / (1 + torch.exp(-gu[:, :F]))) * gu[:, F:]
+    torch.testing.assert_close(s.cpu().float(), want_s.to(torch.bfloat16).float(), atol=3e-2, rtol=3e-2)
+    # down projection (inner size 224 = 7 * 32) added into the stream, with partial sums for the next norm
+    s2 = torch.randn(M, 224).to(torch.bfloat16)
+    bias = torch.randn(H)
+    for rpb in (8, 16):
+        xr = dev(x.clone())
+        ss = ops.skinny_linear(dev(w2.contiguous()), act=dev(s2), epilogue="resid", resid=xr, bias=dev(bias),
+                               ss_out=True, rows_per_block=rpb)
+        want_x = x + s2.float() @ w2.float().t() + bias
+        torch.testing.assert_close(xr.cpu(), want_x, atol=2e-3, rtol=1e-3)
+        assert ss.shape == (ops.skinny_blocks(H, "resid", rpb), M)
+        torch.testing.assert_close(ss.sum(0).cpu(), (want_x ** 2).sum(1), atol=1e-2, rtol=1e-3)
+    # the same call twice gives the same bits (fixed reduction order, no atomics)
+    a = ops.skinny_linear(dev(w13), x=dev(x), ss_in=dev(parts.contiguous()), norm_weight=dev(nw), eps=eps, epilogue="swiglu")
+    assert torch.equal(a, s)
+
+
+def test_skinny_linear_refuses_what_it_cannot_do(ops):
+    w = torch.zeros(64, 80, dtype=torch.bfloat16).cuda()
+    with pytest.raises(ops.KernelError, match="multiple of 32"):
+        ops.skinny_linear(w, act=torch.zeros(2, 80, dtype=torch.bfloat16).cuda(), epilogue="bf16")
+    w = torch.zeros(64, 96, dtype=torch.bfloat16).cuda()
+    with pytest.raises(ops.KernelError, match="more than 16"):
+        ops.skinny_linear(w, act=torch.zeros(17, 96, dtype=torch.bfloat16).cuda(), epilogue="bf16")
+    assert not ops.skinny_applies(17, w) and not ops.skinny_applies(4, w.float()) and ops.skinny_applies(4, w)

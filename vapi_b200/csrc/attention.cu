@@ -64,6 +64,8 @@ paged_attention_kernel(const T* __restrict__ q, long long q_row_stride,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int s = blockIdx.z / splits, sp = blockIdx.z - s * splits;
     const int g = blockIdx.y;
+    pdl_trigger();
+    pdl_wait();
     const int q0 = cu_q[s], qlen = cu_q[s + 1] - q0, klen = seqlens_k[s];
     const int n_rep = nh / nkv;
     const int rows_total = qlen * n_rep;
@@ -213,29 +215,38 @@ paged_attention_kernel(const T* __restrict__ q, long long q_row_stride,
     }
 }
 
-// Combine the partial results of `splits` blocks: one warp per (token, head).
+// Combine the partial results of `splits` (at most 32) blocks: one warp per (token, head).
+// Lane sp holds the weight exp(m_sp - max) of split sp; the sums over the splits run in
+// split order whatever finished first.
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o,
                                          const float* __restrict__ part_ml, T* __restrict__ out,
                                          long long rows, int d, int splits) {
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
+    pdl_trigger();
+    pdl_wait();
     if (row >= rows) return;
-    float mx = -INFINITY;
-    for (int sp = 0; sp < splits; ++sp) mx = fmaxf(mx, part_ml[(row * splits + sp) * 2]);
-    float lsum = 0.f;
-    for (int sp = 0; sp < splits; ++sp) {
-        const float ms = part_ml[(row * splits + sp) * 2];
-        if (ms != -INFINITY) lsum += part_ml[(row * splits + sp) * 2 + 1] * expf(ms - mx);
+    float ms = -INFINITY, ls = 0.f;
+    if (lane < splits) {
+        ms = part_ml[(row * splits + lane) * 2];
+        ls = part_ml[(row * splits + lane) * 2 + 1];
     }
+    const float mx = warp_max(ms);
+    const float w = ms == -INFINITY ? 0.f : expf(ms - mx);
+    float lsum = 0.f;
+    for (int sp = 0; sp < splits; ++sp) lsum += __shfl_sync(0xffffffffu, ls * w, sp);
     const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-    for (int col = lane; col < d; col += 32) {
+    for (int c0 = 0; c0 < d; c0 += 32) {
+        const int col = c0 + lane;
         float o = 0.f;
+#pragma unroll 4
         for (int sp = 0; sp < splits; ++sp) {
-            const float ms = part_ml[(row * splits + sp) * 2];
-            if (ms != -INFINITY) o += part_o[(row * splits + sp) * (size_t)d + col] * expf(ms - mx);
+            const float ws = __shfl_sync(0xffffffffu, w, sp);
+            const float v = col < d ? part_o[(row * splits + sp) * (size_t)d + col] : 0.f;
+            o += v * ws;
         }
-        out[row * d + col] = from_f32<T>(o * inv);
+        if (col < d) out[row * d + col] = from_f32<T>(o * inv);
     }
 }
 
@@ -260,10 +271,9 @@ static int launch_attention(const void* q, long long q_row_stride, const void* c
         if (e != cudaSuccess) return fail(-101, "paged_attention: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
     dim3 grid((unsigned)tiles, nkv, num_seqs * splits);
-    kern<<<grid, ATT_WARPS * 32, smem, stream>>>(
+    return check_launch("paged_attention", launch(kern, grid, ATT_WARPS * 32, smem, stream,
         (const T*)q, q_row_stride, (const T*)cache, block_table, table_stride, cu_q, seqlens_k,
-        (T*)out, part_o, part_ml, nh, nkv, d, page_size, num_pages, scale, window, splits, status);
-    return check_launch("paged_attention");
+        (T*)out, part_o, part_ml, nh, nkv, d, page_size, num_pages, scale, window, splits, status));
 }
 
 // q: [n, *] with `q_row_stride` elements between tokens, head h at h*d.
@@ -287,6 +297,7 @@ VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, cons
     if (page_size <= 0 || num_pages <= 0) return fail(-1, "paged_attention: no pages");
     if (q_row_stride % 4 != 0) return fail(-1, "paged_attention: q row stride %lld is not a multiple of 4", q_row_stride);
     if (splits < 1) splits = 1;
+    if (splits > 32) return fail(-1, "paged_attention: %d splits are more than 32", splits);
     if (splits > 1 && (!part_o || !part_ml))
         return fail(-1, "paged_attention: %d splits need scratch buffers", splits);
     int rc;
@@ -306,8 +317,8 @@ VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, cons
                                  page_size, num_pages, scale, window, splits, status, stream)
     if (fast) {
         const bool few_rows = (long long)max_q * (nh / nkv) <= 16;
-        if (d == 64) { if (few_rows) VAPI_FLASH(64, 1, 4); else VAPI_FLASH(64, 4, 3); }
-        else         { if (few_rows) VAPI_FLASH(128, 1, 4); else VAPI_FLASH(128, 4, 3); }
+        if (d == 64) { if (few_rows) VAPI_FLASH(64, 1, 3); else VAPI_FLASH(64, 4, 3); }
+        else         { if (few_rows) VAPI_FLASH(128, 1, 3); else VAPI_FLASH(128, 4, 3); }
     } else if (dtype == VAPI_F32) {
         if (d <= 64) VAPI_ATT(float, 64); else if (d <= 128) VAPI_ATT(float, 128); else VAPI_ATT(float, 256);
     } else if (dtype == VAPI_BF16) {
@@ -322,11 +333,12 @@ VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, cons
         const long long rows = (long long)n * nh;
         const int wpb = 4;
         const long long blocks = (rows + wpb - 1) / wpb;
+        cudaError_t e;
         if (dtype == VAPI_F32)
-            attention_combine_kernel<float><<<(unsigned)blocks, wpb * 32, 0, stream>>>(part_o, part_ml, (float*)out, rows, d, splits);
+            e = launch(attention_combine_kernel<float>, (unsigned)blocks, wpb * 32, 0, stream, (const float*)part_o, (const float*)part_ml, (float*)out, rows, d, splits);
         else
-            attention_combine_kernel<__nv_bfloat16><<<(unsigned)blocks, wpb * 32, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, rows, d, splits);
-        return check_launch("attention_combine");
+            e = launch(attention_combine_kernel<__nv_bfloat16>, (unsigned)blocks, wpb * 32, 0, stream, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, rows, d, splits);
+        return check_launch("attention_combine", e);
     }
     return 0;
 }

@@ -69,6 +69,8 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
     const int gq = lane >> 2, tq = lane & 3;                          // row / column-pair of the fragment
     const int s = blockIdx.z / splits, sp = blockIdx.z - s * splits;
     const int g = blockIdx.y;
+    pdl_trigger();
+    pdl_wait();
     const int q0 = cu_q[s], qlen = cu_q[s + 1] - q0, klen = seqlens_k[s];
     const int n_rep = nh / nkv;
     const int rows_total = qlen * n_rep;
@@ -297,11 +299,10 @@ static int launch_flash(const void* q, long long q_row_stride, const void* cache
         if (e != cudaSuccess) return fail(-101, "paged_attention: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
     dim3 grid((unsigned)tiles, nkv, num_seqs * splits);
-    kern<<<grid, NWARPS * 32, smem, stream>>>(
+    return check_launch("paged_attention (tensor-core)", launch(kern, grid, NWARPS * 32, smem, stream,
         (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)cache, block_table, table_stride, cu_q,
         seqlens_k, (__nv_bfloat16*)out, part_o, part_ml, nh, nkv, page_size, num_pages,
-        scale * 1.4426950408889634f, window, splits, status);
-    return check_launch("paged_attention (tensor-core)");
+        scale * 1.4426950408889634f, window, splits, status));
 }
 
 }  // namespace vapi

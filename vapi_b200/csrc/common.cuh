@@ -15,6 +15,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdarg.h>
+#include <stdlib.h>
 
 #define VAPI_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -40,6 +41,45 @@ inline int check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(-100, "%s: launch failed: %s", what, cudaGetErrorString(e));
     return 0;
+}
+
+// ---- programmatic dependent launch --------------------------------------------------
+// Kernels of a step are launched so that the next one may begin while the one before it
+// drains: a kernel first does what does not depend on its predecessor (index arithmetic,
+// streaming in weights), then calls pdl_wait(), which returns once every earlier kernel has
+// completed and its writes are visible.  pdl_trigger() lets the following kernel be scheduled
+// as soon as all blocks of this one have started.  Both are no-ops for a kernel launched the
+// ordinary way.  Set VAPI_PDL=0 to launch everything the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("VAPI_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                          cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+inline int check_launch(const char* what, cudaError_t e) {
+    if (e != cudaSuccess) return fail(-100, "%s: launch failed: %s", what, cudaGetErrorString(e));
+    return check_launch(what);
 }
 
 // ---- element conversion ------------------------------------------------------

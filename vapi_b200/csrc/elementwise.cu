@@ -11,11 +11,15 @@ using namespace vapi;
 
 // ---------------------------------------------------------------------------
 // embedding: out[r, :] = float(table[tokens[r], :])
+// ss (optional): the sum of squares of each produced row, [1][n], for a norm that follows
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
-                             float* __restrict__ out, int n, int hidden, int vocab,
-                             int* __restrict__ status) {
+                             float* __restrict__ out, float* __restrict__ ss, int n, int hidden,
+                             int vocab, int* __restrict__ status) {
+    __shared__ float red[33];
     const int r = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
     if (r >= n) return;
     int tok = tokens[r];
     if (tok < 0 || tok >= vocab) {  // never read outside the table
@@ -24,21 +28,31 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
     }
     const TW* src = table + (size_t)tok * hidden;
     float* dst = out + (size_t)r * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_f32(src[c]);
+    float acc = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float v = to_f32(src[c]);
+        dst[c] = v;
+        acc += v * v;
+    }
+    if (ss) {
+        acc = block_sum(acc, red);
+        if (threadIdx.x == 0) ss[r] = acc;
+    }
 }
 
 VAPI_EXPORT int vapi_embed(const void* table, int table_dtype, const int* tokens, float* out,
-                           int n, int hidden, int vocab, int* status, cudaStream_t stream) {
+                           float* ss, int n, int hidden, int vocab, int* status, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (hidden <= 0 || vocab <= 0) return fail(-1, "embed: bad sizes hidden=%d vocab=%d", hidden, vocab);
     const int threads = hidden >= 1024 ? 256 : 128;
+    cudaError_t e;
     if (table_dtype == VAPI_F32)
-        embed_kernel<float><<<n, threads, 0, stream>>>((const float*)table, tokens, out, n, hidden, vocab, status);
+        e = launch(embed_kernel<float>, n, threads, 0, stream, (const float*)table, tokens, out, ss, n, hidden, vocab, status);
     else if (table_dtype == VAPI_BF16)
-        embed_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, n, hidden, vocab, status);
+        e = launch(embed_kernel<__nv_bfloat16>, n, threads, 0, stream, (const __nv_bfloat16*)table, tokens, out, ss, n, hidden, vocab, status);
     else
         return fail(-2, "embed: unsupported table dtype %d", table_dtype);
-    return check_launch("embed");
+    return check_launch("embed", e);
 }
 
 // ---------------------------------------------------------------------------
@@ -57,6 +71,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
                                    int n_out, int hidden, int write_x) {
     __shared__ float red[33];
     const int j = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
     if (j >= n_out) return;
     const int row = rows ? rows[j] : j;
     float* xr = x + (size_t)row * hidden;
@@ -87,13 +103,14 @@ VAPI_EXPORT int vapi_add_rmsnorm(float* x, const void* delta, const float* w, fl
     if (hidden <= 0) return fail(-1, "add_rmsnorm: hidden=%d", hidden);
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     const int write_x = rows ? 0 : 1;
+    cudaError_t e;
     if (out_dtype == VAPI_F32)
-        add_rmsnorm_kernel<float><<<n_out, threads, 0, stream>>>(x, (const float*)delta, w, eps, rows, (float*)out, n_out, hidden, write_x);
+        e = launch(add_rmsnorm_kernel<float>, n_out, threads, 0, stream, x, (const float*)delta, w, eps, rows, (float*)out, n_out, hidden, write_x);
     else if (out_dtype == VAPI_BF16)
-        add_rmsnorm_kernel<__nv_bfloat16><<<n_out, threads, 0, stream>>>(x, (const __nv_bfloat16*)delta, w, eps, rows, (__nv_bfloat16*)out, n_out, hidden, write_x);
+        e = launch(add_rmsnorm_kernel<__nv_bfloat16>, n_out, threads, 0, stream, x, (const __nv_bfloat16*)delta, w, eps, rows, (__nv_bfloat16*)out, n_out, hidden, write_x);
     else
         return fail(-2, "add_rmsnorm: unsupported dtype %d", out_dtype);
-    return check_launch("add_rmsnorm");
+    return check_launch("add_rmsnorm", e);
 }
 
 // residual add alone (used at the very end of a step when nothing follows the
@@ -102,7 +119,41 @@ template <typename T>
 __global__ void add_residual_kernel(float* __restrict__ x, const T* __restrict__ delta, size_t total) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
+    pdl_trigger();
+    pdl_wait();
     for (; i < total; i += stride) x[i] += to_f32(delta[i]);
+}
+
+// x[row] += delta[row] and ss[row] = sum of squares of the new row (one block per row)
+template <typename T>
+__global__ void add_residual_ss_kernel(float* __restrict__ x, const T* __restrict__ delta,
+                                       float* __restrict__ ss, int n, int hidden) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (r >= n) return;
+    float acc = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float v = x[(size_t)r * hidden + c] + to_f32(delta[(size_t)r * hidden + c]);
+        x[(size_t)r * hidden + c] = v;
+        acc += v * v;
+    }
+    acc = block_sum(acc, red);
+    if (threadIdx.x == 0) ss[r] = acc;
+}
+
+VAPI_EXPORT int vapi_add_residual_ss(float* x, const void* delta, int dtype, float* ss, int n,
+                                     int hidden, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    cudaError_t e;
+    if (dtype == VAPI_F32)
+        e = launch(add_residual_ss_kernel<float>, n, 256, 0, stream, x, (const float*)delta, ss, n, hidden);
+    else if (dtype == VAPI_BF16)
+        e = launch(add_residual_ss_kernel<__nv_bfloat16>, n, 256, 0, stream, x, (const __nv_bfloat16*)delta, ss, n, hidden);
+    else
+        return fail(-2, "add_residual_ss: unsupported dtype %d", dtype);
+    return check_launch("add_residual_ss", e);
 }
 
 VAPI_EXPORT int vapi_add_residual(float* x, const void* delta, int dtype, long long total,
@@ -111,13 +162,14 @@ VAPI_EXPORT int vapi_add_residual(float* x, const void* delta, int dtype, long l
     const int threads = 256;
     long long blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
+    cudaError_t e;
     if (dtype == VAPI_F32)
-        add_residual_kernel<float><<<(int)blocks, threads, 0, stream>>>(x, (const float*)delta, (size_t)total);
+        e = launch(add_residual_kernel<float>, (int)blocks, threads, 0, stream, x, (const float*)delta, (size_t)total);
     else if (dtype == VAPI_BF16)
-        add_residual_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(x, (const __nv_bfloat16*)delta, (size_t)total);
+        e = launch(add_residual_kernel<__nv_bfloat16>, (int)blocks, threads, 0, stream, x, (const __nv_bfloat16*)delta, (size_t)total);
     else
         return fail(-2, "add_residual: unsupported dtype %d", dtype);
-    return check_launch("add_residual");
+    return check_launch("add_residual", e);
 }
 
 // ---------------------------------------------------------------------------
@@ -129,6 +181,8 @@ __global__ void swiglu_kernel(const T* __restrict__ g, T* __restrict__ out, int 
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t total = (size_t)rows * ff;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
+    pdl_trigger();
+    pdl_wait();
     for (; i < total; i += stride) {
         const size_t r = i / ff, c = i - r * ff;
         const float a = to_f32(g[r * 2 * ff + c]);
@@ -146,13 +200,14 @@ VAPI_EXPORT int vapi_swiglu(const void* g, void* out, int dtype, int rows, int f
     long long total = (long long)rows * ff;
     long long blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 32) blocks = 148 * 32;
+    cudaError_t e;
     if (dtype == VAPI_F32)
-        swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)g, (float*)out, rows, ff);
+        e = launch(swiglu_kernel<float>, (int)blocks, threads, 0, stream, (const float*)g, (float*)out, rows, ff);
     else if (dtype == VAPI_BF16)
-        swiglu_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>((const __nv_bfloat16*)g, (__nv_bfloat16*)out, rows, ff);
+        e = launch(swiglu_kernel<__nv_bfloat16>, (int)blocks, threads, 0, stream, (const __nv_bfloat16*)g, (__nv_bfloat16*)out, rows, ff);
     else
         return fail(-2, "swiglu: unsupported dtype %d", dtype);
-    return check_launch("swiglu");
+    return check_launch("swiglu", e);
 }
 
 VAPI_EXPORT const char* vapi_last_error() { return error_buffer(); }

@@ -1,0 +1,309 @@
+// Weight-streaming matrix product for decode steps: y[m][n] = sum_k a[m][k] * W[n][k] with
+// few rows m (up to 16 tokens) against a large bfloat16 weight.  At these sizes the product is
+// bound by reading W once from HBM, so the kernel is organised around that stream:
+//
+//  * W is the A operand of mma.sync m16n8k16 (16 weight rows x 16 k), the tokens are the n
+//    dimension (8 per tile).  Each lane reads 16 contiguous bytes of a weight row straight from
+//    global memory into its fragment registers.  That is legal because a dot product does not
+//    care about the order of k: lane (g, t) takes physical k = 32c + 8t .. 8t+7 of rows g and
+//    g+8, uses elements 0..3 for one MMA and 4..7 for the next, and the activation fragment is
+//    read with exactly the same mapping.  The 16-byte pieces travel by cp.async through a
+//    small per-lane queue in shared memory (a lane reads back only what it queued itself), so
+//    several chunks are always in flight whatever the arithmetic is doing, and there is no
+//    barrier in the loop.
+//  * the 8 warps of a block split K and add their partial tiles in a fixed order through shared
+//    memory (deterministic: no atomics), then one thread per output applies the epilogue.
+//  * prologue (what the token operand is): bfloat16 activations, or the float residual stream
+//    normalised on the fly (RMSNorm: x * rsqrt(mean x^2 + eps) * w, the mean taken from partial
+//    sums of squares a producer kernel left, summed here in a fixed order).
+//  * epilogue: bfloat16 out (+bias) | float out (logits) | SwiGLU (a block owns 8 gate rows and
+//    the 8 matching up rows, so silu(gate)*up happens before anything is stored) | add into the
+//    float residual stream (+bias), leaving partial sums of squares of the new stream values
+//    for the norm that follows.
+//
+// The reference does these products with cuBLAS and separate norm / SwiGLU / add kernels
+// (crates/vapi-backend-candle/src/models/lfm2.rs:519-534, 591-593, 645-647).
+#include "common.cuh"
+
+using namespace vapi;
+
+constexpr int GV_WARPS = 8;
+constexpr int GV_STAGES = 6;      // depth of the per-lane copy queue (chunks of 32 k)
+
+enum { GV_PRO_ACT = 0, GV_PRO_NORM = 1 };
+enum { GV_EPI_BF16 = 0, GV_EPI_SWIGLU = 1, GV_EPI_RESID = 2, GV_EPI_F32 = 3 };
+
+struct GvParams {
+    const __nv_bfloat16* W; int N, K, M;
+    const __nv_bfloat16* act;                      // PRO_ACT: [M][K]
+    const float* x; const float* ss_in; int ss_parts; const float* norm_w; float eps;   // PRO_NORM
+    __nv_bfloat16* out_bf16; float* out_f32; long long out_stride;
+    const float* bias;
+    float* resid; float* ss_out;                   // EPI_RESID
+    int ff;                                        // EPI_SWIGLU: N == 2*ff
+    int rows_per_cta;                              // 16 or 8 (always 8 gate + 8 up for SwiGLU)
+};
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    return __ldcs(reinterpret_cast<const uint4*>(p));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+__device__ __forceinline__ void gv_cp16(void* smem_dst, const void* gsrc, int bytes) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(gsrc), "r"(bytes));
+}
+__device__ __forceinline__ void gv_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void gv_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+template <int NT, int PRO>
+__host__ __device__ constexpr int gv_slots() { return 2 + (PRO == GV_PRO_ACT ? NT : 0); }
+
+template <int NT, int PRO>
+static size_t gv_smem_bytes(int K) {
+    size_t b = (size_t)GV_WARPS * GV_STAGES * gv_slots<NT, PRO>() * 32 * sizeof(uint4);
+    if (PRO == GV_PRO_NORM) b += (size_t)8 * NT * (K + 32) * sizeof(__nv_bfloat16);
+    return b;
+}
+
+template <int NT, int PRO, int EPI>
+__global__ void __launch_bounds__(GV_WARPS * 32)
+skinny_linear_kernel(const GvParams p) {
+    constexpr int SLOTS = gv_slots<NT, PRO>();
+    extern __shared__ __align__(16) unsigned char gv_smem[];
+    __shared__ float red[GV_WARPS][16][8 * NT + 1];
+    __shared__ float inv_s[8 * NT];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int R = p.rows_per_cta;
+    uint4* fifo = reinterpret_cast<uint4*>(gv_smem) + (size_t)warp * (GV_STAGES * SLOTS * 32);
+    __nv_bfloat16* act_s = reinterpret_cast<__nv_bfloat16*>(
+        reinterpret_cast<uint4*>(gv_smem) + (size_t)GV_WARPS * GV_STAGES * SLOTS * 32);   // PRO_NORM only
+    const int pitch = p.K + 32;
+
+    // which weight rows this lane streams: MMA rows g and g + 8
+    long long row_lo, row_hi;
+    bool ok_lo, ok_hi;
+    if (EPI == GV_EPI_SWIGLU) {
+        row_lo = (long long)blockIdx.x * 8 + g;            // gate
+        row_hi = (long long)p.ff + row_lo;                 // up
+        ok_lo = ok_hi = row_lo < p.ff;
+    } else {
+        row_lo = (long long)blockIdx.x * R + g;
+        row_hi = row_lo + 8;
+        ok_lo = row_lo < p.N;
+        ok_hi = R == 16 && row_hi < p.N;
+    }
+
+    pdl_trigger();
+    const int nchunks = p.K >> 5;
+    const int cpw = (nchunks + GV_WARPS - 1) / GV_WARPS;
+    const int c_begin = warp * cpw, c_end = min(nchunks, c_begin + cpw);
+    const __nv_bfloat16* w_lo = p.W + (size_t)(ok_lo ? row_lo : 0) * p.K + 8 * t;
+    const __nv_bfloat16* w_hi = p.W + (size_t)(ok_hi ? row_hi : 0) * p.K + 8 * t;
+
+    auto queue_weights = [&](int c, int stage) {
+        if (c < c_end) {
+            gv_cp16(&fifo[(stage * SLOTS + 0) * 32 + lane], w_lo + ((size_t)c << 5), ok_lo ? 16 : 0);
+            gv_cp16(&fifo[(stage * SLOTS + 1) * 32 + lane], w_hi + ((size_t)c << 5), ok_hi ? 16 : 0);
+        }
+    };
+    auto queue_acts = [&](int c, int stage) {
+        if (PRO == GV_PRO_ACT && c < c_end) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int m = nt * 8 + g;
+                const bool ok = m < p.M;
+                gv_cp16(&fifo[(stage * SLOTS + 2 + nt) * 32 + lane],
+                        p.act + (size_t)(ok ? m : 0) * p.K + ((size_t)c << 5) + 8 * t, ok ? 16 : 0);
+            }
+        }
+    };
+    // the weights do not depend on the kernel before this one: start streaming them, then wait
+#pragma unroll
+    for (int st = 0; st < GV_STAGES - 1; ++st) {
+        queue_weights(c_begin + st, st);
+        gv_commit();
+    }
+    pdl_wait();
+
+    if (PRO == GV_PRO_NORM) {
+        // inverse rms of each token's row from the producer's partial sums, in a fixed order
+        for (int m = warp; m < p.M; m += GV_WARPS) {
+            float s = 0.f;
+            for (int i = lane; i < p.ss_parts; i += 32) s += p.ss_in[(size_t)i * p.M + m];
+            s = warp_sum(s);
+            if (lane == 0) inv_s[m] = rsqrtf(s / (float)p.K + p.eps);
+        }
+        __syncthreads();
+        // the normalised tokens, once per block, as bfloat16 rows in shared memory
+        const int k4 = p.K >> 2;
+        for (int idx = threadIdx.x; idx < 8 * NT * k4; idx += GV_WARPS * 32) {
+            const int m = idx / k4, k = (idx - m * k4) << 2;
+            uint2 v = make_uint2(0u, 0u);
+            if (m < p.M) {
+                const float4 xv = *reinterpret_cast<const float4*>(p.x + (size_t)m * p.K + k);
+                const float4 nv = *reinterpret_cast<const float4*>(p.norm_w + k);
+                const float sc = inv_s[m];
+                v.x = pack2(xv.x * sc * nv.x, xv.y * sc * nv.y);
+                v.y = pack2(xv.z * sc * nv.z, xv.w * sc * nv.w);
+            }
+            *reinterpret_cast<uint2*>(act_s + (size_t)m * pitch + k) = v;
+        }
+        __syncthreads();
+    } else {
+#pragma unroll
+        for (int st = 0; st < GV_STAGES - 1; ++st) queue_acts(c_begin + st, st);
+        gv_commit();
+    }
+
+    float acc[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+    int stage = 0;
+    for (int c = c_begin; c < c_end; ++c) {
+        const int nstage = stage == 0 ? GV_STAGES - 1 : stage - 1;      // (stage + STAGES - 1) % STAGES
+        queue_weights(c + GV_STAGES - 1, nstage);
+        queue_acts(c + GV_STAGES - 1, nstage);
+        gv_commit();
+        if (PRO == GV_PRO_ACT && c == c_begin) gv_wait<1>();            // every group queued before the loop
+        else gv_wait<GV_STAGES - 1>();
+        const uint4 wl = fifo[(stage * SLOTS + 0) * 32 + lane];
+        const uint4 wh = fifo[(stage * SLOTS + 1) * 32 + lane];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            uint4 av;
+            if (PRO == GV_PRO_ACT) av = fifo[(stage * SLOTS + 2 + nt) * 32 + lane];
+            else av = *reinterpret_cast<const uint4*>(act_s + (size_t)(nt * 8 + g) * pitch + ((size_t)c << 5) + 8 * t);
+            mma16816(acc[nt], wl.x, wh.x, wl.y, wh.y, av.x, av.y);
+            mma16816(acc[nt], wl.z, wh.z, wl.w, wh.w, av.z, av.w);
+        }
+        stage = stage == GV_STAGES - 1 ? 0 : stage + 1;
+    }
+    gv_wait<0>();
+
+    // partial tiles of the 8 warps, added in warp order
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        red[warp][g][nt * 8 + 2 * t] = acc[nt][0];
+        red[warp][g][nt * 8 + 2 * t + 1] = acc[nt][1];
+        red[warp][g + 8][nt * 8 + 2 * t] = acc[nt][2];
+        red[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
+    }
+    __syncthreads();
+    constexpr int COLS = 8 * NT;
+    const int i = threadIdx.x / COLS, m = threadIdx.x - i * COLS;      // MMA row, token
+    float y = 0.f, y2 = 0.f;
+    if (i < 16) {
+#pragma unroll
+        for (int w = 0; w < GV_WARPS; ++w) y += red[w][i][m];
+        if (EPI == GV_EPI_SWIGLU && i < 8) {
+#pragma unroll
+            for (int w = 0; w < GV_WARPS; ++w) y2 += red[w][i + 8][m];
+        }
+    }
+    if (EPI == GV_EPI_SWIGLU) {
+        const long long col = (long long)blockIdx.x * 8 + i;
+        if (i < 8 && m < p.M && col < p.ff) {
+            const float s = y / (1.f + expf(-y));
+            p.out_bf16[(size_t)m * p.out_stride + col] = __float2bfloat16_rn(s * y2);
+        }
+        return;
+    }
+    const long long n = (long long)blockIdx.x * R + i;
+    const bool valid = i < R && n < p.N && m < p.M;
+    if (valid && p.bias) y += p.bias[n];
+    if (EPI == GV_EPI_BF16) {
+        if (valid) p.out_bf16[(size_t)m * p.out_stride + n] = __float2bfloat16_rn(y);
+    } else if (EPI == GV_EPI_F32) {
+        if (valid) p.out_f32[(size_t)m * p.out_stride + n] = y;
+    } else {   // GV_EPI_RESID
+        float v = 0.f;
+        if (valid) {
+            v = p.resid[(size_t)m * p.N + n] + y;
+            p.resid[(size_t)m * p.N + n] = v;
+        }
+        if (p.ss_out) {
+            __syncthreads();                     // everyone has read its sums out of red[]
+            if (i < 16) red[0][i][m] = v * v;
+            __syncthreads();
+            if (threadIdx.x < COLS && threadIdx.x < p.M) {
+                float s = 0.f;
+#pragma unroll
+                for (int r = 0; r < 16; ++r) s += red[0][r][threadIdx.x];
+                p.ss_out[(size_t)blockIdx.x * p.M + threadIdx.x] = s;
+            }
+        }
+    }
+}
+
+template <int NT, int PRO, int EPI>
+static int launch_gv(const GvParams& p, int blocks, cudaStream_t stream) {
+    const size_t smem = gv_smem_bytes<NT, PRO>(p.K);
+    auto kern = skinny_linear_kernel<NT, PRO, EPI>;
+    if (smem > 200 * 1024) return fail(-1, "skinny_linear: K=%d needs %zu bytes of shared memory", p.K, smem);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(-101, "skinny_linear: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    }
+    return check_launch("skinny_linear", launch(kern, blocks, GV_WARPS * 32, smem, stream, p));
+}
+
+// Number of blocks (and so of partial sums a residual epilogue leaves) for a given shape.
+VAPI_EXPORT int vapi_skinny_linear_blocks(int N, int epi, int rows_per_cta) {
+    if (epi == GV_EPI_SWIGLU) return (N / 2 + 7) / 8;
+    return (N + rows_per_cta - 1) / rows_per_cta;
+}
+
+VAPI_EXPORT int vapi_skinny_linear(const void* W, int N, int K, int M, int pro, const void* act,
+                                   const float* x, const float* ss_in, int ss_parts,
+                                   const float* norm_w, float eps, int epi, void* out_bf16,
+                                   float* out_f32, long long out_stride, const float* bias,
+                                   float* resid, float* ss_out, int rows_per_cta,
+                                   cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (M > 16) return fail(-1, "skinny_linear: %d rows are more than 16", M);
+    if (N <= 0 || K <= 0 || K % 32 != 0) return fail(-1, "skinny_linear: K=%d must be a positive multiple of 32 (N=%d)", K, N);
+    if (rows_per_cta != 8 && rows_per_cta != 16) return fail(-1, "skinny_linear: rows per block must be 8 or 16");
+    if (epi == GV_EPI_SWIGLU && N % 2 != 0) return fail(-1, "skinny_linear: SwiGLU needs an even N");
+    if (pro == GV_PRO_ACT && !act) return fail(-1, "skinny_linear: no activations");
+    if (pro == GV_PRO_NORM && (!x || !ss_in || !norm_w || ss_parts <= 0)) return fail(-1, "skinny_linear: norm prologue needs x, partial sums and a weight");
+    if ((epi == GV_EPI_BF16 || epi == GV_EPI_SWIGLU) && !out_bf16) return fail(-1, "skinny_linear: no output");
+    if (epi == GV_EPI_F32 && !out_f32) return fail(-1, "skinny_linear: no output");
+    if (epi == GV_EPI_RESID && !resid) return fail(-1, "skinny_linear: no residual stream");
+    GvParams p;
+    p.W = (const __nv_bfloat16*)W; p.N = N; p.K = K; p.M = M;
+    p.act = (const __nv_bfloat16*)act; p.x = x; p.ss_in = ss_in; p.ss_parts = ss_parts; p.norm_w = norm_w; p.eps = eps;
+    p.out_bf16 = (__nv_bfloat16*)out_bf16; p.out_f32 = out_f32; p.out_stride = out_stride; p.bias = bias;
+    p.resid = resid; p.ss_out = ss_out; p.ff = N / 2; p.rows_per_cta = epi == GV_EPI_SWIGLU ? 16 : rows_per_cta;
+    const int blocks = vapi_skinny_linear_blocks(N, epi, rows_per_cta);
+#define GV_GO(NT, PRO, EPI) return launch_gv<NT, PRO, EPI>(p, blocks, stream)
+#define GV_EPIS(NT, PRO)                                      \
+    switch (epi) {                                            \
+        case GV_EPI_BF16: GV_GO(NT, PRO, GV_EPI_BF16);        \
+        case GV_EPI_SWIGLU: GV_GO(NT, PRO, GV_EPI_SWIGLU);    \
+        case GV_EPI_RESID: GV_GO(NT, PRO, GV_EPI_RESID);      \
+        case GV_EPI_F32: GV_GO(NT, PRO, GV_EPI_F32);          \
+        default: return fail(-2, "skinny_linear: unknown epilogue %d", epi); \
+    }
+    if (pro == GV_PRO_ACT) {
+        if (M <= 8) { GV_EPIS(1, GV_PRO_ACT) } else { GV_EPIS(2, GV_PRO_ACT) }
+    } else if (pro == GV_PRO_NORM) {
+        if (M <= 8) { GV_EPIS(1, GV_PRO_NORM) } else { GV_EPIS(2, GV_PRO_NORM) }
+    }
+    return fail(-2, "skinny_linear: unknown prologue %d", pro);
+#undef GV_EPIS
+#undef GV_GO
+}
+
+VAPI_EXPORT const char* vapi_last_error() { return error_buffer(); }

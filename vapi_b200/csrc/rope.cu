@@ -16,6 +16,8 @@ __global__ void rope_cos_sin_kernel(const int* __restrict__ positions,
                                     float* __restrict__ cosr, float* __restrict__ sinr,
                                     int n, int half) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
     if (i >= n * half) return;
     const int t = i / half, j = i - t * half;
     const float a = (float)positions[t] * inv_freq[j];
@@ -27,8 +29,8 @@ VAPI_EXPORT int vapi_rope_cos_sin(const int* positions, const float* inv_freq, f
                                   float* sinr, int n, int half, cudaStream_t stream) {
     if (n <= 0 || half <= 0) return 0;
     const int total = n * half;
-    rope_cos_sin_kernel<<<(total + 255) / 256, 256, 0, stream>>>(positions, inv_freq, cosr, sinr, n, half);
-    return check_launch("rope_cos_sin");
+    return check_launch("rope_cos_sin", launch(rope_cos_sin_kernel, (total + 255) / 256, 256, 0, stream,
+                                                 positions, inv_freq, cosr, sinr, n, half));
 }
 
 // One warp per (token, head).  Heads are laid out in a qkv row as
@@ -53,6 +55,8 @@ __global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __re
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = nh + 2 * nkv;
     const long long item = (long long)blockIdx.x * QK_WARPS + warp;
+    pdl_trigger();
+    pdl_wait();
     if (item >= (long long)n * heads) return;
     const int t = (int)(item / heads), h = (int)(item - (long long)t * heads);
     T* src = qkv + (size_t)t * heads * d + (size_t)h * d;
@@ -118,17 +122,18 @@ VAPI_EXPORT int vapi_qk_norm_rope_write(void* qkv, int dtype, const float* qw, c
         return fail(-1, "qk_norm_rope_write: cache given without pages or slot mapping");
     const long long items = (long long)n * (nh + 2 * nkv);
     const int blocks = (int)((items + QK_WARPS - 1) / QK_WARPS);
+    cudaError_t e;
     if (dtype == VAPI_F32)
-        qk_norm_rope_write_kernel<float><<<blocks, QK_WARPS * 32, 0, stream>>>(
-            (float*)qkv, qw, kw, eps, cosr, sinr, rot, (float*)cache, slot_mapping, n, nh, nkv, d,
-            page_size, num_pages, status);
+        e = launch(qk_norm_rope_write_kernel<float>, blocks, QK_WARPS * 32, 0, stream,
+                   (float*)qkv, qw, kw, eps, cosr, sinr, rot, (float*)cache, slot_mapping, n, nh, nkv, d,
+                   page_size, num_pages, status);
     else if (dtype == VAPI_BF16)
-        qk_norm_rope_write_kernel<__nv_bfloat16><<<blocks, QK_WARPS * 32, 0, stream>>>(
-            (__nv_bfloat16*)qkv, qw, kw, eps, cosr, sinr, rot, (__nv_bfloat16*)cache,
-            slot_mapping, n, nh, nkv, d, page_size, num_pages, status);
+        e = launch(qk_norm_rope_write_kernel<__nv_bfloat16>, blocks, QK_WARPS * 32, 0, stream,
+                   (__nv_bfloat16*)qkv, qw, kw, eps, cosr, sinr, rot, (__nv_bfloat16*)cache,
+                   slot_mapping, n, nh, nkv, d, page_size, num_pages, status);
     else
         return fail(-2, "qk_norm_rope_write: unsupported dtype %d", dtype);
-    return check_launch("qk_norm_rope_write");
+    return check_launch("qk_norm_rope_write", e);
 }
 
 VAPI_EXPORT const char* vapi_last_error() { return error_buffer(); }

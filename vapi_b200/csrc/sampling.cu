@@ -59,6 +59,8 @@ sample_rows_kernel(const float* __restrict__ logits, int vocab, long long row_st
     __shared__ float sv[32];
     __shared__ unsigned si[32];
     const int row = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
     const int md = mode ? mode[row] : 1;
     if (md == 0) return;
     const float* l = logits + (size_t)row * row_stride;
@@ -88,8 +90,8 @@ VAPI_EXPORT int vapi_sample_rows(const float* logits, int rows, int vocab, long 
     if (vocab <= 0) return fail(-1, "sample_rows: vocab=%d", vocab);
     if (mode && (!inv_t || !seeds || !draws))
         return fail(-1, "sample_rows: per-row modes need temperatures, seeds and draw counters");
-    sample_rows_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, vocab, row_stride, mode, inv_t, seeds, draws, out);
-    return check_launch("sample_rows");
+    return check_launch("sample_rows", launch(sample_rows_kernel, rows, SAMPLE_THREADS, 0, stream,
+                                                logits, vocab, row_stride, mode, inv_t, seeds, draws, out));
 }
 
 // Penalties on (row, token) pairs, in place
@@ -102,6 +104,8 @@ __global__ void apply_penalties_kernel(float* __restrict__ logits, int vocab, lo
                                        const float* __restrict__ rep, const float* __restrict__ freq,
                                        const float* __restrict__ pres, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
     if (i >= n) return;
     const int r = rows[i], t = toks[i];
     if (t < 0 || t >= vocab) return;
@@ -119,8 +123,8 @@ VAPI_EXPORT int vapi_apply_penalties(float* logits, int vocab, long long row_str
                                      const float* rep, const float* freq, const float* pres,
                                      int n, cudaStream_t stream) {
     if (n <= 0) return 0;
-    apply_penalties_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, vocab, row_stride, rows, toks, counts, rep, freq, pres, n);
-    return check_launch("apply_penalties");
+    return check_launch("apply_penalties", launch(apply_penalties_kernel, (n + 255) / 256, 256, 0, stream,
+                                                    logits, vocab, row_stride, rows, toks, counts, rep, freq, pres, n));
 }
 
 VAPI_EXPORT const char* vapi_last_error() { return error_buffer(); }

@@ -55,6 +55,8 @@ __global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restri
                                  int hidden, int L, int num_slots, int* __restrict__ status) {
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int r = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
     if (c >= hidden || r >= n) return;
     const int s = tok_seq[r];
     const int r0 = cu_q[s], q = cu_q[s + 1] - r0;
@@ -133,18 +135,19 @@ VAPI_EXPORT int vapi_shortconv(const void* h3, int dtype, const float* in_bias, 
     const int cblocks = (hidden + threads - 1) / threads;
     if (cblocks > 65535) return fail(-1, "shortconv: hidden=%d is too wide for the grid", hidden);
     dim3 grid(n, cblocks);
+    cudaError_t e;
     if (dtype == VAPI_F32)
-        shortconv_kernel<float><<<grid, threads, 0, stream>>>(
-            (const float*)h3, in_bias, taps, conv_bias, (float*)state, slot_stride, state_slots,
-            tok_seq, cu_q, positions, (float*)out, n, hidden, L, num_slots, status);
+        e = launch(shortconv_kernel<float>, grid, threads, 0, stream,
+                   (const float*)h3, in_bias, taps, conv_bias, (float*)state, slot_stride, state_slots,
+                   tok_seq, cu_q, positions, (float*)out, n, hidden, L, num_slots, status);
     else if (dtype == VAPI_BF16)
-        shortconv_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
-            (const __nv_bfloat16*)h3, in_bias, taps, conv_bias, (__nv_bfloat16*)state, slot_stride,
-            state_slots, tok_seq, cu_q, positions, (__nv_bfloat16*)out, n, hidden, L, num_slots,
-            status);
+        e = launch(shortconv_kernel<__nv_bfloat16>, grid, threads, 0, stream,
+                   (const __nv_bfloat16*)h3, in_bias, taps, conv_bias, (__nv_bfloat16*)state, slot_stride,
+                   state_slots, tok_seq, cu_q, positions, (__nv_bfloat16*)out, n, hidden, L, num_slots,
+                   status);
     else
         return fail(-2, "shortconv: unsupported dtype %d", dtype);
-    return check_launch("shortconv");
+    return check_launch("shortconv", e);
 }
 
 VAPI_EXPORT const char* vapi_last_error() { return error_buffer(); }

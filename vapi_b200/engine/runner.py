@@ -146,16 +146,42 @@ class ModelRunner:
         """Device work of a step for a prepared context; returns float32 logits [rows, vocab]
         or None when no logits are wanted (the caches are written either way)."""
         plan = self.plan
-        x = plan.embedding.forward(ctx)
         for pe in plan.position_encodings:
             ctx.pos[pe.name] = pe.prepare(ctx)
         views = self.views(ctx)
+        ctx.fused = (self.device.type == "cuda" and self.dtype == torch.bfloat16 and ops.use_skinny
+                     and ctx.n <= ops.SKINNY_MAX_ROWS)
+        if ctx.fused:
+            return self._forward_few_rows(ctx, views)
+        x = plan.embedding.forward(ctx)
         delta = None
         for i, call in enumerate(plan.order):
             delta = plan.layers[call.layer].forward(x, delta, ctx, views[i])
         if ctx.logits_rows is None:
             return None
         xn = plan.final_norm.apply(x, delta, ctx.dtype, rows=ctx.logits_rows)
+        return plan.head.forward(xn)
+
+    def _forward_few_rows(self, ctx: StepContext, views: List[CacheView]) -> Optional[torch.Tensor]:
+        """The same model for a step of at most 16 rows (decode): every block runs in its
+        stream form, see :meth:`PreNormBlock.forward_stream`."""
+        plan = self.plan
+        x, ss = plan.embedding.forward(ctx, want_ss=True)
+        for i, call in enumerate(plan.order):
+            blk = plan.layers[call.layer]
+            if hasattr(blk, "forward_stream"):
+                ss = blk.forward_stream(x, ss, ctx, views[i])
+            else:
+                ss = ops.add_residual_ss(x, blk.forward(x, None, ctx, views[i]))
+        if ctx.logits_rows is None:
+            return None
+        if ctx.rows_identity:
+            a = plan.final_norm.deferred(x, ss)
+            if a is not None:
+                logits = plan.head.forward_stream(a)
+                if logits is not NotImplemented:
+                    return logits
+        xn = plan.final_norm.apply(x, None, ctx.dtype, rows=ctx.logits_rows)
         return plan.head.forward(xn)
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:

@@ -58,6 +58,8 @@ class StepContext:
     dtype: torch.dtype
     status: Optional[torch.Tensor] = None
     attention_splits: Optional[int] = None
+    rows_identity: bool = False     # the wanted rows are exactly rows 0 .. n-1 in order
+    fused: bool = False             # a step of few rows: norms and adds ride on the matrix products
     pos: Dict[str, Any] = field(default_factory=dict)
     extras: Dict[str, Any] = field(default_factory=dict)
 
@@ -246,7 +248,7 @@ class StepPacker:
             cu_q=view("cu_q", s_eff + 1), seqlens_k=view("seqlens_k", s_eff),
             state_slots=view("state_slots", s_eff),
             logits_rows=view("rows", len(rows)) if rows else None,
-            groups=groups, dtype=dtype, status=status)
+            groups=groups, dtype=dtype, status=status, rows_identity=rows == list(range(n_eff)))
 
     # a page per group that padding rows may scribble on; set by whoever captures graphs
     _pad_pages: Optional[List[int]] = None

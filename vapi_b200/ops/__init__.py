@@ -12,6 +12,7 @@ taps) are always float32.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from typing import Dict, Optional, Tuple
 
@@ -94,16 +95,31 @@ def _f32(t: Optional[torch.Tensor], what: str) -> None:
 
 
 # ---------------------------------------------------------------------------------------
-def embed(table: torch.Tensor, tokens: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Rows of ``table`` [V, H] for ``tokens`` [n] as the float32 residual stream [n, H]."""
+def embed(table: torch.Tensor, tokens: torch.Tensor, status: Optional[torch.Tensor] = None,
+          want_ss: bool = False):
+    """Rows of ``table`` [V, H] for ``tokens`` [n] as the float32 residual stream [n, H].
+    With ``want_ss`` also the sum of squares of every row, [1, n], for a norm that follows."""
     _cuda(table, tokens)
     _contig(table, "embedding table")
     _i32(tokens, "tokens")
     n, (vocab, hidden) = tokens.numel(), table.shape
     out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    ss = torch.empty((1, n), dtype=torch.float32, device=table.device) if want_ss else None
     lib = _lib("elementwise")
-    _check(lib, lib.vapi_embed(_p(table), _dt(table), _p(tokens), _p(out), n, hidden, vocab, _p(status), _stream()))
-    return out
+    _check(lib, lib.vapi_embed(_p(table), _dt(table), _p(tokens), _p(out), _p(ss), n, hidden, vocab, _p(status), _stream()))
+    return (out, ss) if want_ss else out
+
+
+def add_residual_ss(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """``x += delta`` on the float32 stream; returns the sum of squares of every new row, [1, n]."""
+    _cuda(x, delta)
+    _f32(x, "residual stream")
+    _contig(delta, "delta")
+    n, hidden = x.shape
+    ss = torch.empty((1, n), dtype=torch.float32, device=x.device)
+    lib = _lib("elementwise")
+    _check(lib, lib.vapi_add_residual_ss(_p(x), _p(delta), _dt(delta), _p(ss), n, hidden, _stream()))
+    return ss
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
@@ -155,14 +171,106 @@ def swiglu(g: torch.Tensor) -> torch.Tensor:
     return out
 
 
+SKINNY_MAX_ROWS = 16
+#: set False to send every product to the library (for comparisons)
+use_skinny = os.environ.get("VAPI_SKINNY", "1") != "0"
+
+_PRO = {"act": 0, "norm": 1}
+_EPI = {"bf16": 0, "swiglu": 1, "resid": 2, "f32": 3}
+
+
+def skinny_applies(rows: int, weight: torch.Tensor) -> bool:
+    """Whether the weight-streaming kernel takes this product: bfloat16 weight, at most 16
+    rows, inner size a multiple of 32."""
+    return (use_skinny and weight.is_cuda and weight.dtype == torch.bfloat16 and 0 < rows <= SKINNY_MAX_ROWS
+            and weight.dim() == 2 and weight.shape[1] % 32 == 0 and weight.is_contiguous())
+
+
+def skinny_blocks(n_out: int, epilogue: str, rows_per_block: int = 16) -> int:
+    if epilogue == "swiglu":
+        return (n_out // 2 + 7) // 8
+    return -(-n_out // rows_per_block)
+
+
+def skinny_rows_per_block(n_out: int) -> int:
+    """16 weight rows a block when that still gives every SM work, else 8."""
+    return 16 if n_out // 16 >= 296 else 8
+
+
+def skinny_linear(weight: torch.Tensor, *, act: Optional[torch.Tensor] = None,
+                  x: Optional[torch.Tensor] = None, ss_in: Optional[torch.Tensor] = None,
+                  norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, epilogue: str = "bf16",
+                  bias: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
+                  ss_out: bool = False, rows_per_block: Optional[int] = None):
+    """The weight-streaming product for decode steps (at most 16 rows), with its fusions.
+
+    Token operand: ``act`` [M, K] bfloat16, or the float32 stream ``x`` [M, K] normalised on
+    the fly with ``norm_weight`` and the partial sums of squares ``ss_in`` [parts, M] that the
+    producer of ``x`` left.  ``epilogue``: "bf16" -> [M, N] bfloat16; "f32" -> [M, N] float32;
+    "swiglu" -> [M, N/2] bfloat16 = silu(first half) * second half; "resid" -> adds into
+    ``resid`` [M, N] in place and returns, when ``ss_out``, the partial sums of squares
+    [blocks, M] of the new stream values (else None).
+    """
+    _cuda(weight, act, x, ss_in, norm_weight, bias, resid)
+    N, K = weight.shape
+    pro = "act" if act is not None else "norm"
+    src = act if act is not None else x
+    M = src.shape[0]
+    if weight.dtype != torch.bfloat16 or not weight.is_contiguous():
+        raise KernelError("skinny_linear needs a contiguous bfloat16 weight")
+    if src.shape[1] != K or not src.is_contiguous():
+        raise KernelError(f"skinny_linear: token operand {tuple(src.shape)} does not fit a weight of {N}x{K}")
+    if pro == "act" and act.dtype != torch.bfloat16:
+        raise KernelError("skinny_linear: activations must be bfloat16")
+    if pro == "norm":
+        _f32(x, "residual stream")
+        _f32(ss_in, "partial sums")
+        _f32(norm_weight, "norm weight")
+        if ss_in.dim() != 2 or ss_in.shape[1] != M:
+            raise KernelError("partial sums must be [parts, M]")
+    _f32(bias, "bias")
+    rpb = rows_per_block or skinny_rows_per_block(N)
+    out_bf16 = out_f32 = sso = None
+    out_stride = N
+    if epilogue == "bf16":
+        out_bf16 = torch.empty((M, N), dtype=torch.bfloat16, device=weight.device)
+    elif epilogue == "f32":
+        out_f32 = torch.empty((M, N), dtype=torch.float32, device=weight.device)
+    elif epilogue == "swiglu":
+        out_stride = N // 2
+        out_bf16 = torch.empty((M, N // 2), dtype=torch.bfloat16, device=weight.device)
+    elif epilogue == "resid":
+        _f32(resid, "residual stream")
+        if tuple(resid.shape) != (M, N):
+            raise KernelError("the residual stream must be [M, N]")
+        if ss_out:
+            sso = torch.empty((skinny_blocks(N, epilogue, rpb), M), dtype=torch.float32, device=weight.device)
+    else:
+        raise KernelError(f"unknown epilogue {epilogue}")
+    lib = _lib("gemv")
+    _check(lib, lib.vapi_skinny_linear(
+        _p(weight), N, K, M, _PRO[pro], _p(act), _p(x), _p(ss_in), 0 if ss_in is None else ss_in.shape[0],
+        _p(norm_weight), ctypes.c_float(eps), _EPI[epilogue], _p(out_bf16), _p(out_f32),
+        ctypes.c_longlong(out_stride), _p(bias), _p(resid), _p(sso), rpb, _stream()))
+    if epilogue == "resid":
+        return sso
+    return out_bf16 if out_bf16 is not None else out_f32
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """``x @ weight.T (+ bias)``: the library matrix product.
+    """``x @ weight.T (+ bias)``.  The library matrix product, except for decode-sized
+    bfloat16 products (at most 16 rows), which go to the weight-streaming kernel.
 
     float32 runs without any reduced-precision mode (see :func:`strict_fp32`).  A weight kept
     in float32 beside bfloat16 activations is multiplied in float32.
     """
     _cuda(x, weight)
+    if x.dtype == torch.bfloat16 and skinny_applies(x.shape[0], weight) and x.is_contiguous():
+        if out_dtype in (None, torch.bfloat16):
+            return skinny_linear(weight, act=x, epilogue="bf16", bias=bias)
+        if out_dtype == torch.float32:
+            return skinny_linear(weight, act=x, epilogue="f32", bias=bias)
     if weight.dtype != x.dtype:
         y = torch.mm(x.to(torch.float32), weight.to(torch.float32).t())
         if bias is not None:
@@ -238,14 +346,17 @@ def qk_norm_rope_write(qkv: torch.Tensor, nh: int, nkv: int, d: int,
 
 def attention_splits(num_seqs: int, max_q: int, max_k: int, nh: int, nkv: int) -> int:
     """How many blocks share the keys of one row tile: 1 unless the step is so small that
-    the device would sit idle (decode of few sequences over long contexts)."""
+    the device would sit idle (decode of few sequences over long contexts).  A decode block
+    is one warp with 48 KB of shared memory, so 4 fit on an SM: aim at one full wave of
+    148 x 4 blocks, each with at least 128 keys."""
     n_rep = nh // nkv
-    tiles = -(-(max_q * n_rep) // 16)
+    rows = max_q * n_rep
+    tiles = -(-rows // (16 if rows <= 16 else 64))
     blocks = max(1, num_seqs * nkv * tiles)
-    if max_q > 1 and blocks >= 148:
+    if rows > 16 and blocks >= 148:
         return 1
-    want = -(-592 // blocks)
-    by_len = max(1, max_k // 256)
+    want = max(1, 592 // blocks)
+    by_len = max(1, max_k // 128)
     return max(1, min(want, by_len, 32))
 
 

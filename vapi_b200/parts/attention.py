@@ -76,8 +76,20 @@ class GQAttention(Mixer):
             self.k_w = tensors[f"{prefix}{n['k_norm']}.weight"].contiguous()
 
     def forward(self, a: torch.Tensor, ctx: Any, cache: CacheView) -> torch.Tensor:
-        nh, nkv, d = self.nh, self.nkv, self.d
         qkv = ops.linear(a, self.w_qkv, self.b_qkv)
+        return ops.linear(self._attend(qkv, ctx, cache), self.w_o, self.b_o)
+
+    def forward_stream(self, a, ctx, cache, x):
+        n = x.shape[0]
+        if not (ops.skinny_applies(n, self.w_qkv) and ops.skinny_applies(n, self.w_o)):
+            return NotImplemented
+        qkv = ops.skinny_linear(self.w_qkv, x=a.x, ss_in=a.ss, norm_weight=a.weight, eps=a.eps,
+                                epilogue="bf16", bias=self.b_qkv)
+        y = self._attend(qkv, ctx, cache)
+        return ops.skinny_linear(self.w_o, act=y, epilogue="resid", resid=x, bias=self.b_o, ss_out=True)
+
+    def _attend(self, qkv: torch.Tensor, ctx: Any, cache: CacheView) -> torch.Tensor:
+        nh, nkv, d = self.nh, self.nkv, self.d
         cos = sin = None
         if self.pos is not None:
             cos, sin = ctx.pos[self.pos]
@@ -89,7 +101,7 @@ class GQAttention(Mixer):
         y = ops.paged_attention(qkv, qkv.stride(0), cache.tensor, grp.block_table, ctx.cu_q,
                                 ctx.seqlens_k, ctx.n, ctx.num_seqs, ctx.max_q, ctx.max_k, nh, nkv, d,
                                 self.scale, self.window, ctx.attention_splits, ctx.status)
-        return ops.linear(y, self.w_o, self.b_o)
+        return y
 
 
 register_mixer("gqa_attention", GQAttention)

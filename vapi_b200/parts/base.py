@@ -92,6 +92,23 @@ class CacheView:
     write: bool = True
 
 
+@dataclass
+class NormedStream:
+    """The float32 residual stream seen through a norm that has not been applied yet.
+
+    Decode steps are a handful of rows, so a norm of its own costs a launch for almost no
+    work.  In that regime a norm hands its consumer this description instead of a tensor, and
+    the consumer's first matrix product normalises on the fly: ``x`` [n, H] float32, ``ss``
+    [parts, n] partial sums of squares of the rows of ``x`` (whoever last wrote ``x`` left
+    them), the norm's ``weight`` and ``eps``.
+    """
+
+    x: torch.Tensor
+    ss: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+
+
 # --------------------------------------------------------------------------------------
 # the parts
 
@@ -116,6 +133,11 @@ class Norm(Part):
         With ``rows`` only those rows are produced and ``x`` is left unchanged."""
         raise NotImplementedError
 
+    def deferred(self, x: torch.Tensor, ss: torch.Tensor) -> Optional[NormedStream]:
+        """This norm of ``x`` as a :class:`NormedStream` for a consumer that applies it
+        itself, or None if the norm cannot be expressed that way."""
+        return None
+
 
 class PositionEncoding(Part):
     """Prepares, once per step, what mixers need to place tokens (e.g. cos/sin rows)."""
@@ -138,10 +160,20 @@ class Mixer(Part):
         contribution to the residual stream, [n, H] in the activation dtype."""
         raise NotImplementedError
 
+    def forward_stream(self, a: NormedStream, ctx: "Any", cache: CacheView, x: torch.Tensor):
+        """Optional fast form for steps of a few rows: take the normed input lazily, add the
+        result into the stream ``x`` in place, and return the partial sums of squares
+        [parts, n] of the new ``x``.  Return ``NotImplemented`` to be run the ordinary way."""
+        return NotImplemented
+
 
 class FeedForward(Part):
     def forward(self, f: torch.Tensor, ctx: "Any") -> torch.Tensor:
         raise NotImplementedError
+
+    def forward_stream(self, f: NormedStream, ctx: "Any", x: torch.Tensor):
+        """As :meth:`Mixer.forward_stream`."""
+        return NotImplemented
 
 
 # --------------------------------------------------------------------------------------

@@ -54,5 +54,23 @@ class PreNormBlock(Part):
         f = self.ffn_norm.apply(x, d1, ctx.dtype)
         return self.ffn.forward(f, ctx)
 
+    def forward_stream(self, x: torch.Tensor, ss: torch.Tensor, ctx: Any, cache: CacheView) -> torch.Tensor:
+        """The same block for steps of a few rows: norms are applied inside their consumer's
+        first product, results are added into ``x`` by the last product of each part, and the
+        partial sums of squares of ``x`` travel from producer to consumer as ``ss``.  A part
+        without a stream form is run the ordinary way between two small kernels."""
+        from .. import ops
+        a = self.mixer_norm.deferred(x, ss)
+        out = self.mixer.forward_stream(a, ctx, cache, x) if a is not None else NotImplemented
+        if out is NotImplemented:
+            delta = self.mixer.forward(self.mixer_norm.apply(x, None, ctx.dtype), ctx, cache)
+            out = ops.add_residual_ss(x, delta)
+        f = self.ffn_norm.deferred(x, out)
+        out2 = self.ffn.forward_stream(f, ctx, x) if f is not None else NotImplemented
+        if out2 is NotImplemented:
+            delta = self.ffn.forward(self.ffn_norm.apply(x, None, ctx.dtype), ctx)
+            out2 = ops.add_residual_ss(x, delta)
+        return out2
+
 
 register_block("prenorm", PreNormBlock)

@@ -23,8 +23,8 @@ class TokenEmbedding(Part):
     def bind(self, tensors, prefix, dtype):
         self.table = tensors[self.name].contiguous()
 
-    def forward(self, ctx: Any) -> torch.Tensor:
-        return ops.embed(self.table, ctx.tokens, ctx.status)
+    def forward(self, ctx: Any, want_ss: bool = False):
+        return ops.embed(self.table, ctx.tokens, ctx.status, want_ss)
 
 
 class OutputHead(Part):
@@ -50,3 +50,9 @@ class OutputHead(Part):
 
     def forward(self, xn: torch.Tensor) -> torch.Tensor:
         return ops.linear(xn, self.weight, None, torch.float32)
+
+    def forward_stream(self, a):
+        """Logits of every row of a lazily normed stream (decode steps), or NotImplemented."""
+        if not ops.skinny_applies(a.x.shape[0], self.weight):
+            return NotImplemented
+        return ops.skinny_linear(self.weight, x=a.x, ss_in=a.ss, norm_weight=a.weight, eps=a.eps, epilogue="f32")

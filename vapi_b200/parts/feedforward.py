@@ -39,5 +39,12 @@ class SwiGLU(FeedForward):
         g = ops.linear(f, self.w_gate_up)
         return ops.linear(ops.swiglu(g), self.w_down)
 
+    def forward_stream(self, f, ctx, x):
+        n = x.shape[0]
+        if not (ops.skinny_applies(n, self.w_gate_up) and ops.skinny_applies(n, self.w_down)):
+            return NotImplemented
+        s = ops.skinny_linear(self.w_gate_up, x=f.x, ss_in=f.ss, norm_weight=f.weight, eps=f.eps, epilogue="swiglu")
+        return ops.skinny_linear(self.w_down, act=s, epilogue="resid", resid=x, ss_out=True)
+
 
 register_feed_forward("swiglu", SwiGLU)

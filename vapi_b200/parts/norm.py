@@ -6,7 +6,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import ops
-from .base import Norm, TensorSpec, register_norm
+from .base import Norm, NormedStream, TensorSpec, register_norm
 
 
 class RMSNorm(Norm):
@@ -26,6 +26,9 @@ class RMSNorm(Norm):
 
     def apply(self, x, delta, dtype, rows=None):
         return ops.add_rmsnorm(x, delta, self.weight, self.eps, dtype, rows)
+
+    def deferred(self, x, ss):
+        return NormedStream(x, ss, self.weight, self.eps)
 
 
 register_norm("rmsnorm", RMSNorm)
