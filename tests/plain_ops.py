@@ -17,14 +17,16 @@ def _f(t):
     return t.to(torch.float32)
 
 
-def embed(table, tokens, status=None, want_ss=False):
+def embed(table, tokens, status=None, next_weight=None):
     out = _f(table[tokens.long()])
-    return (out, (out ** 2).sum(1)[None, :]) if want_ss else out
+    if next_weight is None:
+        return out
+    return out, (out ** 2).sum(1)[None, :], (out * next_weight).to(torch.bfloat16)
 
 
-def add_residual_ss(x, delta):
+def add_residual_ss(x, delta, next_weight):
     x += _f(delta)
-    return (x ** 2).sum(1)[None, :]
+    return (x ** 2).sum(1)[None, :], (x * next_weight).to(torch.bfloat16)
 
 
 def skinny_applies(rows, weight):

@@ -371,35 +371,65 @@ def test_skinny_linear_plain_products(ops, M, N, K):
 
 @pytest.mark.parametrize("M", [1, 8, 13])
 def test_skinny_linear_fusions(ops, M):
-    """Norm prologue from partial sums, SwiGLU epilogue, residual epilogue with new partial sums:
-    a feed-forward of a decode step as two launches."""
+    """Deferred-norm prologue, SwiGLU epilogue, residual epilogue that prepares the next norm: a
+    feed-forward of a decode step as two launches."""
     torch.manual_seed(21)
     H, F, eps = 96, 200, 1e-6
     x = torch.randn(M, H) * 2
     nw = 1 + 0.1 * torch.randn(H)
     w13 = (torch.randn(2 * F, H) * 0.2).to(torch.bfloat16)
-    w2 = (torch.randn(H, 224) * 0.2).to(torch.bfloat16)[:, :224]
-    # partial sums of squares of x as some producer with 5 blocks would leave them
-    parts = torch.stack([(x[:, i * 20:(i + 1) * 20] ** 2).sum(1) for i in range(4)] + [(x[:, 80:] ** 2).sum(1)])
-    s = ops.skinny_linear(dev(w13), x=dev(x), ss_in=dev(parts.contiguous()), norm_weight=dev(nw), eps=eps, epilogue="swiglu")
-    xn = (x * torch.rsqrt((x ** 2).mean(1, keepdim=True) + eps) * nw).to(torch.bfloat16).float()
-    gu = xn @ w13.float().t()
+    w2 = (torch.randn(H, 224) * 0.2).to(torch.bfloat16)
+    # what a producer with 5 blocks would leave: partial sums of squares and bfloat16(x * weight)
+    parts = torch.stack([(x[:, i * 20:(i + 1) * 20] ** 2).sum(1) for i in range(4)] + [(x[:, 80:] ** 2).sum(1)]).contiguous()
+    xw = (x * nw).to(torch.bfloat16)
+    s = ops.skinny_linear(dev(w13), xw=dev(xw), ss_in=dev(parts), eps=eps, epilogue="swiglu")
+    inv = torch.rsqrt((x ** 2).mean(1, keepdim=True) + eps)
+    gu = (xw.float() @ w13.float().t()) * inv
     want_s = (gu[:, :F] / (1 + torch.exp(-gu[:, :F]))) * gu[:, F:]
     torch.testing.assert_close(s.cpu().float(), want_s.to(torch.bfloat16).float(), atol=3e-2, rtol=3e-2)
-    # down projection (inner size 224 = 7 * 32) added into the stream, with partial sums for the next norm
+    # and against the norm done the ordinary way (rounding the normed row instead of x * w)
+    xn = (x * inv * nw).to(torch.bfloat16).float()
+    gu2 = xn @ w13.float().t()
+    torch.testing.assert_close(s.cpu().float(), ((gu2[:, :F] / (1 + torch.exp(-gu2[:, :F]))) * gu2[:, F:]), atol=6e-2, rtol=6e-2)
+    # down projection (inner size 224 = 7 * 32) added into the stream, preparing the next norm
     s2 = torch.randn(M, 224).to(torch.bfloat16)
-    bias = torch.randn(H)
+    bias, nw2 = torch.randn(H), 1 + 0.1 * torch.randn(H)
     for rpb in (8, 16):
         xr = dev(x.clone())
-        ss = ops.skinny_linear(dev(w2.contiguous()), act=dev(s2), epilogue="resid", resid=xr, bias=dev(bias),
-                               ss_out=True, rows_per_block=rpb)
+        ss, xw2 = ops.skinny_linear(dev(w2), act=dev(s2), epilogue="resid", resid=xr, bias=dev(bias),
+                                    next_weight=dev(nw2), rows_per_block=rpb)
         want_x = x + s2.float() @ w2.float().t() + bias
         torch.testing.assert_close(xr.cpu(), want_x, atol=2e-3, rtol=1e-3)
         assert ss.shape == (ops.skinny_blocks(H, "resid", rpb), M)
         torch.testing.assert_close(ss.sum(0).cpu(), (want_x ** 2).sum(1), atol=1e-2, rtol=1e-3)
+        torch.testing.assert_close(xw2.cpu().float(), (want_x * nw2).to(torch.bfloat16).float(), atol=3e-2, rtol=2e-2)
+    none = ops.skinny_linear(dev(w2), act=dev(s2), epilogue="resid", resid=dev(x.clone()))
+    assert none == (None, None)
     # the same call twice gives the same bits (fixed reduction order, no atomics)
-    a = ops.skinny_linear(dev(w13), x=dev(x), ss_in=dev(parts.contiguous()), norm_weight=dev(nw), eps=eps, epilogue="swiglu")
+    a = ops.skinny_linear(dev(w13), xw=dev(xw), ss_in=dev(parts), eps=eps, epilogue="swiglu")
     assert torch.equal(a, s)
+    # logits epilogue through the deferred norm
+    wv = (torch.randn(300, H) * 0.2).to(torch.bfloat16)
+    lg = ops.skinny_linear(dev(wv), xw=dev(xw), ss_in=dev(parts), eps=eps, epilogue="f32")
+    torch.testing.assert_close(lg.cpu(), (xw.float() @ wv.float().t()) * inv, atol=2e-3, rtol=1e-3)
+
+
+def test_embed_and_residual_add_prepare_the_next_norm(ops):
+    torch.manual_seed(22)
+    table = torch.randn(50, 72).to(torch.bfloat16)
+    toks = torch.tensor([3, 49, 0, 3], dtype=torch.int32)
+    nw = 1 + 0.1 * torch.randn(72)
+    x, ss, xw = ops.embed(dev(table), dev(toks), None, dev(nw))
+    want = table[toks.long()].float()
+    torch.testing.assert_close(x.cpu(), want, atol=0, rtol=0)
+    torch.testing.assert_close(ss.cpu(), (want ** 2).sum(1)[None], atol=1e-4, rtol=1e-5)
+    torch.testing.assert_close(xw.cpu().float(), (want * nw).to(torch.bfloat16).float(), atol=1e-2, rtol=1e-2)
+    delta = torch.randn(4, 72).to(torch.bfloat16)
+    ss2, xw2 = ops.add_residual_ss(x, dev(delta), dev(nw))
+    want2 = want + delta.float()
+    torch.testing.assert_close(x.cpu(), want2, atol=1e-6, rtol=1e-6)
+    torch.testing.assert_close(ss2.cpu(), (want2 ** 2).sum(1)[None], atol=1e-4, rtol=1e-5)
+    torch.testing.assert_close(xw2.cpu().float(), (want2 * nw).to(torch.bfloat16).float(), atol=2e-2, rtol=1e-2)
 
 
 def test_skinny_linear_refuses_what_it_cannot_do(ops):

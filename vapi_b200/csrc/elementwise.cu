@@ -11,11 +11,13 @@ using namespace vapi;
 
 // ---------------------------------------------------------------------------
 // embedding: out[r, :] = float(table[tokens[r], :])
-// ss (optional): the sum of squares of each produced row, [1][n], for a norm that follows
+// For a norm that follows (optional): ss = the sum of squares of each produced row, [1][n];
+// xw = bfloat16(row * next_w), [n][hidden].
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
-                             float* __restrict__ out, float* __restrict__ ss, int n, int hidden,
-                             int vocab, int* __restrict__ status) {
+                             float* __restrict__ out, float* __restrict__ ss,
+                             const float* __restrict__ next_w, __nv_bfloat16* __restrict__ xw,
+                             int n, int hidden, int vocab, int* __restrict__ status) {
     __shared__ float red[33];
     const int r = blockIdx.x;
     pdl_trigger();
@@ -32,6 +34,7 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         const float v = to_f32(src[c]);
         dst[c] = v;
+        if (xw) xw[(size_t)r * hidden + c] = __float2bfloat16_rn(v * next_w[c]);
         acc += v * v;
     }
     if (ss) {
@@ -41,15 +44,17 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
 }
 
 VAPI_EXPORT int vapi_embed(const void* table, int table_dtype, const int* tokens, float* out,
-                           float* ss, int n, int hidden, int vocab, int* status, cudaStream_t stream) {
+                           float* ss, const float* next_w, void* xw, int n, int hidden, int vocab,
+                           int* status, cudaStream_t stream) {
+    if (xw && !next_w) return fail(-1, "embed: a weighted copy needs the next norm's weight");
     if (n <= 0) return 0;
     if (hidden <= 0 || vocab <= 0) return fail(-1, "embed: bad sizes hidden=%d vocab=%d", hidden, vocab);
     const int threads = hidden >= 1024 ? 256 : 128;
     cudaError_t e;
     if (table_dtype == VAPI_F32)
-        e = launch(embed_kernel<float>, n, threads, 0, stream, (const float*)table, tokens, out, ss, n, hidden, vocab, status);
+        e = launch(embed_kernel<float>, n, threads, 0, stream, (const float*)table, tokens, out, ss, next_w, (__nv_bfloat16*)xw, n, hidden, vocab, status);
     else if (table_dtype == VAPI_BF16)
-        e = launch(embed_kernel<__nv_bfloat16>, n, threads, 0, stream, (const __nv_bfloat16*)table, tokens, out, ss, n, hidden, vocab, status);
+        e = launch(embed_kernel<__nv_bfloat16>, n, threads, 0, stream, (const __nv_bfloat16*)table, tokens, out, ss, next_w, (__nv_bfloat16*)xw, n, hidden, vocab, status);
     else
         return fail(-2, "embed: unsupported table dtype %d", table_dtype);
     return check_launch("embed", e);
@@ -124,10 +129,12 @@ __global__ void add_residual_kernel(float* __restrict__ x, const T* __restrict__
     for (; i < total; i += stride) x[i] += to_f32(delta[i]);
 }
 
-// x[row] += delta[row] and ss[row] = sum of squares of the new row (one block per row)
+// x[row] += delta[row]; ss[row] = sum of squares of the new row; xw = bfloat16(new row * next_w)
+// (one block per row)
 template <typename T>
 __global__ void add_residual_ss_kernel(float* __restrict__ x, const T* __restrict__ delta,
-                                       float* __restrict__ ss, int n, int hidden) {
+                                       float* __restrict__ ss, const float* __restrict__ next_w,
+                                       __nv_bfloat16* __restrict__ xw, int n, int hidden) {
     __shared__ float red[33];
     const int r = blockIdx.x;
     pdl_trigger();
@@ -137,20 +144,23 @@ __global__ void add_residual_ss_kernel(float* __restrict__ x, const T* __restric
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         const float v = x[(size_t)r * hidden + c] + to_f32(delta[(size_t)r * hidden + c]);
         x[(size_t)r * hidden + c] = v;
+        if (xw) xw[(size_t)r * hidden + c] = __float2bfloat16_rn(v * next_w[c]);
         acc += v * v;
     }
     acc = block_sum(acc, red);
     if (threadIdx.x == 0) ss[r] = acc;
 }
 
-VAPI_EXPORT int vapi_add_residual_ss(float* x, const void* delta, int dtype, float* ss, int n,
-                                     int hidden, cudaStream_t stream) {
+VAPI_EXPORT int vapi_add_residual_ss(float* x, const void* delta, int dtype, float* ss,
+                                     const float* next_w, void* xw, int n, int hidden,
+                                     cudaStream_t stream) {
     if (n <= 0) return 0;
+    if (xw && !next_w) return fail(-1, "add_residual_ss: a weighted copy needs the next norm's weight");
     cudaError_t e;
     if (dtype == VAPI_F32)
-        e = launch(add_residual_ss_kernel<float>, n, 256, 0, stream, x, (const float*)delta, ss, n, hidden);
+        e = launch(add_residual_ss_kernel<float>, n, 256, 0, stream, x, (const float*)delta, ss, next_w, (__nv_bfloat16*)xw, n, hidden);
     else if (dtype == VAPI_BF16)
-        e = launch(add_residual_ss_kernel<__nv_bfloat16>, n, 256, 0, stream, x, (const __nv_bfloat16*)delta, ss, n, hidden);
+        e = launch(add_residual_ss_kernel<__nv_bfloat16>, n, 256, 0, stream, x, (const __nv_bfloat16*)delta, ss, next_w, (__nv_bfloat16*)xw, n, hidden);
     else
         return fail(-2, "add_residual_ss: unsupported dtype %d", dtype);
     return check_launch("add_residual_ss", e);

@@ -13,13 +13,15 @@
 //    barrier in the loop.
 //  * the 8 warps of a block split K and add their partial tiles in a fixed order through shared
 //    memory (deterministic: no atomics), then one thread per output applies the epilogue.
-//  * prologue (what the token operand is): bfloat16 activations, or the float residual stream
-//    normalised on the fly (RMSNorm: x * rsqrt(mean x^2 + eps) * w, the mean taken from partial
-//    sums of squares a producer kernel left, summed here in a fixed order).
+//  * prologue (what the token operand is): bfloat16 activations, or the residual stream seen
+//    through an RMSNorm that was not applied yet.  RMSNorm is x * w * rsqrt(mean x^2 + eps): the
+//    last factor is one number per token, so the product runs on bfloat16(x * w), which the
+//    producer of x left beside it, and the epilogue multiplies each token's column by its factor,
+//    taken from the partial sums of squares the producer left (summed here in a fixed order).
 //  * epilogue: bfloat16 out (+bias) | float out (logits) | SwiGLU (a block owns 8 gate rows and
 //    the 8 matching up rows, so silu(gate)*up happens before anything is stored) | add into the
-//    float residual stream (+bias), leaving partial sums of squares of the new stream values
-//    for the norm that follows.
+//    float residual stream (+bias), leaving for the norm that follows the partial sums of squares
+//    of the new stream values and bfloat16(new value * that norm's weight).
 //
 // The reference does these products with cuBLAS and separate norm / SwiGLU / add kernels
 // (crates/vapi-backend-candle/src/models/lfm2.rs:519-534, 591-593, 645-647).
@@ -28,7 +30,10 @@
 using namespace vapi;
 
 constexpr int GV_WARPS = 8;
-constexpr int GV_STAGES = 6;      // depth of the per-lane copy queue (chunks of 32 k)
+#ifndef GV_STAGES_N
+#define GV_STAGES_N 8
+#endif
+constexpr int GV_STAGES = GV_STAGES_N;      // depth of the per-lane copy queue (chunks of 32 k)
 
 enum { GV_PRO_ACT = 0, GV_PRO_NORM = 1 };
 enum { GV_EPI_BF16 = 0, GV_EPI_SWIGLU = 1, GV_EPI_RESID = 2, GV_EPI_F32 = 3 };
@@ -36,12 +41,14 @@ enum { GV_EPI_BF16 = 0, GV_EPI_SWIGLU = 1, GV_EPI_RESID = 2, GV_EPI_F32 = 3 };
 struct GvParams {
     const __nv_bfloat16* W; int N, K, M;
     const __nv_bfloat16* act;                      // PRO_ACT: [M][K]
-    const float* x; const float* ss_in; int ss_parts; const float* norm_w; float eps;   // PRO_NORM
+    const __nv_bfloat16* xw; const float* ss_in; int ss_parts; float eps;   // PRO_NORM: [M][K] stream * norm weight
     __nv_bfloat16* out_bf16; float* out_f32; long long out_stride;
     const float* bias;
     float* resid; float* ss_out;                   // EPI_RESID
+    const float* next_w; __nv_bfloat16* xw_out;    // EPI_RESID: weight of the norm that follows, [M][N] out
     int ff;                                        // EPI_SWIGLU: N == 2*ff
     int rows_per_cta;                              // 16 or 8 (always 8 gate + 8 up for SwiGLU)
+    int num_tiles;                                 // tiles of rows_per_cta weight rows (8 gate/up pairs)
 };
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
@@ -79,9 +86,10 @@ template <int NT, int PRO, int EPI>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 skinny_linear_kernel(const GvParams p) {
     constexpr int SLOTS = gv_slots<NT, PRO>();
+    constexpr int COLS = 8 * NT;
     extern __shared__ __align__(16) unsigned char gv_smem[];
-    __shared__ float red[GV_WARPS][16][8 * NT + 1];
-    __shared__ float inv_s[8 * NT];
+    __shared__ float red[GV_WARPS][16][COLS + 1];
+    __shared__ float inv_s[COLS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int R = p.rows_per_cta;
@@ -90,161 +98,196 @@ skinny_linear_kernel(const GvParams p) {
         reinterpret_cast<uint4*>(gv_smem) + (size_t)GV_WARPS * GV_STAGES * SLOTS * 32);   // PRO_NORM only
     const int pitch = p.K + 32;
 
-    // which weight rows this lane streams: MMA rows g and g + 8
-    long long row_lo, row_hi;
-    bool ok_lo, ok_hi;
-    if (EPI == GV_EPI_SWIGLU) {
-        row_lo = (long long)blockIdx.x * 8 + g;            // gate
-        row_hi = (long long)p.ff + row_lo;                 // up
-        ok_lo = ok_hi = row_lo < p.ff;
-    } else {
-        row_lo = (long long)blockIdx.x * R + g;
-        row_hi = row_lo + 8;
-        ok_lo = row_lo < p.N;
-        ok_hi = R == 16 && row_hi < p.N;
-    }
-
-    pdl_trigger();
+    // A block works through tiles blockIdx.x, blockIdx.x + gridDim.x, ...; a warp owns the
+    // same slice of K in every tile, so its copy queue runs on across tile boundaries.
+    const int my_tiles = (int)blockIdx.x < p.num_tiles ? (p.num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
     const int nchunks = p.K >> 5;
     const int cpw = (nchunks + GV_WARPS - 1) / GV_WARPS;
-    const int c_begin = warp * cpw, c_end = min(nchunks, c_begin + cpw);
-    const __nv_bfloat16* w_lo = p.W + (size_t)(ok_lo ? row_lo : 0) * p.K + 8 * t;
-    const __nv_bfloat16* w_hi = p.W + (size_t)(ok_hi ? row_hi : 0) * p.K + 8 * t;
+    const int c_begin = min(nchunks, warp * cpw), c_end = min(nchunks, c_begin + cpw);
+    const int len = c_end - c_begin;
 
-    auto queue_weights = [&](int c, int stage) {
-        if (c < c_end) {
-            gv_cp16(&fifo[(stage * SLOTS + 0) * 32 + lane], w_lo + ((size_t)c << 5), ok_lo ? 16 : 0);
-            gv_cp16(&fifo[(stage * SLOTS + 1) * 32 + lane], w_hi + ((size_t)c << 5), ok_hi ? 16 : 0);
+    // the two weight rows (MMA rows g and g + 8) this lane streams in a given tile
+    auto rows_of = [&](int tile, long long& row_lo, long long& row_hi, bool& ok_lo, bool& ok_hi) {
+        if (EPI == GV_EPI_SWIGLU) {
+            row_lo = (long long)tile * 8 + g;               // gate
+            row_hi = (long long)p.ff + row_lo;              // up
+            ok_lo = ok_hi = row_lo < p.ff;
+        } else {
+            row_lo = (long long)tile * R + g;
+            row_hi = row_lo + 8;
+            ok_lo = row_lo < p.N;
+            ok_hi = R == 16 && row_hi < p.N;
         }
     };
-    auto queue_acts = [&](int c, int stage) {
-        if (PRO == GV_PRO_ACT && c < c_end) {
+    // the copy queue's own position: tile ordinal and chunk of the next piece to request
+    int q_tile = 0, q_c = c_begin;
+    const __nv_bfloat16 *q_lo = p.W, *q_hi = p.W;
+    int q_lo_bytes = 0, q_hi_bytes = 0;
+    auto queue_enter_tile = [&]() {
+        if (q_tile < my_tiles) {
+            long long row_lo, row_hi;
+            bool ok_lo, ok_hi;
+            rows_of((int)blockIdx.x + q_tile * (int)gridDim.x, row_lo, row_hi, ok_lo, ok_hi);
+            q_lo = p.W + (size_t)(ok_lo ? row_lo : 0) * p.K + 8 * t;
+            q_hi = p.W + (size_t)(ok_hi ? row_hi : 0) * p.K + 8 * t;
+            q_lo_bytes = ok_lo ? 16 : 0;
+            q_hi_bytes = ok_hi ? 16 : 0;
+        }
+    };
+    auto queue_act_chunk = [&](int c, int stage) {
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const int m = nt * 8 + g;
-                const bool ok = m < p.M;
-                gv_cp16(&fifo[(stage * SLOTS + 2 + nt) * 32 + lane],
-                        p.act + (size_t)(ok ? m : 0) * p.K + ((size_t)c << 5) + 8 * t, ok ? 16 : 0);
+        for (int nt = 0; nt < NT; ++nt) {
+            const int m = nt * 8 + g;
+            const bool ok = m < p.M;
+            gv_cp16(&fifo[(stage * SLOTS + 2 + nt) * 32 + lane],
+                    p.act + (size_t)(ok ? m : 0) * p.K + ((size_t)c << 5) + 8 * t, ok ? 16 : 0);
+        }
+    };
+    // request the next chunk's weights (and, in the loop, its activations) into `stage`
+    auto queue_next = [&](int stage, bool with_acts) {
+        if (len > 0 && q_tile < my_tiles) {
+            const size_t k = (size_t)q_c << 5;
+            gv_cp16(&fifo[(stage * SLOTS + 0) * 32 + lane], q_lo + k, q_lo_bytes);
+            gv_cp16(&fifo[(stage * SLOTS + 1) * 32 + lane], q_hi + k, q_hi_bytes);
+            if (PRO == GV_PRO_ACT && with_acts) queue_act_chunk(q_c, stage);
+            if (++q_c == c_end) {
+                q_c = c_begin;
+                ++q_tile;
+                queue_enter_tile();
             }
         }
     };
+
+    pdl_trigger();
+    queue_enter_tile();
     // the weights do not depend on the kernel before this one: start streaming them, then wait
 #pragma unroll
     for (int st = 0; st < GV_STAGES - 1; ++st) {
-        queue_weights(c_begin + st, st);
+        queue_next(st, false);
         gv_commit();
     }
     pdl_wait();
 
     if (PRO == GV_PRO_NORM) {
-        // inverse rms of each token's row from the producer's partial sums, in a fixed order
+        // every token's row (already multiplied by the norm's weight) into shared memory, by
+        // asynchronous copies that overlap the weights already on their way
+        const int k8 = p.K >> 3;
+        for (int idx = threadIdx.x; idx < COLS * k8; idx += GV_WARPS * 32) {
+            const int m = idx / k8, k = (idx - m * k8) << 3;
+            const bool ok = m < p.M;
+            gv_cp16(act_s + (size_t)m * pitch + k, p.xw + (size_t)(ok ? m : 0) * p.K + k, ok ? 16 : 0);
+        }
+        gv_commit();
+        // the token's factor rsqrt(mean x^2 + eps) from the producer's partial sums, in a fixed order
         for (int m = warp; m < p.M; m += GV_WARPS) {
             float s = 0.f;
             for (int i = lane; i < p.ss_parts; i += 32) s += p.ss_in[(size_t)i * p.M + m];
             s = warp_sum(s);
             if (lane == 0) inv_s[m] = rsqrtf(s / (float)p.K + p.eps);
         }
-        __syncthreads();
-        // the normalised tokens, once per block, as bfloat16 rows in shared memory
-        const int k4 = p.K >> 2;
-        for (int idx = threadIdx.x; idx < 8 * NT * k4; idx += GV_WARPS * 32) {
-            const int m = idx / k4, k = (idx - m * k4) << 2;
-            uint2 v = make_uint2(0u, 0u);
-            if (m < p.M) {
-                const float4 xv = *reinterpret_cast<const float4*>(p.x + (size_t)m * p.K + k);
-                const float4 nv = *reinterpret_cast<const float4*>(p.norm_w + k);
-                const float sc = inv_s[m];
-                v.x = pack2(xv.x * sc * nv.x, xv.y * sc * nv.y);
-                v.y = pack2(xv.z * sc * nv.z, xv.w * sc * nv.w);
-            }
-            *reinterpret_cast<uint2*>(act_s + (size_t)m * pitch + k) = v;
-        }
+        gv_wait<0>();
         __syncthreads();
     } else {
+        // activations of the chunks whose weights are already on their way
+        if (len > 0 && my_tiles > 0) {
+            int c = c_begin, tl = 0;
 #pragma unroll
-        for (int st = 0; st < GV_STAGES - 1; ++st) queue_acts(c_begin + st, st);
-        gv_commit();
-    }
-
-    float acc[NT][4];
-#pragma unroll
-    for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-
-    int stage = 0;
-    for (int c = c_begin; c < c_end; ++c) {
-        const int nstage = stage == 0 ? GV_STAGES - 1 : stage - 1;      // (stage + STAGES - 1) % STAGES
-        queue_weights(c + GV_STAGES - 1, nstage);
-        queue_acts(c + GV_STAGES - 1, nstage);
-        gv_commit();
-        if (PRO == GV_PRO_ACT && c == c_begin) gv_wait<1>();            // every group queued before the loop
-        else gv_wait<GV_STAGES - 1>();
-        const uint4 wl = fifo[(stage * SLOTS + 0) * 32 + lane];
-        const uint4 wh = fifo[(stage * SLOTS + 1) * 32 + lane];
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            uint4 av;
-            if (PRO == GV_PRO_ACT) av = fifo[(stage * SLOTS + 2 + nt) * 32 + lane];
-            else av = *reinterpret_cast<const uint4*>(act_s + (size_t)(nt * 8 + g) * pitch + ((size_t)c << 5) + 8 * t);
-            mma16816(acc[nt], wl.x, wh.x, wl.y, wh.y, av.x, av.y);
-            mma16816(acc[nt], wl.z, wh.z, wl.w, wh.w, av.z, av.w);
-        }
-        stage = stage == GV_STAGES - 1 ? 0 : stage + 1;
-    }
-    gv_wait<0>();
-
-    // partial tiles of the 8 warps, added in warp order
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        red[warp][g][nt * 8 + 2 * t] = acc[nt][0];
-        red[warp][g][nt * 8 + 2 * t + 1] = acc[nt][1];
-        red[warp][g + 8][nt * 8 + 2 * t] = acc[nt][2];
-        red[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
-    }
-    __syncthreads();
-    constexpr int COLS = 8 * NT;
-    const int i = threadIdx.x / COLS, m = threadIdx.x - i * COLS;      // MMA row, token
-    float y = 0.f, y2 = 0.f;
-    if (i < 16) {
-#pragma unroll
-        for (int w = 0; w < GV_WARPS; ++w) y += red[w][i][m];
-        if (EPI == GV_EPI_SWIGLU && i < 8) {
-#pragma unroll
-            for (int w = 0; w < GV_WARPS; ++w) y2 += red[w][i + 8][m];
-        }
-    }
-    if (EPI == GV_EPI_SWIGLU) {
-        const long long col = (long long)blockIdx.x * 8 + i;
-        if (i < 8 && m < p.M && col < p.ff) {
-            const float s = y / (1.f + expf(-y));
-            p.out_bf16[(size_t)m * p.out_stride + col] = __float2bfloat16_rn(s * y2);
-        }
-        return;
-    }
-    const long long n = (long long)blockIdx.x * R + i;
-    const bool valid = i < R && n < p.N && m < p.M;
-    if (valid && p.bias) y += p.bias[n];
-    if (EPI == GV_EPI_BF16) {
-        if (valid) p.out_bf16[(size_t)m * p.out_stride + n] = __float2bfloat16_rn(y);
-    } else if (EPI == GV_EPI_F32) {
-        if (valid) p.out_f32[(size_t)m * p.out_stride + n] = y;
-    } else {   // GV_EPI_RESID
-        float v = 0.f;
-        if (valid) {
-            v = p.resid[(size_t)m * p.N + n] + y;
-            p.resid[(size_t)m * p.N + n] = v;
-        }
-        if (p.ss_out) {
-            __syncthreads();                     // everyone has read its sums out of red[]
-            if (i < 16) red[0][i][m] = v * v;
-            __syncthreads();
-            if (threadIdx.x < COLS && threadIdx.x < p.M) {
-                float s = 0.f;
-#pragma unroll
-                for (int r = 0; r < 16; ++r) s += red[0][r][threadIdx.x];
-                p.ss_out[(size_t)blockIdx.x * p.M + threadIdx.x] = s;
+            for (int st = 0; st < GV_STAGES - 1; ++st) {
+                if (tl < my_tiles) queue_act_chunk(c, st);
+                if (++c == c_end) { c = c_begin; ++tl; }
             }
         }
+        gv_commit();
     }
+
+    bool first = true;
+    int stage = 0;
+    for (int ti = 0; ti < my_tiles; ++ti) {
+        const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+        float acc[NT][4];
+#pragma unroll
+        for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+        for (int c = c_begin; c < c_end; ++c) {
+            const int nstage = stage == 0 ? GV_STAGES - 1 : stage - 1;      // (stage + STAGES - 1) % STAGES
+            queue_next(nstage, true);
+            gv_commit();
+            if (PRO == GV_PRO_ACT && first) gv_wait<1>();                   // every group queued before the loop
+            else gv_wait<GV_STAGES - 1>();
+            first = false;
+            const uint4 wl = fifo[(stage * SLOTS + 0) * 32 + lane];
+            const uint4 wh = fifo[(stage * SLOTS + 1) * 32 + lane];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                uint4 av;
+                if (PRO == GV_PRO_ACT) av = fifo[(stage * SLOTS + 2 + nt) * 32 + lane];
+                else av = *reinterpret_cast<const uint4*>(act_s + (size_t)(nt * 8 + g) * pitch + ((size_t)c << 5) + 8 * t);
+                mma16816(acc[nt], wl.x, wh.x, wl.y, wh.y, av.x, av.y);
+                mma16816(acc[nt], wl.z, wh.z, wl.w, wh.w, av.z, av.w);
+            }
+            stage = stage == GV_STAGES - 1 ? 0 : stage + 1;
+        }
+
+        // partial tiles of the 8 warps, added in warp order
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            red[warp][g][nt * 8 + 2 * t] = acc[nt][0];
+            red[warp][g][nt * 8 + 2 * t + 1] = acc[nt][1];
+            red[warp][g + 8][nt * 8 + 2 * t] = acc[nt][2];
+            red[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
+        }
+        __syncthreads();
+        const int i = threadIdx.x / COLS, m = threadIdx.x - i * COLS;      // MMA row, token
+        float y = 0.f, y2 = 0.f;
+        if (i < 16) {
+#pragma unroll
+            for (int w = 0; w < GV_WARPS; ++w) y += red[w][i][m];
+            if (EPI == GV_EPI_SWIGLU && i < 8) {
+#pragma unroll
+                for (int w = 0; w < GV_WARPS; ++w) y2 += red[w][i + 8][m];
+            }
+        }
+        if (PRO == GV_PRO_NORM && m < p.M) {
+            y *= inv_s[m];
+            y2 *= inv_s[m];
+        }
+        if (EPI == GV_EPI_SWIGLU) {
+            const long long col = (long long)tile * 8 + i;
+            if (i < 8 && m < p.M && col < p.ff) {
+                const float sg = y / (1.f + expf(-y));
+                p.out_bf16[(size_t)m * p.out_stride + col] = __float2bfloat16_rn(sg * y2);
+            }
+        } else {
+            const long long n = (long long)tile * R + i;
+            const bool valid = i < R && n < p.N && m < p.M;
+            if (valid && p.bias) y += p.bias[n];
+            if (EPI == GV_EPI_BF16) {
+                if (valid) p.out_bf16[(size_t)m * p.out_stride + n] = __float2bfloat16_rn(y);
+            } else if (EPI == GV_EPI_F32) {
+                if (valid) p.out_f32[(size_t)m * p.out_stride + n] = y;
+            } else {   // GV_EPI_RESID
+                float v = 0.f;
+                if (valid) {
+                    v = p.resid[(size_t)m * p.N + n] + y;
+                    p.resid[(size_t)m * p.N + n] = v;
+                    if (p.xw_out) p.xw_out[(size_t)m * p.N + n] = __float2bfloat16_rn(v * p.next_w[n]);
+                }
+                if (p.ss_out) {
+                    __syncthreads();                     // everyone has read its sums out of red[]
+                    if (i < 16) red[0][i][m] = v * v;
+                    __syncthreads();
+                    if (threadIdx.x < COLS && threadIdx.x < p.M) {
+                        float sq = 0.f;
+#pragma unroll
+                        for (int r = 0; r < 16; ++r) sq += red[0][r][threadIdx.x];
+                        p.ss_out[(size_t)tile * p.M + threadIdx.x] = sq;
+                    }
+                }
+            }
+        }
+        __syncthreads();                                 // red[] is free for the next tile
+    }
+    gv_wait<0>();
 }
 
 template <int NT, int PRO, int EPI>
@@ -256,7 +299,20 @@ static int launch_gv(const GvParams& p, int blocks, cudaStream_t stream) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(-101, "skinny_linear: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
-    return check_launch("skinny_linear", launch(kern, blocks, GV_WARPS * 32, smem, stream, p));
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    // a fixed number of blocks per SM, each walking its share of the tiles
+    static int per_sm = -1;
+    if (per_sm < 0) {
+        const char* e = getenv("VAPI_GV_BLOCKS_PER_SM");
+        per_sm = e ? atoi(e) : 2;
+    }
+    const int cap = per_sm > 0 ? sms * per_sm : blocks;
+    return check_launch("skinny_linear", launch(kern, blocks < cap ? blocks : cap, GV_WARPS * 32, smem, stream, p));
 }
 
 // Number of blocks (and so of partial sums a residual epilogue leaves) for a given shape.
@@ -266,10 +322,10 @@ VAPI_EXPORT int vapi_skinny_linear_blocks(int N, int epi, int rows_per_cta) {
 }
 
 VAPI_EXPORT int vapi_skinny_linear(const void* W, int N, int K, int M, int pro, const void* act,
-                                   const float* x, const float* ss_in, int ss_parts,
-                                   const float* norm_w, float eps, int epi, void* out_bf16,
-                                   float* out_f32, long long out_stride, const float* bias,
-                                   float* resid, float* ss_out, int rows_per_cta,
+                                   const void* xw, const float* ss_in, int ss_parts, float eps,
+                                   int epi, void* out_bf16, float* out_f32, long long out_stride,
+                                   const float* bias, float* resid, float* ss_out,
+                                   const float* next_w, void* xw_out, int rows_per_cta,
                                    cudaStream_t stream) {
     if (M <= 0) return 0;
     if (M > 16) return fail(-1, "skinny_linear: %d rows are more than 16", M);
@@ -277,16 +333,19 @@ VAPI_EXPORT int vapi_skinny_linear(const void* W, int N, int K, int M, int pro, 
     if (rows_per_cta != 8 && rows_per_cta != 16) return fail(-1, "skinny_linear: rows per block must be 8 or 16");
     if (epi == GV_EPI_SWIGLU && N % 2 != 0) return fail(-1, "skinny_linear: SwiGLU needs an even N");
     if (pro == GV_PRO_ACT && !act) return fail(-1, "skinny_linear: no activations");
-    if (pro == GV_PRO_NORM && (!x || !ss_in || !norm_w || ss_parts <= 0)) return fail(-1, "skinny_linear: norm prologue needs x, partial sums and a weight");
+    if (pro == GV_PRO_NORM && (!xw || !ss_in || ss_parts <= 0)) return fail(-1, "skinny_linear: norm prologue needs the weighted stream and its partial sums");
+    if (xw_out && !next_w) return fail(-1, "skinny_linear: a weighted copy of the stream needs the next norm's weight");
     if ((epi == GV_EPI_BF16 || epi == GV_EPI_SWIGLU) && !out_bf16) return fail(-1, "skinny_linear: no output");
     if (epi == GV_EPI_F32 && !out_f32) return fail(-1, "skinny_linear: no output");
     if (epi == GV_EPI_RESID && !resid) return fail(-1, "skinny_linear: no residual stream");
     GvParams p;
     p.W = (const __nv_bfloat16*)W; p.N = N; p.K = K; p.M = M;
-    p.act = (const __nv_bfloat16*)act; p.x = x; p.ss_in = ss_in; p.ss_parts = ss_parts; p.norm_w = norm_w; p.eps = eps;
+    p.act = (const __nv_bfloat16*)act; p.xw = (const __nv_bfloat16*)xw; p.ss_in = ss_in; p.ss_parts = ss_parts; p.eps = eps;
+    p.next_w = next_w; p.xw_out = (__nv_bfloat16*)xw_out;
     p.out_bf16 = (__nv_bfloat16*)out_bf16; p.out_f32 = out_f32; p.out_stride = out_stride; p.bias = bias;
     p.resid = resid; p.ss_out = ss_out; p.ff = N / 2; p.rows_per_cta = epi == GV_EPI_SWIGLU ? 16 : rows_per_cta;
     const int blocks = vapi_skinny_linear_blocks(N, epi, rows_per_cta);
+    p.num_tiles = blocks;
 #define GV_GO(NT, PRO, EPI) return launch_gv<NT, PRO, EPI>(p, blocks, stream)
 #define GV_EPIS(NT, PRO)                                      \
     switch (epi) {                                            \

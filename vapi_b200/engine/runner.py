@@ -165,18 +165,39 @@ class ModelRunner:
     def _forward_few_rows(self, ctx: StepContext, views: List[CacheView]) -> Optional[torch.Tensor]:
         """The same model for a step of at most 16 rows (decode): every block runs in its
         stream form, see :meth:`PreNormBlock.forward_stream`."""
+        from ..parts.base import StreamState
         plan = self.plan
-        x, ss = plan.embedding.forward(ctx, want_ss=True)
-        for i, call in enumerate(plan.order):
+        order = plan.order
+
+        def reader_weight(i: int):
+            """Weight of the norm that reads the stream before run-order entry i (or the final norm)."""
+            if i >= len(order):
+                return plan.final_norm.stream_weight()
+            blk = plan.layers[order[i].layer]
+            return blk.first_norm().stream_weight() if hasattr(blk, "first_norm") else None
+
+        w0 = reader_weight(0)
+        if w0 is not None:
+            x, ss, xw = plan.embedding.forward(ctx, w0)
+            state = StreamState(xw, ss)
+        else:
+            x, state = plan.embedding.forward(ctx), None
+        for i, call in enumerate(order):
             blk = plan.layers[call.layer]
+            nw = reader_weight(i + 1)
             if hasattr(blk, "forward_stream"):
-                ss = blk.forward_stream(x, ss, ctx, views[i])
+                state = blk.forward_stream(x, state, ctx, views[i], nw)
             else:
-                ss = ops.add_residual_ss(x, blk.forward(x, None, ctx, views[i]))
+                delta = blk.forward(x, None, ctx, views[i])
+                if nw is None:
+                    ops.add_residual(x, delta)
+                    state = None
+                else:
+                    state = StreamState(*reversed(ops.add_residual_ss(x, delta, nw)))
         if ctx.logits_rows is None:
             return None
-        if ctx.rows_identity:
-            a = plan.final_norm.deferred(x, ss)
+        if ctx.rows_identity and state is not None:
+            a = plan.final_norm.deferred(state)
             if a is not None:
                 logits = plan.head.forward_stream(a)
                 if logits is not NotImplemented:

@@ -96,30 +96,42 @@ def _f32(t: Optional[torch.Tensor], what: str) -> None:
 
 # ---------------------------------------------------------------------------------------
 def embed(table: torch.Tensor, tokens: torch.Tensor, status: Optional[torch.Tensor] = None,
-          want_ss: bool = False):
+          next_weight: Optional[torch.Tensor] = None):
     """Rows of ``table`` [V, H] for ``tokens`` [n] as the float32 residual stream [n, H].
-    With ``want_ss`` also the sum of squares of every row, [1, n], for a norm that follows."""
-    _cuda(table, tokens)
+
+    With ``next_weight`` (the weight of the norm that will read the stream) the call also
+    returns what a deferred norm needs: the sums of squares of the rows, [1, n], and
+    bfloat16(row * next_weight), [n, H]: ``(x, ss, xw)``."""
+    _cuda(table, tokens, next_weight)
     _contig(table, "embedding table")
     _i32(tokens, "tokens")
+    _f32(next_weight, "norm weight")
     n, (vocab, hidden) = tokens.numel(), table.shape
     out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
-    ss = torch.empty((1, n), dtype=torch.float32, device=table.device) if want_ss else None
+    ss = xw = None
+    if next_weight is not None:
+        ss = torch.empty((1, n), dtype=torch.float32, device=table.device)
+        xw = torch.empty((n, hidden), dtype=torch.bfloat16, device=table.device)
     lib = _lib("elementwise")
-    _check(lib, lib.vapi_embed(_p(table), _dt(table), _p(tokens), _p(out), _p(ss), n, hidden, vocab, _p(status), _stream()))
-    return (out, ss) if want_ss else out
+    _check(lib, lib.vapi_embed(_p(table), _dt(table), _p(tokens), _p(out), _p(ss), _p(next_weight), _p(xw), n,
+                               hidden, vocab, _p(status), _stream()))
+    return (out, ss, xw) if next_weight is not None else out
 
 
-def add_residual_ss(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
-    """``x += delta`` on the float32 stream; returns the sum of squares of every new row, [1, n]."""
-    _cuda(x, delta)
+def add_residual_ss(x: torch.Tensor, delta: torch.Tensor, next_weight: torch.Tensor):
+    """``x += delta`` on the float32 stream; returns ``(ss, xw)`` for the norm that follows:
+    the sums of squares of the new rows, [1, n], and bfloat16(new row * next_weight)."""
+    _cuda(x, delta, next_weight)
     _f32(x, "residual stream")
+    _f32(next_weight, "norm weight")
     _contig(delta, "delta")
     n, hidden = x.shape
     ss = torch.empty((1, n), dtype=torch.float32, device=x.device)
+    xw = torch.empty((n, hidden), dtype=torch.bfloat16, device=x.device)
     lib = _lib("elementwise")
-    _check(lib, lib.vapi_add_residual_ss(_p(x), _p(delta), _dt(delta), _p(ss), n, hidden, _stream()))
-    return ss
+    _check(lib, lib.vapi_add_residual_ss(_p(x), _p(delta), _dt(delta), _p(ss), _p(next_weight), _p(xw), n, hidden,
+                                         _stream()))
+    return ss, xw
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
@@ -192,45 +204,40 @@ def skinny_blocks(n_out: int, epilogue: str, rows_per_block: int = 16) -> int:
     return -(-n_out // rows_per_block)
 
 
-def skinny_rows_per_block(n_out: int) -> int:
-    """16 weight rows a block when that still gives every SM work, else 8."""
-    return 16 if n_out // 16 >= 296 else 8
-
-
 def skinny_linear(weight: torch.Tensor, *, act: Optional[torch.Tensor] = None,
-                  x: Optional[torch.Tensor] = None, ss_in: Optional[torch.Tensor] = None,
-                  norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, epilogue: str = "bf16",
-                  bias: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
-                  ss_out: bool = False, rows_per_block: Optional[int] = None):
+                  xw: Optional[torch.Tensor] = None, ss_in: Optional[torch.Tensor] = None, eps: float = 0.0,
+                  epilogue: str = "bf16", bias: Optional[torch.Tensor] = None,
+                  resid: Optional[torch.Tensor] = None, next_weight: Optional[torch.Tensor] = None,
+                  rows_per_block: Optional[int] = None):
     """The weight-streaming product for decode steps (at most 16 rows), with its fusions.
 
-    Token operand: ``act`` [M, K] bfloat16, or the float32 stream ``x`` [M, K] normalised on
-    the fly with ``norm_weight`` and the partial sums of squares ``ss_in`` [parts, M] that the
-    producer of ``x`` left.  ``epilogue``: "bf16" -> [M, N] bfloat16; "f32" -> [M, N] float32;
-    "swiglu" -> [M, N/2] bfloat16 = silu(first half) * second half; "resid" -> adds into
-    ``resid`` [M, N] in place and returns, when ``ss_out``, the partial sums of squares
-    [blocks, M] of the new stream values (else None).
+    Token operand: ``act`` [M, K] bfloat16; or the residual stream seen through an RMSNorm not
+    applied yet: ``xw`` [M, K] = bfloat16(stream * norm weight) with the partial sums of squares
+    ``ss_in`` [parts, M] of the stream's rows (both left by whoever wrote the stream last) and the
+    norm's ``eps``.  ``epilogue``: "bf16" -> [M, N] bfloat16; "f32" -> [M, N] float32; "swiglu" ->
+    [M, N/2] bfloat16 = silu(first half) * second half; "resid" -> adds into ``resid`` [M, N]
+    float32 in place and returns ``(ss, xw)`` of the new stream for the norm whose weight is
+    ``next_weight`` (``(None, None)`` without it).
     """
-    _cuda(weight, act, x, ss_in, norm_weight, bias, resid)
+    _cuda(weight, act, xw, ss_in, bias, resid, next_weight)
     N, K = weight.shape
     pro = "act" if act is not None else "norm"
-    src = act if act is not None else x
+    src = act if act is not None else xw
+    if src is None:
+        raise KernelError("skinny_linear needs a token operand (act or xw)")
     M = src.shape[0]
     if weight.dtype != torch.bfloat16 or not weight.is_contiguous():
         raise KernelError("skinny_linear needs a contiguous bfloat16 weight")
-    if src.shape[1] != K or not src.is_contiguous():
-        raise KernelError(f"skinny_linear: token operand {tuple(src.shape)} does not fit a weight of {N}x{K}")
-    if pro == "act" and act.dtype != torch.bfloat16:
-        raise KernelError("skinny_linear: activations must be bfloat16")
+    if src.shape[1] != K or not src.is_contiguous() or src.dtype != torch.bfloat16:
+        raise KernelError(f"skinny_linear: token operand {tuple(src.shape)} / {src.dtype} does not fit a weight of {N}x{K}")
     if pro == "norm":
-        _f32(x, "residual stream")
         _f32(ss_in, "partial sums")
-        _f32(norm_weight, "norm weight")
-        if ss_in.dim() != 2 or ss_in.shape[1] != M:
+        if ss_in is None or ss_in.dim() != 2 or ss_in.shape[1] != M:
             raise KernelError("partial sums must be [parts, M]")
     _f32(bias, "bias")
-    rpb = rows_per_block or skinny_rows_per_block(N)
-    out_bf16 = out_f32 = sso = None
+    _f32(next_weight, "norm weight")
+    rpb = rows_per_block or 16
+    out_bf16 = out_f32 = sso = xwo = None
     out_stride = N
     if epilogue == "bf16":
         out_bf16 = torch.empty((M, N), dtype=torch.bfloat16, device=weight.device)
@@ -241,19 +248,20 @@ def skinny_linear(weight: torch.Tensor, *, act: Optional[torch.Tensor] = None,
         out_bf16 = torch.empty((M, N // 2), dtype=torch.bfloat16, device=weight.device)
     elif epilogue == "resid":
         _f32(resid, "residual stream")
-        if tuple(resid.shape) != (M, N):
+        if resid is None or tuple(resid.shape) != (M, N):
             raise KernelError("the residual stream must be [M, N]")
-        if ss_out:
+        if next_weight is not None:
             sso = torch.empty((skinny_blocks(N, epilogue, rpb), M), dtype=torch.float32, device=weight.device)
+            xwo = torch.empty((M, N), dtype=torch.bfloat16, device=weight.device)
     else:
         raise KernelError(f"unknown epilogue {epilogue}")
     lib = _lib("gemv")
     _check(lib, lib.vapi_skinny_linear(
-        _p(weight), N, K, M, _PRO[pro], _p(act), _p(x), _p(ss_in), 0 if ss_in is None else ss_in.shape[0],
-        _p(norm_weight), ctypes.c_float(eps), _EPI[epilogue], _p(out_bf16), _p(out_f32),
-        ctypes.c_longlong(out_stride), _p(bias), _p(resid), _p(sso), rpb, _stream()))
+        _p(weight), N, K, M, _PRO[pro], _p(act), _p(xw), _p(ss_in), 0 if ss_in is None else ss_in.shape[0],
+        ctypes.c_float(eps), _EPI[epilogue], _p(out_bf16), _p(out_f32), ctypes.c_longlong(out_stride), _p(bias),
+        _p(resid), _p(sso), _p(next_weight), _p(xwo), rpb, _stream()))
     if epilogue == "resid":
-        return sso
+        return sso, xwo
     return out_bf16 if out_bf16 is not None else out_f32
 
 

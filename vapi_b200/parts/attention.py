@@ -7,7 +7,7 @@ from typing import Any, Dict, List, Optional
 import torch
 
 from .. import ops
-from .base import CacheView, Mixer, PagedSpec, TensorSpec, register_mixer
+from .base import CacheView, Mixer, PagedSpec, StreamState, TensorSpec, register_mixer
 
 
 class GQAttention(Mixer):
@@ -79,14 +79,14 @@ class GQAttention(Mixer):
         qkv = ops.linear(a, self.w_qkv, self.b_qkv)
         return ops.linear(self._attend(qkv, ctx, cache), self.w_o, self.b_o)
 
-    def forward_stream(self, a, ctx, cache, x):
+    def forward_stream(self, a, ctx, cache, x, next_weight):
         n = x.shape[0]
         if not (ops.skinny_applies(n, self.w_qkv) and ops.skinny_applies(n, self.w_o)):
             return NotImplemented
-        qkv = ops.skinny_linear(self.w_qkv, x=a.x, ss_in=a.ss, norm_weight=a.weight, eps=a.eps,
-                                epilogue="bf16", bias=self.b_qkv)
+        qkv = ops.skinny_linear(self.w_qkv, xw=a.xw, ss_in=a.ss, eps=a.eps, epilogue="bf16", bias=self.b_qkv)
         y = self._attend(qkv, ctx, cache)
-        return ops.skinny_linear(self.w_o, act=y, epilogue="resid", resid=x, bias=self.b_o, ss_out=True)
+        ss, xw = ops.skinny_linear(self.w_o, act=y, epilogue="resid", resid=x, bias=self.b_o, next_weight=next_weight)
+        return StreamState(xw, ss)
 
     def _attend(self, qkv: torch.Tensor, ctx: Any, cache: CacheView) -> torch.Tensor:
         nh, nkv, d = self.nh, self.nkv, self.d

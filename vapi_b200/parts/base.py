@@ -93,19 +93,26 @@ class CacheView:
 
 
 @dataclass
+class StreamState:
+    """What the last writer of the float32 residual stream ``x`` [n, H] left for the norm that
+    reads it next, in steps of a few rows (decode): ``xw`` [n, H] = bfloat16(x * that norm's
+    weight) and ``ss`` [parts, n], partial sums of squares of the rows of ``x``."""
+
+    xw: torch.Tensor
+    ss: torch.Tensor
+
+
+@dataclass
 class NormedStream:
-    """The float32 residual stream seen through a norm that has not been applied yet.
+    """The residual stream seen through a norm that has not been applied yet.
 
     Decode steps are a handful of rows, so a norm of its own costs a launch for almost no
-    work.  In that regime a norm hands its consumer this description instead of a tensor, and
-    the consumer's first matrix product normalises on the fly: ``x`` [n, H] float32, ``ss``
-    [parts, n] partial sums of squares of the rows of ``x`` (whoever last wrote ``x`` left
-    them), the norm's ``weight`` and ``eps``.
-    """
+    work.  RMSNorm is ``x * w * rsqrt(mean x^2 + eps)`` and the last factor is one number per
+    row, so a consumer's first matrix product can run on ``xw`` = bfloat16(x * w) and scale each
+    row of its result by that number, which it gets from ``ss`` and ``eps``."""
 
-    x: torch.Tensor
+    xw: torch.Tensor
     ss: torch.Tensor
-    weight: torch.Tensor
     eps: float
 
 
@@ -133,9 +140,14 @@ class Norm(Part):
         With ``rows`` only those rows are produced and ``x`` is left unchanged."""
         raise NotImplementedError
 
-    def deferred(self, x: torch.Tensor, ss: torch.Tensor) -> Optional[NormedStream]:
-        """This norm of ``x`` as a :class:`NormedStream` for a consumer that applies it
-        itself, or None if the norm cannot be expressed that way."""
+    def stream_weight(self) -> Optional[torch.Tensor]:
+        """The float32 weight vector a producer should multiply the stream by on this norm's
+        behalf (see :class:`StreamState`), or None if this norm cannot be deferred."""
+        return None
+
+    def deferred(self, state: "StreamState") -> Optional[NormedStream]:
+        """This norm as a :class:`NormedStream` for a consumer that applies it itself; ``state``
+        must have been produced with this norm's :meth:`stream_weight`."""
         return None
 
 
@@ -160,10 +172,12 @@ class Mixer(Part):
         contribution to the residual stream, [n, H] in the activation dtype."""
         raise NotImplementedError
 
-    def forward_stream(self, a: NormedStream, ctx: "Any", cache: CacheView, x: torch.Tensor):
+    def forward_stream(self, a: NormedStream, ctx: "Any", cache: CacheView, x: torch.Tensor,
+                       next_weight: torch.Tensor):
         """Optional fast form for steps of a few rows: take the normed input lazily, add the
-        result into the stream ``x`` in place, and return the partial sums of squares
-        [parts, n] of the new ``x``.  Return ``NotImplemented`` to be run the ordinary way."""
+        result into the stream ``x`` in place, and return the :class:`StreamState` of the new
+        ``x`` for the norm whose weight is ``next_weight``.  Return ``NotImplemented`` to be run
+        the ordinary way."""
         return NotImplemented
 
 
@@ -171,7 +185,7 @@ class FeedForward(Part):
     def forward(self, f: torch.Tensor, ctx: "Any") -> torch.Tensor:
         raise NotImplementedError
 
-    def forward_stream(self, f: NormedStream, ctx: "Any", x: torch.Tensor):
+    def forward_stream(self, f: NormedStream, ctx: "Any", x: torch.Tensor, next_weight: torch.Tensor):
         """As :meth:`Mixer.forward_stream`."""
         return NotImplemented
 

@@ -5,7 +5,7 @@ from typing import Any, Callable, Dict, List, Optional
 
 import torch
 
-from .base import CacheView, FeedForward, Mixer, Norm, Part, TensorSpec
+from .base import CacheView, FeedForward, Mixer, Norm, Part, StreamState, TensorSpec
 
 BLOCKS: Dict[str, Callable[..., "Part"]] = {}
 
@@ -54,23 +54,38 @@ class PreNormBlock(Part):
         f = self.ffn_norm.apply(x, d1, ctx.dtype)
         return self.ffn.forward(f, ctx)
 
-    def forward_stream(self, x: torch.Tensor, ss: torch.Tensor, ctx: Any, cache: CacheView) -> torch.Tensor:
-        """The same block for steps of a few rows: norms are applied inside their consumer's
-        first product, results are added into ``x`` by the last product of each part, and the
-        partial sums of squares of ``x`` travel from producer to consumer as ``ss``.  A part
-        without a stream form is run the ordinary way between two small kernels."""
+    def first_norm(self) -> Norm:
+        """The norm that reads the stream first in this block (its producer works for it)."""
+        return self.mixer_norm
+
+    def forward_stream(self, x: torch.Tensor, state: StreamState, ctx: Any, cache: CacheView,
+                       next_weight: torch.Tensor) -> StreamState:
+        """The same block for steps of a few rows: a norm is not run but handed, as a
+        description, to its consumer's first product; each part's last product adds into ``x``
+        and leaves the :class:`StreamState` the following norm needs (``next_weight`` is the
+        weight of the norm that reads the stream after this block).  A part without a stream
+        form is run the ordinary way between two small kernels."""
         from .. import ops
-        a = self.mixer_norm.deferred(x, ss)
-        out = self.mixer.forward_stream(a, ctx, cache, x) if a is not None else NotImplemented
+        mid_weight = self.ffn_norm.stream_weight()
+        a = self.mixer_norm.deferred(state) if state is not None else None
+        out = self.mixer.forward_stream(a, ctx, cache, x, mid_weight) if (a is not None and mid_weight is not None) else NotImplemented
         if out is NotImplemented:
             delta = self.mixer.forward(self.mixer_norm.apply(x, None, ctx.dtype), ctx, cache)
-            out = ops.add_residual_ss(x, delta)
-        f = self.ffn_norm.deferred(x, out)
-        out2 = self.ffn.forward_stream(f, ctx, x) if f is not None else NotImplemented
+            out = self._add(ops, x, delta, mid_weight)
+        f = self.ffn_norm.deferred(out) if out is not None else None
+        out2 = self.ffn.forward_stream(f, ctx, x, next_weight) if (f is not None and next_weight is not None) else NotImplemented
         if out2 is NotImplemented:
             delta = self.ffn.forward(self.ffn_norm.apply(x, None, ctx.dtype), ctx)
-            out2 = ops.add_residual_ss(x, delta)
+            out2 = self._add(ops, x, delta, next_weight)
         return out2
+
+    @staticmethod
+    def _add(ops, x, delta, weight):
+        if weight is None:
+            ops.add_residual(x, delta)
+            return None
+        ss, xw = ops.add_residual_ss(x, delta, weight)
+        return StreamState(xw, ss)
 
 
 register_block("prenorm", PreNormBlock)

@@ -23,8 +23,9 @@ class TokenEmbedding(Part):
     def bind(self, tensors, prefix, dtype):
         self.table = tensors[self.name].contiguous()
 
-    def forward(self, ctx: Any, want_ss: bool = False):
-        return ops.embed(self.table, ctx.tokens, ctx.status, want_ss)
+    def forward(self, ctx: Any, next_weight: Optional[torch.Tensor] = None):
+        """The stream; with ``next_weight`` also what a deferred norm needs: ``(x, ss, xw)``."""
+        return ops.embed(self.table, ctx.tokens, ctx.status, next_weight)
 
 
 class OutputHead(Part):
@@ -53,6 +54,6 @@ class OutputHead(Part):
 
     def forward_stream(self, a):
         """Logits of every row of a lazily normed stream (decode steps), or NotImplemented."""
-        if not ops.skinny_applies(a.x.shape[0], self.weight):
+        if not ops.skinny_applies(a.xw.shape[0], self.weight):
             return NotImplemented
-        return ops.skinny_linear(self.weight, x=a.x, ss_in=a.ss, norm_weight=a.weight, eps=a.eps, epilogue="f32")
+        return ops.skinny_linear(self.weight, xw=a.xw, ss_in=a.ss, eps=a.eps, epilogue="f32")

@@ -6,7 +6,7 @@ from typing import Any, Dict, List, Optional
 import torch
 
 from .. import ops
-from .base import FeedForward, TensorSpec, register_feed_forward
+from .base import FeedForward, StreamState, TensorSpec, register_feed_forward
 
 
 class SwiGLU(FeedForward):
@@ -39,12 +39,13 @@ class SwiGLU(FeedForward):
         g = ops.linear(f, self.w_gate_up)
         return ops.linear(ops.swiglu(g), self.w_down)
 
-    def forward_stream(self, f, ctx, x):
+    def forward_stream(self, f, ctx, x, next_weight):
         n = x.shape[0]
         if not (ops.skinny_applies(n, self.w_gate_up) and ops.skinny_applies(n, self.w_down)):
             return NotImplemented
-        s = ops.skinny_linear(self.w_gate_up, x=f.x, ss_in=f.ss, norm_weight=f.weight, eps=f.eps, epilogue="swiglu")
-        return ops.skinny_linear(self.w_down, act=s, epilogue="resid", resid=x, ss_out=True)
+        s = ops.skinny_linear(self.w_gate_up, xw=f.xw, ss_in=f.ss, eps=f.eps, epilogue="swiglu")
+        ss, xw = ops.skinny_linear(self.w_down, act=s, epilogue="resid", resid=x, next_weight=next_weight)
+        return StreamState(xw, ss)
 
 
 register_feed_forward("swiglu", SwiGLU)

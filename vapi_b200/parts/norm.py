@@ -27,8 +27,11 @@ class RMSNorm(Norm):
     def apply(self, x, delta, dtype, rows=None):
         return ops.add_rmsnorm(x, delta, self.weight, self.eps, dtype, rows)
 
-    def deferred(self, x, ss):
-        return NormedStream(x, ss, self.weight, self.eps)
+    def stream_weight(self):
+        return self.weight
+
+    def deferred(self, state):
+        return NormedStream(state.xw, state.ss, self.eps)
 
 
 register_norm("rmsnorm", RMSNorm)

@@ -6,7 +6,7 @@ from typing import Any, Dict, List, Optional
 import torch
 
 from .. import ops
-from .base import CacheView, Mixer, StateSpec, TensorSpec, register_mixer
+from .base import CacheView, Mixer, StateSpec, StreamState, TensorSpec, register_mixer
 
 
 class ShortConv(Mixer):
@@ -63,14 +63,15 @@ class ShortConv(Mixer):
                           ctx.tok_seq, ctx.cu_q, ctx.positions, ctx.status)
         return ops.linear(y, self.w_out, self.b_out)
 
-    def forward_stream(self, a, ctx, cache, x):
+    def forward_stream(self, a, ctx, cache, x, next_weight):
         n = x.shape[0]
         if not (ops.skinny_applies(n, self.w_in) and ops.skinny_applies(n, self.w_out)):
             return NotImplemented
-        h3 = ops.skinny_linear(self.w_in, x=a.x, ss_in=a.ss, norm_weight=a.weight, eps=a.eps, epilogue="bf16")
+        h3 = ops.skinny_linear(self.w_in, xw=a.xw, ss_in=a.ss, eps=a.eps, epilogue="bf16")
         y = ops.shortconv(h3, self.b_in, self.taps, self.b_conv, cache.tensor, ctx.state_slots,
                           ctx.tok_seq, ctx.cu_q, ctx.positions, ctx.status)
-        return ops.skinny_linear(self.w_out, act=y, epilogue="resid", resid=x, bias=self.b_out, ss_out=True)
+        ss, xw = ops.skinny_linear(self.w_out, act=y, epilogue="resid", resid=x, bias=self.b_out, next_weight=next_weight)
+        return StreamState(xw, ss)
 
 
 register_mixer("shortconv", ShortConv)
