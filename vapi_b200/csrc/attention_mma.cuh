@@ -70,12 +70,15 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
     const int s = blockIdx.z / splits, sp = blockIdx.z - s * splits;
     const int g = blockIdx.y;
     pdl_trigger();
-    pdl_wait();
+    // index data was copied from the host before the step's first kernel: safe before the wait
     const int q0 = cu_q[s], qlen = cu_q[s + 1] - q0, klen = seqlens_k[s];
     const int n_rep = nh / nkv;
     const int rows_total = qlen * n_rep;
     const int tile_start = blockIdx.x * ROWS;
-    if (tile_start >= rows_total) return;
+    if (tile_start >= rows_total) {
+        pdl_wait();
+        return;
+    }
     const int last_row = min(rows_total, tile_start + ROWS) - 1;
     const int base_pos = klen - qlen;
     const int p_min = base_pos + tile_start / n_rep;
@@ -105,23 +108,6 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
     const bool warp_has_rows = w_first < rows_total;
     const int w_pos_min = base_pos + w_first / n_rep;
     const int w_pos_max = base_pos + (min(rows_total, w_first + 16) - 1) / n_rep;
-
-    // Q fragments, kept for the whole kernel
-    unsigned qf[KSTEPS][4];
-#pragma unroll
-    for (int kk = 0; kk < KSTEPS; ++kk) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            unsigned lo = 0u, hi = 0u;
-            if (row_ok[h]) {
-                const __nv_bfloat16* p = q + (size_t)(q0 + row_tok[h]) * q_row_stride + (size_t)row_head[h] * HD + kk * 16 + 2 * tq;
-                lo = *reinterpret_cast<const unsigned*>(p);
-                hi = *reinterpret_cast<const unsigned*>(p + 8);
-            }
-            qf[kk][h] = lo;          // a0 (row g) / a1 (row g+8): columns 2t, 2t+1
-            qf[kk][2 + h] = hi;      // a2 / a3: columns 2t+8, 2t+9
-        }
-    }
 
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o_acc[HD / 8][4];
@@ -153,11 +139,43 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
         }
     };
 
+    // Tiles that hold only keys of earlier steps do not depend on the kernel before this one
+    // (which wrote this step's keys and rotated this step's queries): bring them in first.
+    const int kt_old_end = base_pos / FA_BK;
+    const int pre = max(0, min(min(STAGES - 1, nt), kt_old_end - kt_begin));
 #pragma unroll
     for (int st = 0; st < STAGES - 1; ++st) {
-        if (st < nt) load_tile(kt_begin + st, st);
-        cp_async_commit();
+        if (st < pre) {
+            load_tile(kt_begin + st, st);
+            cp_async_commit();
+        }
     }
+    pdl_wait();
+#pragma unroll
+    for (int st = 0; st < STAGES - 1; ++st) {
+        if (st >= pre) {
+            if (st < nt) load_tile(kt_begin + st, st);
+            cp_async_commit();
+        }
+    }
+
+    // Q fragments, kept for the whole kernel
+    unsigned qf[KSTEPS][4];
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            unsigned lo = 0u, hi = 0u;
+            if (row_ok[h]) {
+                const __nv_bfloat16* p = q + (size_t)(q0 + row_tok[h]) * q_row_stride + (size_t)row_head[h] * HD + kk * 16 + 2 * tq;
+                lo = *reinterpret_cast<const unsigned*>(p);
+                hi = *reinterpret_cast<const unsigned*>(p + 8);
+            }
+            qf[kk][h] = lo;          // a0 (row g) / a1 (row g+8): columns 2t, 2t+1
+            qf[kk][2 + h] = hi;      // a2 / a3: columns 2t+8, 2t+9
+        }
+    }
+
 
     for (int it = 0; it < nt; ++it) {
         cp_async_wait<STAGES - 2>();

@@ -25,8 +25,10 @@ CSRC_DIR = os.path.dirname(os.path.abspath(__file__))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC",
                 "-Xcompiler", "-fvisibility=hidden"]
-#: extra nvcc flags and libraries per source
+#: extra nvcc flags and libraries per source; VAPI_NVCC_FLAGS adds flags to every source
+#: (tuning experiments: e.g. -DGV_STAGES_N=6)
 EXTRA: Dict[str, List[str]] = {}
+_ENV_FLAGS = os.environ.get("VAPI_NVCC_FLAGS", "").split()
 
 
 class BuildError(RuntimeError):
@@ -72,7 +74,7 @@ def _digest(name: str) -> str:
         with open(path, "rb") as f:
             h.update(f.read())
         h.update(b"\0")
-    h.update(" ".join(ARCH_FLAGS + COMMON_FLAGS + EXTRA.get(name, [])).encode())
+    h.update(" ".join(ARCH_FLAGS + COMMON_FLAGS + EXTRA.get(name, []) + _ENV_FLAGS).encode())
     return h.hexdigest()[:12]
 
 
@@ -124,7 +126,7 @@ def build(name: str, verbose: bool = True) -> str:
     out_dir = _writable_dir()
     out = os.path.join(out_dir, f"lib{name}-{_digest(name)}.so")
     tmp = out + f".tmp{os.getpid()}"
-    cmd = [nvcc] + ARCH_FLAGS + COMMON_FLAGS + ["-I", CSRC_DIR] + EXTRA.get(name, []) + ["-o", tmp, src]
+    cmd = [nvcc] + ARCH_FLAGS + COMMON_FLAGS + ["-I", CSRC_DIR] + EXTRA.get(name, []) + _ENV_FLAGS + ["-o", tmp, src]
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
     if verbose:
@@ -152,7 +154,7 @@ def build(name: str, verbose: bool = True) -> str:
             pass
         raise BuildError(f"nvcc failed on {name}.cu:\n{' '.join(cmd)}\n{log.decode(errors='replace')}")
     os.replace(tmp, out)
-    for old in os.listdir(out_dir):          # earlier builds of this source are of no use any more
+    for old in ([] if _ENV_FLAGS else os.listdir(out_dir)):          # earlier builds of this source are of no use any more
         if old.startswith(f"lib{name}-") and old.endswith(".so") and os.path.join(out_dir, old) != out:
             try:
                 os.remove(os.path.join(out_dir, old))

@@ -56,9 +56,13 @@ __global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __re
     const int heads = nh + 2 * nkv;
     const long long item = (long long)blockIdx.x * QK_WARPS + warp;
     pdl_trigger();
-    pdl_wait();
-    if (item >= (long long)n * heads) return;
+    if (item >= (long long)n * heads) {
+        pdl_wait();
+        return;
+    }
     const int t = (int)(item / heads), h = (int)(item - (long long)t * heads);
+    const int slot_pre = (cache && h >= nh) ? slot_mapping[t] : 0;     // host-copied index data: safe before the wait
+    pdl_wait();
     T* src = qkv + (size_t)t * heads * d + (size_t)h * d;
     const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
     const float* w = is_q ? qw : (is_k ? kw : nullptr);
@@ -82,7 +86,7 @@ __global__ void qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __re
     if (is_q) {
         dst = src;
     } else if (cache) {
-        const int slot = slot_mapping[t];
+        const int slot = slot_pre;
         const int page = slot / page_size, off = slot - page * page_size;
         if (slot < 0 || page >= num_pages) {
             if (lane == 0 && status) atomicExch(status, 2);

@@ -49,29 +49,38 @@ __device__ __forceinline__ void block_argmax(float& bv, unsigned& bi, float* sv,
     }
 }
 
-// One block per row.  mode[row]: 0 = skip (out untouched), 1 = greedy, 2 = Gumbel-max.
-// mode == nullptr: every row greedy.
+// mode[row]: 0 = skip (out untouched), 1 = greedy, 2 = Gumbel-max; mode == nullptr: all greedy.
+// A row of logits is cut into gridDim.y slices; each block finds the best (value, id) of its
+// slice; the block that finishes a row last (a counter per row) reduces the slices in slice
+// order, so the result does not depend on which block that is.
+constexpr int SAMPLE_MAX_SLICES = 32;
+
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
                    const int* __restrict__ mode, const float* __restrict__ inv_t,
                    const unsigned long long* __restrict__ seeds,
-                   const unsigned long long* __restrict__ draws, int* __restrict__ out) {
+                   const unsigned long long* __restrict__ draws, int* __restrict__ out,
+                   float* __restrict__ part_v, unsigned* __restrict__ part_i,
+                   unsigned* __restrict__ counters) {
     __shared__ float sv[32];
     __shared__ unsigned si[32];
-    const int row = blockIdx.x;
+    __shared__ bool last;
+    const int row = blockIdx.x, slice = blockIdx.y, slices = gridDim.y;
     pdl_trigger();
     pdl_wait();
     const int md = mode ? mode[row] : 1;
     if (md == 0) return;
     const float* l = logits + (size_t)row * row_stride;
+    const unsigned per = ((unsigned)vocab + slices - 1) / slices;
+    const unsigned lo = slice * per, hi = min((unsigned)vocab, lo + per);
     float bv = -INFINITY;
     unsigned bi = 0xffffffffu;
     if (md == 1) {
-        for (unsigned i = threadIdx.x; i < (unsigned)vocab; i += blockDim.x) arg_better(bv, bi, l[i], i);
+        for (unsigned i = lo + threadIdx.x; i < hi; i += blockDim.x) arg_better(bv, bi, l[i], i);
     } else {
         const float it = inv_t[row];
         const unsigned long long key = mix64(seeds[row] ^ mix64(draws[row] + 0x9E3779B97F4A7C15ULL));
-        for (unsigned i = threadIdx.x; i < (unsigned)vocab; i += blockDim.x) {
+        for (unsigned i = lo + threadIdx.x; i < hi; i += blockDim.x) {
             const unsigned long long h = mix64(key + (unsigned long long)i * 0xBF58476D1CE4E5B9ULL);
             const float u = ((float)(h >> 40) + 0.5f) * (1.0f / 16777216.0f);
             const float g = -logf(-logf(u));
@@ -79,19 +88,46 @@ sample_rows_kernel(const float* __restrict__ logits, int vocab, long long row_st
         }
     }
     block_argmax(bv, bi, sv, si);
-    if (threadIdx.x == 0) out[row] = bi == 0xffffffffu ? 0 : (int)bi;
+    if (slices == 1) {
+        if (threadIdx.x == 0) out[row] = bi == 0xffffffffu ? 0 : (int)bi;
+        return;
+    }
+    if (threadIdx.x == 0) {
+        part_v[(size_t)row * slices + slice] = bv;
+        part_i[(size_t)row * slices + slice] = bi;
+        __threadfence();
+        last = atomicAdd(&counters[row], 1u) == (unsigned)slices - 1;
+    }
+    __syncthreads();
+    if (!last) return;
+    if (threadIdx.x == 0) {
+        __threadfence();
+        float fv = -INFINITY;
+        unsigned fi = 0xffffffffu;
+        for (int sidx = 0; sidx < slices; ++sidx)
+            arg_better(fv, fi, part_v[(size_t)row * slices + sidx], part_i[(size_t)row * slices + sidx]);
+        out[row] = fi == 0xffffffffu ? 0 : (int)fi;
+        counters[row] = 0;                      // ready for the next call
+    }
 }
 
+// scratch: rows * slices floats + rows * slices + rows unsigned (the counters must be zero at
+// the first call; every call leaves them zero)
 VAPI_EXPORT int vapi_sample_rows(const float* logits, int rows, int vocab, long long row_stride,
                                  const int* mode, const float* inv_t,
                                  const unsigned long long* seeds,
-                                 const unsigned long long* draws, int* out, cudaStream_t stream) {
+                                 const unsigned long long* draws, int* out, int slices,
+                                 float* part_v, unsigned* part_i, unsigned* counters,
+                                 cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return fail(-1, "sample_rows: vocab=%d", vocab);
     if (mode && (!inv_t || !seeds || !draws))
         return fail(-1, "sample_rows: per-row modes need temperatures, seeds and draw counters");
-    return check_launch("sample_rows", launch(sample_rows_kernel, rows, SAMPLE_THREADS, 0, stream,
-                                                logits, vocab, row_stride, mode, inv_t, seeds, draws, out));
+    if (slices < 1 || slices > SAMPLE_MAX_SLICES) return fail(-1, "sample_rows: %d slices are outside 1..%d", slices, SAMPLE_MAX_SLICES);
+    if (slices > 1 && (!part_v || !part_i || !counters)) return fail(-1, "sample_rows: slices need scratch");
+    return check_launch("sample_rows", launch(sample_rows_kernel, dim3(rows, slices), SAMPLE_THREADS, 0, stream,
+                                                logits, vocab, row_stride, mode, inv_t, seeds, draws, out,
+                                                part_v, part_i, counters));
 }
 
 // Penalties on (row, token) pairs, in place

@@ -56,14 +56,35 @@ __global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restri
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int r = blockIdx.x;
     pdl_trigger();
-    pdl_wait();
-    if (c >= hidden || r >= n) return;
+    if (c >= hidden || r >= n) {
+        pdl_wait();
+        return;
+    }
+    // Everything read up to pdl_wait() was written before this step's first kernel began
+    // (index data copied from the host, weights, the state the previous step left), so it can
+    // be fetched while the kernel before this one is still finishing.
     const int s = tok_seq[r];
     const int r0 = cu_q[s], q = cu_q[s + 1] - r0;
     const int i = r - r0;
     float w[CONV_LMAX];
 #pragma unroll
     for (int k = 0; k < CONV_LMAX; ++k) w[k] = k < L ? taps[(size_t)k * hidden + c] : 0.f;
+    int slot = -1, p0 = 0;
+    float hist[CONV_LMAX];
+#pragma unroll
+    for (int j = 0; j < CONV_LMAX; ++j) hist[j] = 0.f;
+    if (i == 0 && L > 1) {
+        slot = state_slots[s];
+        p0 = positions[r];
+        if (slot >= 0 && slot < num_slots) {
+            const T* st0 = state + (size_t)slot * slot_stride;
+            // hist[0 .. L-2] = g at positions p0-(L-1) .. p0-1; hist[L-1] = the current token
+#pragma unroll
+            for (int j = 0; j < CONV_LMAX; ++j)
+                if (j < L - 1 && p0 - (L - 1) + j >= 0) hist[j] = to_f32(st0[(size_t)j * hidden + c]);
+        }
+    }
+    pdl_wait();
 
     if (i >= L - 1) {
         // every tap lies inside this step's rows
@@ -76,20 +97,11 @@ __global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restri
     }
     if (i != 0) return;  // tokens 1 .. L-2 of a portion belong to the thread of token 0
 
-    const int slot = state_slots[s];
     if (slot < 0 || slot >= num_slots) {
         if (status) atomicExch(status, 3);
         return;
     }
     T* st = state + (size_t)slot * slot_stride;
-    const int p0 = positions[r];
-    // hist[0 .. L-2] = g at positions p0-(L-1) .. p0-1; hist[L-1] = the current token
-    float hist[CONV_LMAX];
-#pragma unroll
-    for (int j = 0; j < CONV_LMAX; ++j) {
-        hist[j] = 0.f;
-        if (j < L - 1 && p0 - (L - 1) + j >= 0) hist[j] = to_f32(st[(size_t)j * hidden + c]);
-    }
     const int m = q < L - 1 ? q : L - 1;
     for (int ii = 0; ii < m; ++ii) {
         const float g = gate_row(h3, in_bias, (size_t)(r + ii), c, hidden);

@@ -444,6 +444,23 @@ def shortconv(h3: torch.Tensor, in_bias: Optional[torch.Tensor], taps: torch.Ten
     return out
 
 
+_sample_bufs: Dict[str, Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
+
+
+def _sample_scratch(device, rows: int, slices: int):
+    """Persistent scratch of the sliced argmax (the counters start at zero and every launch
+    leaves them zero, so the buffer must not be handed out fresh each call)."""
+    key = str(device)
+    buf = _sample_bufs.get(key)
+    need = rows * slices
+    if buf is None or buf[0].numel() < need or buf[2].numel() < rows:
+        cap_r, cap = max(rows, 256), max(need, 256 * 32)
+        buf = (torch.empty(cap, dtype=torch.float32, device=device), torch.empty(cap, dtype=torch.int32, device=device),
+               torch.zeros(cap_r, dtype=torch.int32, device=device))
+        _sample_bufs[key] = buf
+    return buf
+
+
 def sample_rows(logits: torch.Tensor, mode: Optional[torch.Tensor] = None,
                 inv_t: Optional[torch.Tensor] = None, seeds: Optional[torch.Tensor] = None,
                 draws: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -460,9 +477,17 @@ def sample_rows(logits: torch.Tensor, mode: Optional[torch.Tensor] = None,
     rows, vocab = logits.shape
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    # few rows over a large vocabulary: cut each row into slices so that more than `rows` blocks work
+    slices = 1
+    if rows < 148 and vocab >= 8192:
+        slices = max(1, min(32, 148 // rows, vocab // 4096))
+    part_v = part_i = counters = None
+    if slices > 1:
+        part_v, part_i, counters = _sample_scratch(logits.device, rows, slices)
     lib = _lib("sampling")
     _check(lib, lib.vapi_sample_rows(_p(logits), rows, vocab, ctypes.c_longlong(logits.stride(0)), _p(mode),
-                                     _p(inv_t), _p(seeds), _p(draws), _p(out), _stream()))
+                                     _p(inv_t), _p(seeds), _p(draws), _p(out), slices, _p(part_v), _p(part_i),
+                                     _p(counters), _stream()))
     return out
 
 
