@@ -4,6 +4,8 @@ import sys
 import pytest
 import torch
 
+os.environ.setdefault("VAPI_VALIDATE", "1")      # every batch of every test is checked on the host
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)

@@ -40,12 +40,12 @@ class LLM:
                  cuda_graphs: bool = True, max_concurrent_seqs: int = 64, max_batched_tokens: int = 8192,
                  prefill_chunk_tokens: int = 2048, watermark: float = 0.01, max_step_failures: int = 3,
                  random_weights: Optional[int] = None, config_json: Optional[Dict[str, Any]] = None,
-                 page_size: Optional[int] = None):
+                 page_size: Optional[int] = None, validate: bool = False):
         dt = "float32" if str(dtype).lower() in ("f32", "fp32", "float32") else "bfloat16"
         kw = dict(dtype=dt, device=device, page_size=page_size or ModelRunner.default_page_size,
                   num_pages=num_blocks, max_requests=max_concurrent_seqs,
                   max_batched_tokens=max_batched_tokens, max_context=max_context, watermark=watermark,
-                  kv_cache_fraction=kv_cache_fraction)
+                  kv_cache_fraction=kv_cache_fraction, validate=validate)
         if random_weights is not None:
             if config_json is None:
                 raise ValueError("random weights need a config_json (the architecture's config.json keys)")

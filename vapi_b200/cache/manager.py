@@ -26,6 +26,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..parts.base import CacheView, PagedSpec, StateSpec
@@ -60,6 +61,13 @@ class RequestCache:
     first_live: List[int]           # per paged group: first logical page still held
     num_tokens: int = 0             # positions computed so far
     closed: bool = False
+    # per paged group, the same table as an int32 array for the step packer (released pages
+    # read 0, a valid id no kernel follows); grown in place, `tables` stays the truth
+    tables_np: List[np.ndarray] = field(default_factory=list)
+
+    def table_row(self, group: int, width: int) -> np.ndarray:
+        n = min(width, len(self.tables[group]))
+        return self.tables_np[group][:n]
 
 
 class CacheManager:
@@ -151,7 +159,8 @@ class CacheManager:
         if request_id in self._live:
             raise ValueError(f"request {request_id!r} is already live")
         slot = self.slots.acquire()
-        rc = RequestCache(request_id, slot, [[] for _ in self.paged], [0 for _ in self.paged])
+        rc = RequestCache(request_id, slot, [[] for _ in self.paged], [0 for _ in self.paged],
+                          tables_np=[np.zeros(16, dtype=np.int32) for _ in self.paged])
         self._live[request_id] = rc
         return rc
 
@@ -184,7 +193,14 @@ class CacheManager:
                 return False
         for gi, (g, n) in enumerate(zip(self.paged, need)):
             for _ in range(n):
-                rc.tables[gi].append(g.pool.allocate())
+                page = g.pool.allocate()
+                k = len(rc.tables[gi])
+                if k >= rc.tables_np[gi].size:
+                    grown = np.zeros(max(2 * rc.tables_np[gi].size, k + 1), dtype=np.int32)
+                    grown[:k] = rc.tables_np[gi][:k]
+                    rc.tables_np[gi] = grown
+                rc.tables_np[gi][k] = page
+                rc.tables[gi].append(page)
         return True
 
     def commit(self, rc: RequestCache, total: int) -> None:
@@ -204,6 +220,7 @@ class CacheManager:
                     break
                 g.pool.free(rc.tables[gi][pi])
                 rc.tables[gi][pi] = -1
+                rc.tables_np[gi][pi] = 0
                 rc.first_live[gi] = pi + 1
 
     def close(self, rc: RequestCache) -> None:

@@ -12,6 +12,7 @@ It corresponds to the reference's ``ExecutionBackend::forward`` over
 """
 from __future__ import annotations
 
+import os
 from typing import Any, Dict, List, Optional, Sequence
 
 import torch
@@ -56,7 +57,9 @@ class ModelRunner:
         self.vocab_size = plan.vocab_size
         self.max_context = min(int(max_context or plan.max_positions), plan.max_positions)
         self.max_batched_tokens = int(max_batched_tokens)
-        self.validate = validate
+        # checking every batch on the host is a debugging aid (the reference does it in debug
+        # builds, crates/vapi-backend-candle/src/backend.rs:486-487); VAPI_VALIDATE=1 forces it
+        self.validate = bool(validate) or os.environ.get("VAPI_VALIDATE") == "1"
         sites = plan.cache_sites()
         if num_pages is None:
             num_pages = self._pages_from_memory(sites, page_size, max_requests, kv_cache_fraction)

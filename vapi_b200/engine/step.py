@@ -196,10 +196,13 @@ class StepPacker:
             rows.extend(pos_n + int(w) for w in e.want)
             for g in range(self.G):
                 tb = e.cache.tables[g]
-                slots[g].extend(tb[p // P] * P + p % P for p in range(st, st + q))
-                row = [max(p, 0) for p in tb[:w_c]]
+                if q == 1:
+                    slots[g].append(tb[st // P] * P + st % P)
+                else:
+                    slots[g].extend(tb[p // P] * P + p % P for p in range(st, st + q))
+                row = e.cache.table_row(g, w_c)
                 o = lay[f"table{g}"] + si * w_c
-                hb[o:o + len(row)] = row
+                hb[o:o + row.size] = row
             hb[lay["seqlens_k"] + si] = st + q
             hb[lay["state_slots"] + si] = e.cache.slot
             pos_n += q
