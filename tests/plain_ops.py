@@ -33,6 +33,14 @@ def skinny_applies(rows, weight):
     return False
 
 
+def tc_applies(rows, weight):
+    return False
+
+
+def few_rows_applies(rows, weight):
+    return False
+
+
 def add_rmsnorm(x, delta, weight, eps, out_dtype, rows=None):
     """crates/vapi-backend-candle/src/models/lfm2.rs:633-648: residual add, then RMSNorm."""
     if rows is None:
@@ -223,6 +231,6 @@ def apply_penalties(logits, rows, toks, counts, rep, freq, pres):
         logits[r, t] = v
 
 
-ALL = ["embed", "add_rmsnorm", "add_residual", "add_residual_ss", "skinny_applies", "swiglu", "linear", "strict_fp32", "rope_cos_sin",
+ALL = ["embed", "add_rmsnorm", "add_residual", "add_residual_ss", "skinny_applies", "tc_applies", "few_rows_applies", "swiglu", "linear", "strict_fp32", "rope_cos_sin",
        "qk_norm_rope_write", "attention_splits", "paged_attention", "shortconv", "sample_rows",
        "apply_penalties"]

@@ -440,3 +440,58 @@ def test_skinny_linear_refuses_what_it_cannot_do(ops):
     with pytest.raises(ops.KernelError, match="more than 16"):
         ops.skinny_linear(w, act=torch.zeros(17, 96, dtype=torch.bfloat16).cuda(), epilogue="bf16")
     assert not ops.skinny_applies(17, w) and not ops.skinny_applies(4, w.float()) and ops.skinny_applies(4, w)
+
+
+# ---- the tcgen05 / TMA product of steps of 17..256 rows -------------------------------------
+@pytest.mark.parametrize("M", [17, 32, 64, 100, 256])
+@pytest.mark.parametrize("N,K", [(200, 96), (2048, 2048), (1000, 328), (384, 8192)])
+def test_linear_tc_plain_products(ops, M, N, K):
+    """Tiles that are not full (N no multiple of 128), K that is no multiple of 64, few tiles
+    (split over K with the last-arriver sum), token counts that are not a power of two."""
+    torch.manual_seed(30)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    b = torch.randn(N)
+    want = a.float() @ w.float().t()
+    st = torch.zeros(1, dtype=torch.int32).cuda()
+    got = ops.linear_tc(dev(w), act=dev(a), epilogue="f32", status=st)
+    assert int(st.item()) == 0, "a bounded wait ran out"
+    torch.testing.assert_close(got.cpu(), want, atol=3e-3 * math.sqrt(K / 96), rtol=1e-3)
+    got = ops.linear_tc(dev(w), act=dev(a), epilogue="bf16", bias=dev(b), status=st)
+    torch.testing.assert_close(got.cpu().float(), (want + b).to(torch.bfloat16).float(), atol=3e-2 * math.sqrt(K / 96), rtol=2e-2)
+    again = ops.linear_tc(dev(w), act=dev(a), epilogue="bf16", bias=dev(b), status=st)
+    assert torch.equal(got, again), "the split-K sum must not depend on arrival order"
+    assert int(st.item()) == 0
+    before = ops.launch_count
+    got = ops.linear(dev(a), dev(w), None, torch.float32)
+    assert ops.launch_count == before + 1
+    torch.testing.assert_close(got.cpu(), want, atol=3e-3 * math.sqrt(K / 96), rtol=1e-3)
+
+
+@pytest.mark.parametrize("M", [24, 64, 130])
+def test_linear_tc_fusions(ops, M):
+    torch.manual_seed(31)
+    H, F, eps = 256, 328, 1e-6
+    x = torch.randn(M, H) * 2
+    nw = 1 + 0.1 * torch.randn(H)
+    w13 = (torch.randn(2 * F, H) * 0.1).to(torch.bfloat16)
+    w2 = (torch.randn(H, F) * 0.1).to(torch.bfloat16)
+    parts = torch.stack([(x[:, i * 64:(i + 1) * 64] ** 2).sum(1) for i in range(4)]).contiguous()
+    xw = (x * nw).to(torch.bfloat16)
+    st = torch.zeros(1, dtype=torch.int32).cuda()
+    s = ops.linear_tc(dev(w13), xw=dev(xw), ss_in=dev(parts), eps=eps, epilogue="swiglu", status=st)
+    inv = torch.rsqrt((x ** 2).mean(1, keepdim=True) + eps)
+    gu = (xw.float() @ w13.float().t()) * inv
+    want_s = (gu[:, :F] / (1 + torch.exp(-gu[:, :F]))) * gu[:, F:]
+    torch.testing.assert_close(s.cpu().float(), want_s.to(torch.bfloat16).float(), atol=4e-2, rtol=3e-2)
+    s2 = torch.randn(M, F).to(torch.bfloat16)
+    bias, nw2 = torch.randn(H), 1 + 0.1 * torch.randn(H)
+    xr = dev(x.clone())
+    ss, xw2 = ops.linear_tc(dev(w2), act=dev(s2), epilogue="resid", resid=xr, bias=dev(bias), next_weight=dev(nw2), status=st)
+    want_x = x + s2.float() @ w2.float().t() + bias
+    torch.testing.assert_close(xr.cpu(), want_x, atol=3e-3, rtol=1e-3)
+    torch.testing.assert_close(ss.sum(0).cpu(), (want_x ** 2).sum(1), atol=2e-2, rtol=1e-3)
+    torch.testing.assert_close(xw2.cpu().float(), (want_x * nw2).to(torch.bfloat16).float(), atol=3e-2, rtol=2e-2)
+    lg = ops.linear_tc(dev(w13), xw=dev(xw), ss_in=dev(parts), eps=eps, epilogue="f32", status=st)
+    torch.testing.assert_close(lg.cpu(), (xw.float() @ w13.float().t()) * inv, atol=3e-3, rtol=1e-3)
+    assert int(st.item()) == 0

@@ -265,6 +265,106 @@ def skinny_linear(weight: torch.Tensor, *, act: Optional[torch.Tensor] = None,
     return out_bf16 if out_bf16 is not None else out_f32
 
 
+TC_MAX_ROWS = 256
+#: set False to keep products of 17..256 rows on the library
+use_tc = os.environ.get("VAPI_TC", "1") != "0"
+_tc_bufs: Dict[str, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def tc_applies(rows: int, weight: torch.Tensor) -> bool:
+    """Whether the tcgen05 kernel takes this product: bfloat16 weight, 17..256 rows, inner size
+    a multiple of 8 (16-byte rows for TMA)."""
+    return (use_tc and weight.is_cuda and weight.dtype == torch.bfloat16 and SKINNY_MAX_ROWS < rows <= TC_MAX_ROWS
+            and weight.dim() == 2 and weight.shape[1] % 8 == 0 and weight.is_contiguous())
+
+
+def _tc_plan(N: int, K: int, M: int, epi: int):
+    lib = _lib("linear_tc")
+    t, s, b, need = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_longlong()
+    lib.vapi_linear_tc_plan(N, K, M, epi, ctypes.byref(t), ctypes.byref(s), ctypes.byref(b), ctypes.byref(need))
+    return t.value, s.value, b.value, need.value
+
+
+def _tc_scratch(device, floats: int, tiles: int):
+    """Persistent scratch of the split-K reduction (counters start at zero, every launch leaves
+    them zero)."""
+    key = str(device)
+    buf = _tc_bufs.get(key)
+    if buf is None or buf[0].numel() < floats or buf[1].numel() < tiles:
+        buf = (torch.empty(max(floats, 8 << 20), dtype=torch.float32, device=device),
+               torch.zeros(max(tiles, 4096), dtype=torch.int32, device=device))
+        _tc_bufs[key] = buf
+    return buf
+
+
+def linear_tc(weight: torch.Tensor, *, act: Optional[torch.Tensor] = None, xw: Optional[torch.Tensor] = None,
+              ss_in: Optional[torch.Tensor] = None, eps: float = 0.0, epilogue: str = "bf16",
+              bias: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
+              next_weight: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None):
+    """The tcgen05 / TMA product for 17..256 rows; same operands, epilogues and results as
+    :func:`skinny_linear`."""
+    _cuda(weight, act, xw, ss_in, bias, resid, next_weight)
+    N, K = weight.shape
+    pro = "act" if act is not None else "norm"
+    src = act if act is not None else xw
+    if src is None:
+        raise KernelError("linear_tc needs a token operand (act or xw)")
+    M = src.shape[0]
+    if weight.dtype != torch.bfloat16 or not weight.is_contiguous():
+        raise KernelError("linear_tc needs a contiguous bfloat16 weight")
+    if src.shape[1] != K or not src.is_contiguous() or src.dtype != torch.bfloat16:
+        raise KernelError(f"linear_tc: token operand {tuple(src.shape)} / {src.dtype} does not fit a weight of {N}x{K}")
+    if pro == "norm":
+        _f32(ss_in, "partial sums")
+        if ss_in is None or ss_in.dim() != 2 or ss_in.shape[1] != M:
+            raise KernelError("partial sums must be [parts, M]")
+    _f32(bias, "bias")
+    _f32(next_weight, "norm weight")
+    tiles, splits, bn, need = _tc_plan(N, K, M, _EPI[epilogue])
+    out_bf16 = out_f32 = sso = xwo = scratch = counters = None
+    out_stride = N
+    if epilogue == "bf16":
+        out_bf16 = torch.empty((M, N), dtype=torch.bfloat16, device=weight.device)
+    elif epilogue == "f32":
+        out_f32 = torch.empty((M, N), dtype=torch.float32, device=weight.device)
+    elif epilogue == "swiglu":
+        out_stride = N // 2
+        out_bf16 = torch.empty((M, N // 2), dtype=torch.bfloat16, device=weight.device)
+    elif epilogue == "resid":
+        _f32(resid, "residual stream")
+        if resid is None or tuple(resid.shape) != (M, N):
+            raise KernelError("the residual stream must be [M, N]")
+        if next_weight is not None:
+            sso = torch.empty((tiles, M), dtype=torch.float32, device=weight.device)
+            xwo = torch.empty((M, N), dtype=torch.bfloat16, device=weight.device)
+    else:
+        raise KernelError(f"unknown epilogue {epilogue}")
+    if splits > 1:
+        scratch, counters = _tc_scratch(weight.device, need, tiles)
+    lib = _lib("linear_tc")
+    _check(lib, lib.vapi_linear_tc(
+        _p(weight), N, K, M, _PRO[pro], _p(src), _p(ss_in), 0 if ss_in is None else ss_in.shape[0], ctypes.c_float(eps),
+        _EPI[epilogue], _p(out_bf16), _p(out_f32), ctypes.c_longlong(out_stride), _p(bias), _p(resid), _p(sso),
+        _p(next_weight), _p(xwo), _p(scratch), _p(counters), _p(status), _stream()))
+    if epilogue == "resid":
+        return sso, xwo
+    return out_bf16 if out_bf16 is not None else out_f32
+
+
+def few_rows_applies(rows: int, weight: torch.Tensor) -> bool:
+    """Whether one of this package's own products (with their fused prologues and epilogues)
+    takes a step of ``rows`` rows against ``weight``."""
+    return skinny_applies(rows, weight) or tc_applies(rows, weight)
+
+
+def few_rows_linear(weight: torch.Tensor, **kw):
+    """:func:`skinny_linear` up to 16 rows, :func:`linear_tc` up to 256."""
+    src = kw.get("act") if kw.get("act") is not None else kw.get("xw")
+    if src.shape[0] <= SKINNY_MAX_ROWS:
+        return skinny_linear(weight, **kw)
+    return linear_tc(weight, **kw)
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """``x @ weight.T (+ bias)``.  The library matrix product, except for decode-sized
@@ -279,6 +379,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
             return skinny_linear(weight, act=x, epilogue="bf16", bias=bias)
         if out_dtype == torch.float32:
             return skinny_linear(weight, act=x, epilogue="f32", bias=bias)
+    if x.dtype == torch.bfloat16 and tc_applies(x.shape[0], weight) and x.is_contiguous():
+        if out_dtype in (None, torch.bfloat16):
+            return linear_tc(weight, act=x, epilogue="bf16", bias=bias)
+        if out_dtype == torch.float32:
+            return linear_tc(weight, act=x, epilogue="f32", bias=bias)
     if weight.dtype != x.dtype:
         y = torch.mm(x.to(torch.float32), weight.to(torch.float32).t())
         if bias is not None:

@@ -81,11 +81,11 @@ class GQAttention(Mixer):
 
     def forward_stream(self, a, ctx, cache, x, next_weight):
         n = x.shape[0]
-        if not (ops.skinny_applies(n, self.w_qkv) and ops.skinny_applies(n, self.w_o)):
+        if not (ops.few_rows_applies(n, self.w_qkv) and ops.few_rows_applies(n, self.w_o)):
             return NotImplemented
-        qkv = ops.skinny_linear(self.w_qkv, xw=a.xw, ss_in=a.ss, eps=a.eps, epilogue="bf16", bias=self.b_qkv)
+        qkv = ops.few_rows_linear(self.w_qkv, xw=a.xw, ss_in=a.ss, eps=a.eps, epilogue="bf16", bias=self.b_qkv)
         y = self._attend(qkv, ctx, cache)
-        ss, xw = ops.skinny_linear(self.w_o, act=y, epilogue="resid", resid=x, bias=self.b_o, next_weight=next_weight)
+        ss, xw = ops.few_rows_linear(self.w_o, act=y, epilogue="resid", resid=x, bias=self.b_o, next_weight=next_weight)
         return StreamState(xw, ss)
 
     def _attend(self, qkv: torch.Tensor, ctx: Any, cache: CacheView) -> torch.Tensor:

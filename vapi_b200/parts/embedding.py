@@ -54,6 +54,6 @@ class OutputHead(Part):
 
     def forward_stream(self, a):
         """Logits of every row of a lazily normed stream (decode steps), or NotImplemented."""
-        if not ops.skinny_applies(a.xw.shape[0], self.weight):
+        if not ops.few_rows_applies(a.xw.shape[0], self.weight):
             return NotImplemented
-        return ops.skinny_linear(self.weight, xw=a.xw, ss_in=a.ss, eps=a.eps, epilogue="f32")
+        return ops.few_rows_linear(self.weight, xw=a.xw, ss_in=a.ss, eps=a.eps, epilogue="f32")

@@ -41,10 +41,10 @@ class SwiGLU(FeedForward):
 
     def forward_stream(self, f, ctx, x, next_weight):
         n = x.shape[0]
-        if not (ops.skinny_applies(n, self.w_gate_up) and ops.skinny_applies(n, self.w_down)):
+        if not (ops.few_rows_applies(n, self.w_gate_up) and ops.few_rows_applies(n, self.w_down)):
             return NotImplemented
-        s = ops.skinny_linear(self.w_gate_up, xw=f.xw, ss_in=f.ss, eps=f.eps, epilogue="swiglu")
-        ss, xw = ops.skinny_linear(self.w_down, act=s, epilogue="resid", resid=x, next_weight=next_weight)
+        s = ops.few_rows_linear(self.w_gate_up, xw=f.xw, ss_in=f.ss, eps=f.eps, epilogue="swiglu")
+        ss, xw = ops.few_rows_linear(self.w_down, act=s, epilogue="resid", resid=x, next_weight=next_weight)
         return StreamState(xw, ss)
 
 

@@ -65,12 +65,12 @@ class ShortConv(Mixer):
 
     def forward_stream(self, a, ctx, cache, x, next_weight):
         n = x.shape[0]
-        if not (ops.skinny_applies(n, self.w_in) and ops.skinny_applies(n, self.w_out)):
+        if not (ops.few_rows_applies(n, self.w_in) and ops.few_rows_applies(n, self.w_out)):
             return NotImplemented
-        h3 = ops.skinny_linear(self.w_in, xw=a.xw, ss_in=a.ss, eps=a.eps, epilogue="bf16")
+        h3 = ops.few_rows_linear(self.w_in, xw=a.xw, ss_in=a.ss, eps=a.eps, epilogue="bf16")
         y = ops.shortconv(h3, self.b_in, self.taps, self.b_conv, cache.tensor, ctx.state_slots,
                           ctx.tok_seq, ctx.cu_q, ctx.positions, ctx.status)
-        ss, xw = ops.skinny_linear(self.w_out, act=y, epilogue="resid", resid=x, bias=self.b_out, next_weight=next_weight)
+        ss, xw = ops.few_rows_linear(self.w_out, act=y, epilogue="resid", resid=x, bias=self.b_out, next_weight=next_weight)
         return StreamState(xw, ss)
 
 
