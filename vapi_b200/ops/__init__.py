@@ -268,7 +268,6 @@ def skinny_linear(weight: torch.Tensor, *, act: Optional[torch.Tensor] = None,
 TC_MAX_ROWS = 256
 #: set False to keep products of 17..256 rows on the library
 use_tc = os.environ.get("VAPI_TC", "1") != "0"
-_tc_bufs: Dict[str, Tuple[torch.Tensor, torch.Tensor]] = {}
 
 
 def tc_applies(rows: int, weight: torch.Tensor) -> bool:
@@ -280,21 +279,9 @@ def tc_applies(rows: int, weight: torch.Tensor) -> bool:
 
 def _tc_plan(N: int, K: int, M: int, epi: int):
     lib = _lib("linear_tc")
-    t, s, b, need = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_longlong()
-    lib.vapi_linear_tc_plan(N, K, M, epi, ctypes.byref(t), ctypes.byref(s), ctypes.byref(b), ctypes.byref(need))
-    return t.value, s.value, b.value, need.value
-
-
-def _tc_scratch(device, floats: int, tiles: int):
-    """Persistent scratch of the split-K reduction (counters start at zero, every launch leaves
-    them zero)."""
-    key = str(device)
-    buf = _tc_bufs.get(key)
-    if buf is None or buf[0].numel() < floats or buf[1].numel() < tiles:
-        buf = (torch.empty(max(floats, 8 << 20), dtype=torch.float32, device=device),
-               torch.zeros(max(tiles, 4096), dtype=torch.int32, device=device))
-        _tc_bufs[key] = buf
-    return buf
+    t, s, b = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    lib.vapi_linear_tc_plan(N, K, M, epi, ctypes.byref(t), ctypes.byref(s), ctypes.byref(b))
+    return t.value, s.value, b.value
 
 
 def linear_tc(weight: torch.Tensor, *, act: Optional[torch.Tensor] = None, xw: Optional[torch.Tensor] = None,
@@ -320,8 +307,8 @@ def linear_tc(weight: torch.Tensor, *, act: Optional[torch.Tensor] = None, xw: O
             raise KernelError("partial sums must be [parts, M]")
     _f32(bias, "bias")
     _f32(next_weight, "norm weight")
-    tiles, splits, bn, need = _tc_plan(N, K, M, _EPI[epilogue])
-    out_bf16 = out_f32 = sso = xwo = scratch = counters = None
+    tiles, splits, bn = _tc_plan(N, K, M, _EPI[epilogue])
+    out_bf16 = out_f32 = sso = xwo = None
     out_stride = N
     if epilogue == "bf16":
         out_bf16 = torch.empty((M, N), dtype=torch.bfloat16, device=weight.device)
@@ -339,13 +326,11 @@ def linear_tc(weight: torch.Tensor, *, act: Optional[torch.Tensor] = None, xw: O
             xwo = torch.empty((M, N), dtype=torch.bfloat16, device=weight.device)
     else:
         raise KernelError(f"unknown epilogue {epilogue}")
-    if splits > 1:
-        scratch, counters = _tc_scratch(weight.device, need, tiles)
     lib = _lib("linear_tc")
     _check(lib, lib.vapi_linear_tc(
         _p(weight), N, K, M, _PRO[pro], _p(src), _p(ss_in), 0 if ss_in is None else ss_in.shape[0], ctypes.c_float(eps),
         _EPI[epilogue], _p(out_bf16), _p(out_f32), ctypes.c_longlong(out_stride), _p(bias), _p(resid), _p(sso),
-        _p(next_weight), _p(xwo), _p(scratch), _p(counters), _p(status), _stream()))
+        _p(next_weight), _p(xwo), _p(status), _stream()))
     if epilogue == "resid":
         return sso, xwo
     return out_bf16 if out_bf16 is not None else out_f32
