@@ -343,4 +343,49 @@ VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, cons
     return 0;
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same attention with its scratch inside the library (see attention_noalloc.h for who needs
+// this and what it costs).  In host code the name of a __device__ array is only a handle: the
+// address a kernel can use has to be asked for, once per device, with that device current.
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) float vapi_attn_noalloc_scratch[VAPI_ATTN_NOALLOC_MAX_FLOATS];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static float* noalloc_scratch_addr[NOALLOC_MAX_DEVICES] = {nullptr};
+
+VAPI_EXPORT int vapi_paged_attention_noalloc(const void* q, long long q_row_stride, const void* cache,
+                                             int dtype, const int* block_table, int table_stride,
+                                             const int* cu_q, const int* seqlens_k, void* out, int n,
+                                             int num_seqs, int max_q, int nh, int nkv, int d,
+                                             int page_size, int num_pages, float scale, int window,
+                                             int splits, int impl, int* status, cudaStream_t stream) {
+    if (splits < 1) splits = 1;
+    float* part_o = nullptr;
+    float* part_ml = nullptr;
+    if (splits > 1 && n > 0) {
+        const long long rows = (long long)n * nh * splits;
+        const long long need = rows * ((long long)d + 2);
+        if (n < 0 || nh <= 0 || d <= 0 || need > VAPI_ATTN_NOALLOC_MAX_FLOATS)
+            return fail(-4, "paged_attention_noalloc: %d tokens x %d heads x %d splits x (head size %d + 2) = %lld floats "
+                            "of scratch, the built-in array holds %d", n, nh, splits, d, need, VAPI_ATTN_NOALLOC_MAX_FLOATS);
+        int dev = -1;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES)
+            return fail(-5, "paged_attention_noalloc: cannot tell the current device: %s", cudaGetErrorString(e));
+        if (!noalloc_scratch_addr[dev]) {                  // set-up: once per device, before any capture
+            float* addr = nullptr;
+            e = cudaGetSymbolAddress((void**)&addr, vapi_attn_noalloc_scratch);
+            if (e != cudaSuccess || !addr)
+                return fail(-6, "paged_attention_noalloc: the scratch array has no address on device %d: %s", dev, cudaGetErrorString(e));
+            noalloc_scratch_addr[dev] = addr;
+        }
+        part_o = noalloc_scratch_addr[dev];
+        part_ml = part_o + rows * d;                       // rows * d is a multiple of 16 floats: stays aligned
+    }
+    return vapi_paged_attention(q, q_row_stride, cache, dtype, block_table, table_stride, cu_q, seqlens_k, out,
+                                part_o, part_ml, n, num_seqs, max_q, nh, nkv, d, page_size, num_pages, scale,
+                                window, splits, impl, status, stream);
+}
+
 VAPI_EXPORT const char* vapi_last_error() { return error_buffer(); }
