@@ -43,7 +43,7 @@ def test_embed(ops, wdt):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden", [72, 2048, 1000])
+@pytest.mark.parametrize("hidden", [72, 2048, 1000, 70, 5000])
 def test_add_rmsnorm(ops, dtype, hidden):
     torch.manual_seed(1)
     n = 13
@@ -72,7 +72,7 @@ def test_add_rmsnorm(ops, dtype, hidden):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu(ops, dtype):
     torch.manual_seed(2)
-    for rows, ff in ((1, 8), (7, 24), (33, 1000)):
+    for rows, ff in ((1, 8), (7, 24), (33, 1000), (5, 10), (3, 4099)):
         g = (torch.randn(rows, 2 * ff) * 4).to(dtype)
         torch.testing.assert_close(ops.swiglu(dev(g)).cpu().float(), plain_ops.swiglu(g).float(), **tol(dtype))
 
@@ -236,7 +236,7 @@ def test_tensor_core_attention_is_refused_where_it_does_not_apply(ops):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("L,bias,hidden", [(3, False, 72), (4, True, 96), (2, True, 40), (1, False, 64), (8, False, 130)])
+@pytest.mark.parametrize("L,bias,hidden", [(3, False, 72), (4, True, 96), (2, True, 40), (1, False, 64), (8, False, 130), (3, True, 2048)])
 def test_shortconv_portions_and_state(ops, dtype, L, bias, hidden):
     """Several steps over the same requests: portions shorter than the state, single tokens,
     a fresh request in a slot another one used (stale state must not leak in)."""

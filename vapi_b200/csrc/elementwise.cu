@@ -101,6 +101,75 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
     }
 }
 
+// The same with 16-byte accesses and the row held in registers between the two passes
+// (hidden a multiple of 4, at most 4 * 4 * blockDim elements): one read of x and delta, one
+// write of x, one write of the output.
+template <typename T> struct Pack4;
+template <> struct Pack4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Pack4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<unsigned*>(&a);
+        u.y = *reinterpret_cast<unsigned*>(&b);
+        *reinterpret_cast<uint2*>(p) = u;
+    }
+};
+
+constexpr int NORM_KMAX = 4;
+
+template <typename T>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta,
+                                       const float* __restrict__ w, float eps,
+                                       const int* __restrict__ rows, T* __restrict__ out,
+                                       int n_out, int hidden, int write_x) {
+    __shared__ float red[33];
+    const int j = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (j >= n_out) return;
+    const int row = rows ? rows[j] : j;
+    float* xr = x + (size_t)row * hidden;
+    const T* dr = delta ? delta + (size_t)row * hidden : nullptr;
+    const int h4 = hidden >> 2;
+    float4 v[NORM_KMAX];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_KMAX; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < h4) {
+            v[k] = Pack4<float>::load(xr + 4 * c);
+            if (dr) {
+                const float4 d = Pack4<T>::load(dr + 4 * c);
+                v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
+                if (write_x) Pack4<float>::store(xr + 4 * c, v[k]);
+            }
+            ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        }
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)hidden + eps);
+    T* orow = out + (size_t)j * hidden;
+#pragma unroll
+    for (int k = 0; k < NORM_KMAX; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < h4) {
+            const float4 wv = Pack4<float>::load(w + 4 * c);
+            Pack4<T>::store(orow + 4 * c, make_float4(v[k].x * inv * wv.x, v[k].y * inv * wv.y, v[k].z * inv * wv.z, v[k].w * inv * wv.w));
+        }
+    }
+}
+
 VAPI_EXPORT int vapi_add_rmsnorm(float* x, const void* delta, const float* w, float eps,
                                  const int* rows, void* out, int out_dtype, int n_out,
                                  int hidden, cudaStream_t stream) {
@@ -109,6 +178,16 @@ VAPI_EXPORT int vapi_add_rmsnorm(float* x, const void* delta, const float* w, fl
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     const int write_x = rows ? 0 : 1;
     cudaError_t e;
+    if (hidden % 4 == 0 && hidden <= 4 * NORM_KMAX * 256 && (out_dtype == VAPI_F32 || out_dtype == VAPI_BF16)) {
+        const int vt = hidden >= 1024 ? 256 : 128;
+        if (hidden / 4 <= NORM_KMAX * vt) {
+            if (out_dtype == VAPI_F32)
+                e = launch(add_rmsnorm_vec_kernel<float>, n_out, vt, 0, stream, x, (const float*)delta, w, eps, rows, (float*)out, n_out, hidden, write_x);
+            else
+                e = launch(add_rmsnorm_vec_kernel<__nv_bfloat16>, n_out, vt, 0, stream, x, (const __nv_bfloat16*)delta, w, eps, rows, (__nv_bfloat16*)out, n_out, hidden, write_x);
+            return check_launch("add_rmsnorm", e);
+        }
+    }
     if (out_dtype == VAPI_F32)
         e = launch(add_rmsnorm_kernel<float>, n_out, threads, 0, stream, x, (const float*)delta, w, eps, rows, (float*)out, n_out, hidden, write_x);
     else if (out_dtype == VAPI_BF16)
@@ -202,6 +281,24 @@ __global__ void swiglu_kernel(const T* __restrict__ g, T* __restrict__ out, int 
     }
 }
 
+// four outputs per thread with 16-byte (float) / 8-byte (bfloat16) accesses; ff a multiple of 4
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ g, T* __restrict__ out, int rows, int ff) {
+    const int f4 = ff >> 2;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)rows * f4;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    pdl_trigger();
+    pdl_wait();
+    for (; i < total; i += stride) {
+        const size_t r = i / f4, c = (i - r * f4) << 2;
+        const float4 a = Pack4<T>::load(g + r * 2 * ff + c);
+        const float4 b = Pack4<T>::load(g + r * 2 * ff + ff + c);
+        Pack4<T>::store(out + r * ff + c, make_float4(a.x / (1.f + expf(-a.x)) * b.x, a.y / (1.f + expf(-a.y)) * b.y,
+                                                      a.z / (1.f + expf(-a.z)) * b.z, a.w / (1.f + expf(-a.w)) * b.w));
+    }
+}
+
 VAPI_EXPORT int vapi_swiglu(const void* g, void* out, int dtype, int rows, int ff,
                             cudaStream_t stream) {
     if (rows <= 0) return 0;
@@ -211,6 +308,13 @@ VAPI_EXPORT int vapi_swiglu(const void* g, void* out, int dtype, int rows, int f
     long long blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 32) blocks = 148 * 32;
     cudaError_t e;
+    if (ff % 4 == 0 && (dtype == VAPI_F32 || dtype == VAPI_BF16)) {
+        long long vb = (total / 4 + threads - 1) / threads;
+        if (vb > 148 * 16) vb = 148 * 16;
+        if (dtype == VAPI_F32) e = launch(swiglu_vec_kernel<float>, (int)vb, threads, 0, stream, (const float*)g, (float*)out, rows, ff);
+        else e = launch(swiglu_vec_kernel<__nv_bfloat16>, (int)vb, threads, 0, stream, (const __nv_bfloat16*)g, (__nv_bfloat16*)out, rows, ff);
+        return check_launch("swiglu", e);
+    }
     if (dtype == VAPI_F32)
         e = launch(swiglu_kernel<float>, (int)blocks, threads, 0, stream, (const float*)g, (float*)out, rows, ff);
     else if (dtype == VAPI_BF16)

@@ -23,29 +23,70 @@ using namespace vapi;
 
 constexpr int CONV_LMAX = 8;
 
-template <typename T>
-__device__ __forceinline__ float gate_row(const T* __restrict__ h3, const float* __restrict__ in_bias,
-                                          size_t row, int c, int hidden) {
-    const T* r = h3 + row * 3 * (size_t)hidden;
-    float b = to_f32(r[c]), x = to_f32(r[2 * hidden + c]);
-    if (in_bias) {
-        b += in_bias[c];
-        x += in_bias[2 * hidden + c];
+// V consecutive channels of one row as floats (V = 1, or 4 with one 16-byte / 8-byte access)
+template <typename T, int V> struct Chan;
+template <typename T> struct Chan<T, 1> {
+    static __device__ __forceinline__ void load(const T* p, float (&v)[1]) { v[0] = to_f32(p[0]); }
+    static __device__ __forceinline__ void store(T* p, const float (&v)[1]) { p[0] = from_f32<T>(v[0]); }
+};
+template <> struct Chan<float, 4> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 f = *reinterpret_cast<const float4*>(p);
+        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
     }
-    return round_to<T>(b * x);
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Chan<__nv_bfloat16, 4> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4]) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 u;
+        u.x = *reinterpret_cast<unsigned*>(&a);
+        u.y = *reinterpret_cast<unsigned*>(&b);
+        *reinterpret_cast<uint2*>(p) = u;
+    }
+};
+
+// g = (B + bias_B) * (x + bias_x) of one row, rounded to the storage type
+template <typename T, int V>
+__device__ __forceinline__ void gate_row(const T* __restrict__ h3, const float* __restrict__ in_bias,
+                                         size_t row, int c, int hidden, float (&g)[V]) {
+    const T* r = h3 + row * 3 * (size_t)hidden;
+    float b[V], x[V];
+    Chan<T, V>::load(r + c, b);
+    Chan<T, V>::load(r + 2 * hidden + c, x);
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+        if (in_bias) {
+            b[v] += in_bias[c + v];
+            x[v] += in_bias[2 * hidden + c + v];
+        }
+        g[v] = round_to<T>(b[v] * x[v]);
+    }
 }
 
-template <typename T>
+template <typename T, int V>
 __device__ __forceinline__ void emit(const T* __restrict__ h3, const float* __restrict__ in_bias,
                                      const float* __restrict__ conv_bias, T* __restrict__ out,
-                                     size_t row, int c, int hidden, float acc) {
-    float cc = to_f32(h3[row * 3 * (size_t)hidden + hidden + c]);
-    if (in_bias) cc += in_bias[hidden + c];
-    if (conv_bias) acc += conv_bias[c];
-    out[row * (size_t)hidden + c] = from_f32<T>(cc * acc);
+                                     size_t row, int c, int hidden, const float (&acc)[V]) {
+    float cc[V], y[V];
+    Chan<T, V>::load(h3 + row * 3 * (size_t)hidden + hidden + c, cc);
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+        if (in_bias) cc[v] += in_bias[hidden + c + v];
+        y[v] = cc[v] * (acc[v] + (conv_bias ? conv_bias[c + v] : 0.f));
+    }
+    Chan<T, V>::store(out + row * (size_t)hidden + c, y);
 }
 
-template <typename T>
+template <typename T, int V>
 __global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restrict__ in_bias,
                                  const float* __restrict__ taps,  // [L, H], k = 0 oldest
                                  const float* __restrict__ conv_bias, T* __restrict__ state,
@@ -53,7 +94,7 @@ __global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restri
                                  const int* __restrict__ tok_seq, const int* __restrict__ cu_q,
                                  const int* __restrict__ positions, T* __restrict__ out, int n,
                                  int hidden, int L, int num_slots, int* __restrict__ status) {
-    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
     const int r = blockIdx.x;
     pdl_trigger();
     if (c >= hidden || r >= n) {
@@ -66,13 +107,17 @@ __global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restri
     const int s = tok_seq[r];
     const int r0 = cu_q[s], q = cu_q[s + 1] - r0;
     const int i = r - r0;
-    float w[CONV_LMAX];
+    float w[CONV_LMAX][V];
 #pragma unroll
-    for (int k = 0; k < CONV_LMAX; ++k) w[k] = k < L ? taps[(size_t)k * hidden + c] : 0.f;
+    for (int k = 0; k < CONV_LMAX; ++k)
+#pragma unroll
+        for (int v = 0; v < V; ++v) w[k][v] = k < L ? taps[(size_t)k * hidden + c + v] : 0.f;
     int slot = -1, p0 = 0;
-    float hist[CONV_LMAX];
+    float hist[CONV_LMAX][V];
 #pragma unroll
-    for (int j = 0; j < CONV_LMAX; ++j) hist[j] = 0.f;
+    for (int j = 0; j < CONV_LMAX; ++j)
+#pragma unroll
+        for (int v = 0; v < V; ++v) hist[j][v] = 0.f;
     if (i == 0 && L > 1) {
         slot = state_slots[s];
         p0 = positions[r];
@@ -81,18 +126,25 @@ __global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restri
             // hist[0 .. L-2] = g at positions p0-(L-1) .. p0-1; hist[L-1] = the current token
 #pragma unroll
             for (int j = 0; j < CONV_LMAX; ++j)
-                if (j < L - 1 && p0 - (L - 1) + j >= 0) hist[j] = to_f32(st0[(size_t)j * hidden + c]);
+                if (j < L - 1 && p0 - (L - 1) + j >= 0) Chan<T, V>::load(st0 + (size_t)j * hidden + c, hist[j]);
         }
     }
     pdl_wait();
 
     if (i >= L - 1) {
         // every tap lies inside this step's rows
-        float acc = 0.f;
+        float acc[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v] = 0.f;
 #pragma unroll
         for (int k = 0; k < CONV_LMAX; ++k)
-            if (k < L) acc += w[k] * gate_row(h3, in_bias, (size_t)(r - (L - 1 - k)), c, hidden);
-        emit(h3, in_bias, conv_bias, out, (size_t)r, c, hidden, acc);
+            if (k < L) {
+                float g[V];
+                gate_row<T, V>(h3, in_bias, (size_t)(r - (L - 1 - k)), c, hidden, g);
+#pragma unroll
+                for (int v = 0; v < V; ++v) acc[v] += w[k][v] * g[v];
+            }
+        emit<T, V>(h3, in_bias, conv_bias, out, (size_t)r, c, hidden, acc);
         return;
     }
     if (i != 0) return;  // tokens 1 .. L-2 of a portion belong to the thread of token 0
@@ -104,31 +156,40 @@ __global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restri
     T* st = state + (size_t)slot * slot_stride;
     const int m = q < L - 1 ? q : L - 1;
     for (int ii = 0; ii < m; ++ii) {
-        const float g = gate_row(h3, in_bias, (size_t)(r + ii), c, hidden);
-        float acc = 0.f;
+        float g[V], acc[V];
+        gate_row<T, V>(h3, in_bias, (size_t)(r + ii), c, hidden, g);
 #pragma unroll
-        for (int k = 0; k < CONV_LMAX; ++k) {
-            if (k < L - 1) acc += w[k] * hist[k];
-            if (k == L - 1) acc += w[k] * g;
-        }
-        emit(h3, in_bias, conv_bias, out, (size_t)(r + ii), c, hidden, acc);
+        for (int v = 0; v < V; ++v) acc[v] = 0.f;
+#pragma unroll
+        for (int k = 0; k < CONV_LMAX; ++k)
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                if (k < L - 1) acc[v] += w[k][v] * hist[k][v];
+                if (k == L - 1) acc[v] += w[k][v] * g[v];
+            }
+        emit<T, V>(h3, in_bias, conv_bias, out, (size_t)(r + ii), c, hidden, acc);
         // slide: drop the oldest row, the current one becomes the newest of the history
 #pragma unroll
         for (int k = 0; k < CONV_LMAX - 1; ++k)
-            if (k < L - 2) hist[k] = hist[k + 1];
+#pragma unroll
+            for (int v = 0; v < V; ++v)
+                if (k < L - 2) hist[k][v] = hist[k + 1][v];
 #pragma unroll
         for (int k = 0; k < CONV_LMAX; ++k)
-            if (k == L - 2) hist[k] = g;
+#pragma unroll
+            for (int v = 0; v < V; ++v)
+                if (k == L - 2) hist[k][v] = g[v];
     }
     // the new state: the last L-1 rows of g up to position p0 + q - 1
     if (q <= L - 1) {
 #pragma unroll
         for (int j = 0; j < CONV_LMAX; ++j)
-            if (j < L - 1) st[(size_t)j * hidden + c] = from_f32<T>(hist[j]);
+            if (j < L - 1) Chan<T, V>::store(st + (size_t)j * hidden + c, hist[j]);
     } else {
         for (int j = 0; j < L - 1; ++j) {
-            const float g = gate_row(h3, in_bias, (size_t)(r + q - (L - 1) + j), c, hidden);
-            st[(size_t)j * hidden + c] = from_f32<T>(g);
+            float g[V];
+            gate_row<T, V>(h3, in_bias, (size_t)(r + q - (L - 1) + j), c, hidden, g);
+            Chan<T, V>::store(st + (size_t)j * hidden + c, g);
         }
     }
 }
@@ -144,21 +205,21 @@ VAPI_EXPORT int vapi_shortconv(const void* h3, int dtype, const float* in_bias, 
     if (hidden <= 0) return fail(-1, "shortconv: hidden=%d", hidden);
     if (L > 1 && (!state || num_slots <= 0)) return fail(-1, "shortconv: no state buffer");
     const int threads = 128;
-    const int cblocks = (hidden + threads - 1) / threads;
+    // four channels a thread when rows and state rows stay 16-byte (float) / 8-byte (bfloat16) aligned
+    const bool vec = hidden % 4 == 0 && slot_stride % 4 == 0;
+    const int per = vec ? 4 : 1;
+    const int cblocks = (hidden / per + threads - 1) / threads;
     if (cblocks > 65535) return fail(-1, "shortconv: hidden=%d is too wide for the grid", hidden);
     dim3 grid(n, cblocks);
     cudaError_t e;
-    if (dtype == VAPI_F32)
-        e = launch(shortconv_kernel<float>, grid, threads, 0, stream,
-                   (const float*)h3, in_bias, taps, conv_bias, (float*)state, slot_stride, state_slots,
-                   tok_seq, cu_q, positions, (float*)out, n, hidden, L, num_slots, status);
-    else if (dtype == VAPI_BF16)
-        e = launch(shortconv_kernel<__nv_bfloat16>, grid, threads, 0, stream,
-                   (const __nv_bfloat16*)h3, in_bias, taps, conv_bias, (__nv_bfloat16*)state, slot_stride,
-                   state_slots, tok_seq, cu_q, positions, (__nv_bfloat16*)out, n, hidden, L, num_slots,
-                   status);
-    else
-        return fail(-2, "shortconv: unsupported dtype %d", dtype);
+#define SC_LAUNCH(T, V)                                                                            \
+    e = launch(shortconv_kernel<T, V>, grid, threads, 0, stream, (const T*)h3, in_bias, taps, conv_bias, \
+               (T*)state, slot_stride, state_slots, tok_seq, cu_q, positions, (T*)out, n, hidden, L,      \
+               num_slots, status)
+    if (dtype == VAPI_F32) { if (vec) SC_LAUNCH(float, 4); else SC_LAUNCH(float, 1); }
+    else if (dtype == VAPI_BF16) { if (vec) SC_LAUNCH(__nv_bfloat16, 4); else SC_LAUNCH(__nv_bfloat16, 1); }
+    else return fail(-2, "shortconv: unsupported dtype %d", dtype);
+#undef SC_LAUNCH
     return check_launch("shortconv", e);
 }
 
