@@ -66,7 +66,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -214,8 +214,8 @@ def run(args):
     # ---- other batch sizes ----------------------------------------------------------
     points = {}
     for b in (1, 64):
-        st = max(16, args.steps // 2)
-        m, _, _, _ = decode_point(b, st, max(3, args.warmup // 2))
+        st = max(16, min(128, args.steps // 2))
+        m, _, _, _ = decode_point(b, st, max(3, min(16, args.warmup // 2)))
         points[f"decode_b{b}"] = round(b * st / (m / 1e3), 1)
         print(f"[bench] decode b{b}: {points[f'decode_b{b}']} tok/s", file=sys.stderr, flush=True)
 
@@ -335,8 +335,8 @@ def reference_arm():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=128)
-    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--steps", type=int, default=512)
+    ap.add_argument("--warmup", type=int, default=32)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0 = all)")

@@ -50,7 +50,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 constexpr int FA_BK = 64;
 
 template <int HD, int NWARPS, int STAGES>
-__global__ void __launch_bounds__(NWARPS * 32)
+__global__ void __launch_bounds__(NWARPS * 32, (HD <= 64 && NWARPS == 4) ? 4 : 1)
 flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
                    const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_table,
                    int table_stride, const int* __restrict__ cu_q, const int* __restrict__ seqlens_k,
@@ -74,7 +74,9 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
     const int q0 = cu_q[s], qlen = cu_q[s + 1] - q0, klen = seqlens_k[s];
     const int n_rep = nh / nkv;
     const int rows_total = qlen * n_rep;
-    const int tile_start = blockIdx.x * ROWS;
+    // row tiles late in a sequence see the most keys: hand them out first, so that the last
+    // blocks to start are the short ones
+    const int tile_start = ((int)gridDim.x - 1 - (int)blockIdx.x) * ROWS;
     if (tile_start >= rows_total) {
         pdl_wait();
         return;
