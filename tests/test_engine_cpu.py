@@ -35,7 +35,9 @@ def test_plain_is_causal_and_stable_in_float64(tiny_dirs):
     assert (a - b).abs().max() < 2e-4
     # a later token cannot change an earlier position
     toks2 = toks[:20] + [t ^ 1 for t in toks[20:]]
-    assert torch.equal(p32.logits(toks2)[:20], a[:20]) and not torch.allclose(p32.logits(toks2)[20:], a[20:])
+    # (within rounding: the CPU library may split a product differently from one call to the next)
+    c = p32.logits(toks2)
+    assert (c[:20] - a[:20]).abs().max() < 1e-5 and not torch.allclose(c[20:], a[20:], atol=1e-2)
 
 
 def test_plain_shortconv_by_hand():

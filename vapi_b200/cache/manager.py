@@ -23,13 +23,14 @@ positions < total in every paged group; False when pages run out, nothing kept) 
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
 
 from ..parts.base import CacheView, PagedSpec, StateSpec
+from .. import hostlib
 from .pool import OutOfPages, OutOfSlots, PagePool, SlotPool
 
 
@@ -51,23 +52,38 @@ class StateGroup:
     tensor: torch.Tensor            # [slots + 1, sites, *shape]
 
 
-@dataclass
 class RequestCache:
-    """What one live request holds."""
+    """What one live request holds.  The books themselves (block tables per paged group, the
+    state slot, the count of computed positions) live in the host runtime; this object is the
+    request's handle to them."""
 
-    request_id: object
-    slot: int
-    tables: List[List[int]]         # per paged group: page id per logical page, -1 once released
-    first_live: List[int]           # per paged group: first logical page still held
-    num_tokens: int = 0             # positions computed so far
-    closed: bool = False
-    # per paged group, the same table as an int32 array for the step packer (released pages
-    # read 0, a valid id no kernel follows); grown in place, `tables` stays the truth
-    tables_np: List[np.ndarray] = field(default_factory=list)
+    __slots__ = ("request_id", "handle", "slot", "closed", "_mgr", "_final_tokens")
 
-    def table_row(self, group: int, width: int) -> np.ndarray:
-        n = min(width, len(self.tables[group]))
-        return self.tables_np[group][:n]
+    def __init__(self, mgr: "CacheManager", request_id, handle: int, slot: int):
+        self._mgr, self.request_id, self.handle, self.slot = mgr, request_id, handle, slot
+        self.closed = False
+        self._final_tokens = 0
+
+    @property
+    def num_tokens(self) -> int:
+        """Positions computed so far."""
+        if self.closed:
+            return self._final_tokens
+        return self._mgr._lib.vh_num_tokens(self._mgr._h, self.handle)
+
+    @property
+    def tables(self) -> List[List[int]]:
+        """Per paged group: page id per logical page, -1 once the window released it."""
+        if self.closed:
+            return [[] for _ in self._mgr.paged]
+        return [self._mgr._table(self.handle, g) for g in range(len(self._mgr.paged))]
+
+    @property
+    def first_live(self) -> List[int]:
+        """Per paged group: first logical page still held."""
+        if self.closed:
+            return [0 for _ in self._mgr.paged]
+        return [self._mgr._lib.vh_first_live(self._mgr._h, self.handle, g) for g in range(len(self._mgr.paged))]
 
 
 class CacheManager:
@@ -90,18 +106,29 @@ class CacheManager:
                 by_state.setdefault(spec, []).append(site)
             else:
                 raise TypeError(f"run order entry {site}: unknown cache spec {spec!r}")
-        for spec, ss in by_paged.items():
+        if self.max_requests <= 0:
+            raise ValueError("a slot pool needs at least one slot")
+        sizes = []
+        for spec in by_paged:
             n_pages = int((pages_per_group or {}).get(spec, num_pages))
             if n_pages <= 0:
                 raise ValueError("the cache needs at least one page per group")
             wm = int(-(-n_pages * watermark // 1)) if watermark > 0 else 0
-            t = torch.empty((len(ss), n_pages, 2, spec.n_kv, self.page_size, spec.head_dim),
+            sizes.append((n_pages, wm, max(int(spec.window), 0)))
+        self._lib = hostlib.lib()
+        cols = [hostlib.i32([z[k] for z in sizes] or [0]) for k in range(3)]
+        self._h = self._lib.vh_cache_new(len(sizes), self.page_size, cols[0].ctypes.data, cols[1].ctypes.data,
+                                         cols[2].ctypes.data, self.max_requests)
+        if not self._h:
+            raise ValueError(hostlib.last_error())
+        for gi, (spec, ss) in enumerate(by_paged.items()):
+            t = torch.empty((len(ss), sizes[gi][0], 2, spec.n_kv, self.page_size, spec.head_dim),
                             dtype=dtype, device=self.device)
-            gi = len(self.paged)
-            self.paged.append(PagedGroup(spec, list(ss), PagePool(n_pages, wm), t))
+            pool = PagePool(borrowed=self._lib.vh_cache_group_pool(self._h, gi), owner=self)
+            self.paged.append(PagedGroup(spec, list(ss), pool, t))
             for j, s in enumerate(ss):
                 self._site[s] = ("paged", gi, j)
-        self.slots = SlotPool(self.max_requests)
+        self.slots = SlotPool(borrowed=self._lib.vh_cache_slot_pool(self._h), owner=self)
         for spec, ss in by_state.items():
             t = torch.empty((self.max_requests + 1, len(ss)) + tuple(spec.shape),
                             dtype=spec.dtype or dtype, device=self.device)
@@ -110,7 +137,24 @@ class CacheManager:
             for j, s in enumerate(ss):
                 self._site[s] = ("state", gi, j)
         self._live: Dict[object, RequestCache] = {}
-        self._set_aside: List[List[int]] = [[] for _ in self.paged]
+        self._scratch = np.empty(64, dtype=np.int32)
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.vh_cache_delete(h)
+
+    @property
+    def native(self) -> int:
+        """The host runtime's handle of this cache's books (for the packer and the scheduler)."""
+        return self._h
+
+    def _table(self, handle: int, group: int) -> List[int]:
+        n = self._lib.vh_table(self._h, handle, group, self._scratch.ctypes.data, self._scratch.size)
+        if n > self._scratch.size:
+            self._scratch = np.empty(2 * n, dtype=np.int32)
+            n = self._lib.vh_table(self._h, handle, group, self._scratch.ctypes.data, self._scratch.size)
+        return self._scratch[:n].tolist()
 
     # ---- what the model sees -------------------------------------------------------
     @property
@@ -135,14 +179,10 @@ class CacheManager:
         """Take one page per paged group out of circulation (for the padding rows of a
         fixed-shape decode step, like the reference's reserved blocks,
         crates/vapi-backend-candle/src/backend.rs:426-438).  None if a group has no free page."""
-        if any(g.pool.num_free == 0 for g in self.paged):
+        out = np.zeros(max(len(self.paged), 1), dtype=np.int32)
+        if not self._lib.vh_set_aside(self._h, out.ctypes.data):
             return None
-        pages = []
-        for gi, g in enumerate(self.paged):
-            p = g.pool.allocate()
-            self._set_aside[gi].append(p)
-            pages.append(p)
-        return pages
+        return out[:len(self.paged)].tolist()
 
     # ---- sizing -----------------------------------------------------------------------
     def pages_for(self, tokens: int) -> int:
@@ -158,28 +198,37 @@ class CacheManager:
     def open(self, request_id) -> RequestCache:
         if request_id in self._live:
             raise ValueError(f"request {request_id!r} is already live")
-        slot = self.slots.acquire()
-        rc = RequestCache(request_id, slot, [[] for _ in self.paged], [0 for _ in self.paged],
-                          tables_np=[np.zeros(16, dtype=np.int32) for _ in self.paged])
+        h = self._lib.vh_open(self._h)
+        if h < 0:
+            raise OutOfSlots("no free state slot")
+        rc = RequestCache(self, request_id, h, self._lib.vh_slot(self._h, h))
         self._live[request_id] = rc
         return rc
+
+    def adopt(self, request_id, handle: int) -> RequestCache:
+        """The Python face of a request that the host runtime's scheduler opened itself."""
+        rc = RequestCache(self, request_id, handle, self._lib.vh_slot(self._h, handle))
+        self._live[request_id] = rc
+        return rc
+
+    def forget(self, rc: RequestCache) -> None:
+        """The host runtime's scheduler has closed this request; only the Python face remains."""
+        if not rc.closed:
+            rc._final_tokens = 0
+            rc.closed = True
+        self._live.pop(rc.request_id, None)
 
     def live(self, request_id) -> Optional[RequestCache]:
         return self._live.get(request_id)
 
     def pages_needed(self, rc: Optional[RequestCache], total: int) -> List[int]:
         """New pages each group would need so that positions < total are covered."""
-        out = []
-        for gi, g in enumerate(self.paged):
-            have = len(rc.tables[gi]) if rc is not None else 0
-            out.append(max(0, self.pages_for(total) - have))
-        return out
+        have = [len(t) for t in rc.tables] if rc is not None else [0] * len(self.paged)
+        return [max(0, self.pages_for(total) - h) for h in have]
 
     def can_admit(self, total: int) -> bool:
         """Whether a new request of ``total`` tokens fits while leaving the watermark."""
-        if self.slots.num_free == 0:
-            return False
-        return all(g.pool.can_allocate(n) for g, n in zip(self.paged, self.pages_needed(None, total)))
+        return bool(self._lib.vh_can_admit(self._h, int(total)))
 
     def reserve(self, rc: RequestCache, total: int, guarded: bool = False) -> bool:
         """Make sure every paged group covers positions < ``total``.  All or nothing: on
@@ -187,54 +236,29 @@ class CacheManager:
         (admission); running requests reserve unguarded, as in the reference
         (crates/vapi-engine/src/scheduler.rs:464-507)."""
         assert not rc.closed
-        need = self.pages_needed(rc, total)
-        for g, n in zip(self.paged, need):
-            if (guarded and not g.pool.can_allocate(n)) or g.pool.num_free < n:
-                return False
-        for gi, (g, n) in enumerate(zip(self.paged, need)):
-            for _ in range(n):
-                page = g.pool.allocate()
-                k = len(rc.tables[gi])
-                if k >= rc.tables_np[gi].size:
-                    grown = np.zeros(max(2 * rc.tables_np[gi].size, k + 1), dtype=np.int32)
-                    grown[:k] = rc.tables_np[gi][:k]
-                    rc.tables_np[gi] = grown
-                rc.tables_np[gi][k] = page
-                rc.tables[gi].append(page)
-        return True
+        r = self._lib.vh_reserve(self._h, rc.handle, int(total), 1 if guarded else 0)
+        if r < 0:
+            raise ValueError(hostlib.last_error())
+        return r == 1
 
     def commit(self, rc: RequestCache, total: int) -> None:
         """The request has computed positions < ``total``.  A windowed group gives back
         every page all of whose positions are out of reach of any later query: the next
         query sits at a position >= total and sees keys > total - window."""
         assert not rc.closed
-        rc.num_tokens = int(total)
-        for gi, g in enumerate(self.paged):
-            w = g.spec.window
-            if w <= 0:
-                continue
-            dead_upto = total - w          # keys <= dead_upto are never read again
-            while True:
-                pi = rc.first_live[gi]
-                if pi >= len(rc.tables[gi]) or (pi + 1) * self.page_size - 1 > dead_upto:
-                    break
-                g.pool.free(rc.tables[gi][pi])
-                rc.tables[gi][pi] = -1
-                rc.tables_np[gi][pi] = 0
-                rc.first_live[gi] = pi + 1
+        self._lib.vh_commit(self._h, rc.handle, int(total))
 
     def close(self, rc: RequestCache) -> None:
         if rc.closed:
             raise ValueError(f"request {rc.request_id!r} is closed twice")
-        for gi, g in enumerate(self.paged):
-            g.pool.free_all(p for p in rc.tables[gi] if p >= 0)
-            rc.tables[gi] = []
-        self.slots.release(rc.slot)
+        rc._final_tokens = rc.num_tokens
+        if self._lib.vh_close(self._h, rc.handle) != 0:
+            raise ValueError(f"request {rc.request_id!r}: {hostlib.last_error()}")
         rc.closed = True
         self._live.pop(rc.request_id, None)
 
     def slot_of(self, rc: RequestCache, group: int, position: int) -> int:
-        page = rc.tables[group][position // self.page_size]
+        page = self._table(rc.handle, group)[position // self.page_size]
         if page < 0:
             raise ValueError(f"position {position} lies in a page the window has released")
         return page * self.page_size + position % self.page_size
@@ -242,12 +266,5 @@ class CacheManager:
     # ---- checks ----------------------------------------------------------------------
     def check_invariants(self) -> None:
         """No page lost, held twice or freed twice; the same for slots."""
-        for gi, g in enumerate(self.paged):
-            g.pool.check_invariants()
-            held = sorted([p for rc in self._live.values() for p in rc.tables[gi] if p >= 0] + self._set_aside[gi])
-            assert len(set(held)) == len(held), "a page is held by two requests"
-            assert held == g.pool.held_pages(), "pool and requests disagree about held pages"
-        self.slots.check_invariants()
-        slots = [rc.slot for rc in self._live.values()]
-        assert len(set(slots)) == len(slots), "a slot is held by two requests"
-        assert self.slots.num_free + len(slots) == self.slots.num_slots, "a slot is lost"
+        if self._lib.vh_cache_check(self._h) != 0:
+            raise AssertionError(hostlib.last_error())

@@ -1,15 +1,19 @@
 """Page and slot allocators (host side, no tensors).
 
-``PagePool`` is the allocator of the reference's block pool without its content index
-(crates/vapi-cache/src/pool.rs:80-247): a free list, an owner count per page, and a
+The books are kept by the host runtime in C++ (``csrc/host.cpp``); these classes are its
+Python face.  ``PagePool`` is the allocator of the reference's block pool without its
+content index (crates/vapi-cache/src/pool.rs:80-247): a free list, a held flag per page, and a
 watermark of pages that admission may not touch (``can_allocate``) while running requests
 still may (``allocate``).  Freed pages go to the front of the list and are handed out
 again first, so a small pool reuses pages quickly.
 """
 from __future__ import annotations
 
-from collections import deque
-from typing import Deque, Iterable, List
+from typing import Iterable, List, Optional
+
+import numpy as np
+
+from .. import hostlib
 
 
 class OutOfPages(RuntimeError):
@@ -20,85 +24,99 @@ class OutOfSlots(RuntimeError):
     pass
 
 
-class PagePool:
-    def __init__(self, num_pages: int, watermark_pages: int = 0):
-        if num_pages <= 0:
-            raise ValueError("a page pool needs at least one page")
-        self.num_pages = int(num_pages)
-        self.watermark = max(0, min(int(watermark_pages), self.num_pages - 1))
-        self._free: Deque[int] = deque(range(self.num_pages))
-        self._held = [False] * self.num_pages
+class _Pool:
+    _what = "id"
+
+    def __init__(self, count: int, watermark: int = 0, *, borrowed: Optional[int] = None, owner=None):
+        self._lib = hostlib.lib()
+        if borrowed is not None:
+            self._h, self._own, self._owner = borrowed, False, owner     # lives inside a cache's books
+        else:
+            if count <= 0:
+                raise ValueError(f"a {self._what} pool needs at least one {self._what}")
+            self._h, self._own, self._owner = self._lib.vh_pool_new(int(count), int(watermark)), True, None
+        self._n = self._lib.vh_pool_size(self._h)
+
+    def __del__(self):
+        if getattr(self, "_own", False) and self._h:
+            self._lib.vh_pool_delete(self._h)
+            self._h = None
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return self._lib.vh_pool_num_free(self._h)
+
+    def _take(self) -> int:
+        return self._lib.vh_pool_allocate(self._h)
+
+    def _give(self, i: int, twice: str) -> None:
+        rc = self._lib.vh_pool_release(self._h, int(i))
+        if rc == -1:
+            raise ValueError(f"{self._what} {i} is outside the pool")
+        if rc == -2:
+            raise ValueError(f"{self._what} {i} is {twice} twice")
+
+    def held(self) -> List[int]:
+        out = np.empty(self._n, dtype=np.int32)
+        k = self._lib.vh_pool_held(self._h, out.ctypes.data, self._n)
+        return out[:k].tolist()
+
+    def check_invariants(self) -> None:
+        if self._lib.vh_pool_check(self._h) != 0:
+            raise AssertionError(hostlib.last_error())
+
+
+class PagePool(_Pool):
+    _what = "page"
+
+    def __init__(self, num_pages: int = 0, watermark_pages: int = 0, **kw):
+        super().__init__(num_pages, watermark_pages, **kw)
+
+    @property
+    def num_pages(self) -> int:
+        return self._n
+
+    @property
+    def watermark(self) -> int:
+        return self._lib.vh_pool_watermark(self._h)
 
     def can_allocate(self, n: int) -> bool:
         """Whether admission may take ``n`` pages and still leave the watermark."""
-        return self.num_free >= n + self.watermark
+        return bool(self._lib.vh_pool_can_allocate(self._h, int(n)))
 
     def allocate(self) -> int:
-        if not self._free:
+        p = self._take()
+        if p < 0:
             raise OutOfPages("no free page")
-        p = self._free.popleft()
-        self._held[p] = True
         return p
 
     def free(self, page: int) -> None:
-        if not 0 <= page < self.num_pages:
-            raise ValueError(f"page {page} is outside the pool")
-        if not self._held[page]:
-            raise ValueError(f"page {page} is freed twice")
-        self._held[page] = False
-        self._free.appendleft(page)
+        self._give(page, "freed")
 
     def free_all(self, pages: Iterable[int]) -> None:
         for p in pages:
             self.free(p)
 
     def held_pages(self) -> List[int]:
-        return [i for i, h in enumerate(self._held) if h]
-
-    def check_invariants(self) -> None:
-        free = list(self._free)
-        assert len(set(free)) == len(free), "a page is on the free list twice"
-        for p in free:
-            assert not self._held[p], f"page {p} is free and held"
-        assert len(free) + sum(self._held) == self.num_pages, "a page is lost"
+        return self.held()
 
 
-class SlotPool:
+class SlotPool(_Pool):
     """Slots for per-request state of fixed size."""
+    _what = "slot"
 
-    def __init__(self, num_slots: int):
-        if num_slots <= 0:
-            raise ValueError("a slot pool needs at least one slot")
-        self.num_slots = int(num_slots)
-        self._free: Deque[int] = deque(range(self.num_slots))
-        self._held = [False] * self.num_slots
+    def __init__(self, num_slots: int = 0, **kw):
+        super().__init__(num_slots, 0, **kw)
 
     @property
-    def num_free(self) -> int:
-        return len(self._free)
+    def num_slots(self) -> int:
+        return self._n
 
     def acquire(self) -> int:
-        if not self._free:
+        s = self._take()
+        if s < 0:
             raise OutOfSlots("no free state slot")
-        s = self._free.popleft()
-        self._held[s] = True
         return s
 
     def release(self, slot: int) -> None:
-        if not 0 <= slot < self.num_slots:
-            raise ValueError(f"slot {slot} is outside the pool")
-        if not self._held[slot]:
-            raise ValueError(f"slot {slot} is released twice")
-        self._held[slot] = False
-        self._free.appendleft(slot)
-
-    def check_invariants(self) -> None:
-        free = list(self._free)
-        assert len(set(free)) == len(free), "a slot is on the free list twice"
-        for s in free:
-            assert not self._held[s]
-        assert len(free) + sum(self._held) == self.num_slots, "a slot is lost"
+        self._give(slot, "released")

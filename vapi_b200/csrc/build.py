@@ -1,6 +1,7 @@
-"""Builds the CUDA sources of this package for sm_100a, one shared library per source.
+"""Builds the native sources of this package, one shared library per source: CUDA sources
+(``.cu``) for sm_100a with nvcc, host sources (``.cpp``: the host runtime) with the C++ compiler.
 
-Each ``<name>.cu`` becomes ``_build/lib<name>-<hash>.so`` next to it, where the hash covers
+Each ``<name>.cu`` / ``<name>.cpp`` becomes ``_build/lib<name>-<hash>.so`` next to it, where the hash covers
 the source, the shared headers and the compiler flags, so a stale library is never picked
 up.  A library is built the first time something asks for it, which means a program only
 compiles what the model it runs needs.  While nvcc runs, a line is printed to stderr now and
@@ -35,9 +36,35 @@ class BuildError(RuntimeError):
     pass
 
 
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+
+
 def sources() -> List[str]:
-    """Names (without .cu) of every kernel source of the package."""
-    return sorted(f[:-3] for f in os.listdir(CSRC_DIR) if f.endswith(".cu"))
+    """Names (without extension) of every native source of the package."""
+    return sorted(os.path.splitext(f)[0] for f in os.listdir(CSRC_DIR) if f.endswith((".cu", ".cpp")))
+
+
+def _source(name: str) -> str:
+    for ext in (".cu", ".cpp"):
+        p = os.path.join(CSRC_DIR, name + ext)
+        if os.path.isfile(p):
+            return p
+    raise BuildError(f"no native source {os.path.join(CSRC_DIR, name)}.cu or .cpp")
+
+
+def _is_host(name: str) -> bool:
+    return _source(name).endswith(".cpp")
+
+
+def find_cxx() -> str:
+    for c in (os.environ.get("VAPI_CXX"), os.environ.get("CXX"), "g++", "c++", "clang++"):
+        if not c:
+            continue
+        path = c if os.path.isabs(c) else shutil.which(c)
+        if path and os.access(path, os.X_OK):
+            return path
+    raise BuildError("no C++ compiler was found (set VAPI_CXX or CXX); the host runtime of vapi_b200 "
+                     "cannot be built and there is no fallback")
 
 
 def find_nvcc() -> str:
@@ -56,7 +83,7 @@ def _headers(name: str) -> List[str]:
     """The package's own headers that ``name``.cu includes, directly or through another."""
     import re
     seen: List[str] = []
-    todo = [os.path.join(CSRC_DIR, name + ".cu")]
+    todo = [_source(name)]
     while todo:
         path = todo.pop()
         with open(path, "r", encoding="utf-8") as f:
@@ -70,11 +97,12 @@ def _headers(name: str) -> List[str]:
 
 def _digest(name: str) -> str:
     h = hashlib.sha256()
-    for path in [os.path.join(CSRC_DIR, name + ".cu")] + _headers(name):
+    for path in [_source(name)] + _headers(name):
         with open(path, "rb") as f:
             h.update(f.read())
         h.update(b"\0")
-    h.update(" ".join(ARCH_FLAGS + COMMON_FLAGS + EXTRA.get(name, []) + _ENV_FLAGS).encode())
+    flags = HOST_FLAGS if _is_host(name) else ARCH_FLAGS + COMMON_FLAGS + _ENV_FLAGS
+    h.update(" ".join(flags + EXTRA.get(name, [])).encode())
     return h.hexdigest()[:12]
 
 
@@ -116,21 +144,23 @@ def _writable_dir() -> str:
 
 def build(name: str, verbose: bool = True) -> str:
     """Build one source if needed and return the library path."""
-    src = os.path.join(CSRC_DIR, name + ".cu")
-    if not os.path.isfile(src):
-        raise BuildError(f"no kernel source {src}")
+    src = _source(name)
+    base = os.path.basename(src)
     have = library_path(name)
     if have:
         return have
-    nvcc = find_nvcc()
     out_dir = _writable_dir()
     out = os.path.join(out_dir, f"lib{name}-{_digest(name)}.so")
     tmp = out + f".tmp{os.getpid()}"
-    cmd = [nvcc] + ARCH_FLAGS + COMMON_FLAGS + ["-I", CSRC_DIR] + EXTRA.get(name, []) + _ENV_FLAGS + ["-o", tmp, src]
+    if _is_host(name):
+        cmd = [find_cxx()] + HOST_FLAGS + ["-I", CSRC_DIR] + EXTRA.get(name, []) + ["-o", tmp, src]
+    else:
+        cmd = [find_nvcc()] + ARCH_FLAGS + COMMON_FLAGS + ["-I", CSRC_DIR] + EXTRA.get(name, []) + _ENV_FLAGS + ["-o", tmp, src]
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
     if verbose:
-        print(f"[vapi_b200] compiling {name}.cu for sm_100a ...", file=sys.stderr, flush=True)
+        print(f"[vapi_b200] compiling {base}" + ("" if _is_host(name) else " for sm_100a") + " ...",
+              file=sys.stderr, flush=True)
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, env=env, cwd=out_dir)
     done = threading.Event()
@@ -138,7 +168,7 @@ def build(name: str, verbose: bool = True) -> str:
     def ticker() -> None:
         while not done.wait(10.0):
             if verbose:
-                print(f"[vapi_b200] still compiling {name}.cu ({time.time() - t0:.0f} s)",
+                print(f"[vapi_b200] still compiling {base} ({time.time() - t0:.0f} s)",
                       file=sys.stderr, flush=True)
 
     th = threading.Thread(target=ticker, daemon=True)
@@ -152,7 +182,7 @@ def build(name: str, verbose: bool = True) -> str:
             os.remove(tmp)
         except OSError:
             pass
-        raise BuildError(f"nvcc failed on {name}.cu:\n{' '.join(cmd)}\n{log.decode(errors='replace')}")
+        raise BuildError(f"the compiler failed on {base}:\n{' '.join(cmd)}\n{log.decode(errors='replace')}")
     os.replace(tmp, out)
     for old in ([] if _ENV_FLAGS else os.listdir(out_dir)):          # earlier builds of this source are of no use any more
         if old.startswith(f"lib{name}-") and old.endswith(".so") and os.path.join(out_dir, old) != out:

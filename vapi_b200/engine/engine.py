@@ -62,6 +62,7 @@ class Engine:
         cfg.max_concurrent_seqs = min(cfg.max_concurrent_seqs, runner.cache.max_requests)
         self.cfg = cfg
         self.scheduler = Scheduler(cfg, runner.cache, runner.plan.eos_token_ids)
+        self.scheduler.lazy_entries = True
         self.sampler = Sampler(runner.device)
         self.states: Dict[int, SamplerState] = {}
         self.stats = EngineStats()
@@ -93,11 +94,11 @@ class Engine:
 
     # ---- one step ---------------------------------------------------------------------
     def _run(self, plan: StepPlan) -> Optional[torch.Tensor]:
-        if self.use_graphs and hasattr(self.runner, "step_decode_graph"):
-            out = self.runner.step_decode_graph(plan.entries)
+        if self.use_graphs and plan.pure_decode and hasattr(self.runner, "step_decode_graph"):
+            out = self.runner.step_decode_graph(None, plan=plan)
             if out is not None:
                 return out
-        return self.runner.step(plan.entries)
+        return self.runner.step(None, plan=plan)
 
     def step(self) -> StepOutput:
         out = StepOutput()

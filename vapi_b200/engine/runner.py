@@ -208,18 +208,27 @@ class ModelRunner:
         xn = plan.final_norm.apply(x, None, ctx.dtype, rows=ctx.logits_rows)
         return plan.head.forward(xn)
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Optional[Sequence[StepEntry]], plan=None) -> Optional[torch.Tensor]:
         """Run one batch.  Pages must have been reserved by the caller
         (``cache.reserve(rc, rc.num_tokens + len(tokens))``): what happens when they run out
-        is the scheduler's decision, not the step function's."""
+        is the scheduler's decision, not the step function's.  ``plan``, instead of ``entries``,
+        is a step that the scheduler has planned: the host runtime then packs it straight from
+        its own arrays."""
         if self.validate:
-            validate_step(entries, self.cache, self.vocab_size, self.max_context)
-        ctx = self.packer.pack(entries, self.dtype, status=self.status)
+            validate_step(plan.entries if plan is not None else entries, self.cache, self.vocab_size,
+                          self.max_context)
+        ctx = self.packer.pack(entries, self.dtype, status=self.status, plan=plan)
         logits = self.forward(ctx)
-        for e in entries:
-            self.cache.commit(e.cache, e.start + len(e.tokens))
+        self._commit(entries, plan)
         self.steps_run += 1
         return logits
+
+    def _commit(self, entries, plan) -> None:
+        if plan is not None:
+            plan.commit_cache()
+        else:
+            for e in entries:
+                self.cache.commit(e.cache, e.start + len(e.tokens))
 
     # ---- captured decode steps --------------------------------------------------------
     def _bucket(self, S: int) -> int:
@@ -268,18 +277,23 @@ class ModelRunner:
                 best = max(best, ops.attention_splits(B, 1, self.max_context, m.nh, m.nkv))
         return best
 
-    def step_decode_graph(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step_decode_graph(self, entries: Optional[Sequence[StepEntry]], plan=None) -> Optional[torch.Tensor]:
         """A pure decode step (one token and one wanted row per request) through a captured
         graph; None when the step is not of that shape or graphs are unavailable, in which
         case the caller uses :meth:`step`."""
-        S = len(entries)
+        S = plan.num_entries if plan is not None else len(entries)
         if self._graphs_off or S == 0 or S > self.graph_max_batch:
             return None
-        for e in entries:
-            if len(e.tokens) != 1 or list(e.want) != [0]:
+        if plan is not None:
+            if not plan.pure_decode:
                 return None
+        else:
+            for e in entries:
+                if len(e.tokens) != 1 or list(e.want) != [0]:
+                    return None
         if self.validate:
-            validate_step(entries, self.cache, self.vocab_size, self.max_context)
+            validate_step(plan.entries if plan is not None else entries, self.cache, self.vocab_size,
+                          self.max_context)
         B = self._bucket(S)
         if B not in self._graphs:
             try:
@@ -294,11 +308,11 @@ class ModelRunner:
                 self._graphs_off = True
                 return None
         graph, logits, kernels = self._graphs[B]
-        self.packer.pack(entries, self.dtype, n_cap=B, s_cap=B, width=self.packer.max_width, status=self.status)
+        self.packer.pack(entries, self.dtype, n_cap=B, s_cap=B, width=self.packer.max_width, status=self.status,
+                         plan=plan)
         graph.replay()
         ops.launch_count += kernels
-        for e in entries:
-            self.cache.commit(e.cache, e.start + 1)
+        self._commit(entries, plan)
         self.steps_run += 1
         return logits[:S]
 

@@ -20,18 +20,22 @@ sequence.rs) without its prefix cache and forks:
   finished: EOS (only after at least one generated token) or a stop token id -> STOP;
   ``max_tokens`` or the context limit -> LENGTH.
 
-This is pure host logic: it touches the cache manager's bookkeeping and never a tensor.
+This is pure host logic: it touches the cache manager's bookkeeping and never a tensor.  The
+decisions are made by the host runtime in C++ (``csrc/host.cpp``), which owns the sequences'
+tokens and progress, the queues and the plan of the current step; the classes here are its
+Python face and hold what C++ has no use for (request ids, sampling parameters).
 """
 from __future__ import annotations
 
 import enum
-from collections import deque
-from dataclasses import dataclass, field
-from typing import Deque, Dict, List, Optional, Tuple
+from dataclasses import dataclass
+from typing import Dict, List, Optional
 from typing import Sequence as Seq
 
+import numpy as np
+
+from .. import hostlib
 from ..cache.manager import CacheManager, RequestCache
-from ..cache.pool import OutOfSlots
 from ..sampling.params import FinishReason, SamplingParams
 from .step import StepEntry
 
@@ -57,31 +61,86 @@ class SchedulerConfig:
     max_context: int = 8192
 
 
-class Sequence:
-    """One request's tokens and progress (crates/vapi-engine/src/sequence.rs)."""
+_REASONS = {0: FinishReason.STOP, 1: FinishReason.LENGTH, 2: FinishReason.CANCELLED, 3: FinishReason.ERROR}
+_REASON_CODES = {v: k for k, v in _REASONS.items()}
+# fields of vs_seq_get
+_STATUS, _PROMPT_LEN, _COMPUTED, _TARGET, _HANDLE, _PREEMPTIONS, _REASON, _TOTAL = range(8)
+# lists of vs_list
+(_L_SEQS, _L_HANDLES, _L_STARTS, _L_QLENS, _L_WANT_COUNTS, _L_WANTS, _L_TOKENS, _L_SAMPLED, _L_PREEMPTED,
+ _L_STARTED, _L_RUNNING, _L_WAITING, _L_FINISHED) = range(13)
 
-    def __init__(self, seq_id: int, request_id, prompt: Seq[int], params: SamplingParams):
-        self.seq_id, self.request_id, self.params = seq_id, request_id, params
-        self.tokens: List[int] = [int(t) for t in prompt]
-        self.prompt_len = len(self.tokens)
-        self.num_computed = 0
-        self.prefill_target = self.prompt_len   # known text to push through in portions
-        self.status = SeqStatus.WAITING
-        self.finish_reason: Optional[FinishReason] = None
+
+class Sequence:
+    """One request's tokens and progress (crates/vapi-engine/src/sequence.rs), read through to
+    the host runtime while the request lives and kept as a snapshot once it has been drained."""
+
+    def __init__(self, sched: "Scheduler", seq_id: int, request_id, params: SamplingParams):
+        self._sched, self.seq_id, self.request_id, self.params = sched, seq_id, request_id, params
         self.cache: Optional[RequestCache] = None
-        self.preemptions = 0
+        self._snapshot: Optional[Dict[str, object]] = None
+
+    def _get(self, field: int) -> int:
+        return self._sched._lib.vs_seq_get(self._sched._h, self.seq_id, field)
+
+    def _freeze(self) -> None:
+        self._snapshot = {"tokens": self.tokens, "prompt_len": self.prompt_len, "num_computed": self.num_computed,
+                          "prefill_target": self.prefill_target, "status": self.status,
+                          "finish_reason": self.finish_reason, "preemptions": self.preemptions}
+
+    def _field(self, name: str, field: int) -> int:
+        if self._snapshot is not None:
+            return self._snapshot[name]
+        return self._get(field)
+
+    @property
+    def tokens(self) -> List[int]:
+        if self._snapshot is not None:
+            return self._snapshot["tokens"]
+        return self._sched._seq_tokens(self.seq_id, 0)
+
+    @property
+    def prompt_len(self) -> int:
+        return self._field("prompt_len", _PROMPT_LEN)
+
+    @property
+    def num_computed(self) -> int:
+        return self._field("num_computed", _COMPUTED)
+
+    @property
+    def prefill_target(self) -> int:
+        return self._field("prefill_target", _TARGET)
+
+    @property
+    def preemptions(self) -> int:
+        return self._field("preemptions", _PREEMPTIONS)
+
+    @property
+    def status(self) -> SeqStatus:
+        if self._snapshot is not None:
+            return self._snapshot["status"]
+        return SeqStatus(self._get(_STATUS))
+
+    @property
+    def finish_reason(self) -> Optional[FinishReason]:
+        if self._snapshot is not None:
+            return self._snapshot["finish_reason"]
+        return _REASONS.get(self._get(_REASON))
 
     @property
     def total_len(self) -> int:
-        return len(self.tokens)
+        if self._snapshot is not None:
+            return len(self._snapshot["tokens"])
+        return self._get(_TOTAL)
 
     @property
     def num_generated(self) -> int:
-        return len(self.tokens) - self.prompt_len
+        return self.total_len - self.prompt_len
 
     @property
     def generated(self) -> List[int]:
-        return self.tokens[self.prompt_len:]
+        if self._snapshot is not None:
+            return self._snapshot["tokens"][self.prompt_len:]
+        return self._sched._seq_tokens(self.seq_id, self.prompt_len)
 
     def needs_prefill(self) -> bool:
         return self.num_computed < self.prefill_target
@@ -89,42 +148,54 @@ class Sequence:
     def remaining_prefill(self) -> int:
         return max(0, self.prefill_target - self.num_computed)
 
-    def reset_for_recompute(self) -> None:
-        """After preemption: keep every token, compute again from position 0
-        (sequence.rs:167-176)."""
-        self.num_computed = 0
-        self.prefill_target = len(self.tokens)
-        self.status = SeqStatus.WAITING
-        self.cache = None
-        self.preemptions += 1
 
-    def check_finished(self, eos: Seq[int], max_context: int) -> Optional[FinishReason]:
-        """sequence.rs:179-202."""
-        if self.num_generated > 0:
-            last = self.tokens[-1]
-            if (not self.params.ignore_eos and last in eos) or last in self.params.stop_token_ids:
-                return FinishReason.STOP
-        if self.num_generated >= self.params.max_tokens:
-            return FinishReason.LENGTH
-        if self.total_len >= max_context:
-            return FinishReason.LENGTH
-        return None
-
-
-@dataclass
 class StepPlan:
-    entries: List[StepEntry] = field(default_factory=list)
-    batch_seqs: List[int] = field(default_factory=list)        # sequence of each entry
-    sampled_seqs: List[int] = field(default_factory=list)      # sequence behind each wanted row, in row order
-    preempted: List[int] = field(default_factory=list)
-    started: List[int] = field(default_factory=list)
+    """The step the scheduler has planned.  The arrays live in the host runtime, which packs
+    them for the device itself; ``entries`` builds the Python view of them on demand."""
+
+    def __init__(self, sched: Optional["Scheduler"] = None, info: Seq[int] = (0,) * 8):
+        self._sched = sched
+        (self.num_entries, self.num_tokens, self.num_rows, n_pre, n_start, pure, self.width_needed, _) = info
+        self.pure_decode = bool(pure)
+        self.handle = sched._h if sched is not None else None
+        self.batch_seqs: List[int] = sched._list(_L_SEQS, self.num_entries) if self.num_entries else []
+        self.sampled_seqs: List[int] = sched._list(_L_SAMPLED, self.num_rows) if self.num_rows else []
+        self.preempted: List[int] = sched._list(_L_PREEMPTED, n_pre) if n_pre else []
+        self.started: List[int] = sched._list(_L_STARTED, n_start) if n_start else []
+        self._entries: Optional[List[StepEntry]] = None
+        self._caches: Optional[List[Optional[RequestCache]]] = None
+        self._serial = sched._serial if sched is not None else 0
 
     def is_empty(self) -> bool:
-        return not self.entries
+        return self.num_entries == 0
+
+    def _bind(self) -> None:
+        """Remember which cache each entry belongs to (the faces can change at the next plan)."""
+        self._caches = [self._sched.seqs[sid].cache for sid in self.batch_seqs]
 
     @property
-    def num_tokens(self) -> int:
-        return sum(len(e.tokens) for e in self.entries)
+    def entries(self) -> List[StepEntry]:
+        if self._entries is None:
+            if self._sched is not None and self._sched._serial != self._serial:
+                raise RuntimeError("this plan's entries were not read before the next step was planned")
+            out: List[StepEntry] = []
+            if self.num_entries:
+                s = self._sched
+                qlens = s._list(_L_QLENS, self.num_entries)
+                wants = s._list(_L_WANT_COUNTS, self.num_entries)
+                tokens = s._list(_L_TOKENS, self.num_tokens)
+                o = 0
+                for rc, q, w in zip(self._caches, qlens, wants):
+                    out.append(StepEntry(rc, tokens[o:o + q], [q - 1] if w else []))
+                    o += q
+            self._entries = out
+        return self._entries
+
+    def commit_cache(self) -> None:
+        """What the step function does after it ran this step: every request of the step has
+        computed its tokens."""
+        if self.num_entries and self._sched._lib.vs_commit_cache(self.handle) != 0:
+            raise RuntimeError(hostlib.last_error())
 
 
 class Scheduler:
@@ -132,172 +203,121 @@ class Scheduler:
         self.cfg, self.cache = cfg, cache
         self.eos = tuple(int(e) for e in eos_token_ids)
         self.seqs: Dict[int, Sequence] = {}
-        self.waiting: Deque[int] = deque()
-        self.running: List[int] = []
-        self.finished: List[int] = []
-        self._next_id = 0
+        self._lib = hostlib.lib()
+        eos = hostlib.i32(list(self.eos) or [0])
+        self._h = self._lib.vs_new(cache.native, int(cfg.max_concurrent_seqs), int(cfg.max_batched_tokens),
+                                   int(cfg.prefill_chunk_tokens), int(cfg.max_context), eos.ctypes.data, len(self.eos))
+        self._info = np.zeros(8, dtype=np.int32)
+        self._buf = np.zeros(1024, dtype=np.int32)
+        self._seen_finished = 0
+        self._serial = 0
+        #: False: a plan's ``entries`` are built when it is planned; True (the engine loop):
+        #: only if someone asks before the next plan, since the host runtime packs the step itself
+        self.lazy_entries = False
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.vs_delete(h)
+
+    # ---- reading the host runtime's lists ------------------------------------------------
+    def _room(self, n: int) -> np.ndarray:
+        if n > self._buf.size:
+            self._buf = np.zeros(max(n, 2 * self._buf.size), dtype=np.int32)
+        return self._buf
+
+    def _list(self, which: int, count: int) -> List[int]:
+        buf = self._room(count)
+        n = self._lib.vs_list(self._h, which, buf.ctypes.data, buf.size)
+        return buf[:n].tolist()
+
+    def _seq_tokens(self, sid: int, start: int) -> List[int]:
+        n = self._lib.vs_seq_get(self._h, sid, _TOTAL)
+        buf = self._room(max(n, 1))
+        k = self._lib.vs_seq_tokens(self._h, sid, start, buf.ctypes.data, buf.size)
+        return buf[:max(k, 0)].tolist()
+
+    @property
+    def running(self) -> List[int]:
+        return self._list(_L_RUNNING, self._lib.vs_counts(self._h, 0))
+
+    @property
+    def waiting(self) -> List[int]:
+        return self._list(_L_WAITING, self._lib.vs_counts(self._h, 1))
+
+    @property
+    def finished(self) -> List[int]:
+        return self._list(_L_FINISHED, self._lib.vs_counts(self._h, 2))
 
     # ---- admission ----------------------------------------------------------------------
     def admit(self, request_id, prompt: Seq[int], params: SamplingParams) -> int:
         params.validate()
-        if len(prompt) == 0:
-            raise AdmitError("the prompt is empty")
-        if len(prompt) >= self.cfg.max_context:
-            raise AdmitError(f"the prompt has {len(prompt)} tokens; the context limit is {self.cfg.max_context}")
-        if self.cache.paged and self.cache.pages_for(len(prompt) + 1) > min(g.pool.num_pages for g in self.cache.paged):
-            raise AdmitError(f"the prompt has {len(prompt)} tokens; the whole cache holds fewer")
-        sid = self._next_id
-        self._next_id += 1
-        self.seqs[sid] = Sequence(sid, request_id, prompt, params)
-        self.waiting.append(sid)
+        toks = hostlib.i32([int(t) for t in prompt] or [0])
+        stop = hostlib.i32([int(t) for t in params.stop_token_ids] or [0])
+        sid = self._lib.vs_admit(self._h, toks.ctypes.data, len(prompt), int(params.max_tokens),
+                                 1 if params.ignore_eos else 0, stop.ctypes.data, len(params.stop_token_ids))
+        if sid < 0:
+            raise AdmitError(hostlib.last_error())
+        self.seqs[sid] = Sequence(self, sid, request_id, params)
         return sid
 
     def admission_headroom(self) -> int:
-        return max(0, self.cfg.max_concurrent_seqs - len(self.running) - len(self.waiting))
+        return max(0, self.cfg.max_concurrent_seqs - self.num_running - self.num_waiting)
 
     @property
     def num_waiting(self) -> int:
-        return len(self.waiting)
+        return self._lib.vs_counts(self._h, 1)
 
     @property
     def num_running(self) -> int:
-        return len(self.running)
+        return self._lib.vs_counts(self._h, 0)
 
     def is_idle(self) -> bool:
-        return not self.waiting and not self.running
+        return self.num_waiting == 0 and self.num_running == 0
 
     # ---- one step ---------------------------------------------------------------------
     def schedule(self) -> StepPlan:
-        plan = StepPlan()
-        budget = self.cfg.max_batched_tokens
-        budget = self._schedule_decodes(plan, budget)
-        self._schedule_prefills(plan, budget)
+        self._serial += 1
+        self._lib.vs_schedule(self._h)
+        self._lib.vs_plan_info(self._h, self._info.ctypes.data)
+        info = self._info.tolist()
+        plan = StepPlan(self, info)
+        for sid in plan.preempted:
+            self._drop_face(sid)
+        for sid in plan.started:
+            seq = self.seqs[sid]
+            seq.cache = self.cache.adopt(sid, self._lib.vs_seq_get(self._h, sid, _HANDLE))
+        if info[7] != self._seen_finished:
+            self._note_finished()
+        plan._bind()
+        if not self.lazy_entries:
+            plan.entries
         return plan
 
-    def _schedule_decodes(self, plan: StepPlan, budget: int) -> int:
-        survivors = []
-        for sid in list(self.running):
-            seq = self.seqs.get(sid)
-            if seq is None or seq.status == SeqStatus.FINISHED:
-                continue
-            if seq.needs_prefill() or budget == 0:
-                survivors.append(sid)
-                continue
-            if self.cache.reserve(seq.cache, seq.num_computed + 1):
-                self._push(seq, 1, plan)
-                budget -= 1
-                survivors.append(sid)
-            else:
-                self._preempt(seq)
-                plan.preempted.append(sid)
-        self.running = survivors
-        return budget
+    def _drop_face(self, sid: int) -> None:
+        seq = self.seqs.get(sid)
+        if seq is not None and seq.cache is not None:
+            self.cache.forget(seq.cache)
+            seq.cache = None
 
-    def _schedule_prefills(self, plan: StepPlan, budget: int) -> None:
-        for sid in list(self.running):
-            if budget == 0:
-                return
-            seq = self.seqs.get(sid)
-            if seq is None or not seq.needs_prefill() or seq.status == SeqStatus.FINISHED:
-                continue
-            budget = self._prefill_chunk(seq, plan, budget)
-        while budget > 0 and len(self.running) < self.cfg.max_concurrent_seqs and self.waiting:
-            sid = self.waiting.popleft()
-            seq = self.seqs.get(sid)
-            if seq is None or seq.status == SeqStatus.FINISHED:
-                continue
-            if not self._can_ever_fit(seq):
-                # grown (by generation, then preemption) beyond what the whole cache holds
-                self.finish(sid, FinishReason.LENGTH)
-                continue
-            if not self._try_start(seq):
-                self.waiting.appendleft(sid)
-                return
-            plan.started.append(sid)
-            self.running.append(sid)
-            budget = self._prefill_chunk(seq, plan, budget)
-
-    def _can_ever_fit(self, seq: Sequence) -> bool:
-        need = self.cache.pages_for(seq.prefill_target + 1)
-        return all(need + g.pool.watermark <= g.pool.num_pages for g in self.cache.paged)
-
-    def _try_start(self, seq: Sequence) -> bool:
-        """Pages for the known text plus its first generated token, watermark-checked, and
-        a state slot (scheduler.rs:435-491)."""
-        if not self.cache.can_admit(seq.prefill_target + 1):
-            return False
-        try:
-            rc = self.cache.open(seq.seq_id)
-        except OutOfSlots:
-            return False
-        if not self.cache.reserve(rc, seq.prefill_target + 1, guarded=True):
-            self.cache.close(rc)
-            return False
-        seq.cache = rc
-        seq.status = SeqStatus.PREFILLING
-        return True
-
-    def _prefill_chunk(self, seq: Sequence, plan: StepPlan, budget: int) -> int:
-        q = min(seq.remaining_prefill(), self.cfg.prefill_chunk_tokens, budget)
-        if q == 0:
-            return budget
-        if not self.cache.reserve(seq.cache, seq.num_computed + q):
-            self._preempt(seq)
-            plan.preempted.append(seq.seq_id)
-            return budget
-        self._push(seq, q, plan)
-        return budget - q
-
-    def _push(self, seq: Sequence, q: int, plan: StepPlan) -> None:
-        start = seq.num_computed
-        assert seq.cache is not None and seq.cache.num_tokens == start
-        completes = start + q >= seq.total_len
-        plan.entries.append(StepEntry(seq.cache, seq.tokens[start:start + q], [q - 1] if completes else []))
-        plan.batch_seqs.append(seq.seq_id)
-        if completes:
-            plan.sampled_seqs.append(seq.seq_id)
-
-    def _preempt(self, seq: Sequence) -> None:
-        if seq.cache is not None:
-            self.cache.close(seq.cache)
-        seq.reset_for_recompute()
-        if seq.seq_id in self.running:
-            self.running.remove(seq.seq_id)
-        self.waiting.appendleft(seq.seq_id)
+    def _note_finished(self) -> None:
+        """Requests the host runtime has retired since the last look no longer hold a cache."""
+        ids = self.finished
+        for sid in ids:
+            self._drop_face(sid)
+        self._seen_finished = len(ids)
 
     def commit(self, plan: StepPlan, sampled: Seq[int]) -> None:
         assert len(sampled) == len(plan.sampled_seqs)
-        for sid, e in zip(plan.batch_seqs, plan.entries):
-            seq = self.seqs.get(sid)
-            if seq is None or seq.status == SeqStatus.FINISHED:
-                continue
-            seq.num_computed += len(e.tokens)
-            if not seq.needs_prefill() and seq.status == SeqStatus.PREFILLING:
-                seq.status = SeqStatus.DECODING
-        for sid, tok in zip(plan.sampled_seqs, sampled):
-            seq = self.seqs.get(sid)
-            if seq is None or seq.status == SeqStatus.FINISHED:
-                continue
-            seq.tokens.append(int(tok))
-            seq.prefill_target = max(seq.prefill_target, seq.num_computed)
-            reason = seq.check_finished(self.eos, self.cfg.max_context)
-            if reason is not None:
-                self.finish(sid, reason)
+        arr = hostlib.i32([int(t) for t in sampled] or [0])
+        if self._lib.vs_commit(self._h, arr.ctypes.data, len(sampled)) != 0:
+            raise RuntimeError(hostlib.last_error())
+        if self._lib.vs_counts(self._h, 2) != self._seen_finished:
+            self._note_finished()
 
     def finish(self, sid: int, reason: FinishReason) -> None:
-        seq = self.seqs.get(sid)
-        if seq is None or seq.status == SeqStatus.FINISHED:
-            return
-        seq.status = SeqStatus.FINISHED
-        seq.finish_reason = reason
-        if seq.cache is not None:
-            self.cache.close(seq.cache)
-            seq.cache = None
-        if sid in self.running:
-            self.running.remove(sid)
-        if sid in self.waiting:
-            self.waiting.remove(sid)
-        self.finished.append(sid)
+        self._lib.vs_finish(self._h, int(sid), _REASON_CODES[reason])
+        self._note_finished()
 
     def cancel(self, sid: int) -> None:
         self.finish(sid, FinishReason.CANCELLED)
@@ -305,12 +325,24 @@ class Scheduler:
     def fail_all(self) -> List[int]:
         """A failed step fails every request in flight and frees what they hold; the
         scheduler goes on serving (crates/vapi-worker/src/engine.rs:622-650)."""
-        ids = [s for s in list(self.running) + list(self.waiting)]
-        for sid in ids:
-            self.finish(sid, FinishReason.ERROR)
+        buf = self._room(len(self.seqs) + 1)
+        n = self._lib.vs_fail_all(self._h, buf.ctypes.data, buf.size)
+        ids = buf[:n].tolist()
+        self._note_finished()
         return ids
 
     def drain_finished(self) -> List[Sequence]:
-        out = [self.seqs.pop(sid) for sid in self.finished if sid in self.seqs]
-        self.finished = []
+        if self._lib.vs_counts(self._h, 2) == 0:
+            return []
+        out = []
+        for sid in self.finished:
+            seq = self.seqs.pop(sid, None)
+            if seq is None:
+                continue
+            self._drop_face(sid)
+            seq._freeze()
+            self._lib.vs_erase(self._h, sid)
+            out.append(seq)
+        self._lib.vs_clear_finished(self._h)
+        self._seen_finished = 0
         return out

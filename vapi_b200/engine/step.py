@@ -14,8 +14,10 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
+from .. import hostlib
 from ..cache.manager import CacheManager, RequestCache
 
 
@@ -120,6 +122,10 @@ class StepPacker:
     def __init__(self, cache: CacheManager, device, max_tokens: int, max_seqs: int, max_table_width: int,
                  ring: int = 3):
         self.cache, self.device = cache, torch.device(device)
+        self._lib = hostlib.lib()
+        self._layouts: Dict[tuple, Dict[str, int]] = {}
+        self._info = np.zeros(8, dtype=np.int32)
+        self._pad_np = hostlib.i32([0])
         self.G = len(cache.paged)
         self.max_tokens, self.max_seqs, self.max_width = int(max_tokens), int(max_seqs), int(max_table_width)
         self.capacity = self._layout(self.max_tokens, self.max_seqs, self.max_width, self.max_tokens)["_total"]
@@ -132,47 +138,51 @@ class StepPacker:
         self._next = 0
         self.h2d_bytes_last = 0
 
+    _NAMES = ("cu_q", "seqlens_k", "state_slots")
+
     def _layout(self, n_cap: int, s_cap: int, width: int, r_cap: int) -> Dict[str, int]:
-        off, lay = 0, {}
-
-        def put(name: str, count: int) -> None:
-            nonlocal off
-            lay[name] = off
-            off += _round_up(max(count, 1), 4)
-
-        put("cu_q", s_cap + 1)
-        put("seqlens_k", s_cap)
-        put("state_slots", s_cap)
-        for g in range(self.G):
-            put(f"table{g}", s_cap * width)
-        put("tokens", n_cap)
-        put("positions", n_cap)
-        put("tok_seq", n_cap)
-        for g in range(self.G):
-            put(f"slots{g}", n_cap)
-        put("rows", r_cap)
-        lay["_total"] = off
+        """Offsets of a step's arrays in the buffer (computed by the host runtime, which also
+        fills them)."""
+        key = (n_cap, s_cap, width, r_cap)
+        lay = self._layouts.get(key)
+        if lay is None:
+            G = self.G
+            raw = np.zeros(self._lib.vh_layout_len(G), dtype=np.int32)
+            self._lib.vh_layout(G, n_cap, s_cap, width, r_cap, raw.ctypes.data)
+            names = (["cu_q", "seqlens_k", "state_slots"] + [f"table{g}" for g in range(G)]
+                     + ["tokens", "positions", "tok_seq"] + [f"slots{g}" for g in range(G)] + ["rows", "_total"])
+            lay = dict(zip(names, raw.tolist()))
+            if len(self._layouts) > 256:
+                self._layouts.clear()
+            self._layouts[key] = lay
         return lay
 
     def pack(self, entries: Sequence[StepEntry], dtype: torch.dtype, *, n_cap: Optional[int] = None,
              s_cap: Optional[int] = None, width: Optional[int] = None,
-             status: Optional[torch.Tensor] = None) -> StepContext:
+             status: Optional[torch.Tensor] = None, plan=None) -> StepContext:
         """Build the device context.  With capacities given, the step is padded to them:
         padding sequences hold one token at position 0 that writes to page 0's slot of a
-        page the caller set aside (``pad_page``) and to the scratch state slot."""
-        cache, P = self.cache, self.cache.page_size
-        S = len(entries)
-        n = sum(len(e.tokens) for e in entries)
-        R = sum(len(e.want) for e in entries)
-        w_need = max([cache.pages_for(e.start + len(e.tokens)) for e in entries] or [1])
+        page the caller set aside (``pad_page``) and to the scratch state slot.  ``plan`` is a
+        step the host runtime's scheduler has planned (its handle): the arrays are then taken
+        from there and ``entries`` is not looked at."""
+        cache = self.cache
         pad = n_cap is not None
+        if plan is not None:
+            S, n, R, w_need = plan.num_entries, plan.num_tokens, plan.num_rows, plan.width_needed
+        else:
+            S = len(entries)
+            qlens = [len(e.tokens) for e in entries]
+            n = sum(qlens)
+            R = sum(len(e.want) for e in entries)
+            w_need = max([cache.pages_for(e.start + q) for e, q in zip(entries, qlens)] or [1])
         n_c = n_cap if pad else n
         s_c = s_cap if pad else S
         w_c = width if width is not None else _round_up(w_need, 4)
         if n > n_c or S > s_c or w_need > w_c or n_c > self.max_tokens or s_c > self.max_seqs or w_c > self.max_width:
             raise StepError(f"step of {n} tokens / {S} sequences / {w_need} pages exceeds the packer's capacity "
                             f"({self.max_tokens} / {self.max_seqs} / {self.max_width})")
-        lay = self._layout(n_c, s_c, w_c, n_c if pad else max(R, 1))
+        r_c = n_c if pad else max(R, 1)
+        lay = self._layout(n_c, s_c, w_c, r_c)
         total = lay["_total"]
 
         slot = self._ring[self._next]
@@ -180,53 +190,25 @@ class StepPacker:
         host, event, used = slot
         if used and event is not None:
             event.synchronize()
-        hb = host.numpy()
-        hb[:total] = 0
-
-        cu_q, pos_n = [0], 0
-        toks, poss, tseq, rows = [], [], [], []
-        slots: List[List[int]] = [[] for _ in range(self.G)]
-        max_q = max_k = 1 if pad else 0
-        for si, e in enumerate(entries):
-            q, st = len(e.tokens), e.start
-            max_q, max_k = max(max_q, q), max(max_k, st + q)
-            toks.extend(int(t) for t in e.tokens)
-            poss.extend(range(st, st + q))
-            tseq.extend([si] * q)
-            rows.extend(pos_n + int(w) for w in e.want)
-            for g in range(self.G):
-                tb = e.cache.tables[g]
-                if q == 1:
-                    slots[g].append(tb[st // P] * P + st % P)
-                else:
-                    slots[g].extend(tb[p // P] * P + p % P for p in range(st, st + q))
-                row = e.cache.table_row(g, w_c)
-                o = lay[f"table{g}"] + si * w_c
-                hb[o:o + row.size] = row
-            hb[lay["seqlens_k"] + si] = st + q
-            hb[lay["state_slots"] + si] = e.cache.slot
-            pos_n += q
-            cu_q.append(pos_n)
-        # padding sequences of a fixed-shape step: one token each, nothing of theirs is read back
-        for si in range(S, s_c):
-            cu_q.append(cu_q[-1] + 1)
-            hb[lay["seqlens_k"] + si] = 1
-            hb[lay["state_slots"] + si] = cache.scratch_slot
-            rows.append(len(toks))
-            tseq.append(si)
-            toks.append(0)
-            poss.append(0)
-            for g in range(self.G):
-                slots[g].append(self.pad_slot(g))
-                hb[lay[f"table{g}"] + si * w_c] = self.pad_page(g)
-        n_tot = len(toks)
-        hb[lay["cu_q"]:lay["cu_q"] + len(cu_q)] = cu_q
-        hb[lay["tokens"]:lay["tokens"] + n_tot] = toks
-        hb[lay["positions"]:lay["positions"] + n_tot] = poss
-        hb[lay["tok_seq"]:lay["tok_seq"] + n_tot] = tseq
-        for g in range(self.G):
-            hb[lay[f"slots{g}"]:lay[f"slots{g}"] + n_tot] = slots[g]
-        hb[lay["rows"]:lay["rows"] + len(rows)] = rows
+        info = self._info
+        pads = self._pad_np.ctypes.data if (pad and S < s_c) else 0
+        if pad and S < s_c and self._pad_pages is None:
+            raise StepError("padding a step needs a page set aside for it")
+        if plan is not None:
+            rc = self._lib.vs_pack_plan(plan.handle, n_c, s_c, w_c, r_c, 1 if pad else 0, pads, cache.scratch_slot,
+                                        host.data_ptr(), info.ctypes.data)
+        else:
+            handles = hostlib.i32([e.cache.handle for e in entries] or [0])
+            ql = hostlib.i32(qlens or [0])
+            toks = hostlib.i32([t for e in entries for t in e.tokens] or [0])
+            wc = hostlib.i32([len(e.want) for e in entries] or [0])
+            wants = hostlib.i32([w for e in entries for w in e.want] or [0])
+            rc = self._lib.vh_pack(cache.native, S, handles.ctypes.data, ql.ctypes.data, toks.ctypes.data,
+                                   wc.ctypes.data, wants.ctypes.data, n_c, s_c, w_c, r_c, 1 if pad else 0, pads,
+                                   cache.scratch_slot, host.data_ptr(), info.ctypes.data)
+        if rc != 0:
+            raise StepError(f"the step cannot be packed: {hostlib.last_error()}")
+        _, _, num_rows, max_q, max_k, identity = info[:6].tolist()
 
         if self.cuda:
             self.dev[:total].copy_(host[:total], non_blocking=True)
@@ -246,18 +228,19 @@ class StepPacker:
                             d[lay[f"table{g}"]:lay[f"table{g}"] + s_eff * w_c].view(s_eff, w_c))
                   for g in range(self.G)]
         return StepContext(
-            n=n_eff, num_seqs=s_eff, num_rows=len(rows), max_q=max_q, max_k=max_k,
+            n=n_eff, num_seqs=s_eff, num_rows=num_rows, max_q=max_q, max_k=max_k,
             tokens=view("tokens", n_eff), positions=view("positions", n_eff), tok_seq=view("tok_seq", n_eff),
             cu_q=view("cu_q", s_eff + 1), seqlens_k=view("seqlens_k", s_eff),
             state_slots=view("state_slots", s_eff),
-            logits_rows=view("rows", len(rows)) if rows else None,
-            groups=groups, dtype=dtype, status=status, rows_identity=rows == list(range(n_eff)))
+            logits_rows=view("rows", num_rows) if num_rows else None,
+            groups=groups, dtype=dtype, status=status, rows_identity=bool(identity) and num_rows == n_eff)
 
     # a page per group that padding rows may scribble on; set by whoever captures graphs
     _pad_pages: Optional[List[int]] = None
 
     def set_pad_pages(self, pages: List[int]) -> None:
         self._pad_pages = list(pages)
+        self._pad_np = hostlib.i32(list(pages) or [0])
 
     def pad_page(self, g: int) -> int:
         if self._pad_pages is None:
