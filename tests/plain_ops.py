@@ -24,6 +24,12 @@ def embed(table, tokens, status=None, next_weight=None):
     return out, (out ** 2).sum(1)[None, :], (out * next_weight).to(torch.bfloat16)
 
 
+def resolve_tokens(tokens, src, prev, status=None):
+    """tokens[i] = prev[src[i]] where src[i] >= 0 (tokens the step before sampled on the device)."""
+    m = src >= 0
+    tokens[m] = prev[src[m].long()]
+
+
 def add_residual_ss(x, delta, next_weight):
     x += _f(delta)
     return (x ** 2).sum(1)[None, :], (x * next_weight).to(torch.bfloat16)
@@ -231,6 +237,6 @@ def apply_penalties(logits, rows, toks, counts, rep, freq, pres):
         logits[r, t] = v
 
 
-ALL = ["embed", "add_rmsnorm", "add_residual", "add_residual_ss", "skinny_applies", "tc_applies", "few_rows_applies", "swiglu", "linear", "strict_fp32", "rope_cos_sin",
+ALL = ["embed", "resolve_tokens", "add_rmsnorm", "add_residual", "add_residual_ss", "skinny_applies", "tc_applies", "few_rows_applies", "swiglu", "linear", "strict_fp32", "rope_cos_sin",
        "qk_norm_rope_write", "attention_splits", "paged_attention", "shortconv", "sample_rows",
        "apply_penalties"]

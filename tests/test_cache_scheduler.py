@@ -291,3 +291,92 @@ def test_cancel_and_fail_all_free_everything():
     assert done == {"a": FinishReason.CANCELLED, "b": FinishReason.ERROR}
     assert all(g.pool.num_free == g.pool.num_pages for g in s.cache.paged) and s.cache.slots.num_free == 4
     assert s.is_idle()
+
+
+# ---------------------------------------------------------------------------------------
+# planning one step ahead of the sampled tokens
+
+
+class ScriptAhead(Script):
+    """The engine's way of running one step ahead, on the scripted model: a step is planned and
+    advanced before the tokens of the step before it are given to the scheduler."""
+
+    def run(self, max_steps=1000):
+        inflight = None
+        self.ahead = 0
+        for _ in range(max_steps):
+            if self.sched.is_idle() and inflight is None:
+                return
+            if inflight is not None and not self.sched.can_run_ahead():
+                self.sched.resolve(*inflight)
+                inflight = None
+            plan = self.sched.schedule()
+            self.plans.append(plan)
+            assert not plan.preempted or inflight is None, "a preemption while a token is unknown"
+            if plan.is_empty():
+                if inflight is not None:
+                    self.sched.resolve(*inflight)
+                    inflight = None
+                continue
+            # what the scripted model will sample for this step: decided by how many tokens the
+            # request has, unknown ones included
+            sampled = []
+            for sid in plan.sampled_seqs:
+                seq = self.sched.seqs[sid]
+                sampled.append(self.script[seq.request_id][seq.num_generated])
+            for e in plan.entries:
+                self.sched.cache.commit(e.cache, e.start + len(e.tokens))
+            self.sched.advance(plan)
+            if inflight is not None:
+                self.ahead += 1
+                self.sched.resolve(*inflight)
+            inflight = (plan, sampled)
+            self.sched.cache.check_invariants()
+        raise AssertionError("the scheduler did not finish")
+
+
+@pytest.mark.parametrize("pages", [64, 9])
+def test_planning_one_step_ahead_ends_every_request_the_same_way(pages):
+    script, results = {}, {}
+    for i in range(6):
+        script[i] = [1000 + 10 * i + k for k in range(30)]
+    script[1][4] = 99            # EOS in the middle
+    script[3][9] = 42            # a stop id in the middle
+    script[4][0] = 99            # EOS as the very first generated token
+    for cls in (Script, ScriptAhead):
+        s = sched(num_pages=pages, page=16, max_requests=4, max_context=200, prefill_chunk_tokens=16)
+        for i in range(6):
+            s.admit(i, list(range(1, 20 + i)), SamplingParams(max_tokens=12 + 3 * i, temperature=0.0,
+                                                              stop_token_ids=(42,) if i == 3 else ()))
+        sc = cls(s, script)
+        sc.run(5000)
+        results[cls] = {q.request_id: (q.generated, q.finish_reason, q.total_len) for q in s.drain_finished()}
+        assert all(g.pool.num_free == g.pool.num_pages for g in s.cache.paged) and s.cache.slots.num_free == 4
+        if cls is ScriptAhead:
+            assert sc.ahead > 10
+    assert results[Script] == results[ScriptAhead]
+    r = results[Script]
+    assert r[1][0] == script[1][:5] and r[1][1] == FinishReason.STOP
+    assert r[3][0] == script[3][:10] and r[3][1] == FinishReason.STOP
+    assert r[4][0] == [99] and r[0][1] == FinishReason.LENGTH and len(r[0][0]) == 12
+
+
+def test_an_unknown_token_is_marked_for_the_device_to_fetch():
+    s = sched(num_pages=16, max_context=256)
+    s.admit("a", [1, 2, 3], SamplingParams(max_tokens=5, temperature=0.0))
+    s.admit("b", [4, 5], SamplingParams(max_tokens=5, temperature=0.0))
+    p0 = s.schedule()
+    assert not p0.has_unknown and p0.sampled_seqs == [0, 1]
+    for e in p0.entries:
+        s.cache.commit(e.cache, e.start + len(e.tokens))
+    s.advance(p0)
+    p1 = s.schedule()                      # both decode a token nobody knows yet
+    assert p1.has_unknown and p1.pure_decode
+    assert s._list(13, 2) == [0, 1]        # token sources: rows of the step before
+    for e in p1.entries:
+        s.cache.commit(e.cache, e.start + 1)
+    s.advance(p1)
+    assert s.resolve(p0, [7, 99]) == [True, True]          # b ends on EOS ...
+    assert s.resolve(p1, [8, 9]) == [True, False]          # ... so what the step ahead made for it is dropped
+    done = {q.request_id: q.generated for q in s.drain_finished()}
+    assert done == {"b": [99]} and s.seqs[0].generated == [7, 8]

@@ -110,6 +110,44 @@ def test_temperature_sampling_is_seeded_and_batch_independent(tiny_dirs):
     assert one[0].tokens == greedy[0].tokens
 
 
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_running_one_step_ahead_changes_no_token(tiny_dirs, dtype):
+    """The engine enqueues a step before it has read the tokens of the step before it.  With
+    stops in the middle of the text, different lengths, seeded temperature, late admissions and a
+    pool so small that requests are preempted, every request must end with the tokens and the
+    reason it has without running ahead."""
+    from vapi_b200 import LLM, SamplingParams
+    prompts = _prompts(TINY_B, 9, [5, 40, 97, 3, 18, 64])
+
+    def run(ahead, params, blocks):
+        llm = LLM(tiny_dirs["B"], dtype=dtype, num_blocks=blocks, page_size=16, max_concurrent_seqs=4,
+                  max_batched_tokens=64, max_context=256, prefill_chunk_tokens=16, run_ahead=ahead)
+        out = llm.generate(prompts, params)
+        llm.runner.check_status()
+        llm.runner.cache.check_invariants()
+        assert all(g.pool.num_free + 1 >= g.pool.num_pages for g in llm.runner.cache.paged)   # one page is set aside
+        return [(c.tokens, c.finish_reason) for c in out], llm.engine.stats
+
+    free = [SamplingParams(temperature=0.0, max_tokens=20 + 3 * i, ignore_eos=True) for i in range(6)]
+    base, st0 = run(False, free, 40)
+    assert st0.ahead_steps == 0
+    # stop ids taken from the middle of what is generated, so that requests end on a stop while
+    # the step after it is already enqueued
+    stops = [SamplingParams(temperature=0.0, max_tokens=20 + 3 * i, ignore_eos=True,
+                            stop_token_ids=(base[i][0][7 + i],)) for i in range(6)]
+    want, _ = run(False, stops, 40)
+    assert any(r == "stop" for _, r in want) and all(len(t) <= 20 + 3 * i for i, (t, _) in enumerate(want))
+    got, st = run(True, stops, 40)
+    assert got == want and st.ahead_steps > 10
+    # a pool that forces preemptions (recompute must not need a token that is still in flight)
+    want_small, st_s = run(False, free, 13)
+    got_small, st_a = run(True, free, 13)
+    assert st_s.preemptions > 0 and got_small == want_small
+    # seeded temperature on the device: the draw counters advance the same way
+    temp = [SamplingParams(temperature=0.9, seed=11 + i, max_tokens=16, ignore_eos=True) for i in range(6)]
+    assert run(True, temp, 40)[0] == run(False, temp, 40)[0]
+
+
 def test_penalties_change_what_is_generated(tiny_dirs):
     from vapi_b200 import LLM, SamplingParams
     p = _prompts(TINY_A, 6, [12])

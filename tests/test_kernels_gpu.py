@@ -42,6 +42,19 @@ def test_embed(ops, wdt):
     torch.testing.assert_close(got.cpu(), plain_ops.embed(table, toks), atol=0, rtol=0)
 
 
+def test_resolve_tokens(ops):
+    g = torch.Generator().manual_seed(5)
+    toks = torch.randint(0, 1000, (300,), generator=g, dtype=torch.int32)
+    src = torch.full((300,), -1, dtype=torch.int32)
+    src[torch.randperm(300, generator=g)[:77]] = torch.randint(0, 64, (77,), generator=g, dtype=torch.int32)
+    prev = torch.randint(0, 1000, (64,), generator=g, dtype=torch.int32)
+    want = toks.clone()
+    plain_ops.resolve_tokens(want, src, prev)
+    got = dev(toks.clone())
+    ops.resolve_tokens(got, dev(src), dev(prev))
+    assert torch.equal(got.cpu(), want) and not torch.equal(want, toks)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("hidden", [72, 2048, 1000, 70, 5000])
 def test_add_rmsnorm(ops, dtype, hidden):

@@ -40,7 +40,7 @@ class LLM:
                  cuda_graphs: bool = True, max_concurrent_seqs: int = 64, max_batched_tokens: int = 8192,
                  prefill_chunk_tokens: int = 2048, watermark: float = 0.01, max_step_failures: int = 3,
                  random_weights: Optional[int] = None, config_json: Optional[Dict[str, Any]] = None,
-                 page_size: Optional[int] = None, validate: bool = False):
+                 page_size: Optional[int] = None, validate: bool = False, run_ahead: Optional[bool] = None):
         dt = "float32" if str(dtype).lower() in ("f32", "fp32", "float32") else "bfloat16"
         kw = dict(dtype=dt, device=device, page_size=page_size or ModelRunner.default_page_size,
                   num_pages=num_blocks, max_requests=max_concurrent_seqs,
@@ -57,7 +57,7 @@ class LLM:
         self.engine = Engine(self.runner, SchedulerConfig(
             max_concurrent_seqs=max_concurrent_seqs, max_batched_tokens=max_batched_tokens,
             prefill_chunk_tokens=prefill_chunk_tokens, max_context=max_context),
-            max_step_failures=max_step_failures, use_graphs=cuda_graphs)
+            max_step_failures=max_step_failures, use_graphs=cuda_graphs, run_ahead=run_ahead)
         self._next = 0
 
     @classmethod

@@ -61,6 +61,33 @@ VAPI_EXPORT int vapi_embed(const void* table, int table_dtype, const int* tokens
 }
 
 // ---------------------------------------------------------------------------
+// tokens the host does not know yet: tokens[i] = prev[src[i]] where src[i] >= 0.
+// An engine that runs one step ahead enqueues a step before it has read what the step before
+// sampled; `prev` is that step's sampled output on the device.  Rows outside `prev` are refused.
+__global__ void resolve_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ src,
+                                      const int* __restrict__ prev, int n, int prev_rows,
+                                      int* __restrict__ status) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (i < n) {
+        const int r = src[i];
+        if (r >= 0) {
+            if (r < prev_rows) tokens[i] = prev[r];
+            else if (status) atomicExch(status, 1);
+        }
+    }
+}
+
+VAPI_EXPORT int vapi_resolve_tokens(int* tokens, const int* src, const int* prev, int n, int prev_rows,
+                                    int* status, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!tokens || !src || !prev || prev_rows <= 0) return fail(-1, "resolve_tokens: missing array");
+    cudaError_t e = launch(resolve_tokens_kernel, (n + 127) / 128, 128, 0, stream, tokens, src, prev, n, prev_rows, status);
+    return check_launch("resolve_tokens", e);
+}
+
+// ---------------------------------------------------------------------------
 // fused residual add + RMSNorm.
 //   if delta: x[row] += float(delta[row])           (x is the float residual stream)
 //   out[j]   = T( x[row] * rsqrt(mean(x[row]^2) + eps) * w )

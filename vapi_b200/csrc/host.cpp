@@ -214,7 +214,9 @@ struct Cache {
 // (token capacity, sequence capacity, table width, row capacity): a captured decode step of a
 // given bucket always finds its inputs at the same offsets.  Arrays start on 16-byte
 // boundaries.  Order: cu_q, seqlens_k, state_slots, table[g]..., tokens, positions, tok_seq,
-// slots[g]..., rows, and the total as the last entry.
+// slots[g]..., rows, token_src, and the total as the last entry.  token_src[i] >= 0 says
+// that token i is not known to the host yet: it is that row of the previous step's sampled
+// output, and a kernel at the head of the step fetches it from there.
 inline int round4(int x) { return (std::max(x, 1) + 3) / 4 * 4; }
 
 void layout(int G, int n_cap, int s_cap, int width, int r_cap, int* out) {
@@ -229,6 +231,7 @@ void layout(int G, int n_cap, int s_cap, int width, int r_cap, int* out) {
     put(n_cap);
     for (int g = 0; g < G; ++g) put(n_cap);
     put(r_cap);
+    put(n_cap);
     out[k] = off;
 }
 
@@ -239,6 +242,7 @@ struct PackArgs {
     const int* tokens;          // [sum qlens]
     const int* want_counts;     // [S]
     const int* wants;           // [sum want_counts] places within each entry's tokens
+    const int* token_src;       // [sum qlens] or null: see the layout
     int n_cap, s_cap, width, r_cap;
     int padded;                 // 1: fill up to (n_cap, s_cap) with padding sequences
     const int* pad_pages;       // [G] when padded
@@ -248,18 +252,20 @@ struct PackArgs {
 // info: n, sequences, rows, max_q, max_k, rows_identity, total
 int pack(Cache& c, const PackArgs& a, int* out, int* info) {
     const int G = (int)c.groups.size(), P = c.page_size;
-    std::vector<int> lay(2 * G + 9);
+    std::vector<int> lay(2 * G + 10);
     layout(G, a.n_cap, a.s_cap, a.width, a.r_cap, lay.data());
     const int o_cu = lay[0], o_k = lay[1], o_state = lay[2];
     const int* o_table = &lay[3];
     const int o_tok = lay[3 + G], o_pos = lay[4 + G], o_seq = lay[5 + G];
     const int* o_slots = &lay[6 + G];
-    const int o_rows = lay[6 + 2 * G], total = lay[7 + 2 * G];
+    const int o_rows = lay[6 + 2 * G], o_src = lay[7 + 2 * G], total = lay[8 + 2 * G];
     std::memset(out, 0, sizeof(int) * (size_t)total);
 
     int n = 0, rows = 0, max_q = a.padded ? 1 : 0, max_k = a.padded ? 1 : 0;
     const int* tk = a.tokens;
     const int* wt = a.wants;
+    const int* ts = a.token_src;
+    for (int i = 0; i < a.n_cap; ++i) out[o_src + i] = -1;
     bool identity = true;
     if (a.S > a.s_cap) return fail(-3, "more sequences than the step's capacity");
     out[o_cu] = 0;
@@ -286,6 +292,7 @@ int pack(Cache& c, const PackArgs& a, int* out, int* info) {
         }
         for (int j = 0; j < q; ++j) {
             out[o_tok + n + j] = tk[j];
+            if (ts) out[o_src + n + j] = ts[j];
             out[o_pos + n + j] = st + j;
             out[o_seq + n + j] = si;
         }
@@ -296,6 +303,7 @@ int pack(Cache& c, const PackArgs& a, int* out, int* info) {
             out[o_rows + rows++] = n + wt[j];
         }
         tk += q;
+        if (ts) ts += q;
         wt += a.want_counts[si];
         out[o_k + si] = st + q;
         out[o_state + si] = r->slot;
@@ -331,6 +339,7 @@ int pack(Cache& c, const PackArgs& a, int* out, int* info) {
 }
 
 // ---- sequences and the scheduler -----------------------------------------------------------
+constexpr int UNKNOWN = -1;      // a token that a step in flight has yet to produce
 enum Status { WAITING = 0, PREFILLING = 1, DECODING = 2, FINISHED = 3 };
 enum Reason { R_NONE = -1, R_STOP = 0, R_LENGTH = 1, R_CANCELLED = 2, R_ERROR = 3 };
 
@@ -345,6 +354,14 @@ struct Seq {
     int max_tokens = 0;
     bool ignore_eos = false;
     std::vector<int> stop_ids;
+    // Running one step ahead: a token that a step in flight will produce stands in `tokens` as
+    // UNKNOWN until the step's result has been read.  `pending` lists where those stand,
+    // oldest first; `last_row` is the row of the newest one in its step's sampled output (the
+    // next step's device-side input reads it from there); `parked` marks a request that has
+    // reached a length limit and only waits for its last token.
+    std::deque<int> pending;
+    int last_row = -1;
+    bool parked = false;
 
     int total_len() const { return (int)tokens.size(); }
     int num_generated() const { return (int)tokens.size() - prompt_len; }
@@ -353,10 +370,14 @@ struct Seq {
 
 struct Plan {
     std::vector<int> seq_ids, handles, starts, qlens, want_counts, wants, tokens;
+    std::vector<int> token_src;     // per token: row of the previous step's sampled output it is, or -1
     std::vector<int> sampled, preempted, started;
+    bool has_unknown = false, advanced = false;
     void clear() {
         seq_ids.clear(); handles.clear(); starts.clear(); qlens.clear(); want_counts.clear();
         wants.clear(); tokens.clear(); sampled.clear(); preempted.clear(); started.clear();
+        token_src.clear();
+        has_unknown = advanced = false;
     }
 };
 
@@ -406,7 +427,12 @@ struct Sched {
         plan.handles.push_back(s.handle);
         plan.starts.push_back(start);
         plan.qlens.push_back(q);
-        plan.tokens.insert(plan.tokens.end(), s.tokens.begin() + start, s.tokens.begin() + start + q);
+        for (int t = start; t < start + q; ++t) {
+            const int tok = s.tokens[t];
+            plan.tokens.push_back(tok == UNKNOWN ? 0 : tok);
+            plan.token_src.push_back(tok == UNKNOWN ? s.last_row : -1);
+            plan.has_unknown = plan.has_unknown || tok == UNKNOWN;
+        }
         plan.want_counts.push_back(completes ? 1 : 0);
         if (completes) {
             plan.wants.push_back(q - 1);
@@ -459,6 +485,9 @@ struct Sched {
         if (!s || s->status == FINISHED) return;
         s->status = FINISHED;
         s->reason = reason;
+        s->parked = false;
+        while (!s->tokens.empty() && s->tokens.back() == UNKNOWN) s->tokens.pop_back();   // never learnt
+        s->pending.clear();
         if (s->handle >= 0) cache->close(s->handle);
         s->handle = -1;
         erase(running, sid);
@@ -509,35 +538,81 @@ struct Sched {
         }
         return (int)plan.seq_ids.size();
     }
-    int check_finished(const Seq& s) const {
-        if (s.num_generated() > 0) {
-            int last = s.tokens.back();
-            bool is_eos = !s.ignore_eos && std::find(eos.begin(), eos.end(), last) != eos.end();
-            if (is_eos || std::find(s.stop_ids.begin(), s.stop_ids.end(), last) != s.stop_ids.end()) return R_STOP;
-        }
-        if (s.num_generated() >= s.max_tokens) return R_LENGTH;
-        if (s.total_len() >= max_context) return R_LENGTH;
-        return R_NONE;
+    // Whether the token at `idx` ends the request: EOS (unless ignored) or a stop id, and
+    // only for a generated token (sequence.rs:179-202).
+    bool stops_at(const Seq& s, int idx) const {
+        if (idx < s.prompt_len) return false;
+        const int tok = s.tokens[idx];
+        const bool is_eos = !s.ignore_eos && std::find(eos.begin(), eos.end(), tok) != eos.end();
+        return is_eos || std::find(s.stop_ids.begin(), s.stop_ids.end(), tok) != s.stop_ids.end();
     }
-    // Advance every request of the planned step, append the sampled tokens, retire what
-    // finished; the cache's commit (window release) belongs to whoever ran the step.
-    int commit(const int* sampled, int n) {
-        if (n != (int)plan.sampled.size()) return fail(-1, "one sampled token per wanted row is needed");
+    bool at_length_limit(const Seq& s) const {
+        return s.num_generated() >= s.max_tokens || s.total_len() >= max_context;
+    }
+    // The part of a commit that does not depend on what was sampled: every request of the
+    // planned step has computed its tokens; a request that asked for logits gains a token whose
+    // value is not known yet.  One that reaches a length limit with it is parked: it takes part
+    // in no further step and is retired when the token's value arrives.
+    int advance() {
+        if (plan.advanced) return fail(-1, "the planned step has been advanced already");
+        plan.advanced = true;
         for (size_t i = 0; i < plan.seq_ids.size(); ++i) {
             Seq* s = get(plan.seq_ids[i]);
             if (!s || s->status == FINISHED) continue;
             s->num_computed += plan.qlens[i];
             if (!s->needs_prefill() && s->status == PREFILLING) s->status = DECODING;
         }
-        for (int i = 0; i < n; ++i) {
+        for (size_t i = 0; i < plan.sampled.size(); ++i) {
             Seq* s = get(plan.sampled[i]);
             if (!s || s->status == FINISHED) continue;
-            s->tokens.push_back(sampled[i]);
+            s->pending.push_back((int)s->tokens.size());
+            s->tokens.push_back(UNKNOWN);
+            s->last_row = (int)i;
             s->prefill_target = std::max(s->prefill_target, s->num_computed);
-            int reason = check_finished(*s);
-            if (reason != R_NONE) finish(s->id, reason);
+            if (at_length_limit(*s)) {
+                s->parked = true;
+                erase(running, s->id);
+            }
         }
         return 0;
+    }
+    // The values of tokens that an advanced step produced, for the requests `sids` in the
+    // order of that step's wanted rows.  Retires what finished: EOS or a stop id -> STOP (what a
+    // later step in flight has appended for the request in the meantime is dropped);
+    // a length limit -> LENGTH.
+    int resolve(const int* sids, const int* toks, int n, int* accepted) {
+        for (int i = 0; i < n; ++i) {
+            Seq* s = get(sids[i]);
+            const bool takes = s && s->status != FINISHED && !s->pending.empty();
+            if (accepted) accepted[i] = takes ? 1 : 0;      // 0: the request had ended before this token
+            if (!takes) continue;
+            const int idx = s->pending.front();
+            s->pending.pop_front();
+            s->tokens[idx] = toks[i];
+            if (stops_at(*s, idx)) {
+                s->tokens.resize(idx + 1);
+                s->pending.clear();
+                finish(s->id, R_STOP);
+            } else if (s->parked && s->pending.empty()) {
+                finish(s->id, R_LENGTH);
+            }
+        }
+        return 0;
+    }
+    // Advance the planned step and give its sampled tokens at once.
+    int commit(const int* sampled, int n) {
+        if (n != (int)plan.sampled.size()) return fail(-1, "one sampled token per wanted row is needed");
+        if (!plan.advanced && advance() != 0) return -1;
+        std::vector<int> sids = plan.sampled;
+        return resolve(sids.data(), sampled, n, nullptr);
+    }
+    // Whether the next step can be planned before the last one's tokens are known without any
+    // risk of a preemption (whose recompute would need those tokens): every running request
+    // can take one more page in every group.
+    bool can_run_ahead() const {
+        for (const Group& g : cache->groups)
+            if (g.pool.num_free() < (int)running.size()) return false;
+        return true;
     }
 };
 
@@ -637,15 +712,15 @@ API int vh_cache_check(void* c) {
 }
 
 // ---- the packed step -----------------------------------------------------------------------
-API int vh_layout_len(int G) { return 2 * G + 8; }
+API int vh_layout_len(int G) { return 2 * G + 9; }
 API void vh_layout(int G, int n_cap, int s_cap, int width, int r_cap, int* out) {
     layout(G, n_cap, s_cap, width, r_cap, out);
 }
 API int vh_pack(void* c, int S, const int* handles, const int* qlens, const int* tokens, const int* want_counts,
                 const int* wants, int n_cap, int s_cap, int width, int r_cap, int padded, const int* pad_pages,
                 int scratch_slot, int* out, int* info) {
-    PackArgs a{S, handles, qlens, tokens, want_counts, wants, n_cap, s_cap, width, r_cap, padded, pad_pages,
-               scratch_slot};
+    PackArgs a{S, handles, qlens, tokens, want_counts, wants, nullptr, n_cap, s_cap, width, r_cap, padded,
+               pad_pages, scratch_slot};
     return pack(*(Cache*)c, a, out, info);
 }
 
@@ -666,11 +741,18 @@ API int vs_admit(void* s, const int* prompt, int n, int max_tokens, int ignore_e
 }
 API int vs_schedule(void* s) { return ((Sched*)s)->schedule(); }
 API int vs_commit(void* s, const int* sampled, int n) { return ((Sched*)s)->commit(sampled, n); }
+API int vs_advance(void* s) { return ((Sched*)s)->advance(); }
+API int vs_resolve(void* s, const int* sids, const int* toks, int n, int* accepted) {
+    return ((Sched*)s)->resolve(sids, toks, n, accepted);
+}
+API int vs_can_run_ahead(void* s) { return ((Sched*)s)->can_run_ahead() ? 1 : 0; }
 API void vs_finish(void* s, int sid, int reason) { ((Sched*)s)->finish(sid, reason); }
 API int vs_fail_all(void* s, int* out, int cap) {
     Sched* k = (Sched*)s;
-    std::vector<int> ids(k->running);
-    ids.insert(ids.end(), k->waiting.begin(), k->waiting.end());
+    std::vector<int> ids;
+    for (auto& kv : k->seqs)
+        if (kv.second.status != FINISHED) ids.push_back(kv.first);
+    std::sort(ids.begin(), ids.end());
     for (int sid : ids) k->finish(sid, R_ERROR);
     return copy_out(ids, out, cap);
 }
@@ -693,11 +775,13 @@ API int vs_list(void* s, int which, int* out, int cap) {
         case 10: return copy_out(k->running, out, cap);
         case 11: { std::vector<int> w(k->waiting.begin(), k->waiting.end()); return copy_out(w, out, cap); }
         case 12: return copy_out(k->finished, out, cap);
+        case 13: return copy_out(p.token_src, out, cap);
     }
     return fail(-1, "unknown list");
 }
 // sizes of the planned step: entries, tokens, wanted rows, preempted, started, pure decode (1/0),
-// pages the longest entry's block table must cover, requests finished and not yet drained
+// pages the longest entry's block table must cover, requests finished and not yet drained,
+// whether a token of the step is still to be produced by the step before it
 API void vs_plan_info(void* s, int* info) {
     Sched* k = (Sched*)s;
     const Plan& p = k->plan;
@@ -705,6 +789,7 @@ API void vs_plan_info(void* s, int* info) {
     for (size_t i = 0; i < p.qlens.size(); ++i) width = std::max(width, k->cache->pages_for(p.starts[i] + p.qlens[i]));
     info[6] = width;
     info[7] = (int)k->finished.size();
+    info[8] = p.has_unknown ? 1 : 0;
     info[0] = (int)p.seq_ids.size();
     info[1] = (int)p.tokens.size();
     info[2] = (int)p.sampled.size();
@@ -719,7 +804,8 @@ API int vs_pack_plan(void* s, int n_cap, int s_cap, int width, int r_cap, int pa
     Sched* k = (Sched*)s;
     const Plan& p = k->plan;
     PackArgs a{(int)p.seq_ids.size(), p.handles.data(), p.qlens.data(), p.tokens.data(), p.want_counts.data(),
-               p.wants.data(), n_cap, s_cap, width, r_cap, padded, pad_pages, scratch_slot};
+               p.wants.data(), p.has_unknown ? p.token_src.data() : nullptr, n_cap, s_cap, width, r_cap, padded,
+               pad_pages, scratch_slot};
     return pack(*k->cache, a, out, info);
 }
 // What the step function does after it ran the planned step: every entry's request has

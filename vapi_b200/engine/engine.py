@@ -11,12 +11,12 @@ from __future__ import annotations
 
 import time
 from dataclasses import dataclass, field
-from typing import Callable, Dict, List, Optional, Sequence
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from ..sampling.params import FinishReason, SamplingParams
-from ..sampling.sampler import Sampler, SamplerState
+from ..sampling.sampler import PendingSample, Sampler, SamplerState
 from .runner import ModelRunner
 from .scheduler import AdmitError, Scheduler, SchedulerConfig, SeqStatus, StepPlan
 
@@ -46,6 +46,7 @@ class EngineStats:
     tokens_out: int = 0
     preemptions: int = 0
     failed_steps: int = 0
+    ahead_steps: int = 0          # steps that were enqueued before the step before them had been read
     schedule_ms: float = 0.0
     forward_ms: float = 0.0
     sample_ms: float = 0.0
@@ -53,8 +54,16 @@ class EngineStats:
 
 
 class Engine:
+    """``run_ahead`` (on by default on a CUDA device): while every live request is decided on the
+    device alone (greedy, or temperature without truncation or penalties), a step is enqueued
+    before the tokens of the step before it have been read: its input tokens are fetched on the
+    device from that step's sampled output, and the host reads results one step late, while
+    the next step already runs.  ``step()`` then reports the tokens of the step before.  The
+    tokens are the same as without it; a request that ends on EOS or a stop id has taken part
+    in one more step, whose result for it is dropped."""
+
     def __init__(self, runner: ModelRunner, cfg: Optional[SchedulerConfig] = None, *,
-                 max_step_failures: int = 3, use_graphs: bool = True):
+                 max_step_failures: int = 3, use_graphs: bool = True, run_ahead: Optional[bool] = None):
         self.runner = runner
         cfg = cfg or SchedulerConfig()
         cfg.max_context = min(cfg.max_context, runner.max_context)
@@ -70,6 +79,10 @@ class Engine:
         self._failures_in_a_row = 0
         self.last_error: Optional[str] = None
         self.use_graphs = use_graphs
+        on_cuda = torch.device(runner.device).type == "cuda"
+        self.run_ahead = on_cuda if run_ahead is None else (bool(run_ahead) and on_cuda)
+        self._inflight: Optional[Tuple[StepPlan, PendingSample]] = None
+        self._needs_host: set = set()          # live requests whose rows the host has to sample
         #: replaceable in tests: the function that runs a planned batch and returns logits
         self.step_fn: Callable[[StepPlan], Optional[torch.Tensor]] = self._run
 
@@ -84,13 +97,15 @@ class Engine:
         if params.has_penalties:
             st.observe_all(prompt)
         self.states[sid] = st
+        if not Sampler.device_only(params):
+            self._needs_host.add(sid)
         return sid
 
     def cancel(self, sid: int) -> None:
         self.scheduler.cancel(sid)
 
     def is_idle(self) -> bool:
-        return self.scheduler.is_idle() and not self.scheduler.finished
+        return self.scheduler.is_idle() and not self.scheduler.finished and self._inflight is None
 
     # ---- one step ---------------------------------------------------------------------
     def _run(self, plan: StepPlan) -> Optional[torch.Tensor]:
@@ -100,15 +115,43 @@ class Engine:
                 return out
         return self.runner.step(None, plan=plan)
 
+    def _can_run_ahead(self) -> bool:
+        return self.run_ahead and not self._needs_host and self.scheduler.can_run_ahead()
+
+    def _resolve(self, plan: StepPlan, pending: PendingSample, out: StepOutput) -> None:
+        """Read a step's sampled tokens, hand them to the scheduler and report them."""
+        toks = self.sampler.finish(pending)
+        took = self.scheduler.resolve(plan, toks)
+        for sid, tok, ok in zip(plan.sampled_seqs, toks, took):
+            if not ok:
+                continue
+            st = self.states.get(sid)
+            if st is not None:
+                st.observe(tok)
+            seq = self.scheduler.seqs.get(sid)
+            if seq is not None:
+                out.new_tokens[seq.request_id] = tok
+        self.stats.tokens_out += sum(took)
+
+    def _settle(self, out: StepOutput) -> None:
+        """Resolve the step in flight, if there is one."""
+        if self._inflight is not None:
+            plan, pending = self._inflight
+            self._inflight = None
+            self._resolve(plan, pending, out)
+
     def step(self) -> StepOutput:
         out = StepOutput()
         t0 = time.perf_counter()
+        if self._inflight is not None and not self._can_run_ahead():
+            self._settle(out)
         plan = self.scheduler.schedule()
         t1 = time.perf_counter()
         out.preempted = len(plan.preempted)
         self.stats.preemptions += out.preempted
         self.stats.schedule_ms += (t1 - t0) * 1e3
         if plan.is_empty():
+            self._settle(out)
             out.finished = self._drain()
             return out
         out.did_work = True
@@ -116,30 +159,40 @@ class Engine:
         try:
             logits = self.step_fn(plan)
             t2 = time.perf_counter()
-            sampled: List[int] = []
-            if plan.sampled_seqs:
-                rows = [(self.scheduler.seqs[s].params, self.states[s]) for s in plan.sampled_seqs]
-                sampled = self.sampler.sample(logits, rows)
+            rows = [(self.scheduler.seqs[s].params, self.states[s]) for s in plan.sampled_seqs]
+            ahead = (self.run_ahead and not self._needs_host and logits is not None and logits.is_cuda
+                     and bool(rows))
+            if not rows:
+                pending = PendingSample(0, tokens=[])
+            elif ahead:
+                pending = self.sampler.launch(logits, rows, self.runner.sampled)
+            else:
+                self._settle(out)        # the host needs this step's logits: nothing may be ahead of it
+                pending = PendingSample(len(rows), tokens=self.sampler.sample(logits, rows))
+            self.scheduler.advance(plan)
             t3 = time.perf_counter()
         except Exception as exc:
             self.last_error = f"{type(exc).__name__}: {exc}"
             self.stats.failed_steps += 1
             self._failures_in_a_row += 1
+            self._inflight = None
             self.scheduler.fail_all()
             out.finished = self._drain()
             if self._failures_in_a_row >= self.max_step_failures:
                 raise
             return out
         self._failures_in_a_row = 0
-        for sid, tok in zip(plan.sampled_seqs, sampled):
-            self.states[sid].observe(tok)
-            out.new_tokens[self.scheduler.seqs[sid].request_id] = tok
-        self.scheduler.commit(plan, sampled)
+        if self._inflight is not None:
+            self.stats.ahead_steps += 1
+        self._settle(out)
+        if ahead:
+            self._inflight = (plan, pending)
+        else:
+            self._resolve(plan, pending, out)
         t4 = time.perf_counter()
         st = self.stats
         st.steps += 1
         st.tokens_in += plan.num_tokens
-        st.tokens_out += len(sampled)
         st.forward_ms += (t2 - t1) * 1e3
         st.sample_ms += (t3 - t2) * 1e3
         st.commit_ms += (t4 - t3) * 1e3
@@ -150,6 +203,7 @@ class Engine:
         done = []
         for seq in self.scheduler.drain_finished():
             self.states.pop(seq.seq_id, None)
+            self._needs_host.discard(seq.seq_id)
             done.append(Finished(seq.request_id, seq.prompt_len, seq.generated, seq.finish_reason, seq.preemptions))
         return done
 

@@ -70,6 +70,9 @@ class ModelRunner:
         self.packer = StepPacker(self.cache, self.device, self.max_batched_tokens,
                                  max(max_requests, 1) , width)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        #: the tokens the last step sampled on the device, one per wanted row.  A step that is
+        #: enqueued before the host has read them takes its input tokens from here.
+        self.sampled = torch.zeros(max(256, max_requests), dtype=torch.int32, device=self.device)
         # one CacheView skeleton per run-order entry
         self._site_of: List[Optional[int]] = []
         for i, call in enumerate(plan.order):
@@ -149,6 +152,8 @@ class ModelRunner:
         """Device work of a step for a prepared context; returns float32 logits [rows, vocab]
         or None when no logits are wanted (the caches are written either way)."""
         plan = self.plan
+        if ctx.unknown_tokens:
+            ops.resolve_tokens(ctx.tokens, ctx.token_src, self.sampled, self.status)
         for pe in plan.position_encodings:
             ctx.pos[pe.name] = pe.prepare(ctx)
         views = self.views(ctx)
@@ -251,6 +256,7 @@ class ModelRunner:
         width = self.packer.max_width
         ctx = self.packer.pack([], self.dtype, n_cap=B, s_cap=B, width=width, status=self.status)
         ctx.max_k = self.max_context
+        ctx.unknown_tokens = True       # the captured step always looks: token_src says where
         ctx.attention_splits = self._decode_splits(B)
         cur = torch.cuda.current_stream()
         side = torch.cuda.Stream()

@@ -153,10 +153,13 @@ class StepPlan:
     """The step the scheduler has planned.  The arrays live in the host runtime, which packs
     them for the device itself; ``entries`` builds the Python view of them on demand."""
 
-    def __init__(self, sched: Optional["Scheduler"] = None, info: Seq[int] = (0,) * 8):
+    def __init__(self, sched: Optional["Scheduler"] = None, info: Seq[int] = (0,) * 9):
         self._sched = sched
-        (self.num_entries, self.num_tokens, self.num_rows, n_pre, n_start, pure, self.width_needed, _) = info
+        (self.num_entries, self.num_tokens, self.num_rows, n_pre, n_start, pure, self.width_needed, _,
+         unknown) = info
         self.pure_decode = bool(pure)
+        #: some token of this step is what the step before it samples and is not known yet
+        self.has_unknown = bool(unknown)
         self.handle = sched._h if sched is not None else None
         self.batch_seqs: List[int] = sched._list(_L_SEQS, self.num_entries) if self.num_entries else []
         self.sampled_seqs: List[int] = sched._list(_L_SAMPLED, self.num_rows) if self.num_rows else []
@@ -207,7 +210,7 @@ class Scheduler:
         eos = hostlib.i32(list(self.eos) or [0])
         self._h = self._lib.vs_new(cache.native, int(cfg.max_concurrent_seqs), int(cfg.max_batched_tokens),
                                    int(cfg.prefill_chunk_tokens), int(cfg.max_context), eos.ctypes.data, len(self.eos))
-        self._info = np.zeros(8, dtype=np.int32)
+        self._info = np.zeros(9, dtype=np.int32)
         self._buf = np.zeros(1024, dtype=np.int32)
         self._seen_finished = 0
         self._serial = 0
@@ -314,6 +317,36 @@ class Scheduler:
             raise RuntimeError(hostlib.last_error())
         if self._lib.vs_counts(self._h, 2) != self._seen_finished:
             self._note_finished()
+
+    # ---- one step ahead ----------------------------------------------------------------
+    def advance(self, plan: StepPlan) -> None:
+        """The part of ``commit`` that does not depend on what was sampled: the requests of the
+        planned step have computed their tokens, and each that asked for logits gains a token
+        whose value is still unknown.  The next step can be planned after this."""
+        if self._lib.vs_advance(self._h) != 0:
+            raise RuntimeError(hostlib.last_error())
+
+    def resolve(self, plan: StepPlan, sampled: Seq[int]) -> List[bool]:
+        """The values of the tokens an advanced step produced, in the order of its
+        ``sampled_seqs``; retires what finished.  Returns, per token, whether its request took
+        it (a request that ended at an earlier token does not)."""
+        assert len(sampled) == len(plan.sampled_seqs)
+        took: List[bool] = []
+        if sampled:
+            ids = hostlib.i32(plan.sampled_seqs)
+            arr = hostlib.i32([int(t) for t in sampled])
+            acc = np.zeros(len(sampled), dtype=np.int32)
+            self._lib.vs_resolve(self._h, ids.ctypes.data, arr.ctypes.data, len(sampled), acc.ctypes.data)
+            took = acc.astype(bool).tolist()
+        if self._lib.vs_counts(self._h, 2) != self._seen_finished:
+            self._note_finished()
+        return took
+
+    def can_run_ahead(self) -> bool:
+        """Whether the next step can be planned before the last one's tokens are known: no
+        running request can run out of pages in it (a preemption would have to recompute
+        tokens that are not known yet)."""
+        return bool(self._lib.vs_can_run_ahead(self._h))
 
     def finish(self, sid: int, reason: FinishReason) -> None:
         self._lib.vs_finish(self._h, int(sid), _REASON_CODES[reason])

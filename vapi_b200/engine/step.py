@@ -60,6 +60,8 @@ class StepContext:
     dtype: torch.dtype
     status: Optional[torch.Tensor] = None
     attention_splits: Optional[int] = None
+    token_src: Optional[torch.Tensor] = None   # [n] int32: >= 0 where a token is a row of the last sampled output
+    unknown_tokens: bool = False    # some token_src is >= 0: fetch those tokens on the device first
     rows_identity: bool = False     # the wanted rows are exactly rows 0 .. n-1 in order
     fused: bool = False             # a step of few rows: norms and adds ride on the matrix products
     pos: Dict[str, Any] = field(default_factory=dict)
@@ -150,7 +152,8 @@ class StepPacker:
             raw = np.zeros(self._lib.vh_layout_len(G), dtype=np.int32)
             self._lib.vh_layout(G, n_cap, s_cap, width, r_cap, raw.ctypes.data)
             names = (["cu_q", "seqlens_k", "state_slots"] + [f"table{g}" for g in range(G)]
-                     + ["tokens", "positions", "tok_seq"] + [f"slots{g}" for g in range(G)] + ["rows", "_total"])
+                     + ["tokens", "positions", "tok_seq"] + [f"slots{g}" for g in range(G)]
+                     + ["rows", "token_src", "_total"])
             lay = dict(zip(names, raw.tolist()))
             if len(self._layouts) > 256:
                 self._layouts.clear()
@@ -233,7 +236,8 @@ class StepPacker:
             cu_q=view("cu_q", s_eff + 1), seqlens_k=view("seqlens_k", s_eff),
             state_slots=view("state_slots", s_eff),
             logits_rows=view("rows", num_rows) if num_rows else None,
-            groups=groups, dtype=dtype, status=status, rows_identity=bool(identity) and num_rows == n_eff)
+            groups=groups, dtype=dtype, status=status, rows_identity=bool(identity) and num_rows == n_eff,
+            token_src=view("token_src", n_eff), unknown_tokens=bool(plan is not None and plan.has_unknown))
 
     # a page per group that padding rows may scribble on; set by whoever captures graphs
     _pad_pages: Optional[List[int]] = None

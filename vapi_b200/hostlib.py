@@ -38,6 +38,7 @@ _SIGNATURES = {
     "vs_commit": (_I, [_P, _P, _I]), "vs_finish": (None, [_P, _I, _I]), "vs_fail_all": (_I, [_P, _P, _I]),
     "vs_list": (_I, [_P, _I, _P, _I]), "vs_plan_info": (None, [_P, _P]),
     "vs_pack_plan": (_I, [_P, _I, _I, _I, _I, _I, _P, _I, _P, _P]),
+    "vs_advance": (_I, [_P]), "vs_resolve": (_I, [_P, _P, _P, _I, _P]), "vs_can_run_ahead": (_I, [_P]),
     "vs_commit_cache": (_I, [_P]), "vs_clear_finished": (None, [_P]), "vs_erase": (None, [_P, _I]), "vs_seq_get": (_I, [_P, _I, _I]),
     "vs_seq_tokens": (_I, [_P, _I, _I, _P, _I]), "vs_counts": (_I, [_P, _I]),
 }

@@ -134,6 +134,19 @@ def add_residual_ss(x: torch.Tensor, delta: torch.Tensor, next_weight: torch.Ten
     return ss, xw
 
 
+def resolve_tokens(tokens: torch.Tensor, src: torch.Tensor, prev: torch.Tensor,
+                   status: Optional[torch.Tensor] = None) -> None:
+    """In place: ``tokens[i] = prev[src[i]]`` wherever ``src[i] >= 0`` (tokens that the step before
+    sampled and the host has not read yet)."""
+    _cuda(tokens, src, prev)
+    for t, w in ((tokens, "tokens"), (src, "token sources"), (prev, "sampled tokens")):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError(f"{w} must be contiguous int32")
+    lib = _lib("elementwise")
+    _check(lib, lib.vapi_resolve_tokens(_p(tokens), _p(src), _p(prev), tokens.numel(), prev.numel(), _p(status),
+                                        _stream()))
+
+
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x += delta`` (when given) and ``out = rmsnorm(x) * weight``; x is the float32 stream.

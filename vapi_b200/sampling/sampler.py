@@ -88,6 +88,15 @@ def host_sample(logits: np.ndarray, p: SamplingParams, state: SamplerState) -> i
     return int(ids[min(i, len(ids) - 1)])
 
 
+@dataclass
+class PendingSample:
+    """Tokens decided on the device and on their way to the host."""
+    rows: int
+    host: Optional[torch.Tensor] = None         # pinned int32 buffer the copy lands in
+    event: Optional["torch.cuda.Event"] = None
+    tokens: Optional[List[int]] = None          # set when the tokens are already on the host
+
+
 class Sampler:
     """Decides the tokens of a step's rows.  Holds small persistent device buffers so that
     a step costs one upload, one launch (two with penalties) and one download."""
@@ -97,6 +106,55 @@ class Sampler:
         self.max_rows = int(max_rows)
         self.d2h_bytes_last = 0
         self.h2d_bytes_last = 0
+        self._ring: List[list] = []
+        self._next = 0
+
+    @staticmethod
+    def device_only(p: SamplingParams) -> bool:
+        """Whether a row with these parameters is decided by the device launch alone (greedy, or
+        temperature without truncation) and needs nothing of the host but the result."""
+        return (p.is_greedy or p.device_drawable) and not p.has_penalties
+
+    def launch(self, logits: torch.Tensor, rows: Sequence[Tuple[SamplingParams, SamplerState]],
+               out: torch.Tensor) -> PendingSample:
+        """For rows that are all :meth:`device_only`: decide them on the device into ``out`` and
+        start the copy to the host without waiting for it."""
+        R = len(rows)
+        assert logits.shape[0] >= R and all(self.device_only(p) for p, _ in rows)
+        dev = logits.device
+        self.h2d_bytes_last = 0
+        if all(p.is_greedy for p, _ in rows):
+            ops.sample_rows(logits[:R], out=out[:R])
+        else:
+            m64 = torch.empty((2, R), dtype=torch.int64)
+            for r, (p, st) in enumerate(rows):
+                m64[0, r] = st.seed - (1 << 64) if st.seed >= (1 << 63) else st.seed
+                m64[1, r] = st.device_draws
+                if not p.is_greedy:
+                    st.device_draws += 1
+            mode = torch.tensor([1 if p.is_greedy else 2 for p, _ in rows], dtype=torch.int32).to(dev)
+            inv_t = torch.tensor([p.inv_temperature for p, _ in rows], dtype=torch.float32).to(dev)
+            m64d = m64.to(dev)
+            ops.sample_rows(logits[:R], mode, inv_t, m64d[0], m64d[1], out=out[:R])
+            self.h2d_bytes_last += R * 24
+        if not self._ring:
+            for _ in range(3):
+                self._ring.append([torch.zeros(max(self.max_rows, out.numel()), dtype=torch.int32, pin_memory=True),
+                                   torch.cuda.Event()])
+        host, event = self._ring[self._next]
+        self._next = (self._next + 1) % len(self._ring)
+        host[:R].copy_(out[:R], non_blocking=True)
+        event.record(torch.cuda.current_stream())
+        self.d2h_bytes_last = 4 * R
+        return PendingSample(R, host, event)
+
+    def finish(self, pending: PendingSample) -> List[int]:
+        """Wait for a launched sample and return its tokens."""
+        if pending.tokens is not None:
+            return pending.tokens
+        pending.event.synchronize()
+        pending.tokens = pending.host[:pending.rows].tolist()
+        return pending.tokens
 
     def sample(self, logits: torch.Tensor, rows: Sequence[Tuple[SamplingParams, SamplerState]]) -> List[int]:
         R = len(rows)
