@@ -286,6 +286,38 @@ def test_shortconv_portions_and_state(ops, dtype, L, bias, hidden):
             torch.testing.assert_close(state_gpu.cpu().float(), state_ref.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("L,bias,hidden", [(3, False, 2048), (4, True, 96), (2, False, 72), (5, True, 264), (8, False, 64),
+                                           (3, False, 100)])
+def test_shortconv_prompt_sized_steps(ops, dtype, L, bias, hidden):
+    """Steps of hundreds of tokens (token tiles for everything past the first L-1 tokens of a
+    portion, the per-token kernel for those and the state): portions that start in the middle
+    of a tile, a portion shorter than the state beside long ones, a second step that continues
+    from the state the first one left."""
+    torch.manual_seed(15)
+    state_ref = torch.full((4, max(L - 1, 1), hidden), 9.0).to(dtype)[:, :L - 1]
+    state_gpu = dev(state_ref.clone())
+    taps = torch.randn(L, hidden)
+    in_b = torch.randn(3 * hidden) if bias else None
+    cv_b = torch.randn(hidden) if bias else None
+    steps = [[(0, 0, 301), (1, 5, 2), (2, 0, 99)], [(0, 301, 257), (2, 99, 1), (1, 7, 43), (3, 0, 6)]]
+    for step in steps:
+        n = sum(q for _, _, q in step)
+        h3 = torch.randn(n, 3 * hidden).to(dtype)
+        cu, pos, tseq = [0], [], []
+        for i, (_, p0, q) in enumerate(step):
+            cu.append(cu[-1] + q)
+            pos += list(range(p0, p0 + q))
+            tseq += [i] * q
+        ss = torch.tensor([s for s, _, _ in step], dtype=torch.int32)
+        cu_t, pos_t, ts_t = (torch.tensor(v, dtype=torch.int32) for v in (cu, pos, tseq))
+        want = plain_ops.shortconv(h3, in_b, taps, cv_b, state_ref, ss, ts_t, cu_t, pos_t)
+        got = ops.shortconv(dev(h3), dev(in_b), dev(taps), dev(cv_b), state_gpu, dev(ss), dev(ts_t), dev(cu_t),
+                            dev(pos_t))
+        torch.testing.assert_close(got.cpu().float(), want.float(), **tol(dtype))
+        torch.testing.assert_close(state_gpu.cpu().float(), state_ref.float(), **tol(dtype))
+
+
 def test_sample_rows_greedy_ties_and_gumbel(ops):
     torch.manual_seed(6)
     V = 1000

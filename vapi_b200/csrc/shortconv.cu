@@ -54,6 +54,28 @@ template <> struct Chan<__nv_bfloat16, 4> {
     }
 };
 
+template <> struct Chan<__nv_bfloat16, 8> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p);
+        const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+        unsigned w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 a = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<unsigned*>(&a);
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
 // g = (B + bias_B) * (x + bias_x) of one row, rounded to the storage type
 template <typename T, int V>
 __device__ __forceinline__ void gate_row(const T* __restrict__ h3, const float* __restrict__ in_bias,
@@ -93,9 +115,12 @@ __global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restri
                                  long long slot_stride, const int* __restrict__ state_slots,
                                  const int* __restrict__ tok_seq, const int* __restrict__ cu_q,
                                  const int* __restrict__ positions, T* __restrict__ out, int n,
-                                 int hidden, int L, int num_slots, int* __restrict__ status) {
+                                 int hidden, int L, int num_slots, int heads_only,
+                                 int* __restrict__ status) {
+    // heads_only: one block row per sequence, for its first L-1 tokens and its state (the
+    // other tokens are shortconv_tile_kernel's); else one block row per token
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
-    const int r = blockIdx.x;
+    const int r = heads_only ? cu_q[blockIdx.x] : blockIdx.x;
     pdl_trigger();
     if (c >= hidden || r >= n) {
         pdl_wait();
@@ -104,9 +129,13 @@ __global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restri
     // Everything read up to pdl_wait() was written before this step's first kernel began
     // (index data copied from the host, weights, the state the previous step left), so it can
     // be fetched while the kernel before this one is still finishing.
-    const int s = tok_seq[r];
+    const int s = heads_only ? (int)blockIdx.x : tok_seq[r];
     const int r0 = cu_q[s], q = cu_q[s + 1] - r0;
     const int i = r - r0;
+    if (q <= 0) {       // (a sequence without tokens in this step)
+        pdl_wait();
+        return;
+    }
     float w[CONV_LMAX][V];
 #pragma unroll
     for (int k = 0; k < CONV_LMAX; ++k)
@@ -131,7 +160,7 @@ __global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restri
     }
     pdl_wait();
 
-    if (i >= L - 1) {
+    if (i >= L - 1 && !heads_only) {
         // every tap lies inside this step's rows
         float acc[V];
 #pragma unroll
@@ -194,10 +223,83 @@ __global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restri
     }
 }
 
+// Prompt portions: the tokens at index >= L-1 of their portion need nothing but rows of this
+// step.  One thread takes TT consecutive tokens of V channels, so the L-1 predecessor rows are
+// computed once per tile instead of once per token and all of a thread's loads are in flight
+// together.  Tokens nearer to the start of their portion (and the state) are left to
+// shortconv_kernel in its heads_only form.
+template <typename T, int V, int LT, int TT>
+__global__ void shortconv_tile_kernel(const T* __restrict__ h3, const float* __restrict__ in_bias,
+                                      const float* __restrict__ taps, const float* __restrict__ conv_bias,
+                                      const int* __restrict__ tok_seq, const int* __restrict__ cu_q,
+                                      T* __restrict__ out, int n, int hidden) {
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+    const int r0 = blockIdx.x * TT;
+    pdl_trigger();
+    if (c >= hidden) {
+        pdl_wait();
+        return;
+    }
+    bool mine[TT], any = false;
+#pragma unroll
+    for (int t = 0; t < TT; ++t) {
+        const int r = r0 + t;
+        mine[t] = r < n && (r - cu_q[tok_seq[r < n ? r : n - 1]]) >= LT - 1;
+        any = any || mine[t];
+    }
+    float w[LT][V];
+#pragma unroll
+    for (int k = 0; k < LT; ++k)
+#pragma unroll
+        for (int v = 0; v < V; ++v) w[k][v] = taps[(size_t)k * hidden + c + v];
+    pdl_wait();
+    if (!any) return;
+    float g[TT + LT - 1][V];
+#pragma unroll
+    for (int j = 0; j < TT + LT - 1; ++j) {
+        const int row = r0 - (LT - 1) + j;
+        if (row >= 0 && row < n) {
+            gate_row<T, V>(h3, in_bias, (size_t)row, c, hidden, g[j]);
+        } else {
+#pragma unroll
+            for (int v = 0; v < V; ++v) g[j][v] = 0.f;
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < TT; ++t) {
+        if (!mine[t]) continue;
+        float acc[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v] = 0.f;
+#pragma unroll
+        for (int k = 0; k < LT; ++k)
+#pragma unroll
+            for (int v = 0; v < V; ++v) acc[v] += w[k][v] * g[t + k][v];
+        emit<T, V>(h3, in_bias, conv_bias, out, (size_t)(r0 + t), c, hidden, acc);
+    }
+}
+
+template <typename T, int V>
+static cudaError_t launch_tiles(int L, dim3 grid, int threads, cudaStream_t stream, const void* h3,
+                                const float* in_bias, const float* taps, const float* conv_bias,
+                                const int* tok_seq, const int* cu_q, void* out, int n, int hidden) {
+#define SC_TILE(LT)                                                                                    \
+    return launch(shortconv_tile_kernel<T, V, LT, 4>, grid, threads, 0, stream, (const T*)h3, in_bias, taps, \
+                  conv_bias, tok_seq, cu_q, (T*)out, n, hidden)
+    switch (L) {
+        case 2: SC_TILE(2);
+        case 3: SC_TILE(3);
+        case 4: SC_TILE(4);
+        case 5: SC_TILE(5);
+    }
+#undef SC_TILE
+    return cudaErrorInvalidValue;
+}
+
 VAPI_EXPORT int vapi_shortconv(const void* h3, int dtype, const float* in_bias, const float* taps,
                                const float* conv_bias, void* state, long long slot_stride,
                                const int* state_slots, const int* tok_seq, const int* cu_q,
-                               const int* positions, void* out, int n, int hidden, int L,
+                               const int* positions, void* out, int n, int num_seqs, int hidden, int L,
                                int num_slots, int* status, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (L < 1 || L > CONV_LMAX)
@@ -210,16 +312,28 @@ VAPI_EXPORT int vapi_shortconv(const void* h3, int dtype, const float* in_bias, 
     const int per = vec ? 4 : 1;
     const int cblocks = (hidden / per + threads - 1) / threads;
     if (cblocks > 65535) return fail(-1, "shortconv: hidden=%d is too wide for the grid", hidden);
-    dim3 grid(n, cblocks);
+    // prompt-sized steps: tiles of tokens for everything past the first L-1 tokens of a portion,
+    // and the per-token kernel only for those first tokens and the state
+    const int tile_v = dtype == VAPI_BF16 ? 8 : 4;
+    const bool tiled = n >= 256 && num_seqs > 0 && num_seqs * 8 <= n && L >= 2 && L <= 5 && hidden % tile_v == 0;
+    const int heads_only = tiled ? 1 : 0;
+    dim3 grid(tiled ? num_seqs : n, cblocks);
     cudaError_t e;
 #define SC_LAUNCH(T, V)                                                                            \
     e = launch(shortconv_kernel<T, V>, grid, threads, 0, stream, (const T*)h3, in_bias, taps, conv_bias, \
                (T*)state, slot_stride, state_slots, tok_seq, cu_q, positions, (T*)out, n, hidden, L,      \
-               num_slots, status)
+               num_slots, heads_only, status)
     if (dtype == VAPI_F32) { if (vec) SC_LAUNCH(float, 4); else SC_LAUNCH(float, 1); }
     else if (dtype == VAPI_BF16) { if (vec) SC_LAUNCH(__nv_bfloat16, 4); else SC_LAUNCH(__nv_bfloat16, 1); }
     else return fail(-2, "shortconv: unsupported dtype %d", dtype);
 #undef SC_LAUNCH
+    if (e == cudaSuccess && tiled) {
+        dim3 tgrid((n + 3) / 4, (hidden / tile_v + threads - 1) / threads);
+        if (dtype == VAPI_F32)
+            e = launch_tiles<float, 4>(L, tgrid, threads, stream, h3, in_bias, taps, conv_bias, tok_seq, cu_q, out, n, hidden);
+        else
+            e = launch_tiles<__nv_bfloat16, 8>(L, tgrid, threads, stream, h3, in_bias, taps, conv_bias, tok_seq, cu_q, out, n, hidden);
+    }
     return check_launch("shortconv", e);
 }
 
