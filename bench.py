@@ -35,7 +35,23 @@ LFM2_1P2B = {
     "tie_word_embeddings": True, "max_position_embeddings": 128000,
     "layer_types": ["full_attention" if l in (2, 5, 8, 10, 12, 14) else "conv" for l in range(16)],
 }
-FULL_LAYERS = 16
+
+
+def lfm2_sizes(name):
+    """The other two sizes the benchmark configurations name (random weights, so only the layer
+    sizes matter).  The 2.6B stack has 8 attention layers among 30; they are spread evenly here."""
+    cfg = dict(LFM2_1P2B)
+    if name == "1.2b":
+        return cfg
+    if name == "700m":
+        cfg.update(hidden_size=1536, intermediate_size=10240, num_attention_heads=24)
+        return cfg
+    if name == "2.6b":
+        attn = (2, 6, 10, 14, 18, 21, 24, 27)
+        cfg.update(intermediate_size=10752, num_hidden_layers=30,
+                   layer_types=["full_attention" if l in attn else "conv" for l in range(30)])
+        return cfg
+    raise ValueError(name)
 
 
 def peaks():
@@ -127,9 +143,12 @@ def run(args):
     from vapi_b200.sampling.params import SamplingParams
 
     pk = peaks()
-    cfg = dict(LFM2_1P2B)
-    layers = args.layers or FULL_LAYERS
-    if layers != FULL_LAYERS:
+    cfg = lfm2_sizes(args.sizes)
+    full_layers = cfg["num_hidden_layers"]
+    layers = args.layers or full_layers
+    if args.only == "serve":
+        return serve(args, cfg)
+    if layers != full_layers:
         cfg["num_hidden_layers"] = layers
         cfg["layer_types"] = cfg["layer_types"][:layers]
     ctx_len, B = args.context, args.batch
@@ -257,14 +276,14 @@ def run(args):
           f"commit {st.commit_ms / st.steps:.3f}", file=sys.stderr, flush=True)
 
     line = {
-        "metric": "LFM2-1.2B decode tokens/s (batch %d, context %d), random weights" % (B, ctx_len),
+        "metric": "LFM2-%s decode tokens/s (batch %d, context %d), random weights" % (args.sizes.upper(), B, ctx_len),
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded uniform-random token ids, random-init weights N(0, 0.02))",
         "impl": "vapi_b200",
         "config": {
-            "model": "LFM2-1.2B sizes", "global_batch": B, "seq_len": ctx_len, "parallelism": "single GPU",
-            "layers": layers, "layers_of_configuration": FULL_LAYERS, "attention_layers": n_attn,
+            "model": "LFM2-%s sizes" % args.sizes.upper(), "global_batch": B, "seq_len": ctx_len, "parallelism": "single GPU",
+            "layers": layers, "layers_of_configuration": full_layers, "attention_layers": n_attn,
             "hidden_size": c.hidden_size, "intermediate_size": c.intermediate_size, "vocab_size": c.vocab_size,
             "heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads, "head_dim": c.head_dim,
             "conv_L_cache": c.conv_L_cache, "page_size": page, "cuda_graphs": True,
@@ -280,6 +299,51 @@ def run(args):
         "points": points,
     }
     print(json.dumps(line), flush=True)
+    return 0
+
+
+def serve(args, cfg):
+    """Continuous batching: --requests requests with random prompt lengths 128..2,048 arrive at
+    once, each generates --max-tokens tokens (greedy); everything goes through the engine loop.
+    One JSON line: generated tokens per second and all tokens (prompt + generated) per second."""
+    import torch
+    from vapi_b200.engine.engine import Engine
+    from vapi_b200.engine.runner import ModelRunner
+    from vapi_b200.engine.scheduler import SchedulerConfig
+    from vapi_b200.sampling.params import SamplingParams
+    R, ctx = args.requests, args.context
+    page = ModelRunner.default_page_size
+    runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0",
+                                     num_pages=R * (-(-(2048 + args.max_tokens + 1) // page)) + 8, max_requests=R,
+                                     max_batched_tokens=8192, max_context=ctx, validate=False)
+    eng = Engine(runner, SchedulerConfig(max_concurrent_seqs=R, max_batched_tokens=8192, prefill_chunk_tokens=2048,
+                                         max_context=ctx))
+    gen = torch.Generator().manual_seed(7)
+    lens = torch.randint(128, 2049, (R,), generator=gen).tolist()
+
+    def one_round(tag):
+        for i, n in enumerate(lens):
+            eng.admit((tag, i), torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist(),
+                      SamplingParams(temperature=0.0, max_tokens=args.max_tokens, ignore_eos=True))
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        done = eng.run()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        assert len(done) == R and all(len(f.tokens) == args.max_tokens for f in done), eng.last_error
+        return dt
+
+    one_round("warm")           # compiles nothing new afterwards: graphs of every bucket are captured
+    steps0 = eng.stats.steps
+    dt = one_round("timed")
+    runner.check_status()
+    out_toks, in_toks = R * args.max_tokens, sum(lens)
+    print(json.dumps({"only": "serve", "model": "LFM2-%s sizes" % args.sizes.upper(), "requests": R,
+                      "prompt_tokens": in_toks, "generated_tokens": out_toks, "seconds": round(dt, 4),
+                      "generated_tokens_per_s": round(out_toks / dt, 1),
+                      "all_tokens_per_s": round((in_toks + out_toks) / dt, 1),
+                      "steps": eng.stats.steps - steps0, "preemptions": eng.stats.preemptions,
+                      "steps_ahead": eng.stats.ahead_steps}), flush=True)
     return 0
 
 
@@ -342,8 +406,12 @@ def main():
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0 = all)")
     ap.add_argument("--impl", default="vapi_b200", choices=["vapi_b200", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
-                    help="profiling aid: run just the headline decode point, or just the prefill")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "serve"],
+                    help="run just the headline decode point, just the prefill, or (serve) continuous "
+                         "batching of --requests requests with random prompt lengths through the engine loop")
+    ap.add_argument("--sizes", default="1.2b", choices=["1.2b", "700m", "2.6b"], help="layer sizes of LFM2-<sizes>")
+    ap.add_argument("--requests", type=int, default=64)
+    ap.add_argument("--max-tokens", type=int, default=128)
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
