@@ -312,3 +312,129 @@ def test_a_toy_mixer_with_its_own_state_can_be_registered_built_and_stepped(tmp_
     finally:
         unregister_architecture("ToyForCausalLM")
         MIXERS.pop("toy_running_mean", None)
+
+
+# ---- a toy feed-forward with routing and a toy position encoding -----------------------------
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_can_be_registered_built_and_stepped(tmp_path):
+    """Two more kinds of part defined here, neither of them a model of anyone's: a feed-forward
+    that routes each token to one of several small experts (router logits and softmax in
+    float32), and a position encoding that hands mixers a table of sines which a toy mixer adds to
+    its input.  They sit in one plan beside the package's own attention (with its rotary
+    encoding: two position encodings in one model), in layers of different kinds, and are stepped
+    whole, in portions and token by token through the package's step function."""
+    from vapi_b200.config import Architecture, register_architecture, unregister_architecture
+    from vapi_b200.engine.runner import ModelRunner
+    from vapi_b200.engine.step import StepEntry
+    from vapi_b200.models.plan import LayerCall, ModelPlan
+    from vapi_b200.parts import (FEED_FORWARDS, MIXERS, POSITION_ENCODINGS, FeedForward, GQAttention, Mixer, OutputHead,
+                                 PositionEncoding, PreNormBlock, RMSNorm, RotaryEncoding, SwiGLU, TensorSpec,
+                                 TokenEmbedding, make_part, register_feed_forward, register_mixer,
+                                 register_position_encoding)
+    from vapi_b200.weights import write_random_model
+
+    class TopOneExperts(FeedForward):
+        def __init__(self, hidden, width, experts):
+            self.hidden, self.width, self.experts = hidden, width, experts
+
+        def tensor_specs(self, prefix):
+            return [TensorSpec(prefix + "router", (self.experts, self.hidden)),
+                    TensorSpec(prefix + "up", (self.experts * self.width, self.hidden)),
+                    TensorSpec(prefix + "down", (self.experts * self.hidden, self.width))]
+
+        def bind(self, tensors, prefix, dtype):
+            self.router = tensors[prefix + "router"].float()
+            self.up = tensors[prefix + "up"].view(self.experts, self.width, self.hidden)
+            self.down = tensors[prefix + "down"].view(self.experts, self.hidden, self.width)
+
+        def forward(self, f, ctx):
+            prob = torch.softmax(f.float() @ self.router.t(), dim=-1)              # routing in float32
+            top_p, top_e = prob.max(dim=-1)
+            out = torch.zeros_like(f)
+            for e in range(self.experts):
+                rows = (top_e == e).nonzero().flatten()
+                if rows.numel():
+                    h = torch.relu(f[rows] @ self.up[e].t())
+                    out[rows] = ((h @ self.down[e].t()).float() * top_p[rows, None]).to(f.dtype)
+            return out
+
+    class SineTable(PositionEncoding):
+        def __init__(self, hidden, name="sines"):
+            self.hidden, self.name = hidden, name
+
+        def tensor_specs(self, prefix):
+            return []
+
+        def bind(self, tensors, prefix, dtype):
+            pass
+
+        def prepare(self, ctx):
+            freq = torch.arange(1, self.hidden + 1, device=ctx.positions.device, dtype=torch.float32) / self.hidden
+            return torch.sin(ctx.positions.float()[:, None] * freq[None, :])
+
+    class AddPositions(Mixer):
+        def __init__(self, hidden, pos):
+            self.hidden, self.pos = hidden, pos
+
+        def tensor_specs(self, prefix):
+            return [TensorSpec(prefix + "gain", (self.hidden,), role="vector", init="ones")]
+
+        def bind(self, tensors, prefix, dtype):
+            self.gain = tensors[prefix + "gain"]
+
+        def forward(self, a, ctx, cache):
+            return ((a.float() + ctx.pos[self.pos]) * self.gain).to(a.dtype)
+
+    register_feed_forward("toy_top_one_experts", TopOneExperts, replace=True)
+    register_position_encoding("toy_sine_table", SineTable, replace=True)
+    register_mixer("toy_add_positions", AddPositions, replace=True)
+
+    def plan(cfg):
+        H, V, E = cfg["hidden_size"], cfg["vocab_size"], cfg["experts"]
+        emb = TokenEmbedding(V, H, "emb.weight")
+        sub = {"mixer_norm": "n1.", "mixer": "mix.", "ffn_norm": "n2.", "ffn": "ffn."}
+        layers = [
+            PreNormBlock(RMSNorm(H, 1e-5), make_part(MIXERS, "toy_add_positions", hidden=H, pos="sines"), RMSNorm(H, 1e-5),
+                         make_part(FEED_FORWARDS, "toy_top_one_experts", hidden=H, width=40, experts=E), sub),
+            PreNormBlock(RMSNorm(H, 1e-6), GQAttention(H, 3, 1, 16, qk_norm_eps=1e-6, pos="rope"), RMSNorm(H, 1e-6),
+                         SwiGLU(H, 80), sub),
+            PreNormBlock(RMSNorm(H, 1e-5), make_part(MIXERS, "toy_add_positions", hidden=H, pos="sines"), RMSNorm(H, 1e-5),
+                         make_part(FEED_FORWARDS, "toy_top_one_experts", hidden=H, width=40, experts=E), sub),
+        ]
+        return ModelPlan("ToyRoutedForCausalLM", V, H, 512, emb, layers, ["l0.", "l1.", "l2."],
+                         [LayerCall(0), LayerCall(1), LayerCall(2)], RMSNorm(H, 1e-5), "final.",
+                         OutputHead(V, H, True, emb),
+                         position_encodings=[RotaryEncoding(16, 10000.0, 512, "rope"),
+                                             make_part(POSITION_ENCODINGS, "toy_sine_table", hidden=H)])
+
+    register_architecture(Architecture("ToyRoutedForCausalLM", ("toy_routed",), lambda v: v, plan), replace=True)
+    try:
+        cfg = {"architectures": ["ToyRoutedForCausalLM"], "vocab_size": 90, "hidden_size": 48, "experts": 3}
+        d = write_random_model(str(tmp_path / "toy"), cfg, 1, std=0.3, norm_init="perturbed")
+        r = ModelRunner.from_dir(d, dtype="float32", num_pages=6, page_size=16, max_requests=3, max_batched_tokens=64,
+                                 max_context=128)
+        assert len(r.cache.paged) == 1 and not r.cache.state            # only the attention layer owns a cache
+        toks = torch.randint(0, 90, (37,), generator=torch.Generator().manual_seed(2)).tolist()
+        a = r.cache.open("whole")
+        assert r.cache.reserve(a, len(toks))
+        whole = r.step([StepEntry(a, toks, list(range(len(toks))))]).cpu()
+        r.cache.close(a)
+        # the routed feed-forward really routes: more than one expert is in use on these tokens
+        ffn = r.plan.layers[0].ffn
+        x = r.plan.embedding.forward(type("C", (), {"tokens": torch.tensor(toks, dtype=torch.int32, device="cuda"),
+                                                     "status": None})())
+        used = torch.softmax(x.float() @ ffn.router.t(), -1).argmax(-1).unique().numel()
+        assert used >= 2
+        b, other = r.cache.open("cut"), r.cache.open("other")
+        rows, pos = [], 0
+        for q in (2, 1, 9, 1, 1, 16, 7):
+            assert r.cache.reserve(b, pos + q) and r.cache.reserve(other, other.num_tokens + 2)
+            out = r.step([StepEntry(other, [5, 6], []), StepEntry(b, toks[pos:pos + q], list(range(q)))])
+            rows.append(out.cpu())
+            pos += q
+        assert (torch.cat(rows) - whole).abs().max() < 2e-4
+        r.check_status()
+    finally:
+        unregister_architecture("ToyRoutedForCausalLM")
+        MIXERS.pop("toy_add_positions", None)
+        FEED_FORWARDS.pop("toy_top_one_experts", None)
+        POSITION_ENCODINGS.pop("toy_sine_table", None)
