@@ -85,7 +85,7 @@ def test_add_rmsnorm(ops, dtype, hidden):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu(ops, dtype):
     torch.manual_seed(2)
-    for rows, ff in ((1, 8), (7, 24), (33, 1000), (5, 10), (3, 4099)):
+    for rows, ff in ((1, 8), (7, 24), (33, 1000), (5, 10), (3, 4099), (4, 2056)):
         g = (torch.randn(rows, 2 * ff) * 4).to(dtype)
         torch.testing.assert_close(ops.swiglu(dev(g)).cpu().float(), plain_ops.swiglu(g).float(), **tol(dtype))
 

@@ -326,6 +326,28 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ g, T* __restrict__ out, 
     }
 }
 
+// bfloat16, ff a multiple of 8: one thread per eight outputs of one row, 16-byte accesses, no
+// loop and no index division (the row is the block's y index)
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ g, __nv_bfloat16* __restrict__ out, int ff) {
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) << 3;
+    const size_t r = blockIdx.y;
+    pdl_trigger();
+    pdl_wait();
+    if (c >= ff) return;
+    const uint4 a = *reinterpret_cast<const uint4*>(g + r * 2 * ff + c);
+    const uint4 b = *reinterpret_cast<const uint4*>(g + r * 2 * ff + ff + c);
+    const unsigned aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+    unsigned o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
+        const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bw[i]));
+        __nv_bfloat162 y = __floats2bfloat162_rn(x.x / (1.f + expf(-x.x)) * u.x, x.y / (1.f + expf(-x.y)) * u.y);
+        o[i] = *reinterpret_cast<unsigned*>(&y);
+    }
+    *reinterpret_cast<uint4*>(out + r * ff + c) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 VAPI_EXPORT int vapi_swiglu(const void* g, void* out, int dtype, int rows, int ff,
                             cudaStream_t stream) {
     if (rows <= 0) return 0;
@@ -335,6 +357,12 @@ VAPI_EXPORT int vapi_swiglu(const void* g, void* out, int dtype, int rows, int f
     long long blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 32) blocks = 148 * 32;
     cudaError_t e;
+    if (dtype == VAPI_BF16 && ff % 8 == 0 && rows <= 65535) {
+        const int th = 128;
+        dim3 grid((ff / 8 + th - 1) / th, rows);
+        e = launch(swiglu_bf16x8_kernel, grid, th, 0, stream, (const __nv_bfloat16*)g, (__nv_bfloat16*)out, ff);
+        return check_launch("swiglu", e);
+    }
     if (ff % 4 == 0 && (dtype == VAPI_F32 || dtype == VAPI_BF16)) {
         long long vb = (total / 4 + threads - 1) / threads;
         if (vb > 148 * 16) vb = 148 * 16;
