@@ -248,6 +248,55 @@ def test_tensor_core_attention_is_refused_where_it_does_not_apply(ops):
         _attention_case(ops, nh=4, nkv=2, d=64, page=16, lens=[(1, 10)], **TC)
 
 
+# ---- the tcgen05 kernel for prompt portions (bfloat16, head_dim 64, pages of 64n) ----
+T5 = dict(dtype=torch.bfloat16, impl="tcgen05")
+
+
+@pytest.mark.parametrize("nh,nkv,page", [(8, 2, 64), (32, 8, 64), (6, 1, 128), (4, 4, 64), (40, 8, 64), (3, 1, 64)])
+def test_tcgen05_attention_mixed_batch(ops, nh, nkv, page):
+    # whole prompts (shorter and longer than a block's 128 rows, ending inside and at the end of a
+    # page), portions over a cached prefix, single tokens, a 2-token portion at a page edge
+    _attention_case(ops, nh=nh, nkv=nkv, d=64, page=page,
+                    lens=[(150, 150), (9, 200), (1, 64), (1, 65), (1, 1), (2, 129), (128, 128), (70, 390), (33, 63)], **T5)
+
+
+def test_tcgen05_attention_long_prompt_and_far_key(ops):
+    _attention_case(ops, nh=8, nkv=2, d=64, page=64, lens=[(1100, 1100)], **T5)
+    _attention_case(ops, nh=8, nkv=2, d=64, page=64, lens=[(300, 700), (5, 300), (1, 65), (100, 400)], planted=True, **T5)
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 100])
+def test_tcgen05_attention_window(ops, window):
+    _attention_case(ops, nh=4, nkv=2, d=64, page=64, lens=[(90, 90), (7, 300), (1, 64), (200, 500), (1, 129)], window=window, **T5)
+
+
+def test_tcgen05_attention_ignores_garbage_beyond_the_sequence(ops):
+    torch.manual_seed(12)
+    nh, nkv, d, page = 8, 2, 64, 64
+    cache = torch.full((6, 2, nkv, page, d), float("nan")).to(torch.bfloat16)
+    table = torch.tensor([[4, 1, 0, 0], [2, 0, 0, 0]], dtype=torch.int32)
+    cache[4] = torch.randn(2, nkv, page, d)
+    cache[1, :, :, :6] = torch.randn(2, nkv, 6, d).to(torch.bfloat16)
+    cache[2, :, :, :10] = torch.randn(2, nkv, 10, d).to(torch.bfloat16)
+    q = torch.randn(43, nh * d).to(torch.bfloat16)
+    cu, kl = torch.tensor([0, 40, 43], dtype=torch.int32), torch.tensor([70, 10], dtype=torch.int32)
+    want = plain_ops.paged_attention(q, nh * d, cache, table, cu, kl, 43, 2, 40, 70, nh, nkv, d, 0.125)
+    got = ops.paged_attention(dev(q), nh * d, dev(cache), dev(table), dev(cu), dev(kl), 43, 2, 40, 70, nh, nkv, d,
+                              0.125, 0, None, None, "tcgen05")
+    assert torch.isfinite(got.float()).all()
+    torch.testing.assert_close(got.cpu().float(), want.float(), atol=3e-2, rtol=3e-2)
+
+
+def test_attention_picks_its_kernels_for_a_mixed_step(ops):
+    # "auto": prompt portions on tcgen05, the decode tokens and short portions beside them on the flash kernel
+    before = ops.launch_count
+    _attention_case(ops, dtype=torch.bfloat16, nh=32, nkv=8, d=64, page=64,
+                    lens=[(1, 500), (300, 300), (1, 64), (31, 95), (32, 96), (1, 1), (64, 1000)], splits=1)
+    assert ops.launch_count - before == 2
+    with pytest.raises(ops.KernelError, match="tcgen05 kernel needs"):
+        _attention_case(ops, nh=4, nkv=2, d=128, page=64, lens=[(70, 70)], **T5)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("L,bias,hidden", [(3, False, 72), (4, True, 96), (2, True, 40), (1, False, 64), (8, False, 130), (3, True, 2048)])
 def test_shortconv_portions_and_state(ops, dtype, L, bias, hidden):

@@ -20,6 +20,7 @@
 // in a fixed order.
 #include "common.cuh"
 #include "attention_mma.cuh"
+#include "attention_tc.cuh"
 
 using namespace vapi;
 
@@ -279,9 +280,11 @@ static int launch_attention(const void* q, long long q_row_stride, const void* c
 // q: [n, *] with `q_row_stride` elements between tokens, head h at h*d.
 // cache: one layer, [num_pages, 2, nkv, page_size, d].  out: [n, nh*d].
 // splits > 1 needs part_o [n*nh*splits*d] and part_ml [n*nh*splits*2] floats of scratch.
-// impl: 0 = the tensor-core kernel where it applies (bfloat16, head_dim 64 or 128, page size a
-// multiple of 64), else the general one; 1 = the general kernel; 2 = the tensor-core kernel or
-// an error.
+// impl: 0 = the fastest kernel that applies: for bfloat16, head_dim 64 or 128 and a page size
+// that is a multiple of 64 the mma.sync flash kernel, and for steps with prompt portions (head_dim
+// 64, no split) the tcgen05 kernel for every sequence of at least FT_MIN_Q tokens beside the flash
+// kernel for the shorter ones; else the general kernel.  1 = the general kernel; 2 = the mma.sync
+// flash kernel or an error; 3 = the tcgen05 kernel for every sequence, or an error.
 VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, const void* cache,
                                      int dtype, const int* block_table, int table_stride,
                                      const int* cu_q, const int* seqlens_k, void* out,
@@ -307,6 +310,22 @@ VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, cons
         return fail(-3, "paged_attention: the tensor-core kernel needs bfloat16, head_dim 64 or 128 and a page "
                         "size that is a multiple of 64 (got dtype %d, head_dim %d, page size %d)", dtype, d, page_size);
     const bool fast = fast_ok && impl != 1;
+    const bool tc_ok = fast_ok && d == FT_HD && splits == 1 && q_row_stride % 8 == 0 && scale > 0.f;
+    if (impl == 3 && !tc_ok)
+        return fail(-3, "paged_attention: the tcgen05 kernel needs bfloat16, head_dim 64, a page size that is a multiple "
+                        "of 64, no split and a positive scale (got dtype %d, head_dim %d, page size %d, %d splits)",
+                    dtype, d, page_size, splits);
+    if (impl == 3 || (impl == 0 && tc_ok && max_q >= FT_AUTO_MAX_Q)) {
+        // prompt portions on tcgen05; in a mixed step the short sequences (decode tokens) go to the
+        // flash kernel, whose small blocks suit them: each kernel skips the other's sequences
+        const int min_q = (impl == 3 || num_seqs == 1) ? 1 : FT_MIN_Q;
+        rc = launch_flash_tc(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, num_seqs, max_q,
+                             nh, nkv, page_size, num_pages, scale, window, min_q, status, stream);
+        if (rc != 0 || min_q == 1) return rc;
+        return launch_flash<64, 4, 3>(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, part_o,
+                                      part_ml, num_seqs, FT_MIN_Q - 1, nh, nkv, page_size, num_pages, scale, window, 1,
+                                      status, stream, FT_MIN_Q);
+    }
 #define VAPI_FLASH(HD, NW, ST)                                                                   \
     rc = launch_flash<HD, NW, ST>(q, q_row_stride, cache, block_table, table_stride, cu_q,       \
                                   seqlens_k, out, part_o, part_ml, num_seqs, max_q, nh, nkv,     \

@@ -26,15 +26,13 @@
 // Every mbarrier wait is bounded: after TC_WAIT_LIMIT polls a role gives up, records status
 // 16 and the block drains to its end (tensor memory is released on every path; the cluster
 // barriers are hardware barriers that every thread reaches on every path).
-#include "common.cuh"
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 using namespace vapi;
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;                 // 64 bf16 = 128 bytes: one swizzle row
 constexpr int TC_THREADS = 192;
-constexpr unsigned TC_WAIT_LIMIT = 1u << 24;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;
 
 enum { TC_PRO_ACT = 0, TC_PRO_NORM = 1 };
@@ -57,56 +55,6 @@ template <int BN> struct TcCfg {
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + 4 * 256 * 4 /*sums*/ + 256 * 4;
 };
 
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// bounded wait on a phase parity; false when the limit ran out
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-    for (unsigned i = 0; i < TC_WAIT_LIMIT; ++i) {
-        unsigned done;
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
-                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, unsigned bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-// shared-memory matrix descriptor: K-major tile of rows of 128 bytes, 128-byte swizzle,
-// 8-row groups 1024 bytes apart
-__device__ __forceinline__ unsigned long long umma_desc(unsigned smem_addr) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((smem_addr >> 4) & 0x3FFF);        // start address
-    d |= (unsigned long long)1 << 16;                             // leading byte offset (unused with swizzle)
-    d |= (unsigned long long)(1024 >> 4) << 32;                   // stride byte offset: 8 rows * 128 B
-    d |= (unsigned long long)1 << 46;                             // descriptor version of this architecture
-    d |= (unsigned long long)2 << 61;                             // 128-byte swizzle
-    return d;
-}
-__device__ __forceinline__ void umma_f16(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc, unsigned accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
-                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(unsigned taddr, float (&v)[16]) {
-    unsigned r[16];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -373,21 +321,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 }
 
 // ---- host side -------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)ptr;
-    }
-    return fn;
-}
-
 // a [rows][K] bfloat16 matrix, K contiguous, tiled in boxes of 64 k x box_rows rows, 128-byte swizzle
 static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, int box_rows) {
     EncodeTiledFn fn = encode_fn();

@@ -480,7 +480,9 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tenso
 
     ``q`` may be a view into a fused qkv tensor: head h of token t is at
     ``t*q_row_stride + h*d``.  ``window`` > 0 limits each query to the last ``window`` keys.
-    ``impl``: "auto" picks the tensor-core kernel where it applies (bfloat16, head_dim 64 or
+    ``impl``: "tcgen05" forces the kernel on the fifth-generation tensor cores (bfloat16, head_dim 64,
+    pages of 64n, no split), which "auto" uses for steps with prompt portions of 64 tokens or more;
+    "auto" otherwise picks the tensor-core kernel where it applies (bfloat16, head_dim 64 or
     128, page size a multiple of 64) and the general kernel elsewhere; "general" and
     "tensor_core" force one (the latter raises where it does not apply).
     """
@@ -495,18 +497,23 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tenso
         raise KernelError("block table must be [S, width] with unit inner stride")
     num_pages, page_size = cache_layer.shape[0], cache_layer.shape[3]
     if splits is None:
-        splits = attention_splits(num_seqs, max_q, max_k, nh, nkv)
+        splits = 1 if impl == "tcgen05" else attention_splits(num_seqs, max_q, max_k, nh, nkv)
     out = torch.empty((n, nh * d), dtype=q.dtype, device=q.device)
     part_o = part_ml = None
     if splits > 1:
         part_o = torch.empty((n * nh * splits * d,), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n * nh * splits * 2,), dtype=torch.float32, device=q.device)
     lib = _lib("attention")
+    # how many kernels the library launches (its own rule, restated for the launch count): the
+    # tcgen05 kernel takes steps with prompt portions, beside the flash kernel in a mixed step
+    tc = impl == "tcgen05" or (impl == "auto" and q.dtype == torch.bfloat16 and d == 64 and page_size % 64 == 0
+                               and splits == 1 and max_q >= 64 and q_row_stride % 8 == 0 and scale > 0)
+    launches = (1 if impl == "tcgen05" or num_seqs == 1 else 2) if tc else (2 if splits > 1 else 1)
     _check(lib, lib.vapi_paged_attention(
         _p(q), ctypes.c_longlong(q_row_stride), _p(cache_layer), _dt(q), _p(block_table),
         block_table.stride(0), _p(cu_q), _p(seqlens_k), _p(out), _p(part_o), _p(part_ml), n, num_seqs,
         max_q, nh, nkv, d, page_size, num_pages, ctypes.c_float(scale), window, splits,
-        {"auto": 0, "general": 1, "tensor_core": 2}[impl], _p(status), _stream()), 2 if splits > 1 else 1)
+        {"auto": 0, "general": 1, "tensor_core": 2, "tcgen05": 3}[impl], _p(status), _stream()), launches)
     return out
 
 
