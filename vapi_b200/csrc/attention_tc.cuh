@@ -18,8 +18,9 @@
 // The running maximum is only raised when a tile exceeds it by more than 2^8 (the exponentials
 // stay below 256, which float accumulation and bfloat16 P carry without loss of accuracy), so
 // the accumulator in tensor memory is rescaled a few times per row, not once per tile.
-// S(i+1) is issued before P.V(i), so the tensor core works on the next tile's scores while the
-// softmax warps are busy; two blocks per SM overlap the rest.
+// S and P are double-buffered and S(i+1) is issued before P.V(i), so the softmax warps wait
+// for the tensor core only when they must rescale the accumulator; two blocks per SM overlap
+// the rest.
 //
 // Keys beyond the sequence's end in its last page may hold anything (memory is never cleared):
 // their scores are replaced by -inf by selection, and their V rows are zeroed in shared memory
@@ -39,7 +40,7 @@ constexpr int FT_STAGES = 3;
 constexpr int FT_THREADS = 192;
 constexpr int FT_TMEM_COLS = 256;                  // S0 | S1 | O, 64 columns each (a power of two is allocated)
 constexpr int FT_TILE_BYTES = FT_BK * FT_HD * 2;   // one K or V tile
-constexpr size_t FT_SMEM = 1024 + 2 * FT_ROWS * FT_HD * 2 + (size_t)FT_STAGES * 2 * FT_TILE_BYTES + 256;
+constexpr size_t FT_SMEM = 1024 + 3 * FT_ROWS * FT_HD * 2 + (size_t)FT_STAGES * 2 * FT_TILE_BYTES + 256;
 constexpr int FT_MIN_Q = 32;                       // in a mixed step, sequences with fewer tokens go to the flash kernel
 constexpr int FT_AUTO_MAX_Q = 64;                  // the dispatcher picks this kernel from this longest portion on
 constexpr float FT_RAISE = 8.f;                    // log2 units by which a tile must exceed the running maximum to raise it
@@ -66,8 +67,8 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const FaTcParams p) {
     extern __shared__ unsigned char ft_smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(ft_smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* sQ = base;                                   // [128 rows][128 B], 128-byte swizzle
-    unsigned char* sP = base + FT_ROWS * FT_HD * 2;             // the same shape: P of the current tile
-    unsigned char* sKV = sP + FT_ROWS * FT_BK * 2;              // [stage][K tile | V tile]
+    unsigned char* sP = base + FT_ROWS * FT_HD * 2;             // two buffers of the same shape: P of tile i in buffer i & 1
+    unsigned char* sKV = sP + 2 * FT_ROWS * FT_BK * 2;          // [stage][K tile | V tile]
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(sKV + (size_t)FT_STAGES * 2 * FT_TILE_BYTES);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 16);
     int* flags = reinterpret_cast<int*>(tmem_slot + 1);
@@ -94,14 +95,17 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const FaTcParams p) {
 
     const unsigned kv_full = smem_u32(bars), kv_empty = smem_u32(bars + FT_STAGES);
     const unsigned s_full = smem_u32(bars + 2 * FT_STAGES), s_free = smem_u32(bars + 2 * FT_STAGES + 2);
-    const unsigned p_ready = smem_u32(bars + 2 * FT_STAGES + 4), pv_done = smem_u32(bars + 2 * FT_STAGES + 5);
-    const unsigned q_ready = smem_u32(bars + 2 * FT_STAGES + 6);
+    const unsigned p_ready = smem_u32(bars + 2 * FT_STAGES + 4), pv_done = smem_u32(bars + 2 * FT_STAGES + 6);   // one per P buffer
+    const unsigned q_ready = smem_u32(bars + 2 * FT_STAGES + 8);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < FT_STAGES; ++i) { mbar_init(kv_full + 8 * i, 1); mbar_init(kv_empty + 8 * i, 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(s_full + 8 * i, 1); mbar_init(s_free + 8 * i, 128); }
-        mbar_init(p_ready, 128);
-        mbar_init(pv_done, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(s_full + 8 * i, 1);
+            mbar_init(s_free + 8 * i, 128);
+            mbar_init(p_ready + 8 * i, 128);
+            mbar_init(pv_done + 8 * i, 1);
+        }
         mbar_init(q_ready, 128);
         flags[0] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -150,15 +154,15 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const FaTcParams p) {
             bool ok = true;
             auto pv = [&](int j) {          // O += P(j) . V(j)
                 if (!ok) return;
-                if (!mbar_wait(p_ready, j & 1)) { ok = false; return; }
+                if (!mbar_wait(p_ready + 8 * (j & 1), (j >> 1) & 1)) { ok = false; return; }
                 tc5_fence_after();
                 const int stage = j % FT_STAGES;
-                const unsigned pa = smem_u32(sP);
+                const unsigned pa = smem_u32(sP + (j & 1) * FT_ROWS * FT_BK * 2);
                 const unsigned vb = smem_u32(sKV + (size_t)stage * 2 * FT_TILE_BYTES) + FT_TILE_BYTES;
 #pragma unroll
                 for (int k = 0; k < FT_BK / 16; ++k)
                     umma_f16(tO, umma_desc(pa + k * 32), umma_desc_mn(vb + k * 16 * 128), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-                umma_commit(pv_done);
+                umma_commit(pv_done + 8 * (j & 1));
                 umma_commit(kv_empty + 8 * stage);
             };
             for (int i = 0; i < nt && ok; ++i) {
@@ -210,54 +214,61 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const FaTcParams p) {
             if (!__all_sync(0xffffffffu, mbar_wait(s_full + 8 * sb, (i >> 1) & 1))) { ok = false; break; }
             tc5_fence_after();
             float sv[FT_BK];
+            {
+                unsigned raw[FT_BK / 16][16];                           // all four loads in flight, one wait
 #pragma unroll
-            for (int j = 0; j < FT_BK / 16; ++j) {
-                float t16[16];
-                tmem_ld16(tS0 + sb * 64 + lane_addr + j * 16, t16);
+                for (int j = 0; j < FT_BK / 16; ++j) tmem_ld16_nowait(tS0 + sb * 64 + lane_addr + j * 16, raw[j]);
+                tmem_ld_wait();
 #pragma unroll
-                for (int e = 0; e < 16; ++e) sv[j * 16 + e] = t16[e];
+                for (int j = 0; j < FT_BK / 16; ++j)
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) sv[j * 16 + e] = __uint_as_float(raw[j][e]);
             }
             tc5_fence_before();
             mbar_arrive(s_free + 8 * sb);                           // the scores are in registers
 
             const bool need_mask = partial || (k0 + FT_BK - 1 > p_min) || (k0 + FT_BK > klen) ||
                                    (p.window > 0 && k0 <= p_max - p.window);
-            float mx = -INFINITY;
+            // (four running maxima and, below, four running sums: a single chain of 64 dependent
+            // operations would leave the few warps of an SM waiting on latency)
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (need_mask) {
 #pragma unroll
                 for (int e = 0; e < FT_BK; ++e) {
                     const int kj = k0 + e;
                     const bool vis = kj <= pos && kj < klen && (p.window <= 0 || kj > pos - p.window);
                     sv[e] = vis ? sv[e] : -INFINITY;
-                    mx = fmaxf(mx, sv[e]);
+                    mx4[e & 3] = fmaxf(mx4[e & 3], sv[e]);
                 }
             } else {
 #pragma unroll
-                for (int e = 0; e < FT_BK; ++e) mx = fmaxf(mx, sv[e]);
+                for (int e = 0; e < FT_BK; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], sv[e]);
             }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float mx_s = mx * p.scale_log2e;                  // (the scale is positive)
             const bool grow = mx_s > m_run + FT_RAISE;              // also the first tile with a visible key
             const float m_new = grow ? mx_s : m_run;
             const float alpha = grow ? ex2_approx(m_run - m_new) : 1.f;     // m_run = -inf: 0
-            if (i >= 1) {
-                if (!__all_sync(0xffffffffu, mbar_wait(pv_done, (i - 1) & 1))) { ok = false; break; }   // P is free, O is at rest
+            if (i >= 1 && __any_sync(0xffffffffu, grow)) {
+                // the accumulator must be at rest: P.V of the tile before this one has completed
+                if (!__all_sync(0xffffffffu, mbar_wait(pv_done + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1))) { ok = false; break; }
                 tc5_fence_after();
-                if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll
-                    for (int j = 0; j < FT_HD / 16; ++j) {
-                        float o16[16];
-                        tmem_ld16(tO + lane_addr + j * 16, o16);
+                for (int j = 0; j < FT_HD / 16; ++j) {
+                    float o16[16];
+                    tmem_ld16(tO + lane_addr + j * 16, o16);
 #pragma unroll
-                        for (int e = 0; e < 16; ++e) o16[e] *= alpha;
-                        tmem_st16(tO + lane_addr + j * 16, o16);
-                    }
-                    tmem_st_wait();
+                    for (int e = 0; e < 16; ++e) o16[e] *= alpha;
+                    tmem_st16(tO + lane_addr + j * 16, o16);
                 }
+                tmem_st_wait();
             }
+            // this tile's P buffer was last read by P.V of the tile two before
+            if (i >= 2 && !__all_sync(0xffffffffu, mbar_wait(pv_done + 8 * sb, ((i >> 1) - 1) & 1))) { ok = false; break; }
             l_run *= alpha;
             m_run = m_new;
             const float m_use = m_run == -INFINITY ? 0.f : m_run;
-            float rs = 0.f;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 unsigned w[4];
@@ -265,13 +276,13 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const FaTcParams p) {
                 for (int e = 0; e < 4; ++e) {
                     const float a = ex2_approx(fmaf(sv[c * 8 + 2 * e], p.scale_log2e, -m_use));
                     const float b = ex2_approx(fmaf(sv[c * 8 + 2 * e + 1], p.scale_log2e, -m_use));
-                    rs += a + b;
+                    rs4[e] += a + b;
                     __nv_bfloat162 h2 = __floats2bfloat162_rn(a, b);
                     w[e] = *reinterpret_cast<unsigned*>(&h2);
                 }
-                *reinterpret_cast<uint4*>(sP + row * 128 + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(sP + sb * FT_ROWS * FT_BK * 2 + row * 128 + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            l_run += rs;
+            l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             if (k0 + FT_BK > klen) {
                 // V rows of keys beyond the sequence: zero them (a row is 128 bytes whatever the swizzle)
                 if (!__all_sync(0xffffffffu, mbar_wait(kv_full + 8 * stage, (i / FT_STAGES) & 1))) { ok = false; break; }   // complete already: makes the tile visible here
@@ -283,9 +294,9 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const FaTcParams p) {
             }
             fence_proxy_async();
             tc5_fence_before();
-            mbar_arrive(p_ready);
+            mbar_arrive(p_ready + 8 * sb);
         }
-        if (ok && !__all_sync(0xffffffffu, mbar_wait(pv_done, (nt - 1) & 1))) ok = false;
+        if (ok && !__all_sync(0xffffffffu, mbar_wait(pv_done + 8 * ((nt - 1) & 1), ((nt - 1) >> 1) & 1))) ok = false;
         tc5_fence_after();
         if (ok) {                                                   // (uniform over the warp)
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
