@@ -526,6 +526,44 @@ def test_embed_and_residual_add_prepare_the_next_norm(ops):
     torch.testing.assert_close(xw2.cpu().float(), (want2 * nw).to(torch.bfloat16).float(), atol=2e-2, rtol=1e-2)
 
 
+@pytest.mark.parametrize("M,H,K,L,bias", [(8, 2048, 2048, 3, False), (1, 72, 96, 4, True), (11, 200, 160, 2, True),
+                                          (16, 64, 64, 5, False), (3, 40, 32, 1, False)])
+def test_skinny_shortconv_is_in_proj_then_the_conv_kernel(ops, M, H, K, L, bias):
+    """The decode form of the short-conv mixer in one launch, against the two steps it replaces
+    (in_proj rounded to bfloat16, then the conv kernel's plain restatement), over two steps on the
+    same slots so that the state it leaves is the state it reads, with one request starting over."""
+    torch.manual_seed(31)
+    bf = torch.bfloat16
+    w_in = (torch.randn(3 * H, K) / math.sqrt(K)).to(bf)
+    taps = torch.randn(L, H)
+    in_b = torch.randn(3 * H) if bias else None
+    cv_b = torch.randn(H) if bias else None
+    nw = 1 + 0.1 * torch.randn(K)
+    slots_n = M + 2
+    state_ref = torch.full((slots_n, max(L - 1, 1), H), 9.0).to(bf)[:, :L - 1]
+    state_gpu = dev(state_ref.clone())
+    slots = torch.randperm(slots_n)[:M].to(torch.int32)
+    pos0 = torch.randint(0, 4, (M,), dtype=torch.int32)
+    for step in range(3):
+        pos = pos0 + step
+        if step == 2:
+            pos[0] = 0                                     # a new request in a used slot
+        x = torch.randn(M, K) * 2
+        xw = (x * nw).to(bf)
+        parts = 5
+        ss = torch.stack([(x[:, j::parts] ** 2).sum(1) for j in range(parts)])
+        inv = torch.rsqrt(ss.sum(0) / K + 1e-5)
+        h3 = ((xw.float() @ w_in.float().t()) * inv[:, None]).to(bf)
+        ar = torch.arange(M + 1, dtype=torch.int32)
+        want = plain_ops.shortconv(h3, in_b, taps, cv_b, state_ref, slots, ar[:M].clone(), ar, pos)
+        got = ops.skinny_shortconv(dev(w_in), xw=dev(xw), ss_in=dev(ss), eps=1e-5, in_bias=dev(in_b), taps=dev(taps),
+                                   conv_bias=dev(cv_b), state_layer=state_gpu if L > 1 else None,
+                                   state_slots=dev(slots), positions=dev(pos))
+        torch.testing.assert_close(got.cpu().float(), want.float(), atol=6e-2, rtol=4e-2)
+        if L > 1:
+            torch.testing.assert_close(state_gpu.cpu().float(), state_ref.float(), atol=6e-2, rtol=4e-2)
+
+
 def test_skinny_linear_refuses_what_it_cannot_do(ops):
     w = torch.zeros(64, 80, dtype=torch.bfloat16).cuda()
     with pytest.raises(ops.KernelError, match="multiple of 32"):

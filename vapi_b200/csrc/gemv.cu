@@ -21,7 +21,10 @@
 //  * epilogue: bfloat16 out (+bias) | float out (logits) | SwiGLU (a block owns 8 gate rows and
 //    the 8 matching up rows, so silu(gate)*up happens before anything is stored) | add into the
 //    float residual stream (+bias), leaving for the norm that follows the partial sums of squares
-//    of the new stream values and bfloat16(new value * that norm's weight).
+//    of the new stream values and bfloat16(new value * that norm's weight) | the whole gated
+//    short convolution of a decode step (W is the mixer's in_proj; a block owns the B, C and x
+//    rows of 8 channels, so gate, taps over the request's state, C * conv and the state update
+//    happen before anything is stored; every token must be a sequence of its own).
 //
 // The reference does these products with cuBLAS and separate norm / SwiGLU / add kernels
 // (crates/vapi-backend-candle/src/models/lfm2.rs:519-534, 591-593, 645-647).
@@ -33,10 +36,13 @@ constexpr int GV_WARPS = 8;
 #ifndef GV_STAGES_N
 #define GV_STAGES_N 8
 #endif
-constexpr int GV_STAGES = GV_STAGES_N;      // depth of the per-lane copy queue (chunks of 32 k)
+constexpr int GV_STAGES_DEFAULT = GV_STAGES_N;   // depth of the per-lane copy queue (chunks of 32 k)
+// the conv epilogue streams three weight rows per lane: six stages keep two blocks on an SM
+template <int EPI> __host__ __device__ constexpr int gv_stages() { return EPI == 4 ? (GV_STAGES_DEFAULT < 6 ? GV_STAGES_DEFAULT : 6) : GV_STAGES_DEFAULT; }
 
 enum { GV_PRO_ACT = 0, GV_PRO_NORM = 1 };
-enum { GV_EPI_BF16 = 0, GV_EPI_SWIGLU = 1, GV_EPI_RESID = 2, GV_EPI_F32 = 3 };
+enum { GV_EPI_BF16 = 0, GV_EPI_SWIGLU = 1, GV_EPI_RESID = 2, GV_EPI_F32 = 3, GV_EPI_CONV = 4 };
+constexpr int GV_CONV_LMAX = 8;
 
 struct GvParams {
     const __nv_bfloat16* W; int N, K, M;
@@ -49,6 +55,11 @@ struct GvParams {
     int ff;                                        // EPI_SWIGLU: N == 2*ff
     int rows_per_cta;                              // 16 or 8 (always 8 gate + 8 up for SwiGLU)
     int num_tiles;                                 // tiles of rows_per_cta weight rows (8 gate/up pairs)
+    // EPI_CONV (W is a short-conv in_proj [3*ff][K], rows B | C | x; every token is a sequence of its own)
+    const float* taps; const float* conv_bias;     // [L][ff] oldest tap first, [ff] or null
+    __nv_bfloat16* state; long long slot_stride;   // [slots][L-1][ff]
+    const int* state_slots; const int* positions;  // [M]
+    int L, num_slots; int* status;
 };
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
@@ -72,12 +83,12 @@ __device__ __forceinline__ void gv_cp16(void* smem_dst, const void* gsrc, int by
 __device__ __forceinline__ void gv_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void gv_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-template <int NT, int PRO>
-__host__ __device__ constexpr int gv_slots() { return 2 + (PRO == GV_PRO_ACT ? NT : 0); }
+template <int NT, int PRO, int EPI>
+__host__ __device__ constexpr int gv_slots() { return (EPI == GV_EPI_CONV ? 3 : 2) + (PRO == GV_PRO_ACT ? NT : 0); }
 
-template <int NT, int PRO>
+template <int NT, int PRO, int EPI>
 static size_t gv_smem_bytes(int K) {
-    size_t b = (size_t)GV_WARPS * GV_STAGES * gv_slots<NT, PRO>() * 32 * sizeof(uint4);
+    size_t b = (size_t)GV_WARPS * gv_stages<EPI>() * gv_slots<NT, PRO, EPI>() * 32 * sizeof(uint4);
     if (PRO == GV_PRO_NORM) b += (size_t)8 * NT * (K + 32) * sizeof(__nv_bfloat16);
     return b;
 }
@@ -85,10 +96,13 @@ static size_t gv_smem_bytes(int K) {
 template <int NT, int PRO, int EPI>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 skinny_linear_kernel(const GvParams p) {
-    constexpr int SLOTS = gv_slots<NT, PRO>();
+    constexpr int SLOTS = gv_slots<NT, PRO, EPI>();
+    constexpr int GV_STAGES = gv_stages<EPI>();
+    constexpr int WS = EPI == GV_EPI_CONV ? 3 : 2;     // weight rows a lane streams per chunk
     constexpr int COLS = 8 * NT;
     extern __shared__ __align__(16) unsigned char gv_smem[];
     __shared__ float red[GV_WARPS][16][COLS + 1];
+    __shared__ float red_x[EPI == GV_EPI_CONV ? GV_WARPS : 1][8][COLS + 1];
     __shared__ float inv_s[COLS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -108,9 +122,9 @@ skinny_linear_kernel(const GvParams p) {
 
     // the two weight rows (MMA rows g and g + 8) this lane streams in a given tile
     auto rows_of = [&](int tile, long long& row_lo, long long& row_hi, bool& ok_lo, bool& ok_hi) {
-        if (EPI == GV_EPI_SWIGLU) {
-            row_lo = (long long)tile * 8 + g;               // gate
-            row_hi = (long long)p.ff + row_lo;              // up
+        if (EPI == GV_EPI_SWIGLU || EPI == GV_EPI_CONV) {
+            row_lo = (long long)tile * 8 + g;               // gate | B
+            row_hi = (long long)p.ff + row_lo;              // up | C  (x: 2 ff + row_lo)
             ok_lo = ok_hi = row_lo < p.ff;
         } else {
             row_lo = (long long)tile * R + g;
@@ -121,7 +135,7 @@ skinny_linear_kernel(const GvParams p) {
     };
     // the copy queue's own position: tile ordinal and chunk of the next piece to request
     int q_tile = 0, q_c = c_begin;
-    const __nv_bfloat16 *q_lo = p.W, *q_hi = p.W;
+    const __nv_bfloat16 *q_lo = p.W, *q_hi = p.W, *q_x = p.W;
     int q_lo_bytes = 0, q_hi_bytes = 0;
     auto queue_enter_tile = [&]() {
         if (q_tile < my_tiles) {
@@ -130,6 +144,7 @@ skinny_linear_kernel(const GvParams p) {
             rows_of((int)blockIdx.x + q_tile * (int)gridDim.x, row_lo, row_hi, ok_lo, ok_hi);
             q_lo = p.W + (size_t)(ok_lo ? row_lo : 0) * p.K + 8 * t;
             q_hi = p.W + (size_t)(ok_hi ? row_hi : 0) * p.K + 8 * t;
+            if (EPI == GV_EPI_CONV) q_x = p.W + (size_t)(ok_lo ? 2 * (long long)p.ff + row_lo : 0) * p.K + 8 * t;
             q_lo_bytes = ok_lo ? 16 : 0;
             q_hi_bytes = ok_hi ? 16 : 0;
         }
@@ -139,7 +154,7 @@ skinny_linear_kernel(const GvParams p) {
         for (int nt = 0; nt < NT; ++nt) {
             const int m = nt * 8 + g;
             const bool ok = m < p.M;
-            gv_cp16(&fifo[(stage * SLOTS + 2 + nt) * 32 + lane],
+            gv_cp16(&fifo[(stage * SLOTS + WS + nt) * 32 + lane],
                     p.act + (size_t)(ok ? m : 0) * p.K + ((size_t)c << 5) + 8 * t, ok ? 16 : 0);
         }
     };
@@ -149,6 +164,7 @@ skinny_linear_kernel(const GvParams p) {
             const size_t k = (size_t)q_c << 5;
             gv_cp16(&fifo[(stage * SLOTS + 0) * 32 + lane], q_lo + k, q_lo_bytes);
             gv_cp16(&fifo[(stage * SLOTS + 1) * 32 + lane], q_hi + k, q_hi_bytes);
+            if (EPI == GV_EPI_CONV) gv_cp16(&fifo[(stage * SLOTS + 2) * 32 + lane], q_x + k, q_lo_bytes);
             if (PRO == GV_PRO_ACT && with_acts) queue_act_chunk(q_c, stage);
             if (++q_c == c_end) {
                 q_c = c_begin;
@@ -205,8 +221,11 @@ skinny_linear_kernel(const GvParams p) {
     for (int ti = 0; ti < my_tiles; ++ti) {
         const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
         float acc[NT][4];
+        float acc_x[EPI == GV_EPI_CONV ? NT : 1][4];
 #pragma unroll
         for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+#pragma unroll
+        for (int i = 0; i < (EPI == GV_EPI_CONV ? NT : 1); ++i) acc_x[i][0] = acc_x[i][1] = acc_x[i][2] = acc_x[i][3] = 0.f;
 
         for (int c = c_begin; c < c_end; ++c) {
             const int nstage = stage == 0 ? GV_STAGES - 1 : stage - 1;      // (stage + STAGES - 1) % STAGES
@@ -217,13 +236,19 @@ skinny_linear_kernel(const GvParams p) {
             first = false;
             const uint4 wl = fifo[(stage * SLOTS + 0) * 32 + lane];
             const uint4 wh = fifo[(stage * SLOTS + 1) * 32 + lane];
+            uint4 wx = make_uint4(0u, 0u, 0u, 0u);
+            if (EPI == GV_EPI_CONV) wx = fifo[(stage * SLOTS + 2) * 32 + lane];
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 uint4 av;
-                if (PRO == GV_PRO_ACT) av = fifo[(stage * SLOTS + 2 + nt) * 32 + lane];
+                if (PRO == GV_PRO_ACT) av = fifo[(stage * SLOTS + WS + nt) * 32 + lane];
                 else av = *reinterpret_cast<const uint4*>(act_s + (size_t)(nt * 8 + g) * pitch + ((size_t)c << 5) + 8 * t);
                 mma16816(acc[nt], wl.x, wh.x, wl.y, wh.y, av.x, av.y);
                 mma16816(acc[nt], wl.z, wh.z, wl.w, wh.w, av.z, av.w);
+                if (EPI == GV_EPI_CONV) {                        // the x rows: the MMA's upper eight rows stay empty
+                    mma16816(acc_x[nt], wx.x, 0u, wx.y, 0u, av.x, av.y);
+                    mma16816(acc_x[nt], wx.z, 0u, wx.w, 0u, av.z, av.w);
+                }
             }
             stage = stage == GV_STAGES - 1 ? 0 : stage + 1;
         }
@@ -235,6 +260,10 @@ skinny_linear_kernel(const GvParams p) {
             red[warp][g][nt * 8 + 2 * t + 1] = acc[nt][1];
             red[warp][g + 8][nt * 8 + 2 * t] = acc[nt][2];
             red[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
+            if (EPI == GV_EPI_CONV) {
+                red_x[warp][g][nt * 8 + 2 * t] = acc_x[nt][0];
+                red_x[warp][g][nt * 8 + 2 * t + 1] = acc_x[nt][1];
+            }
         }
         __syncthreads();
         const int i = threadIdx.x / COLS, m = threadIdx.x - i * COLS;      // MMA row, token
@@ -242,16 +271,57 @@ skinny_linear_kernel(const GvParams p) {
         if (i < 16) {
 #pragma unroll
             for (int w = 0; w < GV_WARPS; ++w) y += red[w][i][m];
-            if (EPI == GV_EPI_SWIGLU && i < 8) {
+            if ((EPI == GV_EPI_SWIGLU || EPI == GV_EPI_CONV) && i < 8) {
 #pragma unroll
                 for (int w = 0; w < GV_WARPS; ++w) y2 += red[w][i + 8][m];
             }
         }
+        float y3 = 0.f;
+        if (EPI == GV_EPI_CONV && i < 8) {
+#pragma unroll
+            for (int w = 0; w < GV_WARPS; ++w) y3 += red_x[w][i][m];
+        }
         if (PRO == GV_PRO_NORM && m < p.M) {
             y *= inv_s[m];
             y2 *= inv_s[m];
+            y3 *= inv_s[m];
         }
-        if (EPI == GV_EPI_SWIGLU) {
+        if (EPI == GV_EPI_CONV) {
+            // y, y2, y3 = B, C, x of channel c for token m, which is a sequence of its own.  The
+            // values are rounded where the unfused path stores them (in_proj's output, then g).
+            const long long c = (long long)tile * 8 + i;
+            if (i < 8 && m < p.M && c < p.ff) {
+                float B = __bfloat162float(__float2bfloat16_rn(y));
+                float C = __bfloat162float(__float2bfloat16_rn(y2));
+                float X = __bfloat162float(__float2bfloat16_rn(y3));
+                if (p.bias) { B += p.bias[c]; C += p.bias[p.ff + c]; X += p.bias[2 * (long long)p.ff + c]; }
+                const float gate = __bfloat162float(__float2bfloat16_rn(B * X));
+                const int L = p.L;
+                float conv = p.taps[(size_t)(L - 1) * p.ff + c] * gate;
+                if (L > 1) {
+                    const int slot = p.state_slots[m], p0 = p.positions[m];
+                    if (slot < 0 || slot >= p.num_slots) {
+                        if (p.status) atomicExch(p.status, 3);
+                    } else {
+                        __nv_bfloat16* st = p.state + (size_t)slot * p.slot_stride + c;
+                        float hist[GV_CONV_LMAX];
+#pragma unroll
+                        for (int j = 0; j < GV_CONV_LMAX; ++j)      // rows for positions before 0 count as zero
+                            hist[j] = (j < L - 1 && p0 - (L - 1) + j >= 0) ? __bfloat162float(st[(size_t)j * p.ff]) : 0.f;
+                        float acc_c = 0.f;
+#pragma unroll
+                        for (int j = 0; j < GV_CONV_LMAX; ++j)
+                            if (j < L - 1) acc_c += p.taps[(size_t)j * p.ff + c] * hist[j];
+                        conv += acc_c;
+#pragma unroll
+                        for (int j = 0; j < GV_CONV_LMAX; ++j)
+                            if (j < L - 1) st[(size_t)j * p.ff] = __float2bfloat16_rn(j + 1 < L - 1 ? hist[j + 1 < GV_CONV_LMAX ? j + 1 : 0] : gate);
+                    }
+                }
+                if (p.conv_bias) conv += p.conv_bias[c];
+                p.out_bf16[(size_t)m * p.out_stride + c] = __float2bfloat16_rn(C * conv);
+            }
+        } else if (EPI == GV_EPI_SWIGLU) {
             const long long col = (long long)tile * 8 + i;
             if (i < 8 && m < p.M && col < p.ff) {
                 const float sg = y / (1.f + expf(-y));
@@ -292,7 +362,7 @@ skinny_linear_kernel(const GvParams p) {
 
 template <int NT, int PRO, int EPI>
 static int launch_gv(const GvParams& p, int blocks, cudaStream_t stream) {
-    const size_t smem = gv_smem_bytes<NT, PRO>(p.K);
+    const size_t smem = gv_smem_bytes<NT, PRO, EPI>(p.K);
     auto kern = skinny_linear_kernel<NT, PRO, EPI>;
     if (smem > 200 * 1024) return fail(-1, "skinny_linear: K=%d needs %zu bytes of shared memory", p.K, smem);
     if (smem > 48 * 1024) {
@@ -338,7 +408,7 @@ VAPI_EXPORT int vapi_skinny_linear(const void* W, int N, int K, int M, int pro, 
     if ((epi == GV_EPI_BF16 || epi == GV_EPI_SWIGLU) && !out_bf16) return fail(-1, "skinny_linear: no output");
     if (epi == GV_EPI_F32 && !out_f32) return fail(-1, "skinny_linear: no output");
     if (epi == GV_EPI_RESID && !resid) return fail(-1, "skinny_linear: no residual stream");
-    GvParams p;
+    GvParams p = {};
     p.W = (const __nv_bfloat16*)W; p.N = N; p.K = K; p.M = M;
     p.act = (const __nv_bfloat16*)act; p.xw = (const __nv_bfloat16*)xw; p.ss_in = ss_in; p.ss_parts = ss_parts; p.eps = eps;
     p.next_w = next_w; p.xw_out = (__nv_bfloat16*)xw_out;
@@ -363,6 +433,34 @@ VAPI_EXPORT int vapi_skinny_linear(const void* W, int N, int K, int M, int pro, 
     return fail(-2, "skinny_linear: unknown prologue %d", pro);
 #undef GV_EPIS
 #undef GV_GO
+}
+
+// The short-conv mixer's in_proj with the whole gated convolution of a decode step as its
+// epilogue: W [3H][K] (rows B | C | x), token operand the residual stream seen through a deferred
+// norm, out [M][H] = C * conv(B * x over the request's state), state updated in place.  Every one
+// of the M tokens must be a sequence of its own (one state slot and one position per token).
+VAPI_EXPORT int vapi_skinny_linear_conv(const void* W, int H, int K, int M, const void* xw, const float* ss_in,
+                                        int ss_parts, float eps, const float* in_bias, const float* taps,
+                                        const float* conv_bias, int L, void* state, long long slot_stride,
+                                        int num_slots, const int* state_slots, const int* positions, void* out,
+                                        int* status, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (M > 16) return fail(-1, "skinny_linear_conv: %d rows are more than 16", M);
+    if (H <= 0 || K <= 0 || K % 32 != 0) return fail(-1, "skinny_linear_conv: K=%d must be a positive multiple of 32 (H=%d)", K, H);
+    if (L < 1 || L > GV_CONV_LMAX) return fail(-1, "skinny_linear_conv: kernel length %d is outside 1..%d", L, GV_CONV_LMAX);
+    if (!xw || !ss_in || ss_parts <= 0) return fail(-1, "skinny_linear_conv: the norm prologue needs the weighted stream and its partial sums");
+    if (!taps || !out || !state_slots || !positions) return fail(-1, "skinny_linear_conv: missing array");
+    if (L > 1 && (!state || num_slots <= 0)) return fail(-1, "skinny_linear_conv: no state buffer");
+    GvParams p = {};
+    p.W = (const __nv_bfloat16*)W; p.N = 3 * H; p.K = K; p.M = M;
+    p.xw = (const __nv_bfloat16*)xw; p.ss_in = ss_in; p.ss_parts = ss_parts; p.eps = eps;
+    p.out_bf16 = (__nv_bfloat16*)out; p.out_stride = H; p.bias = in_bias; p.ff = H; p.rows_per_cta = 16;
+    p.taps = taps; p.conv_bias = conv_bias; p.state = (__nv_bfloat16*)state; p.slot_stride = slot_stride;
+    p.state_slots = state_slots; p.positions = positions; p.L = L; p.num_slots = num_slots; p.status = status;
+    const int blocks = (H + 7) / 8;
+    p.num_tiles = blocks;
+    if (M <= 8) return launch_gv<1, GV_PRO_NORM, GV_EPI_CONV>(p, blocks, stream);
+    return launch_gv<2, GV_PRO_NORM, GV_EPI_CONV>(p, blocks, stream);
 }
 
 VAPI_EXPORT const char* vapi_last_error() { return error_buffer(); }

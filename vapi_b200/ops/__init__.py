@@ -283,6 +283,55 @@ TC_MAX_ROWS = 256
 use_tc = os.environ.get("VAPI_TC", "1") != "0"
 
 
+def skinny_shortconv_applies(rows: int, w_in: torch.Tensor, kernel: int, state_layer: Optional[torch.Tensor]) -> bool:
+    """Whether :func:`skinny_shortconv` takes a decode step of ``rows`` single-token sequences."""
+    return (skinny_applies(rows, w_in) and 1 <= kernel <= 8 and w_in.shape[0] % 3 == 0
+            and (kernel == 1 or (state_layer is not None and state_layer.dtype == torch.bfloat16)))
+
+
+def skinny_shortconv(w_in: torch.Tensor, *, xw: torch.Tensor, ss_in: torch.Tensor, eps: float,
+                     in_bias: Optional[torch.Tensor], taps: torch.Tensor, conv_bias: Optional[torch.Tensor],
+                     state_layer: Optional[torch.Tensor], state_slots: torch.Tensor, positions: torch.Tensor,
+                     status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The short-conv mixer up to its out_proj for a decode step, in one launch: in_proj on the
+    stream seen through a deferred norm (``xw``, ``ss_in``, ``eps`` as for :func:`skinny_linear`),
+    gate, taps over each request's state, ``C * conv``, state update.  Every one of the M <= 16
+    tokens must be a sequence of its own: token m uses ``state_slots[m]`` and ``positions[m]``.
+    Returns y [M, H] bfloat16."""
+    _cuda(w_in, xw, ss_in, in_bias, taps, conv_bias, state_layer, state_slots, positions)
+    H3, K = w_in.shape
+    H, M, L = H3 // 3, xw.shape[0], taps.shape[0]
+    if w_in.dtype != torch.bfloat16 or not w_in.is_contiguous() or H3 != 3 * H:
+        raise KernelError("skinny_shortconv needs a contiguous bfloat16 in_proj weight of 3H rows")
+    if xw.dtype != torch.bfloat16 or tuple(xw.shape) != (M, K) or not xw.is_contiguous():
+        raise KernelError("skinny_shortconv: the weighted stream must be [M, K] bfloat16")
+    _f32(ss_in, "partial sums")
+    if ss_in.dim() != 2 or ss_in.shape[1] != M:
+        raise KernelError("partial sums must be [parts, M]")
+    for t, w in ((in_bias, "in_proj bias"), (taps, "conv taps"), (conv_bias, "conv bias")):
+        _f32(t, w)
+    if tuple(taps.shape) != (L, H):
+        raise KernelError("taps must be [L, H]")
+    _i32(state_slots, "state slots")
+    _i32(positions, "positions")
+    if state_slots.numel() < M or positions.numel() < M:
+        raise KernelError("skinny_shortconv: one state slot and one position per token are needed")
+    slot_stride = num_slots = 0
+    if L > 1:
+        if state_layer is None or state_layer.dtype != torch.bfloat16 or tuple(state_layer.shape[1:]) != (L - 1, H):
+            raise KernelError(f"state must be [slots, {L - 1}, {H}] bfloat16")
+        if state_layer.stride(2) != 1 or state_layer.stride(1) != H:
+            raise KernelError("state rows must be contiguous")
+        slot_stride, num_slots = state_layer.stride(0), state_layer.shape[0]
+    out = torch.empty((M, H), dtype=torch.bfloat16, device=w_in.device)
+    lib = _lib("gemv")
+    _check(lib, lib.vapi_skinny_linear_conv(
+        _p(w_in), H, K, M, _p(xw), _p(ss_in), ss_in.shape[0], ctypes.c_float(eps), _p(in_bias), _p(taps), _p(conv_bias),
+        L, _p(state_layer if L > 1 else None), ctypes.c_longlong(slot_stride), num_slots, _p(state_slots),
+        _p(positions), _p(out), _p(status), _stream()))
+    return out
+
+
 def tc_applies(rows: int, weight: torch.Tensor) -> bool:
     """Whether the tcgen05 kernel takes this product: bfloat16 weight, 17..256 rows, inner size
     a multiple of 8 (16-byte rows for TMA)."""

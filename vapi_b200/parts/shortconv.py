@@ -67,9 +67,16 @@ class ShortConv(Mixer):
         n = x.shape[0]
         if not (ops.few_rows_applies(n, self.w_in) and ops.few_rows_applies(n, self.w_out)):
             return NotImplemented
-        h3 = ops.few_rows_linear(self.w_in, xw=a.xw, ss_in=a.ss, eps=a.eps, epilogue="bf16")
-        y = ops.shortconv(h3, self.b_in, self.taps, self.b_conv, cache.tensor, ctx.state_slots,
-                          ctx.tok_seq, ctx.cu_q, ctx.positions, ctx.status)
+        if ctx.max_q == 1 and ctx.n == ctx.num_seqs and ops.skinny_shortconv_applies(n, self.w_in, self.kernel, cache.tensor):
+            # a decode step: every token is a sequence of its own, and the gated convolution rides
+            # on in_proj as its epilogue
+            y = ops.skinny_shortconv(self.w_in, xw=a.xw, ss_in=a.ss, eps=a.eps, in_bias=self.b_in, taps=self.taps,
+                                     conv_bias=self.b_conv, state_layer=cache.tensor, state_slots=ctx.state_slots,
+                                     positions=ctx.positions, status=ctx.status)
+        else:
+            h3 = ops.few_rows_linear(self.w_in, xw=a.xw, ss_in=a.ss, eps=a.eps, epilogue="bf16")
+            y = ops.shortconv(h3, self.b_in, self.taps, self.b_conv, cache.tensor, ctx.state_slots,
+                              ctx.tok_seq, ctx.cu_q, ctx.positions, ctx.status)
         ss, xw = ops.few_rows_linear(self.w_out, act=y, epilogue="resid", resid=x, bias=self.b_out, next_weight=next_weight)
         return StreamState(xw, ss)
 
