@@ -594,9 +594,10 @@ def test_linear_tc_plain_products(ops, M, N, K):
     again = ops.linear_tc(dev(w), act=dev(a), epilogue="bf16", bias=dev(b), status=st)
     assert torch.equal(got, again), "the split-K sum must not depend on arrival order"
     assert int(st.item()) == 0
+    # the dispatcher sends up to TC_MAX_ROWS rows here and larger steps to the library's product
     before = ops.launch_count
     got = ops.linear(dev(a), dev(w), None, torch.float32)
-    assert ops.launch_count == before + 1
+    assert ops.launch_count == before + (1 if M <= ops.TC_MAX_ROWS else 0)
     torch.testing.assert_close(got.cpu(), want, atol=3e-3 * math.sqrt(K / 96), rtol=1e-3)
 
 

@@ -278,8 +278,11 @@ def skinny_linear(weight: torch.Tensor, *, act: Optional[torch.Tensor] = None,
     return out_bf16 if out_bf16 is not None else out_f32
 
 
-TC_MAX_ROWS = 256
-#: set False to keep products of 17..256 rows on the library
+#: Steps of up to this many rows go to the tcgen05 product with its fused epilogues.  The kernel
+#: itself takes up to 256 rows, but beyond 128 it has too few tiles per launch to keep up with the
+#: library's product (measured: 2-7x slower at 256 rows), so larger steps take the unfused path.
+TC_MAX_ROWS = 128
+#: set False to keep products of 17..128 rows on the library
 use_tc = os.environ.get("VAPI_TC", "1") != "0"
 
 
@@ -333,7 +336,7 @@ def skinny_shortconv(w_in: torch.Tensor, *, xw: torch.Tensor, ss_in: torch.Tenso
 
 
 def tc_applies(rows: int, weight: torch.Tensor) -> bool:
-    """Whether the tcgen05 kernel takes this product: bfloat16 weight, 17..256 rows, inner size
+    """Whether the tcgen05 kernel takes this product: bfloat16 weight, 17..TC_MAX_ROWS rows, inner size
     a multiple of 8 (16-byte rows for TMA)."""
     return (use_tc and weight.is_cuda and weight.dtype == torch.bfloat16 and SKINNY_MAX_ROWS < rows <= TC_MAX_ROWS
             and weight.dim() == 2 and weight.shape[1] % 8 == 0 and weight.is_contiguous())
@@ -405,7 +408,7 @@ def few_rows_applies(rows: int, weight: torch.Tensor) -> bool:
 
 
 def few_rows_linear(weight: torch.Tensor, **kw):
-    """:func:`skinny_linear` up to 16 rows, :func:`linear_tc` up to 256."""
+    """:func:`skinny_linear` up to 16 rows, :func:`linear_tc` above."""
     src = kw.get("act") if kw.get("act") is not None else kw.get("xw")
     if src.shape[0] <= SKINNY_MAX_ROWS:
         return skinny_linear(weight, **kw)
