@@ -12,7 +12,7 @@ from __future__ import annotations
 import json
 import math
 import os
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Sequence
 
 import torch
 from safetensors import safe_open

@@ -8,7 +8,6 @@ package imports them, and the package has no CPU path of its own.
 from __future__ import annotations
 
 import math
-from typing import Optional
 
 import torch
 

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from vapi_b200.cache import CacheManager, OutOfPages, OutOfSlots, PagePool, SlotPool
-from vapi_b200.engine.scheduler import AdmitError, Scheduler, SchedulerConfig, SeqStatus
+from vapi_b200.engine.scheduler import AdmitError, Scheduler, SchedulerConfig
 from vapi_b200.engine.step import StepEntry, StepError, validate_step
 from vapi_b200.parts.base import PagedSpec, StateSpec
 from vapi_b200.sampling.params import FinishReason, SamplingParams

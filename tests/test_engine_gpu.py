@@ -2,13 +2,10 @@
 captured decode steps against eager ones, temperature sampling, each part alone against the
 plain model's function for it, and a toy mixer with state of its own that is registered,
 built and stepped without touching the package's files."""
-import math
-
 import pytest
 import torch
 
 import plain_lfm2
-import plain_ops
 from conftest import TINY_A, TINY_B, TINY_C
 
 pytestmark = pytest.mark.gpu
@@ -242,8 +239,6 @@ def test_a_toy_mixer_with_its_own_state_can_be_registered_built_and_stepped(tmp_
     runs through the package's step function, portions and decode tokens alike; the
     package's files are not touched.  Its math is plain torch on the device, which is the
     toy's own business; everything around it is the engine."""
-    import json
-    import os
     from vapi_b200.config import Architecture, register_architecture, unregister_architecture
     from vapi_b200.engine.runner import ModelRunner
     from vapi_b200.engine.step import StepEntry

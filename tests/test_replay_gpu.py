@@ -2,8 +2,6 @@
 tokens decoded one by one, in portions of changing size down to two tokens, and mixed with
 other requests in a pool so small that pages and state slots are used again; in float32 and
 in bfloat16, for tiny configurations that differ in every size and option."""
-import os
-
 import pytest
 import torch
 

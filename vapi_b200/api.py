@@ -17,10 +17,10 @@ from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Sequence, Union
 
 from .config.runtime import RuntimeConfig
-from .engine.engine import Engine, Finished
+from .engine.engine import Engine
 from .engine.runner import ModelRunner
 from .engine.scheduler import SchedulerConfig
-from .sampling.params import FinishReason, SamplingParams
+from .sampling.params import SamplingParams
 
 
 @dataclass

@@ -29,9 +29,9 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..parts.base import CacheView, PagedSpec, StateSpec
+from ..parts.base import PagedSpec, StateSpec
 from .. import hostlib
-from .pool import OutOfPages, OutOfSlots, PagePool, SlotPool
+from .pool import OutOfSlots, PagePool, SlotPool
 
 
 @dataclass

@@ -12,10 +12,9 @@ The LFM2 rules follow the reference's ``Lfm2Config::from_json``
 from __future__ import annotations
 
 import json
-import math
 import os
-from dataclasses import dataclass, field, asdict
-from typing import Any, Callable, Dict, List, Optional, Tuple
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, List, Tuple
 
 
 class ConfigError(ValueError):

@@ -18,7 +18,7 @@ import torch
 from ..sampling.params import FinishReason, SamplingParams
 from ..sampling.sampler import PendingSample, Sampler, SamplerState
 from .runner import ModelRunner
-from .scheduler import AdmitError, Scheduler, SchedulerConfig, SeqStatus, StepPlan
+from .scheduler import AdmitError, Scheduler, SchedulerConfig, StepPlan
 
 
 @dataclass

@@ -18,13 +18,13 @@ from typing import Any, Dict, List, Optional, Sequence
 import torch
 
 from .. import ops
-from ..cache.manager import CacheManager, RequestCache
+from ..cache.manager import CacheManager
 from ..config.model import eos_token_ids, load_config_json, resolve_architecture
 from ..models.plan import ModelPlan
 from ..parts.base import CacheView
 from ..weights.loader import load_tensors
 from ..weights.random import random_tensors
-from .step import StepContext, StepEntry, StepError, StepPacker, validate_step
+from .step import StepContext, StepEntry, StepPacker, validate_step
 
 DTYPES = {"float32": torch.float32, "fp32": torch.float32, "f32": torch.float32,
           "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}

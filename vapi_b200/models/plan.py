@@ -2,11 +2,11 @@
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Sequence, Tuple
+from typing import Any, Dict, List, Optional, Tuple
 
 import torch
 
-from ..parts.base import CacheView, Norm, PagedSpec, Part, PositionEncoding, StateSpec, TensorSpec
+from ..parts.base import Norm, Part, PositionEncoding, TensorSpec
 from ..parts.embedding import OutputHead, TokenEmbedding
 
 

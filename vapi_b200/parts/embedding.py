@@ -1,7 +1,7 @@
 """Token embedding and the output head."""
 from __future__ import annotations
 
-from typing import Any, Dict, List, Optional
+from typing import Any, List, Optional
 
 import torch
 

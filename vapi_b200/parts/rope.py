@@ -1,7 +1,7 @@
 """Rotary position encoding: per-step cos/sin rows in float32."""
 from __future__ import annotations
 
-from typing import Any, Dict, Optional, Tuple
+from typing import Any, Dict, Tuple
 
 import torch
 

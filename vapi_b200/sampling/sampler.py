@@ -11,7 +11,7 @@ counter of its own, so a seeded request does not depend on what else is in the b
 from __future__ import annotations
 
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
