@@ -55,17 +55,29 @@ TINY_C = {
 }
 
 
+# A fourth: head size 64 and widths that are multiples of 32, the shapes the serving kernels
+# want (tensor-core attention, the weight-streaming and tcgen05 products), still tiny
+TINY_D = {
+    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
+    "vocab_size": 1003, "hidden_size": 256, "intermediate_size": 640, "block_auto_adjust_ff_dim": False,
+    "num_hidden_layers": 4, "layer_types": ["conv", "full_attention", "conv", "full_attention"],
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+    "conv_L_cache": 3, "conv_bias": False, "rope_theta": 1000000.0, "norm_eps": 1e-5,
+    "tie_word_embeddings": True, "max_position_embeddings": 512, "eos_token_id": 2,
+}
+
+
 @pytest.fixture(scope="session")
 def tiny_dirs(tmp_path_factory):
     """Model folders of the tiny configurations, float32 weights (perturbed norm weights so a
     dropped norm weight shows)."""
     from vapi_b200.weights import write_random_model
     out = {}
-    for name, cfg, seed in (("A", TINY_A, 0), ("B", TINY_B, 2), ("C", TINY_C, 4)):
+    for name, cfg, seed in (("A", TINY_A, 0), ("B", TINY_B, 2), ("C", TINY_C, 4), ("D", TINY_D, 6)):
         d = tmp_path_factory.mktemp(f"tiny{name}")
         # std 0.2 / perturbed norms as the reference's golden generator uses
         # (tools/gen_lfm2_goldens.py:27-49): activations large enough that faults show.
-        write_random_model(str(d), cfg, seed, std=0.2 if name != "A" else 0.02,
+        write_random_model(str(d), cfg, seed, std={"A": 0.02, "D": 0.1}.get(name, 0.2),
                            norm_init="perturbed" if name != "A" else "ones", dtype=torch.float32)
         out[name] = str(d)
     return out

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import plain_lfm2
-from conftest import TINY_A, TINY_B, TINY_C
+from conftest import TINY_A, TINY_B, TINY_C, TINY_D
 
 pytestmark = pytest.mark.gpu
 
@@ -143,6 +143,29 @@ def test_running_one_step_ahead_changes_no_token(tiny_dirs, dtype):
     # seeded temperature on the device: the draw counters advance the same way
     temp = [SamplingParams(temperature=0.9, seed=11 + i, max_tokens=16, ignore_eos=True) for i in range(6)]
     assert run(True, temp, 40)[0] == run(False, temp, 40)[0]
+
+
+def test_one_step_ahead_and_graphs_with_the_serving_kernels(tmp_path):
+    """Head size 64 and bfloat16 weights: the captured decode step runs the weight-streaming
+    products, the conv epilogue and the tensor-core attention.  Tokens must not depend on whether
+    the engine runs ahead or uses graphs, and must follow the plain model up to near-ties."""
+    from vapi_b200 import LLM, SamplingParams
+    from vapi_b200.weights import write_random_model
+    d = write_random_model(str(tmp_path / "m"), TINY_D, 21, std=0.1, norm_init="perturbed", dtype=torch.bfloat16)
+    plain = plain_lfm2.PlainLfm2(d)
+    prompts = _prompts(TINY_D, 5, [3, 70, 130, 18, 64])
+    params = [SamplingParams(temperature=0.0, max_tokens=12 + 2 * i, ignore_eos=True) for i in range(5)]
+    outs = {}
+    for ahead, graphs in ((True, True), (False, True), (True, False), (False, False)):
+        llm = LLM(d, dtype="bf16", num_blocks=24, max_concurrent_seqs=4, max_batched_tokens=256, max_context=256,
+                  prefill_chunk_tokens=128, run_ahead=ahead, cuda_graphs=graphs)
+        outs[(ahead, graphs)] = [c.tokens for c in llm.generate(prompts, params)]
+        llm.runner.check_status()
+        llm.runner.cache.check_invariants()
+        assert (llm.engine.stats.ahead_steps > 0) == ahead
+    assert outs[(True, True)] == outs[(False, True)] and outs[(True, False)] == outs[(False, False)]
+    for p, got in zip(prompts, outs[(True, True)]):
+        assert _agrees_up_to_a_near_tie(plain, p, got, plain.greedy(p, len(got))), got
 
 
 def test_penalties_change_what_is_generated(tiny_dirs):
