@@ -36,9 +36,17 @@ constexpr int GV_WARPS = 8;
 #ifndef GV_STAGES_N
 #define GV_STAGES_N 8
 #endif
+#ifndef GV_DEEP_STAGES_N
+#define GV_DEEP_STAGES_N 16
+#endif
+constexpr int GV_DEEP_STAGES = GV_DEEP_STAGES_N;
 constexpr int GV_STAGES_DEFAULT = GV_STAGES_N;   // depth of the per-lane copy queue (chunks of 32 k)
 // the conv epilogue streams three weight rows per lane: six stages keep two blocks on an SM
-template <int EPI> __host__ __device__ constexpr int gv_stages() { return EPI == 4 ? (GV_STAGES_DEFAULT < 6 ? GV_STAGES_DEFAULT : 6) : GV_STAGES_DEFAULT; }
+// (DEEP: a product with a long K and no more tiles than SMs has one block per SM anyway and takes
+// a deeper queue instead of a second block)
+template <int EPI, bool DEEP = false> __host__ __device__ constexpr int gv_stages() {
+    return DEEP ? GV_DEEP_STAGES : (EPI == 4 ? (GV_STAGES_DEFAULT < 6 ? GV_STAGES_DEFAULT : 6) : GV_STAGES_DEFAULT);
+}
 
 enum { GV_PRO_ACT = 0, GV_PRO_NORM = 1 };
 enum { GV_EPI_BF16 = 0, GV_EPI_SWIGLU = 1, GV_EPI_RESID = 2, GV_EPI_F32 = 3, GV_EPI_CONV = 4 };
@@ -86,18 +94,18 @@ template <int N> __device__ __forceinline__ void gv_wait() { asm volatile("cp.as
 template <int NT, int PRO, int EPI>
 __host__ __device__ constexpr int gv_slots() { return (EPI == GV_EPI_CONV ? 3 : 2) + (PRO == GV_PRO_ACT ? NT : 0); }
 
-template <int NT, int PRO, int EPI>
+template <int NT, int PRO, int EPI, bool DEEP>
 static size_t gv_smem_bytes(int K) {
-    size_t b = (size_t)GV_WARPS * gv_stages<EPI>() * gv_slots<NT, PRO, EPI>() * 32 * sizeof(uint4);
+    size_t b = (size_t)GV_WARPS * gv_stages<EPI, DEEP>() * gv_slots<NT, PRO, EPI>() * 32 * sizeof(uint4);
     if (PRO == GV_PRO_NORM) b += (size_t)8 * NT * (K + 32) * sizeof(__nv_bfloat16);
     return b;
 }
 
-template <int NT, int PRO, int EPI>
+template <int NT, int PRO, int EPI, bool DEEP = false>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 skinny_linear_kernel(const GvParams p) {
     constexpr int SLOTS = gv_slots<NT, PRO, EPI>();
-    constexpr int GV_STAGES = gv_stages<EPI>();
+    constexpr int GV_STAGES = gv_stages<EPI, DEEP>();
     constexpr int WS = EPI == GV_EPI_CONV ? 3 : 2;     // weight rows a lane streams per chunk
     constexpr int COLS = 8 * NT;
     extern __shared__ __align__(16) unsigned char gv_smem[];
@@ -360,10 +368,10 @@ skinny_linear_kernel(const GvParams p) {
     gv_wait<0>();
 }
 
-template <int NT, int PRO, int EPI>
+template <int NT, int PRO, int EPI, bool DEEP = false>
 static int launch_gv(const GvParams& p, int blocks, cudaStream_t stream) {
-    const size_t smem = gv_smem_bytes<NT, PRO, EPI>(p.K);
-    auto kern = skinny_linear_kernel<NT, PRO, EPI>;
+    const size_t smem = gv_smem_bytes<NT, PRO, EPI, DEEP>(p.K);
+    auto kern = skinny_linear_kernel<NT, PRO, EPI, DEEP>;
     if (smem > 200 * 1024) return fail(-1, "skinny_linear: K=%d needs %zu bytes of shared memory", p.K, smem);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -424,6 +432,15 @@ VAPI_EXPORT int vapi_skinny_linear(const void* W, int N, int K, int M, int pro, 
         case GV_EPI_RESID: GV_GO(NT, PRO, GV_EPI_RESID);      \
         case GV_EPI_F32: GV_GO(NT, PRO, GV_EPI_F32);          \
         default: return fail(-2, "skinny_linear: unknown epilogue %d", epi); \
+    }
+    static int deep_k = -1;
+    if (deep_k < 0) {
+        const char* e = getenv("VAPI_GV_DEEP_K");
+        deep_k = e ? atoi(e) : 4096;
+    }
+    if (pro == GV_PRO_ACT && epi == GV_EPI_RESID && deep_k > 0 && K >= deep_k && blocks <= 148) {
+        if (M <= 8) return launch_gv<1, GV_PRO_ACT, GV_EPI_RESID, true>(p, blocks, stream);
+        return launch_gv<2, GV_PRO_ACT, GV_EPI_RESID, true>(p, blocks, stream);
     }
     if (pro == GV_PRO_ACT) {
         if (M <= 8) { GV_EPIS(1, GV_PRO_ACT) } else { GV_EPIS(2, GV_PRO_ACT) }
