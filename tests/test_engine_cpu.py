@@ -196,3 +196,43 @@ def test_sampling_params_validation():
             SamplingParams(**bad).validate()
     assert SamplingParams(temperature=0.0).is_greedy and not SamplingParams().is_greedy
     assert SamplingParams(temperature=0.7).device_drawable and not SamplingParams(temperature=0.7, top_k=5).device_drawable
+
+
+def test_logprobs_are_the_models_own_distribution(tiny_dirs, plain_kernels):
+    """``logprobs=k``: for every generated token its log-probability under the raw logits and the
+    k most likely tokens, most likely first (crates/vapi-engine/src/sampler.rs:114-153), whatever
+    temperature and penalties do to the choice."""
+    plain = plain_lfm2.PlainLfm2(tiny_dirs["B"])
+    eng = _engine(tiny_dirs["B"], max_context=128)
+    p = _prompts(TINY_B, 7, [9])[0]
+    eng.admit("g", p, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True, logprobs=3))
+    eng.admit("t", p, SamplingParams(temperature=1.3, seed=4, presence_penalty=1.0, max_tokens=5, ignore_eos=True, logprobs=2))
+    eng.admit("n", p, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+    done = {f.request_id: f for f in eng.run()}
+    assert done["n"].logprobs is None and done["n"].tokens == done["g"].tokens
+    for rid, k in (("g", 3), ("t", 2)):
+        f = done[rid]
+        assert len(f.logprobs) == len(f.tokens) == 5
+        text = list(p)
+        for tok, lp in zip(f.tokens, f.logprobs):
+            want = torch.log_softmax(plain.logits(text)[-1].double(), -1)
+            assert lp.token == tok and abs(lp.logprob - float(want[tok])) < 1e-4
+            top = torch.topk(want, k)
+            assert [t for t, _ in lp.top] == top.indices.tolist()
+            assert max(abs(a - float(b)) for (_, a), b in zip(lp.top, top.values)) < 1e-4
+            text.append(tok)
+    assert done["g"].logprobs[0].top[0][0] == done["g"].tokens[0]          # greedy takes the most likely token
+    with pytest.raises(ValueError, match="logprobs"):
+        SamplingParams(logprobs=21).validate()
+    with pytest.raises(ValueError, match="n must"):
+        SamplingParams(n=9).validate()
+
+
+def test_row_logprobs_breaks_ties_by_the_lower_id():
+    from vapi_b200.sampling.sampler import row_logprobs
+    import numpy as np
+    row = np.array([0.5, 2.0, 2.0, -1.0, 2.0, 0.5], dtype=np.float32)
+    lse, top = row_logprobs(row, 4)
+    assert [t for t, _ in top] == [1, 2, 4, 0]
+    assert abs(lse - float(torch.logsumexp(torch.tensor(row), 0))) < 1e-6
+    assert row_logprobs(row, 0)[1] == []

@@ -168,6 +168,26 @@ def test_one_step_ahead_and_graphs_with_the_serving_kernels(tmp_path):
         assert _agrees_up_to_a_near_tie(plain, p, got, plain.greedy(p, len(got))), got
 
 
+def test_several_completions_per_prompt_and_logprobs(tiny_dirs):
+    from vapi_b200 import LLM, SamplingParams
+    prompts = _prompts(TINY_B, 8, [12, 30])
+    llm = LLM(tiny_dirs["B"], dtype="f32", num_blocks=24, max_concurrent_seqs=4, max_batched_tokens=64, max_context=256)
+    sp = SamplingParams(temperature=0.9, seed=40, n=3, max_tokens=8, ignore_eos=True)
+    out = llm.generate(prompts, sp)
+    assert [(c.index, c.prompt_tokens) for c in out] == [(0, 12), (1, 12), (2, 12), (0, 30), (1, 30), (2, 30)]
+    assert len({tuple(c.tokens) for c in out[:3]}) > 1, "three seeds should not all give the same text"
+    for i in range(3):       # completion i is what seed + i gives on its own
+        alone = llm.generate([prompts[1]], SamplingParams(temperature=0.9, seed=40 + i, max_tokens=8, ignore_eos=True))
+        assert alone[0].tokens == out[3 + i].tokens
+    plain = plain_lfm2.PlainLfm2(tiny_dirs["B"])
+    lp = llm.generate([prompts[0]], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True, logprobs=2))[0]
+    text = list(prompts[0])
+    for tok, rec in zip(lp.tokens, lp.logprobs):
+        want = torch.log_softmax(plain.logits(text)[-1], -1)
+        assert rec.token == tok and abs(rec.logprob - float(want[tok])) < 1e-3 and rec.top[0][0] == tok
+        text.append(tok)
+
+
 def test_penalties_change_what_is_generated(tiny_dirs):
     from vapi_b200 import LLM, SamplingParams
     p = _prompts(TINY_A, 6, [12])

@@ -13,7 +13,7 @@ programmatic entry is its decode_profile example
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 from typing import Any, Dict, List, Optional, Sequence, Union
 
 from .config.runtime import RuntimeConfig
@@ -30,6 +30,8 @@ class Completion:
     tokens: List[int]
     finish_reason: str
     preemptions: int = 0
+    index: int = 0                      # which of the prompt's ``n`` completions this is
+    logprobs: Optional[list] = None     # per generated token: sampling.sampler.TokenLogprobs, when asked for
 
 
 class LLM:
@@ -75,7 +77,10 @@ class LLM:
                  params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
                  on_token=None) -> List[Completion]:
         """Generate for every prompt (lists of token ids) with continuous batching; results
-        come back in the order of ``prompts``."""
+        come back in the order of ``prompts``.  With ``n`` above 1 a prompt gets that many
+        completions, one after the other in the result (``Completion.index`` says which); each is
+        a request of its own, seeded ``seed + index`` when a seed is given.  (The reference forks
+        them from one prefill through its prefix cache, which this engine does not have.)"""
         if params is None:
             params = SamplingParams()
         plist = [params] * len(prompts) if isinstance(params, SamplingParams) else list(params)
@@ -83,15 +88,18 @@ class LLM:
             raise ValueError("one SamplingParams per prompt, or one for all")
         ids = []
         for prompt, p in zip(prompts, plist):
-            rid = self._next
-            self._next += 1
-            self.engine.admit(rid, prompt, p)
-            ids.append(rid)
+            p.validate()
+            for i in range(p.n):
+                rid = self._next
+                self._next += 1
+                one = p if p.n == 1 else replace(p, n=1, seed=None if p.seed is None else p.seed + i)
+                self.engine.admit(rid, prompt, one)
+                ids.append((rid, i))
         done = {f.request_id: f for f in self.engine.run(on_token)}
         out = []
-        for rid in ids:
+        for rid, i in ids:
             f = done[rid]
-            out.append(Completion(rid, f.prompt_tokens, f.tokens, f.reason.value, f.preemptions))
+            out.append(Completion(rid, f.prompt_tokens, f.tokens, f.reason.value, f.preemptions, i, f.logprobs))
         return out
 
 

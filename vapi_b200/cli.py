@@ -48,6 +48,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--presence-penalty", type=float, default=0.0)
     g.add_argument("--max-tokens", type=int, default=256)
     g.add_argument("--seed", type=int)
+    g.add_argument("--n", type=int, default=1, help="completions per prompt")
+    g.add_argument("--logprobs", type=int, help="report log-probabilities: the chosen token's and this many top ones")
     g.add_argument("--stop-token-ids", default="", help="comma-separated token ids")
     g = ap.add_argument_group("prompts")
     g.add_argument("--prompt-ids", action="append", default=[], metavar="ID,ID,...",
@@ -103,11 +105,17 @@ def main(argv: Optional[List[str]] = None) -> int:
     params = SamplingParams(
         temperature=args.temperature, top_p=args.top_p, top_k=args.top_k, min_p=args.min_p,
         repetition_penalty=args.repetition_penalty, frequency_penalty=args.frequency_penalty,
-        presence_penalty=args.presence_penalty, max_tokens=args.max_tokens, seed=args.seed,
+        presence_penalty=args.presence_penalty, max_tokens=args.max_tokens, seed=args.seed, n=args.n,
+        logprobs=args.logprobs,
         stop_token_ids=tuple(int(t) for t in args.stop_token_ids.split(",") if t.strip()))
     for c in llm.generate(prompts, params):
-        print(json.dumps({"request": c.request_id, "prompt_tokens": c.prompt_tokens, "tokens": c.tokens,
-                          "finish_reason": c.finish_reason}), flush=True)
+        rec = {"request": c.request_id, "prompt_tokens": c.prompt_tokens, "tokens": c.tokens,
+               "finish_reason": c.finish_reason}
+        if params.n > 1:
+            rec["index"] = c.index
+        if c.logprobs is not None:
+            rec["logprobs"] = [{"token": lp.token, "logprob": lp.logprob, "top": lp.top} for lp in c.logprobs]
+        print(json.dumps(rec), flush=True)
     if args.stats:
         print(json.dumps(llm.engine.stats.__dict__), file=sys.stderr)
     return 0

@@ -16,7 +16,7 @@ from typing import Callable, Dict, List, Optional, Sequence, Tuple
 import torch
 
 from ..sampling.params import FinishReason, SamplingParams
-from ..sampling.sampler import PendingSample, Sampler, SamplerState
+from ..sampling.sampler import PendingSample, Sampler, SamplerState, TokenLogprobs
 from .runner import ModelRunner
 from .scheduler import AdmitError, Scheduler, SchedulerConfig, StepPlan
 
@@ -28,6 +28,7 @@ class Finished:
     tokens: List[int]
     reason: FinishReason
     preemptions: int = 0
+    logprobs: Optional[List[TokenLogprobs]] = None     # one per generated token, when the request asked
 
 
 @dataclass
@@ -83,6 +84,7 @@ class Engine:
         self.run_ahead = on_cuda if run_ahead is None else (bool(run_ahead) and on_cuda)
         self._inflight: Optional[Tuple[StepPlan, PendingSample]] = None
         self._needs_host: set = set()          # live requests whose rows the host has to sample
+        self._logprobs: Dict[int, List[TokenLogprobs]] = {}
         #: replaceable in tests: the function that runs a planned batch and returns logits
         self.step_fn: Callable[[StepPlan], Optional[torch.Tensor]] = self._run
 
@@ -99,6 +101,8 @@ class Engine:
         self.states[sid] = st
         if not Sampler.device_only(params):
             self._needs_host.add(sid)
+        if params.logprobs is not None:
+            self._logprobs[sid] = []
         return sid
 
     def cancel(self, sid: int) -> None:
@@ -169,6 +173,9 @@ class Engine:
             else:
                 self._settle(out)        # the host needs this step's logits: nothing may be ahead of it
                 pending = PendingSample(len(rows), tokens=self.sampler.sample(logits, rows))
+                for sid, lp in zip(plan.sampled_seqs, self.sampler.last_logprobs):
+                    if lp is not None and sid in self._logprobs:
+                        self._logprobs[sid].append(lp)
             self.scheduler.advance(plan)
             t3 = time.perf_counter()
         except Exception as exc:
@@ -204,7 +211,10 @@ class Engine:
         for seq in self.scheduler.drain_finished():
             self.states.pop(seq.seq_id, None)
             self._needs_host.discard(seq.seq_id)
-            done.append(Finished(seq.request_id, seq.prompt_len, seq.generated, seq.finish_reason, seq.preemptions))
+            lps = self._logprobs.pop(seq.seq_id, None)
+            gen = seq.generated
+            done.append(Finished(seq.request_id, seq.prompt_len, gen, seq.finish_reason, seq.preemptions,
+                                 lps[:len(gen)] if lps is not None else None))
         return done
 
     # ---- run to completion ---------------------------------------------------------------

@@ -26,7 +26,9 @@ class SamplingParams:
     frequency_penalty: float = 0.0
     presence_penalty: float = 0.0
     max_tokens: int = 256
+    n: int = 1                          # completions per prompt (each an independent request here)
     seed: Optional[int] = None
+    logprobs: Optional[int] = None      # report the chosen token's log-probability and this many top ones
     stop_token_ids: Tuple[int, ...] = ()
     ignore_eos: bool = False
 
@@ -41,8 +43,12 @@ class SamplingParams:
             raise ValueError("top_k must be >= 1")
         if self.max_tokens < 1:
             raise ValueError("max_tokens must be >= 1")
+        if not 1 <= self.n <= 8:
+            raise ValueError("n must be in [1, 8]")
         if self.repetition_penalty <= 0.0:
             raise ValueError("repetition_penalty must be > 0")
+        if self.logprobs is not None and not 0 <= self.logprobs <= 20:
+            raise ValueError("logprobs must be <= 20")
 
     @property
     def is_greedy(self) -> bool:

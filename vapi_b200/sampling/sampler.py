@@ -89,6 +89,31 @@ def host_sample(logits: np.ndarray, p: SamplingParams, state: SamplerState) -> i
 
 
 @dataclass
+class TokenLogprobs:
+    """Log-probabilities at one generated position under the model's own distribution (the raw
+    logits, before temperature and penalties: crates/vapi-engine/src/sampler.rs:114-153)."""
+    token: int
+    logprob: float
+    top: List[Tuple[int, float]]        # the k most likely tokens, most likely first, ties by lower id
+
+
+def row_logprobs(logits: np.ndarray, k: int):
+    """``(lse, top)`` of a float32 row: log-sum-exp, and the k largest as (token, logprob)."""
+    row = logits.astype(np.float32)
+    mx = np.float32(row.max())
+    lse = float(mx + np.log(np.exp(row - mx, dtype=np.float32).sum(dtype=np.float32)))
+    top: List[Tuple[int, float]] = []
+    if k > 0:
+        k = min(k, row.size)
+        cand = np.argpartition(-row, k - 1)[:k] if k < row.size else np.arange(row.size)
+        # everything tied with the k-th value must compete, so that the lower id wins a tie
+        cand = np.nonzero(row >= row[cand].min())[0]
+        order = np.lexsort((cand, -row[cand]))[:k]
+        top = [(int(cand[i]), float(row[cand[i]]) - lse) for i in order]
+    return lse, top
+
+
+@dataclass
 class PendingSample:
     """Tokens decided on the device and on their way to the host."""
     rows: int
@@ -108,12 +133,14 @@ class Sampler:
         self.h2d_bytes_last = 0
         self._ring: List[list] = []
         self._next = 0
+        #: per row of the last :meth:`sample` call: None, or the :class:`TokenLogprobs` it asked for
+        self.last_logprobs: List[Optional[TokenLogprobs]] = []
 
     @staticmethod
     def device_only(p: SamplingParams) -> bool:
         """Whether a row with these parameters is decided by the device launch alone (greedy, or
         temperature without truncation) and needs nothing of the host but the result."""
-        return (p.is_greedy or p.device_drawable) and not p.has_penalties
+        return (p.is_greedy or p.device_drawable) and not p.has_penalties and p.logprobs is None
 
     def launch(self, logits: torch.Tensor, rows: Sequence[Tuple[SamplingParams, SamplerState]],
                out: torch.Tensor) -> PendingSample:
@@ -161,6 +188,20 @@ class Sampler:
         assert logits.shape[0] >= R
         self.h2d_bytes_last = 0
         dev = logits.device
+        # rows that report log-probabilities: their raw logits, before any penalty touches them
+        raw: Dict[int, Tuple[float, List[Tuple[int, float]], np.ndarray]] = {}
+        for r, (p, _) in enumerate(rows):
+            if p.logprobs is not None:
+                row = logits[r].to(torch.float32).cpu().numpy()
+                lse, top = row_logprobs(row, p.logprobs)
+                raw[r] = (lse, top, row)
+        toks = self._choose(logits, rows, dev)
+        self.last_logprobs = [TokenLogprobs(toks[r], float(raw[r][2][toks[r]]) - raw[r][0], raw[r][1]) if r in raw else None
+                              for r in range(R)]
+        return toks
+
+    def _choose(self, logits: torch.Tensor, rows: Sequence[Tuple[SamplingParams, SamplerState]], dev) -> List[int]:
+        R = len(rows)
         # penalties, on the device, for the rows that have any
         pr, pt, pc = [], [], []
         for r, (p, st) in enumerate(rows):
