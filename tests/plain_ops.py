@@ -222,6 +222,47 @@ def sample_rows(logits, mode=None, inv_t=None, seeds=None, draws=None, out=None)
     return res
 
 
+def sample_truncated(logits, inv_t, top_k, top_p, min_p, seeds, draws, out=None, check=False):
+    """Gumbel-max over the host sampler's survivors; rows with a negative top_k are left alone."""
+    rows, vocab = logits.shape
+    res = torch.zeros(rows, dtype=torch.int32) if out is None else out
+    for r in range(rows):
+        k = int(top_k[r]) if top_k is not None else 0
+        if k < 0:
+            continue
+        ids, _, scaled = truncated_survivors(logits[r].float().numpy(), float(inv_t[r]), k or None,
+                                             float(top_p[r]) if top_p is not None else 1.0,
+                                             float(min_p[r]) if min_p is not None else 0.0)
+        g = gumbel_noise(int(seeds[r]) & ((1 << 64) - 1), int(draws[r]), vocab)
+        best = max(ids.tolist(), key=lambda t: (float(scaled[t]) + float(g[t]), -t))
+        res[r] = best
+    return res
+
+
+def truncated_survivors(row, inv_t, top_k=None, top_p=1.0, min_p=0.0):
+    """Token ids that survive the host sampler's cuts, in its order (probability descending, then
+    id), and their probabilities over the 30-nat window
+    (crates/vapi-engine/src/sampler.rs:302-376): window, top-k, min-p, top-p."""
+    import numpy as np
+    scaled = row.astype(np.float32) * np.float32(inv_t)
+    mx = scaled.max()
+    keep = np.nonzero(scaled >= mx - np.float32(30.0))[0]
+    e = np.exp((scaled[keep] - mx).astype(np.float64))
+    prob = e / e.sum()
+    order = np.lexsort((keep, -prob))
+    ids, prob = keep[order], prob[order]
+    if top_k:
+        ids, prob = ids[:top_k], prob[:top_k]
+    if min_p > 0.0:
+        n = max(int(np.sum(np.cumprod(prob >= min_p * prob[0]))), 1)
+        ids, prob = ids[:n], prob[:n]
+    if top_p < 1.0:
+        cum = np.cumsum(prob)
+        n = max(min(int(np.searchsorted(cum, top_p, side="left")) + 1, len(prob)), 1)
+        ids, prob = ids[:n], prob[:n]
+    return ids, prob, scaled
+
+
 def apply_penalties(logits, rows, toks, counts, rep, freq, pres):
     """crates/vapi-engine/src/sampler.rs:262-283."""
     for i in range(rows.numel()):
@@ -236,6 +277,6 @@ def apply_penalties(logits, rows, toks, counts, rep, freq, pres):
         logits[r, t] = v
 
 
-ALL = ["embed", "resolve_tokens", "add_rmsnorm", "add_residual", "add_residual_ss", "skinny_applies", "tc_applies", "few_rows_applies", "swiglu", "linear", "strict_fp32", "rope_cos_sin",
+ALL = ["embed", "resolve_tokens", "sample_truncated", "add_rmsnorm", "add_residual", "add_residual_ss", "skinny_applies", "tc_applies", "few_rows_applies", "swiglu", "linear", "strict_fp32", "rope_cos_sin",
        "qk_norm_rope_write", "attention_splits", "paged_attention", "shortconv", "sample_rows",
        "apply_penalties"]

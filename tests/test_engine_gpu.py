@@ -101,7 +101,7 @@ def test_temperature_sampling_is_seeded_and_batch_independent(tiny_dirs):
     greedy = LLM(tiny_dirs["B"], dtype="f32", num_blocks=24, max_concurrent_seqs=4, max_batched_tokens=64,
                  max_context=256).generate([prompts[1]], SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
     assert together[1] != greedy[0].tokens, "temperature 0.8 on a flat tiny model should not reproduce greedy"
-    # truncating samplers run on the host from the row of logits
+    # the cuts (top-k, min-p, top-p) are made on the device too; top-k 1 leaves the most likely token
     tk = LLM(tiny_dirs["B"], dtype="f32", num_blocks=24, max_concurrent_seqs=4, max_batched_tokens=64, max_context=256)
     one = tk.generate([prompts[1]], SamplingParams(temperature=1.0, top_k=1, max_tokens=10, seed=1, ignore_eos=True))
     assert one[0].tokens == greedy[0].tokens
@@ -143,6 +143,12 @@ def test_running_one_step_ahead_changes_no_token(tiny_dirs, dtype):
     # seeded temperature on the device: the draw counters advance the same way
     temp = [SamplingParams(temperature=0.9, seed=11 + i, max_tokens=16, ignore_eos=True) for i in range(6)]
     assert run(True, temp, 40)[0] == run(False, temp, 40)[0]
+    # the same with the distribution cut by top-k / top-p / min-p for some of the requests
+    cut = [SamplingParams(temperature=1.1, seed=21 + i, max_tokens=16, ignore_eos=True, top_k=(20 if i % 2 else None),
+                          top_p=(0.9 if i % 3 else 1.0), min_p=(0.02 if i == 4 else 0.0)) for i in range(6)]
+    a, st_cut = run(True, cut, 40)
+    assert a == run(False, cut, 40)[0] and st_cut.ahead_steps > 10
+    assert a != run(True, temp, 40)[0]
 
 
 def test_one_step_ahead_and_graphs_with_the_serving_kernels(tmp_path):

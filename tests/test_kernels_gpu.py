@@ -564,6 +564,74 @@ def test_skinny_shortconv_is_in_proj_then_the_conv_kernel(ops, M, H, K, L, bias)
             torch.testing.assert_close(state_gpu.cpu().float(), state_ref.float(), atol=6e-2, rtol=4e-2)
 
 
+@pytest.mark.parametrize("vocab", [1000, 65536, 70001])
+def test_sample_truncated_cuts_where_the_host_sampler_cuts(ops, vocab):
+    """top-k, min-p and top-p on the device: the survivors are exactly the host sampler's (random
+    logits have no ties), the drawn token is one of them, and the draw is keyed by (seed, draw)."""
+    import numpy as np
+    g = torch.Generator().manual_seed(40)
+    cases = [(1.0, 5, 1.0, 0.0), (0.7, 0, 0.9, 0.0), (1.3, 0, 1.0, 0.05), (0.9, 50, 0.8, 0.01), (2.0, 0, 0.5, 0.0),
+             (1.0, 1, 1.0, 0.0), (0.5, 0, 1.0, 0.0), (1.0, 3000, 0.999, 0.0), (1.0, 0, 0.02, 0.0)]
+    R = len(cases)
+    logits = torch.randn(R, vocab, generator=g) * 3
+    logits[4, 17] += 9.0                                     # one row with a dominant token
+    f = lambda v, dt: torch.tensor(v, dtype=dt).cuda()
+    inv_t = f([1.0 / c[0] for c in cases], torch.float32)
+    top_k = f([c[1] for c in cases], torch.int32)
+    top_p = f([c[2] for c in cases], torch.float32)
+    min_p = f([c[3] for c in cases], torch.float32)
+    seeds = f(list(range(5, 5 + R)), torch.int64)
+    draws = f([0] * R, torch.int64)
+    out, tau, cnt = ops.sample_truncated(dev(logits), inv_t, top_k, top_p, min_p, seeds, draws, check=True)
+    again = ops.sample_truncated(dev(logits), inv_t, top_k, top_p, min_p, seeds, draws)
+    other = ops.sample_truncated(dev(logits), inv_t, top_k, top_p, min_p, seeds, draws + 1)
+    assert torch.equal(out, again)
+    assert not torch.equal(out[[1, 2, 6]], other[[1, 2, 6]]), "another draw should move at least one wide row"
+    for r, (T, k, tp, mp) in enumerate(cases):
+        ids, prob, scaled = plain_ops.truncated_survivors(logits[r].numpy(), 1.0 / T, k or None, tp, mp)
+        assert int(cnt[r]) == len(ids), (r, int(cnt[r]), len(ids))
+        assert int(out[r]) in set(ids.tolist())
+        assert abs(float(tau[r]) - float(scaled[ids].min())) < 1e-5 or len(ids) == int((scaled >= float(tau[r])).sum())
+    # a negative top_k leaves the row to another kernel
+    keep = torch.full((R,), -7, dtype=torch.int32).cuda()
+    ops.sample_truncated(dev(logits), inv_t, torch.full_like(top_k, -1), top_p, min_p, seeds, draws, out=keep)
+    assert keep.tolist() == [-7] * R
+
+
+def test_sample_truncated_draws_from_the_renormalised_distribution(ops):
+    import numpy as np
+    g = torch.Generator().manual_seed(41)
+    vocab, N = 300, 20000
+    row = torch.randn(1, vocab, generator=g) * 2
+    ids, prob, _ = plain_ops.truncated_survivors(row[0].numpy(), 1.0 / 0.8, 12, 0.85, 0.0)
+    want = prob / prob.sum()
+    f = lambda v, dt: torch.tensor(v, dtype=dt).cuda()
+    logits = dev(row).expand(N, vocab)                       # the same row N times, N draws
+    out = ops.sample_truncated(logits, f([1.25] * N, torch.float32), f([12] * N, torch.int32), f([0.85] * N, torch.float32),
+                               f([0.0] * N, torch.float32), f([9] * N, torch.int64), f(list(range(N)), torch.int64))
+    got = np.bincount(out.cpu().numpy(), minlength=vocab) / N
+    assert set(np.nonzero(got)[0].tolist()) <= set(ids.tolist())
+    sigma = np.sqrt(want * (1 - want) / N)
+    assert np.all(np.abs(got[ids] - want) < 5 * sigma + 1e-3), (got[ids], want)
+
+
+@pytest.mark.parametrize("M", [1, 8, 9, 16])
+def test_skinny_linear_long_k_residual_product(ops, M):
+    """w2 of the 1.2B model: K = 8192 and no more tiles than SMs, which takes the deeper copy queue."""
+    torch.manual_seed(33)
+    N, K = 2048, 8192
+    w = (torch.randn(N, K) * 0.02).to(torch.bfloat16)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    x = torch.randn(M, N)
+    nw = 1 + 0.1 * torch.randn(N)
+    xg = dev(x.clone())
+    ss, xw = ops.skinny_linear(dev(w), act=dev(a), epilogue="resid", resid=xg, next_weight=dev(nw))
+    want = x + a.float() @ w.float().t()
+    torch.testing.assert_close(xg.cpu(), want, atol=2e-2, rtol=1e-3)
+    torch.testing.assert_close(ss.sum(0).cpu(), (want ** 2).sum(1), rtol=1e-3, atol=1e-2)
+    torch.testing.assert_close(xw.cpu().float(), (want * nw).to(torch.bfloat16).float(), atol=3e-2, rtol=2e-2)
+
+
 def test_skinny_linear_refuses_what_it_cannot_do(ops):
     w = torch.zeros(64, 80, dtype=torch.bfloat16).cuda()
     with pytest.raises(ops.KernelError, match="multiple of 32"):

@@ -44,8 +44,10 @@ constexpr int GV_STAGES_DEFAULT = GV_STAGES_N;   // depth of the per-lane copy q
 // the conv epilogue streams three weight rows per lane: six stages keep two blocks on an SM
 // (DEEP: a product with a long K and no more tiles than SMs has one block per SM anyway and takes
 // a deeper queue instead of a second block)
-template <int EPI, bool DEEP = false> __host__ __device__ constexpr int gv_stages() {
-    return DEEP ? GV_DEEP_STAGES : (EPI == 4 ? (GV_STAGES_DEFAULT < 6 ? GV_STAGES_DEFAULT : 6) : GV_STAGES_DEFAULT);
+// (16 stages of 3 slots for up to 8 tokens, 12 of 4 slots for up to 16: 196 KB either way)
+template <int EPI, bool DEEP = false, int NT = 1> __host__ __device__ constexpr int gv_stages() {
+    return DEEP ? (NT == 1 ? GV_DEEP_STAGES : (GV_DEEP_STAGES * 3) / 4)
+                : (EPI == 4 ? (GV_STAGES_DEFAULT < 6 ? GV_STAGES_DEFAULT : 6) : GV_STAGES_DEFAULT);
 }
 
 enum { GV_PRO_ACT = 0, GV_PRO_NORM = 1 };
@@ -96,7 +98,7 @@ __host__ __device__ constexpr int gv_slots() { return (EPI == GV_EPI_CONV ? 3 : 
 
 template <int NT, int PRO, int EPI, bool DEEP>
 static size_t gv_smem_bytes(int K) {
-    size_t b = (size_t)GV_WARPS * gv_stages<EPI, DEEP>() * gv_slots<NT, PRO, EPI>() * 32 * sizeof(uint4);
+    size_t b = (size_t)GV_WARPS * gv_stages<EPI, DEEP, NT>() * gv_slots<NT, PRO, EPI>() * 32 * sizeof(uint4);
     if (PRO == GV_PRO_NORM) b += (size_t)8 * NT * (K + 32) * sizeof(__nv_bfloat16);
     return b;
 }
@@ -105,7 +107,7 @@ template <int NT, int PRO, int EPI, bool DEEP = false>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 skinny_linear_kernel(const GvParams p) {
     constexpr int SLOTS = gv_slots<NT, PRO, EPI>();
-    constexpr int GV_STAGES = gv_stages<EPI, DEEP>();
+    constexpr int GV_STAGES = gv_stages<EPI, DEEP, NT>();
     constexpr int WS = EPI == GV_EPI_CONV ? 3 : 2;     // weight rows a lane streams per chunk
     constexpr int COLS = 8 * NT;
     extern __shared__ __align__(16) unsigned char gv_smem[];

@@ -657,6 +657,36 @@ def sample_rows(logits: torch.Tensor, mode: Optional[torch.Tensor] = None,
     return out
 
 
+def sample_truncated(logits: torch.Tensor, inv_t: torch.Tensor, top_k: Optional[torch.Tensor],
+                     top_p: Optional[torch.Tensor], min_p: Optional[torch.Tensor], seeds: torch.Tensor,
+                     draws: torch.Tensor, out: Optional[torch.Tensor] = None, check: bool = False):
+    """One token per row from the temperature distribution cut by top-k (0: none; negative: leave
+    the row alone), min-p (0: none) and top-p (1: none), drawn by Gumbel-max over the survivors
+    with noise keyed by (seed, draw).  With ``check`` also returns the threshold on the scaled
+    logits and the number of survivors per row."""
+    _cuda(logits, inv_t, top_k, top_p, min_p, seeds, draws, out)
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("logits must be float32 with unit inner stride")
+    _f32(inv_t, "inverse temperatures")
+    _f32(top_p, "top_p")
+    _f32(min_p, "min_p")
+    _i32(top_k, "top_k")
+    for t in (seeds, draws):
+        if t.dtype != torch.int64:
+            raise KernelError("seeds and draw counters must be int64")
+    rows, vocab = logits.shape
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    tau = cnt = None
+    if check:
+        tau = torch.zeros((rows,), dtype=torch.float32, device=logits.device)
+        cnt = torch.zeros((rows,), dtype=torch.int32, device=logits.device)
+    lib = _lib("sampling")
+    _check(lib, lib.vapi_sample_truncated(_p(logits), rows, vocab, ctypes.c_longlong(logits.stride(0)), _p(inv_t), _p(top_k),
+                                          _p(top_p), _p(min_p), _p(seeds), _p(draws), _p(out), _p(tau), _p(cnt), _stream()))
+    return (out, tau, cnt) if check else out
+
+
 def apply_penalties(logits: torch.Tensor, rows: torch.Tensor, toks: torch.Tensor, counts: torch.Tensor,
                     rep: torch.Tensor, freq: torch.Tensor, pres: torch.Tensor) -> None:
     """Repetition / frequency / presence penalties on (row, token) pairs, in place."""

@@ -1,12 +1,14 @@
 """Token selection for the rows of a step.
 
-Rows that are greedy, or temperature-only, are decided on the device in one launch (argmax,
-Gumbel-max); penalties are applied on the device before it.  Rows that truncate the
-distribution (top-k, min-p, top-p) are sampled on the host from their row of logits, with
-the reference's pipeline (crates/vapi-engine/src/sampler.rs:162-180, 302-376): scale by
-1/T, keep what lies within 30 nats of the maximum, softmax, sort by probability then id,
-top-k, min-p, top-p, weighted choice.  Every request has a random generator and a draw
-counter of its own, so a seeded request does not depend on what else is in the batch.
+Every row is decided on the device: greedy rows by argmax, temperature rows by the Gumbel-max
+trick, and rows that cut the distribution (top-k, min-p, top-p) by the Gumbel-max trick over the
+survivors of the cuts, which are the reference's (crates/vapi-engine/src/sampler.rs:162-180,
+302-376: scale by 1/T, keep what lies within 30 nats of the maximum, top-k, min-p, top-p).
+Penalties are applied on the device before that.  Which kernel decides a row depends on the
+request's own parameters only, and the noise is keyed by the request's (seed, draw), so a seeded
+request does not depend on what else is in the batch.  ``host_sample`` restates the reference's
+host sampler (sort, cumulative sums, weighted choice with a generator per request); it is what
+the device cuts are checked against and serves logits that live on the host.
 """
 from __future__ import annotations
 
@@ -135,43 +137,81 @@ class Sampler:
         self._next = 0
         #: per row of the last :meth:`sample` call: None, or the :class:`TokenLogprobs` it asked for
         self.last_logprobs: List[Optional[TokenLogprobs]] = []
+        self._out: Optional[torch.Tensor] = None
 
     @staticmethod
     def device_only(p: SamplingParams) -> bool:
-        """Whether a row with these parameters is decided by the device launch alone (greedy, or
-        temperature without truncation) and needs nothing of the host but the result."""
-        return (p.is_greedy or p.device_drawable) and not p.has_penalties and p.logprobs is None
+        """Whether the host has nothing to do for a row with these parameters but read the
+        result: no penalties (their counts are uploaded each step) and no logprobs (the raw row
+        is read back)."""
+        return not p.has_penalties and p.logprobs is None
+
+    def _ring_entry(self, out: torch.Tensor):
+        """The next set of pinned staging buffers (results, per-row sampling data) with the event
+        that says the copies of their last use are done."""
+        if not self._ring:
+            cap = max(self.max_rows, out.numel())
+            for _ in range(3):
+                self._ring.append([torch.zeros(cap, dtype=torch.int32, pin_memory=True),
+                                   torch.zeros(cap * self._META_BYTES, dtype=torch.uint8, pin_memory=True),
+                                   torch.cuda.Event(), False])
+            self._meta_dev = torch.zeros(cap * self._META_BYTES, dtype=torch.uint8, device=out.device)
+        entry = self._ring[self._next]
+        self._next = (self._next + 1) % len(self._ring)
+        if entry[3]:
+            entry[2].synchronize()
+        return entry
+
+    #: bytes of sampling data per row: seed, draw (int64), 1/T, top_p, min_p (float32), mode, top_k (int32)
+    _META_BYTES = 36
 
     def launch(self, logits: torch.Tensor, rows: Sequence[Tuple[SamplingParams, SamplerState]],
                out: torch.Tensor) -> PendingSample:
-        """For rows that are all :meth:`device_only`: decide them on the device into ``out`` and
-        start the copy to the host without waiting for it."""
+        """Decide every row on the device into ``out`` (penalties, if any, must already have been
+        applied to ``logits``) and start the copy to the host without waiting for it."""
         R = len(rows)
-        assert logits.shape[0] >= R and all(self.device_only(p) for p, _ in rows)
-        dev = logits.device
+        assert logits.shape[0] >= R
+        entry = self._ring_entry(out)
+        host, meta_host, event = entry[0], entry[1], entry[2]
         self.h2d_bytes_last = 0
         if all(p.is_greedy for p, _ in rows):
             ops.sample_rows(logits[:R], out=out[:R])
         else:
-            m64 = torch.empty((2, R), dtype=torch.int64)
+            # every row's sampling data in one pinned buffer and one upload: [seeds | draws | 1/T |
+            # top_p | min_p | mode | top_k], each an array over the rows
+            mb = meta_host.numpy()
+            i64 = mb[:16 * R].view(np.int64).reshape(2, R)
+            f32 = mb[16 * R:28 * R].view(np.float32).reshape(3, R)
+            i32 = mb[28 * R:36 * R].view(np.int32).reshape(2, R)
+            plain = cut = False
             for r, (p, st) in enumerate(rows):
-                m64[0, r] = st.seed - (1 << 64) if st.seed >= (1 << 63) else st.seed
-                m64[1, r] = st.device_draws
-                if not p.is_greedy:
+                i64[0, r] = st.seed - (1 << 64) if st.seed >= (1 << 63) else st.seed
+                i64[1, r] = st.device_draws
+                f32[0, r], f32[1, r], f32[2, r] = p.inv_temperature, p.top_p, p.min_p
+                if p.is_greedy:
+                    i32[0, r], i32[1, r] = 1, -1
+                    plain = True
+                elif p.device_drawable:                   # nothing but temperature
+                    i32[0, r], i32[1, r] = 2, -1
                     st.device_draws += 1
-            mode = torch.tensor([1 if p.is_greedy else 2 for p, _ in rows], dtype=torch.int32).to(dev)
-            inv_t = torch.tensor([p.inv_temperature for p, _ in rows], dtype=torch.float32).to(dev)
-            m64d = m64.to(dev)
-            ops.sample_rows(logits[:R], mode, inv_t, m64d[0], m64d[1], out=out[:R])
-            self.h2d_bytes_last += R * 24
-        if not self._ring:
-            for _ in range(3):
-                self._ring.append([torch.zeros(max(self.max_rows, out.numel()), dtype=torch.int32, pin_memory=True),
-                                   torch.cuda.Event()])
-        host, event = self._ring[self._next]
-        self._next = (self._next + 1) % len(self._ring)
+                    plain = True
+                else:                                     # cut by top-k / min-p / top-p: the other kernel
+                    i32[0, r], i32[1, r] = 0, (p.top_k or 0)
+                    st.device_draws += 1
+                    cut = True
+            md = self._meta_dev
+            md[:36 * R].copy_(meta_host[:36 * R], non_blocking=True)
+            self.h2d_bytes_last += 36 * R
+            d64 = md[:16 * R].view(torch.int64).view(2, R)
+            d32f = md[16 * R:28 * R].view(torch.float32).view(3, R)
+            d32i = md[28 * R:36 * R].view(torch.int32).view(2, R)
+            if plain:
+                ops.sample_rows(logits[:R], d32i[0], d32f[0], d64[0], d64[1], out=out[:R])
+            if cut:
+                ops.sample_truncated(logits[:R], d32f[0], d32i[1], d32f[1], d32f[2], d64[0], d64[1], out=out[:R])
         host[:R].copy_(out[:R], non_blocking=True)
         event.record(torch.cuda.current_stream())
+        entry[3] = True
         self.d2h_bytes_last = 4 * R
         return PendingSample(R, host, event)
 
@@ -184,9 +224,11 @@ class Sampler:
         return pending.tokens
 
     def sample(self, logits: torch.Tensor, rows: Sequence[Tuple[SamplingParams, SamplerState]]) -> List[int]:
+        """Tokens for the rows of a step, waiting for them: raw rows are read back for requests
+        that report logprobs, penalties are applied on the device, and every row is then decided
+        as :meth:`launch` decides it (logits on the host: by the host restatement)."""
         R = len(rows)
         assert logits.shape[0] >= R
-        self.h2d_bytes_last = 0
         dev = logits.device
         # rows that report log-probabilities: their raw logits, before any penalty touches them
         raw: Dict[int, Tuple[float, List[Tuple[int, float]], np.ndarray]] = {}
@@ -195,49 +237,51 @@ class Sampler:
                 row = logits[r].to(torch.float32).cpu().numpy()
                 lse, top = row_logprobs(row, p.logprobs)
                 raw[r] = (lse, top, row)
-        toks = self._choose(logits, rows, dev)
+        extra_h2d = self._penalise(logits, rows, dev)
+        if logits.is_cuda:
+            if self._out is None or self._out.numel() < R or self._out.device != dev:
+                self._out = torch.zeros(max(self.max_rows, R), dtype=torch.int32, device=dev)
+            toks = self.finish(self.launch(logits, rows, self._out))
+            self.h2d_bytes_last += extra_h2d
+        else:
+            toks = self._choose_on_host(logits, rows)
         self.last_logprobs = [TokenLogprobs(toks[r], float(raw[r][2][toks[r]]) - raw[r][0], raw[r][1]) if r in raw else None
                               for r in range(R)]
         return toks
 
-    def _choose(self, logits: torch.Tensor, rows: Sequence[Tuple[SamplingParams, SamplerState]], dev) -> List[int]:
-        R = len(rows)
-        # penalties, on the device, for the rows that have any
+    def _penalise(self, logits: torch.Tensor, rows, dev) -> int:
+        """Penalties on the device for the rows that have any; returns the bytes uploaded."""
         pr, pt, pc = [], [], []
         for r, (p, st) in enumerate(rows):
             if p.has_penalties and st.counts:
                 for tok, cnt in st.counts.items():
                     pr.append(r); pt.append(tok); pc.append(float(cnt))
-        if pr:
-            rep = torch.tensor([p.repetition_penalty for p, _ in rows], dtype=torch.float32)
-            frq = torch.tensor([p.frequency_penalty for p, _ in rows], dtype=torch.float32)
-            prs = torch.tensor([p.presence_penalty for p, _ in rows], dtype=torch.float32)
-            ops.apply_penalties(logits, torch.tensor(pr, dtype=torch.int32).to(dev), torch.tensor(pt, dtype=torch.int32).to(dev),
-                                torch.tensor(pc, dtype=torch.float32).to(dev), rep.to(dev), frq.to(dev), prs.to(dev))
-            self.h2d_bytes_last += 12 * len(pr) + 12 * R
-        all_greedy = all(p.is_greedy for p, _ in rows)
-        if all_greedy:
-            out = ops.sample_rows(logits[:R])
-            toks = out.cpu().tolist()
-            self.d2h_bytes_last = 4 * R
-            return [int(t) for t in toks]
+        if not pr:
+            return 0
+        R = len(rows)
+        rep = torch.tensor([p.repetition_penalty for p, _ in rows], dtype=torch.float32)
+        frq = torch.tensor([p.frequency_penalty for p, _ in rows], dtype=torch.float32)
+        prs = torch.tensor([p.presence_penalty for p, _ in rows], dtype=torch.float32)
+        ops.apply_penalties(logits, torch.tensor(pr, dtype=torch.int32).to(dev), torch.tensor(pt, dtype=torch.int32).to(dev),
+                            torch.tensor(pc, dtype=torch.float32).to(dev), rep.to(dev), frq.to(dev), prs.to(dev))
+        return 12 * len(pr) + 12 * R
+
+    def _choose_on_host(self, logits: torch.Tensor, rows) -> List[int]:
+        """Logits that live on the host (tests of the host logic): greedy and plain temperature
+        through the kernels' stand-ins, cuts through the host restatement of the sampler."""
+        R = len(rows)
         mode = [1 if p.is_greedy else (2 if p.device_drawable else 0) for p, _ in rows]
         inv_t = [p.inv_temperature for p, _ in rows]
         seeds = [st.seed - (1 << 64) if st.seed >= (1 << 63) else st.seed for _, st in rows]
         draws = [st.device_draws for _, st in rows]
-        out = ops.sample_rows(logits[:R], torch.tensor(mode, dtype=torch.int32).to(dev),
-                              torch.tensor(inv_t, dtype=torch.float32).to(dev),
-                              torch.tensor(seeds, dtype=torch.int64).to(dev),
-                              torch.tensor(draws, dtype=torch.int64).to(dev),
-                              torch.zeros(R, dtype=torch.int32, device=dev))
-        self.h2d_bytes_last += R * 24
-        toks = [int(t) for t in out.cpu().tolist()]
+        out = ops.sample_rows(logits[:R], torch.tensor(mode, dtype=torch.int32), torch.tensor(inv_t, dtype=torch.float32),
+                              torch.tensor(seeds, dtype=torch.int64), torch.tensor(draws, dtype=torch.int64),
+                              torch.zeros(R, dtype=torch.int32))
+        toks = [int(t) for t in out.tolist()]
         self.d2h_bytes_last = 4 * R
         for r, (p, st) in enumerate(rows):
             if mode[r] == 2:
                 st.device_draws += 1
             elif mode[r] == 0:
-                row = logits[r].to(torch.float32).cpu().numpy()
-                self.d2h_bytes_last += row.nbytes
-                toks[r] = host_sample(row, p, st)
+                toks[r] = host_sample(logits[r].to(torch.float32).numpy(), p, st)
         return toks
