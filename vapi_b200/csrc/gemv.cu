@@ -40,6 +40,10 @@ constexpr int GV_WARPS = 8;
 #define GV_DEEP_STAGES_N 16
 #endif
 constexpr int GV_DEEP_STAGES = GV_DEEP_STAGES_N;
+#ifndef GV_NT2_STAGES_N
+#define GV_NT2_STAGES_N 4
+#endif
+constexpr int GV_NT2_STAGES = GV_NT2_STAGES_N;      // queue depth for 9..16 tokens: with 16 staged rows, two blocks fit on an SM only at 4
 constexpr int GV_STAGES_DEFAULT = GV_STAGES_N;   // depth of the per-lane copy queue (chunks of 32 k)
 // the conv epilogue streams three weight rows per lane: six stages keep two blocks on an SM
 // (DEEP: a product with a long K and no more tiles than SMs has one block per SM anyway and takes
@@ -47,7 +51,7 @@ constexpr int GV_STAGES_DEFAULT = GV_STAGES_N;   // depth of the per-lane copy q
 // (16 stages of 3 slots for up to 8 tokens, 12 of 4 slots for up to 16: 196 KB either way)
 template <int EPI, bool DEEP = false, int NT = 1> __host__ __device__ constexpr int gv_stages() {
     return DEEP ? (NT == 1 ? GV_DEEP_STAGES : (GV_DEEP_STAGES * 3) / 4)
-                : (EPI == 4 ? (GV_STAGES_DEFAULT < 6 ? GV_STAGES_DEFAULT : 6) : GV_STAGES_DEFAULT);
+                : (NT == 2 ? GV_NT2_STAGES : (EPI == 4 ? (GV_STAGES_DEFAULT < 6 ? GV_STAGES_DEFAULT : 6) : GV_STAGES_DEFAULT));
 }
 
 enum { GV_PRO_ACT = 0, GV_PRO_NORM = 1 };

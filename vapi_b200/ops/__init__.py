@@ -196,7 +196,7 @@ def swiglu(g: torch.Tensor) -> torch.Tensor:
     return out
 
 
-SKINNY_MAX_ROWS = 16
+SKINNY_MAX_ROWS = int(os.environ.get("VAPI_SKINNY_MAX_ROWS", "16"))
 #: set False to send every product to the library (for comparisons)
 use_skinny = os.environ.get("VAPI_SKINNY", "1") != "0"
 
