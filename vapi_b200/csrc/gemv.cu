@@ -379,7 +379,7 @@ static int launch_gv(const GvParams& p, int blocks, cudaStream_t stream) {
     const size_t smem = gv_smem_bytes<NT, PRO, EPI, DEEP>(p.K);
     auto kern = skinny_linear_kernel<NT, PRO, EPI, DEEP>;
     if (smem > 200 * 1024) return fail(-1, "skinny_linear: K=%d needs %zu bytes of shared memory", p.K, smem);
-    if (smem > 48 * 1024) {
+    if (smem + 16 * 1024 > 48 * 1024) {      // (static shared memory, up to about 10 KB, counts toward the default limit)
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(-101, "skinny_linear: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
