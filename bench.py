@@ -155,9 +155,9 @@ def run(args):
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     max_b = max(B, 64)
-    page = ModelRunner.default_page_size
+    page = args.page_size or ModelRunner.default_page_size
     pages = max_b * (-(-ctx_len // page)) + 8
-    runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", num_pages=pages,
+    runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", num_pages=pages, page_size=page,
                                      max_requests=max_b, max_batched_tokens=8192, max_context=ctx_len + 256,
                                      watermark=0.0, validate=False)
     wbytes, mm_params = model_numbers(runner)
@@ -410,6 +410,7 @@ def main():
                     help="run just the headline decode point, just the prefill, or (serve) continuous "
                          "batching of --requests requests with random prompt lengths through the engine loop")
     ap.add_argument("--sizes", default="1.2b", choices=["1.2b", "700m", "2.6b"], help="layer sizes of LFM2-<sizes>")
+    ap.add_argument("--page-size", type=int, default=0, help="tokens per cache page (0: the engine's default)")
     ap.add_argument("--requests", type=int, default=64)
     ap.add_argument("--max-tokens", type=int, default=128)
     args = ap.parse_args()
