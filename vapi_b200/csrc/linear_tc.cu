@@ -186,7 +186,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             // 64 features: gate in rows 0..63, up in rows 64..127; two features per lane
             const long long f0 = (long long)n0 + 2 * lane;
             const float g0 = f[2 * lane], g1 = f[2 * lane + 1], u0 = f[64 + 2 * lane], u1 = f[64 + 2 * lane + 1];
-            const float s0 = g0 / (1.f + expf(-g0)) * u0, s1 = g1 / (1.f + expf(-g1)) * u1;
+            // (fast exponential and division: their error is far below the bfloat16 rounding of the result)
+            const float s0 = __fdividef(g0, 1.f + __expf(-g0)) * u0, s1 = __fdividef(g1, 1.f + __expf(-g1)) * u1;
             __nv_bfloat16* o = p.out_bf16 + (size_t)m * p.out_stride + f0;
             if (f0 + 1 < p.ff && (p.out_stride & 1) == 0) *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(s0, s1);
             else {
@@ -271,6 +272,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             }
             if (p.splits == 1) {
                 epi_bar();
+#pragma unroll 4
                 for (int m = g0 + warp - 2; m < min(p.M, g0 + GROUP); m += 4) store_token(m - g0, m);
                 epi_bar();
             }
