@@ -279,10 +279,12 @@ def skinny_linear(weight: torch.Tensor, *, act: Optional[torch.Tensor] = None,
 
 
 #: Steps of up to this many rows go to the tcgen05 product with its fused epilogues.  The kernel
-#: itself takes up to 256 rows, but beyond 128 it has too few tiles per launch to keep up with the
-#: library's product (measured: 2-7x slower at 256 rows), so larger steps take the unfused path.
-TC_MAX_ROWS = 128
-#: set False to keep products of 17..128 rows on the library
+#: itself takes up to 256 rows, but it has one tile per block and pays its fixed costs (cluster
+#: reduction, epilogue) per launch: measured in the captured decode step of LFM2-1.2B sizes it
+#: beats the library's product plus separate norm / SwiGLU / add kernels at 32 rows (1.26 vs 1.33
+#: ms), loses narrowly at 64 (1.71 vs 1.68 ms) and clearly beyond (2-7x slower at 256 rows).
+TC_MAX_ROWS = int(os.environ.get("VAPI_TC_MAX_ROWS", "32"))
+#: set False to keep products of 17..TC_MAX_ROWS rows on the library
 use_tc = os.environ.get("VAPI_TC", "1") != "0"
 
 
