@@ -105,11 +105,11 @@ def mixed(tr: Trace, requests: Dict[str, Sequence[int]], seed: int, max_live: in
 
 
 def run_trace(model_dir: str, dtype: str, tr: Trace, out_dir: str, max_tokens: int = None,
-              extra_env: Dict[str, str] = None, timeout: int = 900) -> Dict[int, np.ndarray]:
+              extra_env: Dict[str, str] = None, timeout: int = 900, extra_args: Sequence[str] = ()) -> Dict[int, np.ndarray]:
     """Run bin/trace_run as a user would; return step -> [wanted, vocab] float32."""
     os.makedirs(out_dir, exist_ok=True)
     cmd = [sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", out_dir,
-           "--max-tokens", str(max_tokens if max_tokens is not None else tr.peak_tokens)]
+           "--max-tokens", str(max_tokens if max_tokens is not None else tr.peak_tokens)] + list(extra_args)
     env = dict(os.environ)
     env.update(extra_env or {})
     inp = "".join(json.dumps(s) + "\n" for s in tr.steps)

@@ -220,6 +220,12 @@ def test_tensor_core_attention_window(ops, window):
     _attention_case(ops, nh=4, nkv=2, d=64, page=64, lens=[(1, 500), (1, 64)], window=window, splits=3, **TC)
 
 
+def test_tensor_core_attention_far_key_in_a_long_context(ops):
+    """Forty thousand keys: the planted key near the start must still be found by a decode token
+    (split keys, offsets beyond 2^15 tokens and a cache of tens of megabytes)."""
+    _attention_case(ops, nh=8, nkv=2, d=64, page=64, lens=[(1, 40000), (1, 33000), (3, 20000)], planted=True, **TC)
+
+
 def test_tensor_core_attention_ignores_garbage_beyond_the_sequence(ops):
     """Cache memory past a sequence's last key (and pages nobody wrote) may hold anything,
     NaN included; it must not reach the result."""

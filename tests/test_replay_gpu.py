@@ -102,29 +102,33 @@ def test_out_of_pages_is_an_error_not_a_wrong_result(tiny_dirs, tmp_path):
         ru.run_trace(tiny_dirs["A"], "float32", tr, str(tmp_path / "out"), max_tokens=128)
 
 
-def test_layers_of_serving_size_in_bfloat16(tmp_path):
+@pytest.mark.parametrize("sizes", ["1.2b", "700m"])
+def test_layers_of_serving_size_in_bfloat16(sizes, tmp_path):
     """Three layers with the sizes of the 1.2B model (hidden 2048, 32 heads over 8 kv heads of 64,
-    feed-forward 8192; conv, attention, conv) and bfloat16 weights: the shapes the serving kernels
-    are tuned for, whole, in portions, token by token and mixed, against the plain model."""
+    feed-forward 8192) and of the 700M model (hidden 1536, 24 heads, feed-forward 6912: three query
+    heads per kv head, widths that are no power of two), conv - attention - conv, bfloat16 weights:
+    the shapes the serving kernels are tuned for, whole, in portions, token by token and mixed,
+    against the plain model."""
     from vapi_b200.weights import write_random_model
+    hidden, heads, inter = {"1.2b": (2048, 32, 12288), "700m": (1536, 24, 10240)}[sizes]
     cfg = {
-        "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2", "vocab_size": 4096, "hidden_size": 2048,
-        "intermediate_size": 12288, "block_auto_adjust_ff_dim": True, "block_ffn_dim_multiplier": 1.0,
+        "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2", "vocab_size": 4096, "hidden_size": hidden,
+        "intermediate_size": inter, "block_auto_adjust_ff_dim": True, "block_ffn_dim_multiplier": 1.0,
         "block_multiple_of": 256, "num_hidden_layers": 3, "layer_types": ["conv", "full_attention", "conv"],
-        "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "conv_L_cache": 3, "conv_bias": False,
+        "num_attention_heads": heads, "num_key_value_heads": 8, "head_dim": 64, "conv_L_cache": 3, "conv_bias": False,
         "rope_theta": 1000000.0, "norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 1024,
     }
     d = write_random_model(str(tmp_path / "m"), cfg, 3, std=0.02, norm_init="perturbed", dtype=torch.bfloat16)
     plain = plain_lfm2.PlainLfm2(d)
-    reqs = _requests(cfg, 8, [300, 40, 150])
+    reqs = _requests(cfg, 8, [300, 40, 150, 20, 9, 25, 33, 12, 70, 3, 16, 48])
     tr = ru.Trace()
     ru.whole(tr, "whole-r0", reqs["r0"])
     ru.tail_decode(tr, "tail-r2", reqs["r2"], tail=6)
     ru.portions(tr, "cut-r0", reqs["r0"], sizes=[100, 2, 64, 17])
     mix = {f"mix-{k}": v for k, v in reqs.items()}
-    ru.mixed(tr, mix, seed=4, decode_tail=5)
+    ru.mixed(tr, mix, seed=4, max_live=12, decode_tail=8)      # up to 12 live: decode steps of 9..16 rows too
     ref_tokens = {"whole-r0": reqs["r0"], "tail-r2": reqs["r2"], "cut-r0": reqs["r0"], **mix}
     ref = {k: plain.logits(v) for k, v in ref_tokens.items()}
-    got = ru.run_trace(d, "bfloat16", tr, str(tmp_path / "out"))
+    got = ru.run_trace(d, "bfloat16", tr, str(tmp_path / "out"), extra_args=["--max-requests", "16"])
     ok, msg = ru.compare(tr, got, ref, "bfloat16")
     assert ok, msg
