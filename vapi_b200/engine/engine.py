@@ -55,8 +55,8 @@ class EngineStats:
 
 
 class Engine:
-    """``run_ahead`` (on by default on a CUDA device): while every live request is decided on the
-    device alone (greedy, or temperature without truncation or penalties), a step is enqueued
+    """``run_ahead`` (on by default on a CUDA device): while the host has nothing to do for any
+    live request but read its token (no penalties, no logprobs), a step is enqueued
     before the tokens of the step before it have been read: its input tokens are fetched on the
     device from that step's sampled output, and the host reads results one step late, while
     the next step already runs.  ``step()`` then reports the tokens of the step before.  The
