@@ -108,19 +108,18 @@ __device__ __forceinline__ void emit(const T* __restrict__ h3, const float* __re
     Chan<T, V>::store(out + row * (size_t)hidden + c, y);
 }
 
+// One block row (index bx) of the per-token form.  heads_only: bx is a sequence, and the work is
+// its first L-1 tokens and its state (the other tokens belong to the tiled form); else bx is a token.
 template <typename T, int V>
-__global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restrict__ in_bias,
-                                 const float* __restrict__ taps,  // [L, H], k = 0 oldest
-                                 const float* __restrict__ conv_bias, T* __restrict__ state,
-                                 long long slot_stride, const int* __restrict__ state_slots,
-                                 const int* __restrict__ tok_seq, const int* __restrict__ cu_q,
-                                 const int* __restrict__ positions, T* __restrict__ out, int n,
-                                 int hidden, int L, int num_slots, int heads_only,
-                                 int* __restrict__ status) {
-    // heads_only: one block row per sequence, for its first L-1 tokens and its state (the
-    // other tokens are shortconv_tile_kernel's); else one block row per token
+__device__ __forceinline__ void shortconv_token_body(
+        const T* __restrict__ h3, const float* __restrict__ in_bias,
+        const float* __restrict__ taps,  // [L, H], k = 0 oldest
+        const float* __restrict__ conv_bias, T* __restrict__ state, long long slot_stride,
+        const int* __restrict__ state_slots, const int* __restrict__ tok_seq, const int* __restrict__ cu_q,
+        const int* __restrict__ positions, T* __restrict__ out, int n, int hidden, int L, int num_slots,
+        int heads_only, int* __restrict__ status, int bx) {
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
-    const int r = heads_only ? cu_q[blockIdx.x] : blockIdx.x;
+    const int r = heads_only ? cu_q[bx] : bx;
     pdl_trigger();
     if (c >= hidden || r >= n) {
         pdl_wait();
@@ -129,7 +128,7 @@ __global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restri
     // Everything read up to pdl_wait() was written before this step's first kernel began
     // (index data copied from the host, weights, the state the previous step left), so it can
     // be fetched while the kernel before this one is still finishing.
-    const int s = heads_only ? (int)blockIdx.x : tok_seq[r];
+    const int s = heads_only ? bx : tok_seq[r];
     const int r0 = cu_q[s], q = cu_q[s + 1] - r0;
     const int i = r - r0;
     if (q <= 0) {       // (a sequence without tokens in this step)
@@ -223,18 +222,30 @@ __global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restri
     }
 }
 
+template <typename T, int V>
+__global__ void shortconv_kernel(const T* __restrict__ h3, const float* __restrict__ in_bias,
+                                 const float* __restrict__ taps, const float* __restrict__ conv_bias,
+                                 T* __restrict__ state, long long slot_stride,
+                                 const int* __restrict__ state_slots, const int* __restrict__ tok_seq,
+                                 const int* __restrict__ cu_q, const int* __restrict__ positions,
+                                 T* __restrict__ out, int n, int hidden, int L, int num_slots,
+                                 int* __restrict__ status) {
+    shortconv_token_body<T, V>(h3, in_bias, taps, conv_bias, state, slot_stride, state_slots, tok_seq, cu_q, positions,
+                               out, n, hidden, L, num_slots, 0, status, (int)blockIdx.x);
+}
+
 // Prompt portions: the tokens at index >= L-1 of their portion need nothing but rows of this
 // step.  One thread takes TT consecutive tokens of V channels, so the L-1 predecessor rows are
 // computed once per tile instead of once per token and all of a thread's loads are in flight
 // together.  Tokens nearer to the start of their portion (and the state) are left to
 // shortconv_kernel in its heads_only form.
 template <typename T, int V, int LT, int TT>
-__global__ void shortconv_tile_kernel(const T* __restrict__ h3, const float* __restrict__ in_bias,
-                                      const float* __restrict__ taps, const float* __restrict__ conv_bias,
-                                      const int* __restrict__ tok_seq, const int* __restrict__ cu_q,
-                                      T* __restrict__ out, int n, int hidden) {
+__device__ __forceinline__ void shortconv_tile_body(const T* __restrict__ h3, const float* __restrict__ in_bias,
+                                                    const float* __restrict__ taps, const float* __restrict__ conv_bias,
+                                                    const int* __restrict__ tok_seq, const int* __restrict__ cu_q,
+                                                    T* __restrict__ out, int n, int hidden, int tile) {
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
-    const int r0 = blockIdx.x * TT;
+    const int r0 = tile * TT;
     pdl_trigger();
     if (c >= hidden) {
         pdl_wait();
@@ -279,20 +290,41 @@ __global__ void shortconv_tile_kernel(const T* __restrict__ h3, const float* __r
     }
 }
 
+// A prompt-sized step in one launch: the first num_seqs block rows do the heads of the sequences
+// (their first L-1 tokens and the state), the others one tile of TT tokens each, side by side.
+template <typename T, int V, int LT, int TT>
+__global__ void shortconv_prompt_kernel(const T* __restrict__ h3, const float* __restrict__ in_bias,
+                                        const float* __restrict__ taps, const float* __restrict__ conv_bias,
+                                        T* __restrict__ state, long long slot_stride,
+                                        const int* __restrict__ state_slots, const int* __restrict__ tok_seq,
+                                        const int* __restrict__ cu_q, const int* __restrict__ positions,
+                                        T* __restrict__ out, int n, int num_seqs, int hidden, int num_slots,
+                                        int* __restrict__ status) {
+    if ((int)blockIdx.x < num_seqs)
+        shortconv_token_body<T, V>(h3, in_bias, taps, conv_bias, state, slot_stride, state_slots, tok_seq, cu_q,
+                                   positions, out, n, hidden, LT, num_slots, 1, status, (int)blockIdx.x);
+    else
+        shortconv_tile_body<T, V, LT, TT>(h3, in_bias, taps, conv_bias, tok_seq, cu_q, out, n, hidden,
+                                          (int)blockIdx.x - num_seqs);
+}
+
 template <typename T, int V>
-static cudaError_t launch_tiles(int L, dim3 grid, int threads, cudaStream_t stream, const void* h3,
-                                const float* in_bias, const float* taps, const float* conv_bias,
-                                const int* tok_seq, const int* cu_q, void* out, int n, int hidden) {
-#define SC_TILE(LT)                                                                                    \
-    return launch(shortconv_tile_kernel<T, V, LT, 4>, grid, threads, 0, stream, (const T*)h3, in_bias, taps, \
-                  conv_bias, tok_seq, cu_q, (T*)out, n, hidden)
+static cudaError_t launch_prompt(int L, dim3 grid, int threads, cudaStream_t stream, const void* h3,
+                                 const float* in_bias, const float* taps, const float* conv_bias, void* state,
+                                 long long slot_stride, const int* state_slots, const int* tok_seq,
+                                 const int* cu_q, const int* positions, void* out, int n, int num_seqs,
+                                 int hidden, int num_slots, int* status) {
+#define SC_PROMPT(LT)                                                                                     \
+    return launch(shortconv_prompt_kernel<T, V, LT, 4>, grid, threads, 0, stream, (const T*)h3, in_bias, taps, \
+                  conv_bias, (T*)state, slot_stride, state_slots, tok_seq, cu_q, positions, (T*)out, n, num_seqs, \
+                  hidden, num_slots, status)
     switch (L) {
-        case 2: SC_TILE(2);
-        case 3: SC_TILE(3);
-        case 4: SC_TILE(4);
-        case 5: SC_TILE(5);
+        case 2: SC_PROMPT(2);
+        case 3: SC_PROMPT(3);
+        case 4: SC_PROMPT(4);
+        case 5: SC_PROMPT(5);
     }
-#undef SC_TILE
+#undef SC_PROMPT
     return cudaErrorInvalidValue;
 }
 
@@ -313,27 +345,31 @@ VAPI_EXPORT int vapi_shortconv(const void* h3, int dtype, const float* in_bias, 
     const int cblocks = (hidden / per + threads - 1) / threads;
     if (cblocks > 65535) return fail(-1, "shortconv: hidden=%d is too wide for the grid", hidden);
     // prompt-sized steps: tiles of tokens for everything past the first L-1 tokens of a portion,
-    // and the per-token kernel only for those first tokens and the state
+    // the per-token form only for those first tokens and the state, in one launch
     const int tile_v = dtype == VAPI_BF16 ? 8 : 4;
-    const bool tiled = n >= 256 && num_seqs > 0 && num_seqs * 8 <= n && L >= 2 && L <= 5 && hidden % tile_v == 0;
-    const int heads_only = tiled ? 1 : 0;
-    dim3 grid(tiled ? num_seqs : n, cblocks);
+    const bool tiled = n >= 256 && num_seqs > 0 && num_seqs * 8 <= n && L >= 2 && L <= 5 && hidden % tile_v == 0 &&
+                       slot_stride % tile_v == 0 && (dtype == VAPI_BF16 || dtype == VAPI_F32);
     cudaError_t e;
+    if (tiled) {
+        const int tcb = (hidden / tile_v + threads - 1) / threads;
+        dim3 grid(num_seqs + (n + 3) / 4, tcb);
+        if (dtype == VAPI_F32)
+            e = launch_prompt<float, 4>(L, grid, threads, stream, h3, in_bias, taps, conv_bias, state, slot_stride,
+                                        state_slots, tok_seq, cu_q, positions, out, n, num_seqs, hidden, num_slots, status);
+        else
+            e = launch_prompt<__nv_bfloat16, 8>(L, grid, threads, stream, h3, in_bias, taps, conv_bias, state, slot_stride,
+                                                state_slots, tok_seq, cu_q, positions, out, n, num_seqs, hidden, num_slots, status);
+        return check_launch("shortconv", e);
+    }
+    dim3 grid(n, cblocks);
 #define SC_LAUNCH(T, V)                                                                            \
     e = launch(shortconv_kernel<T, V>, grid, threads, 0, stream, (const T*)h3, in_bias, taps, conv_bias, \
                (T*)state, slot_stride, state_slots, tok_seq, cu_q, positions, (T*)out, n, hidden, L,      \
-               num_slots, heads_only, status)
+               num_slots, status)
     if (dtype == VAPI_F32) { if (vec) SC_LAUNCH(float, 4); else SC_LAUNCH(float, 1); }
     else if (dtype == VAPI_BF16) { if (vec) SC_LAUNCH(__nv_bfloat16, 4); else SC_LAUNCH(__nv_bfloat16, 1); }
     else return fail(-2, "shortconv: unsupported dtype %d", dtype);
 #undef SC_LAUNCH
-    if (e == cudaSuccess && tiled) {
-        dim3 tgrid((n + 3) / 4, (hidden / tile_v + threads - 1) / threads);
-        if (dtype == VAPI_F32)
-            e = launch_tiles<float, 4>(L, tgrid, threads, stream, h3, in_bias, taps, conv_bias, tok_seq, cu_q, out, n, hidden);
-        else
-            e = launch_tiles<__nv_bfloat16, 8>(L, tgrid, threads, stream, h3, in_bias, taps, conv_bias, tok_seq, cu_q, out, n, hidden);
-    }
     return check_launch("shortconv", e);
 }
 

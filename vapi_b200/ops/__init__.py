@@ -601,14 +601,11 @@ def shortconv(h3: torch.Tensor, in_bias: Optional[torch.Tensor], taps: torch.Ten
         slot_stride, num_slots = state_layer.stride(0), state_layer.shape[0]
     out = torch.empty((n, hidden), dtype=h3.dtype, device=h3.device)
     num_seqs = cu_q.numel() - 1
-    # (the library's own rule for splitting a prompt-sized step into per-sequence heads and token tiles)
-    tiled = (n >= 256 and 0 < num_seqs * 8 <= n and 2 <= L <= 5
-             and hidden % (8 if h3.dtype == torch.bfloat16 else 4) == 0)
     lib = _lib("shortconv")
     _check(lib, lib.vapi_shortconv(
         _p(h3), _dt(h3), _p(in_bias), _p(taps), _p(conv_bias), _p(state_layer if L > 1 else None),
         ctypes.c_longlong(slot_stride), _p(state_slots), _p(tok_seq), _p(cu_q), _p(positions), _p(out),
-        n, num_seqs, hidden, L, num_slots, _p(status), _stream()), launches=2 if tiled else 1)
+        n, num_seqs, hidden, L, num_slots, _p(status), _stream()))
     return out
 
 
