@@ -22,6 +22,10 @@
 using namespace vapi;
 
 constexpr int CONV_LMAX = 8;
+#ifndef SC_TT_N
+#define SC_TT_N 4
+#endif
+constexpr int SC_TT = SC_TT_N;          // tokens of a tile in the prompt-sized form
 
 // V consecutive channels of one row as floats (V = 1, or 4 with one 16-byte / 8-byte access)
 template <typename T, int V> struct Chan;
@@ -315,7 +319,7 @@ static cudaError_t launch_prompt(int L, dim3 grid, int threads, cudaStream_t str
                                  const int* cu_q, const int* positions, void* out, int n, int num_seqs,
                                  int hidden, int num_slots, int* status) {
 #define SC_PROMPT(LT)                                                                                     \
-    return launch(shortconv_prompt_kernel<T, V, LT, 4>, grid, threads, 0, stream, (const T*)h3, in_bias, taps, \
+    return launch(shortconv_prompt_kernel<T, V, LT, SC_TT>, grid, threads, 0, stream, (const T*)h3, in_bias, taps, \
                   conv_bias, (T*)state, slot_stride, state_slots, tok_seq, cu_q, positions, (T*)out, n, num_seqs, \
                   hidden, num_slots, status)
     switch (L) {
@@ -352,7 +356,7 @@ VAPI_EXPORT int vapi_shortconv(const void* h3, int dtype, const float* in_bias, 
     cudaError_t e;
     if (tiled) {
         const int tcb = (hidden / tile_v + threads - 1) / threads;
-        dim3 grid(num_seqs + (n + 3) / 4, tcb);
+        dim3 grid(num_seqs + (n + SC_TT - 1) / SC_TT, tcb);
         if (dtype == VAPI_F32)
             e = launch_prompt<float, 4>(L, grid, threads, stream, h3, in_bias, taps, conv_bias, state, slot_stride,
                                         state_slots, tok_seq, cu_q, positions, out, n, num_seqs, hidden, num_slots, status);
