@@ -59,9 +59,11 @@ class Engine:
     live request but read its token (no penalties, no logprobs), a step is enqueued
     before the tokens of the step before it have been read: its input tokens are fetched on the
     device from that step's sampled output, and the host reads results one step late, while
-    the next step already runs.  ``step()`` then reports the tokens of the step before.  The
-    tokens are the same as without it; a request that ends on EOS or a stop id has taken part
-    in one more step, whose result for it is dropped."""
+    the next step already runs.  ``step()`` then reports the tokens of the step before.  A
+    request that ends on EOS or a stop id has taken part in one more step, whose result for it is
+    dropped.  Every token is computed from the same inputs as without running ahead; only the
+    batch of a step can be one row larger, which in bfloat16 may take another kernel and so
+    another rounding (in float32 the tokens are identical)."""
 
     def __init__(self, runner: ModelRunner, cfg: Optional[SchedulerConfig] = None, *,
                  max_step_failures: int = 3, use_graphs: bool = True, run_ahead: Optional[bool] = None):
