@@ -194,6 +194,42 @@ def test_several_completions_per_prompt_and_logprobs(tiny_dirs):
         text.append(tok)
 
 
+def test_randomized_serving_gives_the_same_tokens_however_it_is_scheduled(tiny_dirs):
+    """120 requests with random lengths, limits, stop ids and samplers (greedy, temperature, top-p,
+    top-k, min-p) through the float32 engine: running ahead or not, and a pool that holds
+    everything or one so small that requests queue and are preempted, must not change one token."""
+    import random
+    from vapi_b200 import LLM, SamplingParams
+    rng = random.Random(2)
+    g = torch.Generator().manual_seed(3)
+    prompts, params = [], []
+    for _ in range(120):
+        n = rng.choice([1, 2, 3, 5, 17, 40, 63, 64, 65, 100, 129, 200])
+        prompts.append(torch.randint(3, TINY_D["vocab_size"], (n,), generator=g).tolist())
+        kw = dict(max_tokens=rng.randint(1, 30), seed=rng.randint(0, 10 ** 6), ignore_eos=rng.random() < 0.5,
+                  stop_token_ids=tuple(rng.sample(range(3, 1003), rng.choice([0, 0, 5, 50]))))
+        kind = rng.choice(["greedy", "temp", "topp", "topk", "minp"])
+        kw.update({"greedy": dict(temperature=0.0), "temp": dict(temperature=rng.uniform(0.3, 1.5)),
+                   "topp": dict(temperature=1.0, top_p=rng.uniform(0.1, 0.99)),
+                   "topk": dict(temperature=1.2, top_k=rng.randint(1, 100)),
+                   "minp": dict(temperature=1.0, min_p=rng.uniform(0.01, 0.3), top_p=0.95)}[kind])
+        params.append(SamplingParams(**kw))
+    res, stats = {}, {}
+    for ahead, blocks in ((False, 200), (True, 200), (True, 14), (False, 14)):
+        llm = LLM(tiny_dirs["D"], dtype="f32", num_blocks=blocks, max_concurrent_seqs=16, max_batched_tokens=512,
+                  max_context=320, prefill_chunk_tokens=96, run_ahead=ahead)
+        res[(ahead, blocks)] = [(c.tokens, c.finish_reason) for c in llm.generate(prompts, params)]
+        llm.runner.check_status()
+        llm.runner.cache.check_invariants()
+        stats[(ahead, blocks)] = llm.engine.stats
+    assert stats[(True, 200)].ahead_steps > 50 and stats[(True, 14)].ahead_steps > 0
+    assert stats[(False, 14)].steps > 1.5 * stats[(False, 200)].steps, "the small pool must make requests wait"
+    assert any(r == "stop" for _, r in res[(False, 200)]) and any(r == "length" for _, r in res[(False, 200)])
+    for key, got in res.items():
+        bad = [i for i, (a, b) in enumerate(zip(res[(False, 200)], got)) if a != b]
+        assert not bad, (key, bad[:5])
+
+
 def test_penalties_change_what_is_generated(tiny_dirs):
     from vapi_b200 import LLM, SamplingParams
     p = _prompts(TINY_A, 6, [12])
