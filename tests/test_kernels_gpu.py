@@ -293,6 +293,69 @@ def test_tcgen05_attention_ignores_garbage_beyond_the_sequence(ops):
     torch.testing.assert_close(got.cpu().float(), want.float(), atol=3e-2, rtol=3e-2)
 
 
+DEC = dict(dtype=torch.bfloat16, impl="decode")
+
+
+@pytest.mark.parametrize("nh,nkv", [(8, 2), (6, 2), (16, 1), (5, 5), (32, 8)])
+@pytest.mark.parametrize("page", [64, 128, 256])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_decode_attention_mixed_lengths(ops, nh, nkv, page, splits):
+    # single tokens over contexts that end at, before and after a tile's and a page's edge, the very
+    # first token, and short portions (as many tokens as 16 rows allow)
+    tokens = 16 // (nh // nkv)
+    lens = [(1, 1), (1, 63), (1, 64), (1, 65), (1, 128), (1, 129), (1, 700), (1, 257), (1, 1000)]
+    if tokens >= 2:
+        lens += [(2, 129), (tokens, 400), (tokens, tokens), (2, 64)]
+    _attention_case(ops, nh=nh, nkv=nkv, d=64, page=page, lens=lens, splits=splits, **DEC)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 32])
+def test_decode_attention_far_key_and_many_slices(ops, splits):
+    _attention_case(ops, nh=8, nkv=2, d=64, page=64, lens=[(1, 2500), (1, 640), (1, 65), (2, 3000)], planted=True,
+                    splits=splits, **DEC)
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 100, 1000])
+def test_decode_attention_window(ops, window):
+    _attention_case(ops, nh=8, nkv=2, d=64, page=64, lens=[(1, 90), (1, 300), (1, 64), (3, 500), (1, 129), (1, 1)],
+                    window=window, **DEC)
+    _attention_case(ops, nh=8, nkv=2, d=64, page=128, lens=[(1, 900), (2, 300)], window=window, splits=4, **DEC)
+
+
+def test_decode_attention_ignores_garbage_beyond_the_sequence(ops):
+    torch.manual_seed(13)
+    nh, nkv, d, page = 8, 2, 64, 128
+    cache = torch.full((6, 2, nkv, page, d), float("nan")).to(torch.bfloat16)
+    table = torch.tensor([[4, 1, 0, 0], [2, 0, 0, 0], [5, 0, 0, 0]], dtype=torch.int32)
+    cache[4] = torch.randn(2, nkv, page, d)
+    cache[1, :, :, :6] = torch.randn(2, nkv, 6, d).to(torch.bfloat16)
+    cache[2, :, :, :10] = torch.randn(2, nkv, 10, d).to(torch.bfloat16)
+    cache[5, :, :, :70] = torch.randn(2, nkv, 70, d).to(torch.bfloat16)
+    q = torch.randn(4, nh * d).to(torch.bfloat16)
+    cu, kl = torch.tensor([0, 1, 2, 4], dtype=torch.int32), torch.tensor([134, 10, 70], dtype=torch.int32)
+    want = plain_ops.paged_attention(q, nh * d, cache, table, cu, kl, 4, 3, 2, 134, nh, nkv, d, 0.125)
+    for splits in (1, 2):
+        got = ops.paged_attention(dev(q), nh * d, dev(cache), dev(table), dev(cu), dev(kl), 4, 3, 2, 134, nh, nkv, d,
+                                  0.125, 0, splits, None, "decode")
+        assert torch.isfinite(got.float()).all()
+        torch.testing.assert_close(got.cpu().float(), want.float(), atol=3e-2, rtol=3e-2)
+
+
+def test_decode_attention_is_what_a_decode_step_gets_and_refuses_what_it_cannot_do(ops):
+    before = ops.launch_count
+    _attention_case(ops, dtype=torch.bfloat16, nh=32, nkv=8, d=64, page=64, lens=[(1, 500), (1, 64), (4, 95)], splits=1)
+    assert ops.launch_count - before == 1
+    assert ops.decode_attention_applies(torch.bfloat16, 64, 64, 16)
+    assert not ops.decode_attention_applies(torch.bfloat16, 128, 64, 4)
+    assert not ops.decode_attention_applies(torch.float32, 64, 64, 4)
+    with pytest.raises(ops.KernelError, match="decode kernel needs"):
+        _attention_case(ops, nh=4, nkv=2, d=128, page=64, lens=[(1, 70)], **DEC)
+    with pytest.raises(ops.KernelError, match="decode kernel needs"):
+        _attention_case(ops, nh=8, nkv=2, d=64, page=64, lens=[(5, 70)], **DEC)
+    with pytest.raises(ops.KernelError, match="decode kernel needs"):
+        _attention_case(ops, nh=8, nkv=2, d=64, page=32, lens=[(1, 70)], **DEC)
+
+
 def test_attention_picks_its_kernels_for_a_mixed_step(ops):
     # "auto": prompt portions on tcgen05, the decode tokens and short portions beside them on the flash kernel
     before = ops.launch_count

@@ -21,6 +21,7 @@
 #include "common.cuh"
 #include "attention_mma.cuh"
 #include "attention_tc.cuh"
+#include "attention_decode.cuh"
 
 using namespace vapi;
 
@@ -281,10 +282,12 @@ static int launch_attention(const void* q, long long q_row_stride, const void* c
 // cache: one layer, [num_pages, 2, nkv, page_size, d].  out: [n, nh*d].
 // splits > 1 needs part_o [n*nh*splits*d] and part_ml [n*nh*splits*2] floats of scratch.
 // impl: 0 = the fastest kernel that applies: for bfloat16, head_dim 64 or 128 and a page size
-// that is a multiple of 64 the mma.sync flash kernel, and for steps with prompt portions (head_dim
-// 64, no split) the tcgen05 kernel for every sequence of at least FT_MIN_Q tokens beside the flash
+// that is a multiple of 64 the mma.sync flash kernel; at head_dim 64 the TMA-fed decode kernel for
+// steps whose sequences bring at most 16 rows per kv head, and for steps with prompt portions (no
+// split) the tcgen05 kernel for every sequence of at least FT_MIN_Q tokens beside the flash
 // kernel for the shorter ones; else the general kernel.  1 = the general kernel; 2 = the mma.sync
-// flash kernel or an error; 3 = the tcgen05 kernel for every sequence, or an error.
+// flash kernel or an error; 3 = the tcgen05 kernel for every sequence, or an error; 4 = the
+// decode kernel, or an error.
 VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, const void* cache,
                                      int dtype, const int* block_table, int table_stride,
                                      const int* cu_q, const int* seqlens_k, void* out,
@@ -334,8 +337,16 @@ VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, cons
     rc = launch_attention<T, DM>(q, q_row_stride, cache, block_table, table_stride, cu_q,       \
                                  seqlens_k, out, part_o, part_ml, num_seqs, max_q, nh, nkv, d,  \
                                  page_size, num_pages, scale, window, splits, status, stream)
-    if (fast) {
-        const bool few_rows = (long long)max_q * (nh / nkv) <= 16;
+    const bool few_rows = (long long)max_q * (nh / nkv) <= FD_MAX_ROWS;
+    const bool dec_ok = fast_ok && d == FD_HD && few_rows && ((uintptr_t)out & 15) == 0;
+    if (impl == 4 && !dec_ok)
+        return fail(-3, "paged_attention: the decode kernel needs bfloat16, head_dim 64, a page size that is a multiple of 64 "
+                        "and at most 16 rows per sequence and kv head (got dtype %d, head_dim %d, page size %d, %lld rows)",
+                    dtype, d, page_size, (long long)max_q * (nh / nkv));
+    if (impl == 4 || (impl == 0 && dec_ok)) {
+        rc = launch_flash_decode(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, part_o, part_ml,
+                                 num_seqs, nh, nkv, page_size, num_pages, scale, window, splits, status, stream);
+    } else if (fast) {
         if (d == 64) { if (few_rows) VAPI_FLASH(64, 1, 3); else VAPI_FLASH(64, 4, 3); }
         else         { if (few_rows) VAPI_FLASH(128, 1, 3); else VAPI_FLASH(128, 4, 3); }
     } else if (dtype == VAPI_F32) {

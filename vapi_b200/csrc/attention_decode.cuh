@@ -1,0 +1,353 @@
+// Paged GQA attention for decode steps: bfloat16, head_dim 64, pages whose size is a multiple of
+// 64, sequences that bring at most 16 rows (query tokens x q heads of one kv head).  The step reads
+// every key and value of every live request once, so the kernel is built around that stream:
+//
+//   * a block owns one (sequence, kv head, slice of the keys) and has five warps.  One is the
+//     producer: it looks the pages up in the block table (32 entries at a time, one per lane)
+//     and brings each 64-key tile of K and of V in with one TMA copy each (a tensor map over the
+//     cache layer as rows of 64 bfloat16, 128-byte swizzle), into a ring of stages guarded by
+//     full/empty mbarriers.  Tiles that hold only keys of earlier steps are requested before the
+//     wait for the kernel that wrote this step's keys.
+//   * the four consumer warps share every tile: warp w takes keys 16w..16w+15 of it, computes
+//     S = Q.K^T for them (mma.sync m16n8k16, the up-to-16 rows as M), keeps an online softmax of
+//     its own over its keys (float registers, base 2) and adds P.V into its own accumulator.  Four
+//     warps on one tile mean four times the warps for the same bytes in flight, which is what a
+//     stream of this kind needs: one warp per tile spends its time on dependent instructions.
+//   * at the end the four partial results are merged through shared memory, in warp order, and
+//     written as the final bfloat16 output, or as this slice's partial result for the combine
+//     kernel.
+//
+// Keys beyond the sequence's end are masked, and their V rows (memory that was never written)
+// are zeroed in shared memory before they are multiplied by a zero weight.  Every mbarrier wait
+// is bounded; when one runs out the block records status 16 and writes nothing.
+#pragma once
+#include "attention_mma.cuh"
+#include "tcgen05.cuh"
+
+namespace vapi {
+
+constexpr int FD_BK = 64;
+constexpr int FD_HD = 64;
+constexpr int FD_CWARPS = 4;                               // consumer warps: 16 keys of every tile each
+constexpr int FD_THREADS = (FD_CWARPS + 1) * 32;
+constexpr int FD_MAX_ROWS = 16;
+constexpr int FD_TILE_BYTES = FD_BK * FD_HD * 2;           // one K (or V) tile
+#ifndef FD_STAGES_N
+#define FD_STAGES_N 4
+#endif
+constexpr int FD_STAGES = FD_STAGES_N;
+constexpr size_t FD_SMEM = (size_t)FD_STAGES * 2 * FD_TILE_BYTES + 1024;     // + room to align to the swizzle's 1024 bytes
+static_assert(FD_STAGES * 2 * FD_TILE_BYTES >= FD_CWARPS * FD_MAX_ROWS * FD_HD * 4, "the merge reuses the stages");
+
+struct FdParams {
+    const __nv_bfloat16* q; long long q_row_stride;
+    const int* block_table; int table_stride;
+    const int* cu_q; const int* seqlens_k;
+    __nv_bfloat16* out; float* part_o; float* part_ml;
+    int nh, nkv, page_size, num_pages;
+    float scale_log2e; int window, splits;
+    int* status;
+};
+
+__global__ void __launch_bounds__(FD_THREADS, 3)
+flash_decode_kernel(const __grid_constant__ CUtensorMap tm_kv, const FdParams p) {
+    extern __shared__ unsigned char fd_smem_raw[];
+    unsigned char* sKV = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fd_smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) unsigned long long bars[2 * FD_STAGES];
+    __shared__ float sM[FD_CWARPS][FD_MAX_ROWS], sL[FD_CWARPS][FD_MAX_ROWS];
+    __shared__ int failed;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int s = blockIdx.z / p.splits, sp = blockIdx.z - s * p.splits;
+    const int g = blockIdx.y;
+    pdl_trigger();
+    // index data was copied from the host before the step's first kernel: safe before the wait
+    const int q0 = p.cu_q[s], qlen = p.cu_q[s + 1] - q0, klen = p.seqlens_k[s];
+    const int n_rep = p.nh / p.nkv;
+    const int rows_total = qlen * n_rep;
+    if (rows_total <= 0 || rows_total > FD_MAX_ROWS) {         // longer portions belong to another kernel
+        pdl_wait();
+        return;
+    }
+    const int base_pos = klen - qlen;
+    const int p_min = base_pos, p_max = klen - 1;
+    const int key_lo = p.window > 0 ? max(0, p_min - p.window + 1) : 0;
+    const int kt_lo = key_lo / FD_BK, kt_hi = p_max / FD_BK;
+    const int ntiles_all = kt_hi - kt_lo + 1;
+    const int chunk = (ntiles_all + p.splits - 1) / p.splits;
+    const int kt_begin = kt_lo + sp * chunk;
+    const int kt_end = min(kt_hi + 1, kt_begin + chunk);
+    const int nt = max(0, kt_end - kt_begin);
+
+    const unsigned full = smem_u32(bars), empty = smem_u32(bars + FD_STAGES);
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < FD_STAGES; ++i) { mbar_init(full + 8 * i, 1); mbar_init(empty + 8 * i, FD_CWARPS); }
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o_acc[FD_HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < FD_HD / 8; ++i) { o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f; }
+    const int gq = lane >> 2, tq = lane & 3;                          // row / column pair of the fragments
+    int row_tok[2], row_head[2], row_pos[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int rr = gq + 8 * h;
+        row_ok[h] = rr < rows_total;
+        row_tok[h] = row_ok[h] ? rr / n_rep : 0;
+        row_head[h] = g * n_rep + (row_ok[h] ? rr - row_tok[h] * n_rep : 0);
+        row_pos[h] = row_ok[h] ? base_pos + row_tok[h] : -1;          // -1: sees nothing
+    }
+    bool ok = true;
+
+    if (warp == FD_CWARPS) {
+        // ---- producer ----
+        const int* bt = p.block_table + (size_t)s * p.table_stride;
+        const int kt_old_end = base_pos / FD_BK;                      // tiles before this one hold keys of earlier steps only
+        bool waited = false;
+        int pg_base = -(1 << 30), entry = 0;
+        for (int it = 0; it < nt; ++it) {
+            const int kt = kt_begin + it, k0 = kt * FD_BK, stage = it % FD_STAGES;
+            if (!waited && kt >= kt_old_end) {
+                pdl_wait();                                           // this step's keys are in the cache now
+                waited = true;
+            }
+            const int pg = k0 / p.page_size;
+            if (pg - pg_base >= 32) {
+                pg_base = pg;
+                const int last_pg = p_max / p.page_size;
+                entry = pg + lane <= last_pg ? bt[pg + lane] : 0;
+            }
+            int page = __shfl_sync(0xffffffffu, entry, pg - pg_base);
+            if (page < 0 || page >= p.num_pages) {
+                if (lane == 0 && p.status) atomicExch(p.status, 4);
+                page = 0;
+            }
+            int good = 1;
+            if (lane == 0) {
+                if (it >= FD_STAGES && !mbar_wait(empty + 8 * stage, ((it / FD_STAGES) - 1) & 1)) good = 0;
+                if (good) {
+                    const int row = ((page * 2) * p.nkv + g) * p.page_size + (k0 % p.page_size);
+                    const unsigned dst = smem_u32(sKV + (size_t)stage * 2 * FD_TILE_BYTES);
+                    mbar_expect_tx(full + 8 * stage, 2 * FD_TILE_BYTES);
+                    tma_load_2d(dst, &tm_kv, full + 8 * stage, 0, row);
+                    tma_load_2d(dst + FD_TILE_BYTES, &tm_kv, full + 8 * stage, 0, row + p.nkv * p.page_size);
+                }
+            }
+            if (!__shfl_sync(0xffffffffu, good, 0)) { ok = false; break; }
+        }
+        if (!waited) pdl_wait();
+    } else {
+        // ---- consumers ----
+        pdl_wait();                                                   // q was rotated by the kernel before this one
+        unsigned qf[FD_HD / 16][4];
+#pragma unroll
+        for (int kk = 0; kk < FD_HD / 16; ++kk) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                unsigned lo = 0u, hi = 0u;
+                if (row_ok[h]) {
+                    const __nv_bfloat16* src = p.q + (size_t)(q0 + row_tok[h]) * p.q_row_stride + (size_t)row_head[h] * FD_HD + kk * 16 + 2 * tq;
+                    lo = *reinterpret_cast<const unsigned*>(src);
+                    hi = *reinterpret_cast<const unsigned*>(src + 8);
+                }
+                qf[kk][h] = lo;
+                qf[kk][2 + h] = hi;
+            }
+        }
+        const int mat = lane >> 3, rin = lane & 7;
+        for (int it = 0; it < nt; ++it) {
+            const int k0 = (kt_begin + it) * FD_BK, stage = it % FD_STAGES;
+            const int kw = k0 + warp * 16;                            // this warp's first key of the tile
+            if (!__all_sync(0xffffffffu, mbar_wait(full + 8 * stage, (it / FD_STAGES) & 1))) { ok = false; break; }
+            // a warp whose keys no row can see (beyond the newest position, behind every window) skips them
+            const bool skip = kw > p_max || (p.window > 0 && kw + 15 <= p_min - p.window);
+            if (!skip) {
+                const __nv_bfloat16* ks = reinterpret_cast<const __nv_bfloat16*>(sKV + (size_t)stage * 2 * FD_TILE_BYTES);
+                __nv_bfloat16* vs = reinterpret_cast<__nv_bfloat16*>(sKV + (size_t)stage * 2 * FD_TILE_BYTES + FD_TILE_BYTES);
+                float sc[2][4];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) { sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f; }
+#pragma unroll
+                for (int kk = 0; kk < FD_HD / 16; ++kk) {
+                    const int key = warp * 16 + (mat >> 1) * 8 + rin;
+                    const int ch = kk * 2 + (mat & 1);
+                    unsigned r0, r1, r2, r3;
+                    ldmatrix_x4(r0, r1, r2, r3, ks + key * FD_HD + ((ch ^ (key & 7)) << 3));
+                    mma_bf16_16816(sc[0], qf[kk], r0, r1);
+                    mma_bf16_16816(sc[1], qf[kk], r2, r3);
+                }
+                if (kw + 16 > klen) {
+                    // V rows of keys beyond the sequence: zero them (two lanes per row of 128 bytes)
+                    const int r = warp * 16 + (lane >> 1);
+                    if (k0 + r >= klen) {
+                        uint4* vr = reinterpret_cast<uint4*>(vs + r * FD_HD) + (lane & 1) * 4;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) vr[c] = make_uint4(0u, 0u, 0u, 0u);
+                        fence_proxy_async();                          // the stage's next writer is a TMA copy
+                    }
+                    __syncwarp();
+                }
+                const bool need_mask = (kw + 15 > p_min) || (kw + 16 > klen) || (p.window > 0 && kw <= p_max - p.window);
+                float alpha[2];
+                bool grew = false;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float mx = -INFINITY;
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            float v = sc[i][2 * h + e] * p.scale_log2e;
+                            if (need_mask) {
+                                const int kj = kw + i * 8 + 2 * tq + e;
+                                const bool vis = kj <= row_pos[h] && kj < klen && (p.window <= 0 || kj > row_pos[h] - p.window);
+                                v = vis ? v : -INFINITY;
+                            }
+                            sc[i][2 * h + e] = v;
+                            mx = fmaxf(mx, v);
+                        }
+                    }
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                    const float m_new = fmaxf(m_run[h], mx);
+                    const float m_use = m_new == -INFINITY ? 0.f : m_new;
+                    alpha[h] = exp2f(m_run[h] - m_use);
+                    grew = grew || m_new > m_run[h];
+                    float rs = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const float pe = exp2f(sc[i][2 * h + e] - m_use);
+                            sc[i][2 * h + e] = pe;
+                            rs += pe;
+                        }
+                    }
+                    l_run[h] = l_run[h] * alpha[h] + rs;        // per-thread part of the row sum; quad-reduced at the end
+                    m_run[h] = m_new;
+                }
+                if (__any_sync(0xffffffffu, grew)) {            // the maximum moves in the first tiles and rarely later
+#pragma unroll
+                    for (int i = 0; i < FD_HD / 8; ++i) {
+                        o_acc[i][0] *= alpha[0]; o_acc[i][1] *= alpha[0];
+                        o_acc[i][2] *= alpha[1]; o_acc[i][3] *= alpha[1];
+                    }
+                }
+                unsigned pa[4];
+                pa[0] = pack_bf16(sc[0][0], sc[0][1]);
+                pa[1] = pack_bf16(sc[0][2], sc[0][3]);
+                pa[2] = pack_bf16(sc[1][0], sc[1][1]);
+                pa[3] = pack_bf16(sc[1][2], sc[1][3]);
+#pragma unroll
+                for (int nd = 0; nd < FD_HD / 16; ++nd) {
+                    const int key = warp * 16 + (mat & 1) * 8 + rin;
+                    const int ch = nd * 2 + (mat >> 1);
+                    unsigned r0, r1, r2, r3;
+                    ldmatrix_x4_trans(r0, r1, r2, r3, vs + key * FD_HD + ((ch ^ (key & 7)) << 3));
+                    mma_bf16_16816(o_acc[2 * nd], pa, r0, r1);
+                    mma_bf16_16816(o_acc[2 * nd + 1], pa, r2, r3);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty + 8 * stage);
+        }
+    }
+
+    if (!ok) failed = 1;
+    __syncthreads();                                                  // every tile that was requested has arrived and been used
+    if (failed) {
+        if (threadIdx.x == 0 && p.status) atomicExch(p.status, 16);
+        return;
+    }
+    // ---- merge the four warps' partial results ----
+    float* sO = reinterpret_cast<float*>(sKV);                        // [warp][16 rows][64]
+    if (warp < FD_CWARPS) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float l = l_run[h];
+            l += __shfl_xor_sync(0xffffffffu, l, 1);
+            l += __shfl_xor_sync(0xffffffffu, l, 2);
+            const int r = gq + 8 * h;
+            if (tq == 0) { sM[warp][r] = m_run[h]; sL[warp][r] = l; }
+#pragma unroll
+            for (int i = 0; i < FD_HD / 8; ++i)
+                *reinterpret_cast<float2*>(sO + ((size_t)warp * FD_MAX_ROWS + r) * FD_HD + i * 8 + 2 * tq) =
+                    make_float2(o_acc[i][2 * h], o_acc[i][2 * h + 1]);
+        }
+    }
+    __syncthreads();
+    if (warp < FD_CWARPS) {
+        const int r = threadIdx.x >> 3, c0 = (threadIdx.x & 7) * 8;  // a row and 8 of its 64 columns
+        if (r < rows_total) {
+            float m = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < FD_CWARPS; ++w) m = fmaxf(m, sM[w][r]);
+            const float m_use = m == -INFINITY ? 0.f : m;
+            float l = 0.f, o[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) o[c] = 0.f;
+#pragma unroll
+            for (int w = 0; w < FD_CWARPS; ++w) {
+                const float a = exp2f(sM[w][r] - m_use);              // -inf: 0
+                l += sL[w][r] * a;
+                const float4 x0 = *reinterpret_cast<const float4*>(sO + ((size_t)w * FD_MAX_ROWS + r) * FD_HD + c0);
+                const float4 x1 = *reinterpret_cast<const float4*>(sO + ((size_t)w * FD_MAX_ROWS + r) * FD_HD + c0 + 4);
+                o[0] += x0.x * a; o[1] += x0.y * a; o[2] += x0.z * a; o[3] += x0.w * a;
+                o[4] += x1.x * a; o[5] += x1.y * a; o[6] += x1.z * a; o[7] += x1.w * a;
+            }
+            const int tok = r / n_rep, head = g * n_rep + (r - tok * n_rep);
+            const size_t grow = (size_t)(q0 + tok) * p.nh + head;
+            if (p.splits == 1) {
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                uint4 w4;
+                w4.x = pack_bf16(o[0] * inv, o[1] * inv); w4.y = pack_bf16(o[2] * inv, o[3] * inv);
+                w4.z = pack_bf16(o[4] * inv, o[5] * inv); w4.w = pack_bf16(o[6] * inv, o[7] * inv);
+                *reinterpret_cast<uint4*>(p.out + grow * FD_HD + c0) = w4;
+            } else {
+                float* po = p.part_o + (grow * p.splits + sp) * (size_t)FD_HD + c0;
+                *reinterpret_cast<float4*>(po) = make_float4(o[0], o[1], o[2], o[3]);
+                *reinterpret_cast<float4*>(po + 4) = make_float4(o[4], o[5], o[6], o[7]);
+                if ((threadIdx.x & 7) == 0) {
+                    // the combine step works with natural-log maxima
+                    p.part_ml[(grow * p.splits + sp) * 2] = m == -INFINITY ? -INFINITY : m * 0.6931471805599453f;
+                    p.part_ml[(grow * p.splits + sp) * 2 + 1] = l;
+                }
+            }
+        }
+    }
+}
+
+static int make_kv_map(CUtensorMap* map, const void* cache, long long rows);
+
+static int launch_flash_decode(const void* q, long long q_row_stride, const void* cache, const int* block_table,
+                               int table_stride, const int* cu_q, const int* seqlens_k, void* out, float* part_o,
+                               float* part_ml, int num_seqs, int nh, int nkv, int page_size, int num_pages,
+                               float scale, int window, int splits, int* status, cudaStream_t stream) {
+    if (nkv > 65535 || (long long)num_seqs * splits > 65535)
+        return fail(-1, "paged_attention: %d kv heads or %d sequences x %d splits exceed the grid", nkv, num_seqs, splits);
+    if (q_row_stride % 2 != 0 || ((uintptr_t)q & 3) != 0 || ((uintptr_t)out & 15) != 0)
+        return fail(-1, "paged_attention: the decode kernel needs 4-byte aligned query rows and a 16-byte aligned output");
+    CUtensorMap map;
+    int rc = make_kv_map(&map, cache, (long long)num_pages * 2 * nkv * page_size);
+    if (rc != 0) return rc;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
+        if (e != cudaSuccess) return fail(-101, "paged_attention: cannot reserve %zu bytes of shared memory: %s", FD_SMEM, cudaGetErrorString(e));
+        attr_set = true;
+    }
+    FdParams p;
+    p.q = (const __nv_bfloat16*)q; p.q_row_stride = q_row_stride; p.block_table = block_table; p.table_stride = table_stride;
+    p.cu_q = cu_q; p.seqlens_k = seqlens_k; p.out = (__nv_bfloat16*)out; p.part_o = part_o; p.part_ml = part_ml;
+    p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.num_pages = num_pages; p.scale_log2e = scale * 1.4426950408889634f;
+    p.window = window; p.splits = splits; p.status = status;
+    dim3 grid(1, nkv, num_seqs * splits);
+    return check_launch("paged_attention (decode)", launch(flash_decode_kernel, grid, FD_THREADS, FD_SMEM, stream, map, p));
+}
+
+}  // namespace vapi

@@ -280,7 +280,8 @@ class ModelRunner:
         for blk in self.plan.layers:
             m = getattr(blk, "mixer", None)
             if isinstance(m, GQAttention):
-                best = max(best, ops.attention_splits(B, 1, self.max_context, m.nh, m.nkv))
+                dec = ops.decode_attention_applies(self.dtype, m.d, self.cache.page_size, m.nh // m.nkv)
+                best = max(best, ops.attention_splits(B, 1, self.max_context, m.nh, m.nkv, dec))
         return best
 
     def step_decode_graph(self, entries: Optional[Sequence[StepEntry]], plan=None) -> Optional[torch.Tensor]:

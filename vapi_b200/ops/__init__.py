@@ -509,15 +509,35 @@ def qk_norm_rope_write(qkv: torch.Tensor, nh: int, nkv: int, d: int,
         _p(cache_layer), _p(slot_mapping), n, nh, nkv, d, page_size, num_pages, _p(status), _stream()))
 
 
-def attention_splits(num_seqs: int, max_q: int, max_k: int, nh: int, nkv: int) -> int:
+# "tma": decode steps at head size 64 on the TMA-fed decode kernel; "mma": on the one-warp flash kernel
+DECODE_ATTENTION = os.environ.get("VAPI_DECODE_ATTENTION", "tma")
+DECODE_ATTENTION_SLOTS = 148 * 3          # blocks of the decode kernel that are resident at once
+
+
+def decode_attention_applies(dtype: torch.dtype, d: int, page_size: int, rows: int) -> bool:
+    """Whether a step whose sequences bring at most ``rows`` rows (tokens x q heads per kv head)
+    runs on the decode kernel (the library's own rule, restated)."""
+    return (DECODE_ATTENTION == "tma" and dtype == torch.bfloat16 and d == 64 and page_size % 64 == 0
+            and rows <= 16)
+
+
+def attention_splits(num_seqs: int, max_q: int, max_k: int, nh: int, nkv: int, decode_kernel: bool = False) -> int:
     """How many blocks share the keys of one row tile: 1 unless the step is so small that
-    the device would sit idle (decode of few sequences over long contexts).  A decode block
-    is one warp with 48 KB of shared memory, so 4 fit on an SM: aim at one full wave of
-    148 x 4 blocks, each with at least 128 keys."""
+    the device would sit idle (decode of few sequences over long contexts).  A block of the
+    one-warp flash kernel has 48 KB of shared memory, so 4 fit on an SM: aim at one full wave of
+    148 x 4 blocks, each with at least 128 keys.  The decode kernel has three blocks of four
+    consumer warps on an SM: one wave of them while the step is small, and once there are more
+    (sequence, kv head) pairs than half a wave, slices fine enough for two waves or more, so that
+    the last blocks do not run alone."""
     n_rep = nh // nkv
     rows = max_q * n_rep
     tiles = -(-rows // (16 if rows <= 16 else 64))
     blocks = max(1, num_seqs * nkv * tiles)
+    if decode_kernel:
+        key_tiles = max(1, -(-max_k // 64))
+        slots = DECODE_ATTENTION_SLOTS
+        want = slots // blocks if 2 * blocks <= slots else -(-2 * slots // blocks)
+        return max(1, min(want, max(1, key_tiles // 2), 32))
     if rows > 16 and blocks >= 148:
         return 1
     want = max(1, 592 // blocks)
@@ -538,7 +558,8 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tenso
     pages of 64n, no split), which "auto" uses for steps with prompt portions of 64 tokens or more;
     "auto" otherwise picks the tensor-core kernel where it applies (bfloat16, head_dim 64 or
     128, page size a multiple of 64) and the general kernel elsewhere; "general" and
-    "tensor_core" force one (the latter raises where it does not apply).
+    "tensor_core" force one (the latter raises where it does not apply); "decode" forces the
+    TMA-fed decode kernel (bfloat16, head_dim 64, at most 16 rows per sequence and kv head).
     """
     _cuda(q, cache_layer, block_table, cu_q, seqlens_k)
     _i32(block_table, "block table")
@@ -551,7 +572,9 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tenso
         raise KernelError("block table must be [S, width] with unit inner stride")
     num_pages, page_size = cache_layer.shape[0], cache_layer.shape[3]
     if splits is None:
-        splits = 1 if impl == "tcgen05" else attention_splits(num_seqs, max_q, max_k, nh, nkv)
+        splits = 1 if impl == "tcgen05" else attention_splits(
+            num_seqs, max_q, max_k, nh, nkv,
+            impl == "decode" or (impl == "auto" and decode_attention_applies(q.dtype, d, page_size, max_q * (nh // nkv))))
     out = torch.empty((n, nh * d), dtype=q.dtype, device=q.device)
     part_o = part_ml = None
     if splits > 1:
@@ -563,11 +586,15 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tenso
     tc = impl == "tcgen05" or (impl == "auto" and q.dtype == torch.bfloat16 and d == 64 and page_size % 64 == 0
                                and splits == 1 and max_q >= 64 and q_row_stride % 8 == 0 and scale > 0)
     launches = (1 if impl == "tcgen05" or num_seqs == 1 else 2) if tc else (2 if splits > 1 else 1)
+    code = {"auto": 0, "general": 1, "tensor_core": 2, "tcgen05": 3, "decode": 4}[impl]
+    if (impl == "auto" and DECODE_ATTENTION != "tma" and q.dtype == torch.bfloat16 and d == 64 and page_size % 64 == 0
+            and max_q * (nh // nkv) <= 16):
+        code = 2                          # keep decode steps on the one-warp flash kernel
     _check(lib, lib.vapi_paged_attention(
         _p(q), ctypes.c_longlong(q_row_stride), _p(cache_layer), _dt(q), _p(block_table),
         block_table.stride(0), _p(cu_q), _p(seqlens_k), _p(out), _p(part_o), _p(part_ml), n, num_seqs,
         max_q, nh, nkv, d, page_size, num_pages, ctypes.c_float(scale), window, splits,
-        {"auto": 0, "general": 1, "tensor_core": 2, "tcgen05": 3}[impl], _p(status), _stream()), launches)
+        code, _p(status), _stream()), launches)
     return out
 
 
