@@ -356,12 +356,24 @@ def test_decode_attention_is_what_a_decode_step_gets_and_refuses_what_it_cannot_
         _attention_case(ops, nh=8, nkv=2, d=64, page=32, lens=[(1, 70)], **DEC)
 
 
-def test_attention_picks_its_kernels_for_a_mixed_step(ops):
-    # "auto": prompt portions on tcgen05, the decode tokens and short portions beside them on the flash kernel
+@pytest.mark.parametrize("splits", [1, 3])
+def test_short_portions_beside_decode_tokens_share_two_kernels(ops, splits):
+    # no portion long enough for tcgen05: portions of more than 16 rows on the four-warp flash kernel, decode
+    # tokens on the decode kernel, and one combine kernel for the slices of both
     before = ops.launch_count
     _attention_case(ops, dtype=torch.bfloat16, nh=32, nkv=8, d=64, page=64,
-                    lens=[(1, 500), (300, 300), (1, 64), (31, 95), (32, 96), (1, 1), (64, 1000)], splits=1)
-    assert ops.launch_count - before == 2
+                    lens=[(10, 300), (1, 500), (4, 100), (5, 64), (1, 1), (20, 20), (1, 1500)], splits=splits, planted=True)
+    assert ops.launch_count - before == (2 if splits == 1 else 3)
+
+
+def test_attention_picks_its_kernels_for_a_mixed_step(ops):
+    # "auto": prompt portions on tcgen05, short portions beside them on the flash kernel, decode tokens
+    # (and portions of at most 16 rows) on the decode kernel
+    before = ops.launch_count
+    _attention_case(ops, dtype=torch.bfloat16, nh=32, nkv=8, d=64, page=64,
+                    lens=[(1, 500), (300, 300), (1, 64), (31, 95), (32, 96), (1, 1), (64, 1000), (4, 200), (5, 201), (1, 2000)],
+                    splits=1, planted=True)
+    assert ops.launch_count - before == 3
     with pytest.raises(ops.KernelError, match="tcgen05 kernel needs"):
         _attention_case(ops, nh=4, nkv=2, d=128, page=64, lens=[(70, 70)], **T5)
 

@@ -285,9 +285,13 @@ static int launch_attention(const void* q, long long q_row_stride, const void* c
 // that is a multiple of 64 the mma.sync flash kernel; at head_dim 64 the TMA-fed decode kernel for
 // steps whose sequences bring at most 16 rows per kv head, and for steps with prompt portions (no
 // split) the tcgen05 kernel for every sequence of at least FT_MIN_Q tokens beside the flash
-// kernel for the shorter ones; else the general kernel.  1 = the general kernel; 2 = the mma.sync
+// kernel and the decode kernel for the shorter ones; else the general kernel.  1 = the general kernel; 2 = the mma.sync
 // flash kernel or an error; 3 = the tcgen05 kernel for every sequence, or an error; 4 = the
 // decode kernel, or an error.
+// whether impl 0 may pick the decode kernel (a switch for comparisons; on unless turned off)
+static int g_decode_kernel = 1;
+VAPI_EXPORT void vapi_attention_use_decode_kernel(int on) { g_decode_kernel = on != 0; }
+
 VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, const void* cache,
                                      int dtype, const int* block_table, int table_stride,
                                      const int* cu_q, const int* seqlens_k, void* out,
@@ -325,9 +329,15 @@ VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, cons
         rc = launch_flash_tc(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, num_seqs, max_q,
                              nh, nkv, page_size, num_pages, scale, window, min_q, status, stream);
         if (rc != 0 || min_q == 1) return rc;
-        return launch_flash<64, 4, 3>(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, part_o,
-                                      part_ml, num_seqs, FT_MIN_Q - 1, nh, nkv, page_size, num_pages, scale, window, 1,
-                                      status, stream, FT_MIN_Q);
+        // (of the shorter ones, those of at most 16 rows - decode tokens, whose contexts can be long -
+        // go to the decode kernel, which puts four warps on their keys where the flash kernel has one)
+        const bool dec_too = g_decode_kernel && nh / nkv <= FD_MAX_ROWS && ((uintptr_t)out & 15) == 0;
+        rc = launch_flash<64, 4, 3>(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, part_o,
+                                    part_ml, num_seqs, FT_MIN_Q - 1, nh, nkv, page_size, num_pages, scale, window, 1,
+                                    status, stream, FT_MIN_Q, dec_too ? FD_MAX_ROWS : 0);
+        if (rc != 0 || !dec_too) return rc;
+        return launch_flash_decode(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, part_o, part_ml,
+                                   num_seqs, nh, nkv, page_size, num_pages, scale, window, 1, status, stream);
     }
 #define VAPI_FLASH(HD, NW, ST)                                                                   \
     rc = launch_flash<HD, NW, ST>(q, q_row_stride, cache, block_table, table_stride, cu_q,       \
@@ -338,7 +348,7 @@ VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, cons
                                  seqlens_k, out, part_o, part_ml, num_seqs, max_q, nh, nkv, d,  \
                                  page_size, num_pages, scale, window, splits, status, stream)
     const bool few_rows = (long long)max_q * (nh / nkv) <= FD_MAX_ROWS;
-    const bool dec_ok = fast_ok && d == FD_HD && few_rows && ((uintptr_t)out & 15) == 0;
+    const bool dec_ok = fast_ok && d == FD_HD && few_rows && ((uintptr_t)out & 15) == 0 && (g_decode_kernel || impl == 4);
     if (impl == 4 && !dec_ok)
         return fail(-3, "paged_attention: the decode kernel needs bfloat16, head_dim 64, a page size that is a multiple of 64 "
                         "and at most 16 rows per sequence and kv head (got dtype %d, head_dim %d, page size %d, %lld rows)",
@@ -346,6 +356,15 @@ VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, cons
     if (impl == 4 || (impl == 0 && dec_ok)) {
         rc = launch_flash_decode(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, part_o, part_ml,
                                  num_seqs, nh, nkv, page_size, num_pages, scale, window, splits, status, stream);
+    } else if (fast && impl == 0 && g_decode_kernel && d == FD_HD && nh / nkv <= FD_MAX_ROWS && ((uintptr_t)out & 15) == 0) {
+        // a step with portions of more than 16 rows: those on the four-warp flash kernel, the decode
+        // tokens beside them on the decode kernel (its slices, if any, go to the combine kernel with the rest)
+        rc = launch_flash<64, 4, 3>(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, part_o,
+                                    part_ml, num_seqs, max_q, nh, nkv, page_size, num_pages, scale, window, splits,
+                                    status, stream, 0, FD_MAX_ROWS);
+        if (rc == 0)
+            rc = launch_flash_decode(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, part_o, part_ml,
+                                     num_seqs, nh, nkv, page_size, num_pages, scale, window, splits, status, stream, false);
     } else if (fast) {
         if (d == 64) { if (few_rows) VAPI_FLASH(64, 1, 3); else VAPI_FLASH(64, 4, 3); }
         else         { if (few_rows) VAPI_FLASH(128, 1, 3); else VAPI_FLASH(128, 4, 3); }
@@ -359,7 +378,8 @@ VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, cons
 #undef VAPI_ATT
 #undef VAPI_FLASH
     if (rc != 0) return rc;
-    if (splits > 1) {
+    const bool combined = (impl == 4 || (impl == 0 && dec_ok)) && flash_decode_combines(num_seqs, nkv, splits);   // the decode kernel's clusters did it
+    if (splits > 1 && !combined) {
         const long long rows = (long long)n * nh;
         const int wpb = 4;
         const long long blocks = (rows + wpb - 1) / wpb;
@@ -372,6 +392,11 @@ VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, cons
     }
     return 0;
 }
+
+// How many blocks of the decode kernel the device holds at once (0: unknown), and the largest
+// number of key slices that it combines inside the kernel.
+VAPI_EXPORT int vapi_decode_attention_slots() { return flash_decode_slots(); }
+VAPI_EXPORT int vapi_decode_attention_cluster() { return FD_MAX_CLUSTER; }
 
 // ---------------------------------------------------------------------------------------------
 // The same attention with its scratch inside the library (see attention_noalloc.h for who needs

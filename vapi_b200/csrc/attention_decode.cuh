@@ -31,13 +31,14 @@ constexpr int FD_HD = 64;
 constexpr int FD_CWARPS = 4;                               // consumer warps: 16 keys of every tile each
 constexpr int FD_THREADS = (FD_CWARPS + 1) * 32;
 constexpr int FD_MAX_ROWS = 16;
+constexpr int FD_MAX_CLUSTER = 8;                          // slices of the keys that combine inside the kernel
 constexpr int FD_TILE_BYTES = FD_BK * FD_HD * 2;           // one K (or V) tile
 #ifndef FD_STAGES_N
 #define FD_STAGES_N 4
 #endif
 constexpr int FD_STAGES = FD_STAGES_N;
 constexpr size_t FD_SMEM = (size_t)FD_STAGES * 2 * FD_TILE_BYTES + 1024;     // + room to align to the swizzle's 1024 bytes
-static_assert(FD_STAGES * 2 * FD_TILE_BYTES >= FD_CWARPS * FD_MAX_ROWS * FD_HD * 4, "the merge reuses the stages");
+static_assert(FD_STAGES * 2 * FD_TILE_BYTES >= (FD_CWARPS + 1) * FD_MAX_ROWS * FD_HD * 4, "the merge reuses the stages");
 
 struct FdParams {
     const __nv_bfloat16* q; long long q_row_stride;
@@ -49,12 +50,36 @@ struct FdParams {
     int* status;
 };
 
+__device__ __forceinline__ void fd_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned fd_peer(const void* local, unsigned rank) {     // this address in the shared memory of block `rank`
+    unsigned remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ float fd_peer_f32(unsigned addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 fd_peer_f32x4(unsigned addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
+// CLUSTER: the blocks of one (sequence, kv head) - its slices of the keys, at most 8 - form a
+// thread-block cluster; each leaves its partial result in its own shared memory and, after a
+// cluster barrier, they share out the rows' final sums among themselves (slice sp is rank sp).
+template <bool CLUSTER>
 __global__ void __launch_bounds__(FD_THREADS, 3)
 flash_decode_kernel(const __grid_constant__ CUtensorMap tm_kv, const FdParams p) {
     extern __shared__ unsigned char fd_smem_raw[];
     unsigned char* sKV = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fd_smem_raw) + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(8) unsigned long long bars[2 * FD_STAGES];
     __shared__ float sM[FD_CWARPS][FD_MAX_ROWS], sL[FD_CWARPS][FD_MAX_ROWS];
+    __shared__ float xM[FD_MAX_ROWS], xL[FD_MAX_ROWS];          // CLUSTER: this slice's result, read by its peers
     __shared__ int failed;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -262,10 +287,15 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tm_kv, const FdParams p)
     __syncthreads();                                                  // every tile that was requested has arrived and been used
     if (failed) {
         if (threadIdx.x == 0 && p.status) atomicExch(p.status, 16);
+        if (CLUSTER) {                                                // the peers wait for this block at both barriers
+            fd_cluster_sync();
+            fd_cluster_sync();
+        }
         return;
     }
     // ---- merge the four warps' partial results ----
     float* sO = reinterpret_cast<float*>(sKV);                        // [warp][16 rows][64]
+    float* xO = sO + FD_CWARPS * FD_MAX_ROWS * FD_HD;                 // CLUSTER: [16 rows][64], behind it
     if (warp < FD_CWARPS) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -281,53 +311,102 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tm_kv, const FdParams p)
         }
     }
     __syncthreads();
-    if (warp < FD_CWARPS) {
-        const int r = threadIdx.x >> 3, c0 = (threadIdx.x & 7) * 8;  // a row and 8 of its 64 columns
-        if (r < rows_total) {
-            float m = -INFINITY;
+    const int r = threadIdx.x >> 3, c0 = (threadIdx.x & 7) * 8;      // a row and 8 of its 64 columns
+    const bool mine = warp < FD_CWARPS && r < rows_total;
+    const int tok = mine ? r / n_rep : 0, head = g * n_rep + (mine ? r - tok * n_rep : 0);
+    const size_t grow = (size_t)(q0 + tok) * p.nh + head;
+    if (mine) {
+        float m = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < FD_CWARPS; ++w) m = fmaxf(m, sM[w][r]);
+        for (int w = 0; w < FD_CWARPS; ++w) m = fmaxf(m, sM[w][r]);
+        const float m_use = m == -INFINITY ? 0.f : m;
+        float l = 0.f, o[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) o[c] = 0.f;
+#pragma unroll
+        for (int w = 0; w < FD_CWARPS; ++w) {
+            const float a = exp2f(sM[w][r] - m_use);              // -inf: 0
+            l += sL[w][r] * a;
+            const float4 x0 = *reinterpret_cast<const float4*>(sO + ((size_t)w * FD_MAX_ROWS + r) * FD_HD + c0);
+            const float4 x1 = *reinterpret_cast<const float4*>(sO + ((size_t)w * FD_MAX_ROWS + r) * FD_HD + c0 + 4);
+            o[0] += x0.x * a; o[1] += x0.y * a; o[2] += x0.z * a; o[3] += x0.w * a;
+            o[4] += x1.x * a; o[5] += x1.y * a; o[6] += x1.z * a; o[7] += x1.w * a;
+        }
+        if (p.splits == 1) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            uint4 w4;
+            w4.x = pack_bf16(o[0] * inv, o[1] * inv); w4.y = pack_bf16(o[2] * inv, o[3] * inv);
+            w4.z = pack_bf16(o[4] * inv, o[5] * inv); w4.w = pack_bf16(o[6] * inv, o[7] * inv);
+            *reinterpret_cast<uint4*>(p.out + grow * FD_HD + c0) = w4;
+        } else if (CLUSTER) {
+            *reinterpret_cast<float4*>(xO + r * FD_HD + c0) = make_float4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<float4*>(xO + r * FD_HD + c0 + 4) = make_float4(o[4], o[5], o[6], o[7]);
+            if ((threadIdx.x & 7) == 0) { xM[r] = m; xL[r] = l; }
+        } else {
+            float* po = p.part_o + (grow * p.splits + sp) * (size_t)FD_HD + c0;
+            *reinterpret_cast<float4*>(po) = make_float4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<float4*>(po + 4) = make_float4(o[4], o[5], o[6], o[7]);
+            if ((threadIdx.x & 7) == 0) {
+                // the combine step works with natural-log maxima
+                p.part_ml[(grow * p.splits + sp) * 2] = m == -INFINITY ? -INFINITY : m * 0.6931471805599453f;
+                p.part_ml[(grow * p.splits + sp) * 2 + 1] = l;
+            }
+        }
+    }
+    if (CLUSTER && p.splits > 1) {
+        fd_cluster_sync();                                            // every slice's result is in place
+        // the (row, 8 columns) pieces go round the slices; each sums its pieces over all slices, in slice order
+        if (mine && (int)(threadIdx.x % (unsigned)p.splits) == sp) {
+            float m = -INFINITY;
+            for (int j = 0; j < p.splits; ++j) m = fmaxf(m, fd_peer_f32(fd_peer(&xM[r], (unsigned)j)));
             const float m_use = m == -INFINITY ? 0.f : m;
             float l = 0.f, o[8];
 #pragma unroll
             for (int c = 0; c < 8; ++c) o[c] = 0.f;
-#pragma unroll
-            for (int w = 0; w < FD_CWARPS; ++w) {
-                const float a = exp2f(sM[w][r] - m_use);              // -inf: 0
-                l += sL[w][r] * a;
-                const float4 x0 = *reinterpret_cast<const float4*>(sO + ((size_t)w * FD_MAX_ROWS + r) * FD_HD + c0);
-                const float4 x1 = *reinterpret_cast<const float4*>(sO + ((size_t)w * FD_MAX_ROWS + r) * FD_HD + c0 + 4);
+            for (int j = 0; j < p.splits; ++j) {
+                const float a = exp2f(fd_peer_f32(fd_peer(&xM[r], (unsigned)j)) - m_use);
+                l += fd_peer_f32(fd_peer(&xL[r], (unsigned)j)) * a;
+                const unsigned src = fd_peer(xO + r * FD_HD + c0, (unsigned)j);
+                const float4 x0 = fd_peer_f32x4(src), x1 = fd_peer_f32x4(src + 16);
                 o[0] += x0.x * a; o[1] += x0.y * a; o[2] += x0.z * a; o[3] += x0.w * a;
                 o[4] += x1.x * a; o[5] += x1.y * a; o[6] += x1.z * a; o[7] += x1.w * a;
             }
-            const int tok = r / n_rep, head = g * n_rep + (r - tok * n_rep);
-            const size_t grow = (size_t)(q0 + tok) * p.nh + head;
-            if (p.splits == 1) {
-                const float inv = l > 0.f ? 1.f / l : 0.f;
-                uint4 w4;
-                w4.x = pack_bf16(o[0] * inv, o[1] * inv); w4.y = pack_bf16(o[2] * inv, o[3] * inv);
-                w4.z = pack_bf16(o[4] * inv, o[5] * inv); w4.w = pack_bf16(o[6] * inv, o[7] * inv);
-                *reinterpret_cast<uint4*>(p.out + grow * FD_HD + c0) = w4;
-            } else {
-                float* po = p.part_o + (grow * p.splits + sp) * (size_t)FD_HD + c0;
-                *reinterpret_cast<float4*>(po) = make_float4(o[0], o[1], o[2], o[3]);
-                *reinterpret_cast<float4*>(po + 4) = make_float4(o[4], o[5], o[6], o[7]);
-                if ((threadIdx.x & 7) == 0) {
-                    // the combine step works with natural-log maxima
-                    p.part_ml[(grow * p.splits + sp) * 2] = m == -INFINITY ? -INFINITY : m * 0.6931471805599453f;
-                    p.part_ml[(grow * p.splits + sp) * 2 + 1] = l;
-                }
-            }
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            uint4 w4;
+            w4.x = pack_bf16(o[0] * inv, o[1] * inv); w4.y = pack_bf16(o[2] * inv, o[3] * inv);
+            w4.z = pack_bf16(o[4] * inv, o[5] * inv); w4.w = pack_bf16(o[6] * inv, o[7] * inv);
+            *reinterpret_cast<uint4*>(p.out + grow * FD_HD + c0) = w4;
         }
+        fd_cluster_sync();                                            // nobody reads this block's memory any more
     }
 }
 
 static int make_kv_map(CUtensorMap* map, const void* cache, long long rows);
 
+// blocks of the decode kernel that one device holds at a time
+static int flash_decode_slots() {
+    static int slots = 0;
+    if (slots == 0) {
+        int dev = 0, sms = 0, per_sm = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+        cudaFuncSetAttribute(flash_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, flash_decode_kernel<false>, FD_THREADS, FD_SMEM) != cudaSuccess) return 0;
+        slots = sms * per_sm;
+    }
+    return slots;
+}
+// Whether the slices of the keys combine inside the kernel, as clusters: only while the whole grid
+// is resident at once.  With more blocks than that, clusters (which start together and leave
+// together) keep places occupied that single blocks would give up as they finish.
+static bool flash_decode_combines(int num_seqs, int nkv, int splits) {
+    return splits > 1 && splits <= FD_MAX_CLUSTER && (long long)num_seqs * nkv * splits <= flash_decode_slots();
+}
+
 static int launch_flash_decode(const void* q, long long q_row_stride, const void* cache, const int* block_table,
                                int table_stride, const int* cu_q, const int* seqlens_k, void* out, float* part_o,
                                float* part_ml, int num_seqs, int nh, int nkv, int page_size, int num_pages,
-                               float scale, int window, int splits, int* status, cudaStream_t stream) {
+                               float scale, int window, int splits, int* status, cudaStream_t stream,
+                               bool may_combine = true) {
     if (nkv > 65535 || (long long)num_seqs * splits > 65535)
         return fail(-1, "paged_attention: %d kv heads or %d sequences x %d splits exceed the grid", nkv, num_seqs, splits);
     if (q_row_stride % 2 != 0 || ((uintptr_t)q & 3) != 0 || ((uintptr_t)out & 15) != 0)
@@ -337,7 +416,8 @@ static int launch_flash_decode(const void* q, long long q_row_stride, const void
     if (rc != 0) return rc;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
         if (e != cudaSuccess) return fail(-101, "paged_attention: cannot reserve %zu bytes of shared memory: %s", FD_SMEM, cudaGetErrorString(e));
         attr_set = true;
     }
@@ -347,7 +427,25 @@ static int launch_flash_decode(const void* q, long long q_row_stride, const void
     p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.num_pages = num_pages; p.scale_log2e = scale * 1.4426950408889634f;
     p.window = window; p.splits = splits; p.status = status;
     dim3 grid(1, nkv, num_seqs * splits);
-    return check_launch("paged_attention (decode)", launch(flash_decode_kernel, grid, FD_THREADS, FD_SMEM, stream, map, p));
+    if (may_combine && flash_decode_combines(num_seqs, nkv, splits)) {
+        // the slices of one (sequence, kv head) are a cluster along z and combine among themselves
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(FD_THREADS);
+        cfg.dynamicSmemBytes = FD_SMEM;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = (unsigned)splits;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_enabled() ? 2 : 1;
+        return check_launch("paged_attention (decode, cluster)", cudaLaunchKernelEx(&cfg, flash_decode_kernel<true>, map, p));
+    }
+    return check_launch("paged_attention (decode)", launch(flash_decode_kernel<false>, grid, FD_THREADS, FD_SMEM, stream, map, p));
 }
 
 }  // namespace vapi

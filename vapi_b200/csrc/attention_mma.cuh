@@ -56,8 +56,10 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
                    int table_stride, const int* __restrict__ cu_q, const int* __restrict__ seqlens_k,
                    __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int nh, int nkv, int page_size, int num_pages,
-                   float scale_log2e, int window, int splits, int q_below, int* __restrict__ status) {
-    // q_below > 0: sequences that bring q_below tokens or more belong to another kernel
+                   float scale_log2e, int window, int splits, int q_below, int rows_above,
+                   int* __restrict__ status) {
+    // q_below > 0: sequences that bring q_below tokens or more belong to another kernel, and so do
+    // sequences of at most rows_above rows (rows_above > 0)
     constexpr int ROWS = NWARPS * 16;
     constexpr int CPR = HD / 8;            // 16-byte chunks in a row
     constexpr int TILE = FA_BK * HD;       // elements of one K (or V) tile
@@ -78,7 +80,7 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
     // row tiles late in a sequence see the most keys: hand them out first, so that the last
     // blocks to start are the short ones
     const int tile_start = ((int)gridDim.x - 1 - (int)blockIdx.x) * ROWS;
-    if (tile_start >= rows_total || (q_below > 0 && qlen >= q_below)) {
+    if (tile_start >= rows_total || (q_below > 0 && qlen >= q_below) || rows_total <= rows_above) {
         pdl_wait();
         return;
     }
@@ -306,7 +308,7 @@ static int launch_flash(const void* q, long long q_row_stride, const void* cache
                         const int* block_table, int table_stride, const int* cu_q,
                         const int* seqlens_k, void* out, float* part_o, float* part_ml, int num_seqs,
                         int max_q, int nh, int nkv, int page_size, int num_pages, float scale,
-                        int window, int splits, int* status, cudaStream_t stream, int q_below = 0) {
+                        int window, int splits, int* status, cudaStream_t stream, int q_below = 0, int rows_above = 0) {
     const int n_rep = nh / nkv;
     const long long max_rows = (long long)max_q * n_rep;
     const long long tiles = (max_rows + NWARPS * 16 - 1) / (NWARPS * 16);
@@ -323,7 +325,7 @@ static int launch_flash(const void* q, long long q_row_stride, const void* cache
     return check_launch("paged_attention (tensor-core)", launch(kern, grid, NWARPS * 32, smem, stream,
         (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)cache, block_table, table_stride, cu_q,
         seqlens_k, (__nv_bfloat16*)out, part_o, part_ml, nh, nkv, page_size, num_pages,
-        scale * 1.4426950408889634f, window, splits, q_below, status));
+        scale * 1.4426950408889634f, window, splits, q_below, rows_above, status));
 }
 
 }  // namespace vapi

@@ -511,7 +511,18 @@ def qk_norm_rope_write(qkv: torch.Tensor, nh: int, nkv: int, d: int,
 
 # "tma": decode steps at head size 64 on the TMA-fed decode kernel; "mma": on the one-warp flash kernel
 DECODE_ATTENTION = os.environ.get("VAPI_DECODE_ATTENTION", "tma")
-DECODE_ATTENTION_SLOTS = 148 * 3          # blocks of the decode kernel that are resident at once
+_decode_limits: Optional[Tuple[int, int]] = None
+
+
+def decode_attention_limits() -> Tuple[int, int]:
+    """(blocks of the decode kernel that the device holds at once, the most slices of the keys that
+    it combines inside the kernel), as the library reports them."""
+    global _decode_limits
+    if _decode_limits is None:
+        lib = _lib("attention")
+        lib.vapi_attention_use_decode_kernel(1 if DECODE_ATTENTION == "tma" else 0)
+        _decode_limits = (int(lib.vapi_decode_attention_slots()) or 148 * 3, int(lib.vapi_decode_attention_cluster()))
+    return _decode_limits
 
 
 def decode_attention_applies(dtype: torch.dtype, d: int, page_size: int, rows: int) -> bool:
@@ -521,23 +532,39 @@ def decode_attention_applies(dtype: torch.dtype, d: int, page_size: int, rows: i
             and rows <= 16)
 
 
+def decode_attention_combines(num_seqs: int, nkv: int, splits: int) -> bool:
+    """Whether the decode kernel combines its slices itself (the library's own rule, restated):
+    at most a cluster's worth of slices, and the whole grid resident at once."""
+    slots, cluster = decode_attention_limits()
+    return 1 < splits <= cluster and num_seqs * nkv * splits <= slots
+
+
 def attention_splits(num_seqs: int, max_q: int, max_k: int, nh: int, nkv: int, decode_kernel: bool = False) -> int:
     """How many blocks share the keys of one row tile: 1 unless the step is so small that
     the device would sit idle (decode of few sequences over long contexts).  A block of the
     one-warp flash kernel has 48 KB of shared memory, so 4 fit on an SM: aim at one full wave of
-    148 x 4 blocks, each with at least 128 keys.  The decode kernel has three blocks of four
-    consumer warps on an SM: one wave of them while the step is small, and once there are more
-    (sequence, kv head) pairs than half a wave, slices fine enough for two waves or more, so that
-    the last blocks do not run alone."""
+    148 x 4 blocks, each with at least 128 keys.
+
+    The decode kernel (measured at head size 64, 8 kv heads, context 4096 and 32768): while the
+    (sequence, kv head) pairs are fewer than two blocks per SM, slices up to that many blocks, and
+    no more than the kernel combines itself unless a slice would then be longer than 32 tiles and
+    there would be fewer blocks than SMs;
+    a step with more pairs than the device holds blocks is cut for about four rounds of blocks, so
+    that the last ones do not run alone."""
     n_rep = nh // nkv
     rows = max_q * n_rep
     tiles = -(-rows // (16 if rows <= 16 else 64))
     blocks = max(1, num_seqs * nkv * tiles)
     if decode_kernel:
         key_tiles = max(1, -(-max_k // 64))
-        slots = DECODE_ATTENTION_SLOTS
-        want = slots // blocks if 2 * blocks <= slots else -(-2 * slots // blocks)
-        return max(1, min(want, max(1, key_tiles // 2), 32))
+        slots, cluster = decode_attention_limits()
+        by_len = max(1, key_tiles // 2)
+        if blocks > slots:
+            return max(1, min(-(-4 * slots // blocks), by_len, 32))
+        want = max(1, int(round(2 * slots / 3 / blocks)))
+        if want > cluster and (key_tiles <= 32 * cluster or 3 * blocks * cluster >= slots):
+            want = cluster
+        return max(1, min(want, by_len, 32))
     if rows > 16 and blocks >= 148:
         return 1
     want = max(1, 592 // blocks)
@@ -581,15 +608,20 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tenso
         part_o = torch.empty((n * nh * splits * d,), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n * nh * splits * 2,), dtype=torch.float32, device=q.device)
     lib = _lib("attention")
+    decode_attention_limits()             # (also tells the library whether the decode kernel is in use)
     # how many kernels the library launches (its own rule, restated for the launch count): the
-    # tcgen05 kernel takes steps with prompt portions, beside the flash kernel in a mixed step
+    # tcgen05 kernel takes steps with prompt portions, beside the flash kernel and the decode kernel in a mixed step
     tc = impl == "tcgen05" or (impl == "auto" and q.dtype == torch.bfloat16 and d == 64 and page_size % 64 == 0
                                and splits == 1 and max_q >= 64 and q_row_stride % 8 == 0 and scale > 0)
-    launches = (1 if impl == "tcgen05" or num_seqs == 1 else 2) if tc else (2 if splits > 1 else 1)
+    launches = (1 if impl == "tcgen05" or num_seqs == 1 else (3 if nh // nkv <= 16 and DECODE_ATTENTION == "tma" else 2)) \
+        if tc else (2 if splits > 1 else 1)
+    if (impl == "decode" or (impl == "auto" and decode_attention_applies(q.dtype, d, page_size, max_q * (nh // nkv)))) \
+            and decode_attention_combines(num_seqs, nkv, splits):
+        launches = 1                      # the decode kernel's slices combine among themselves
+    elif (not tc and impl == "auto" and DECODE_ATTENTION == "tma" and max_q * (nh // nkv) > 16
+            and decode_attention_applies(q.dtype, d, page_size, nh // nkv)):
+        launches += 1                     # short portions on the flash kernel, decode tokens on the decode kernel
     code = {"auto": 0, "general": 1, "tensor_core": 2, "tcgen05": 3, "decode": 4}[impl]
-    if (impl == "auto" and DECODE_ATTENTION != "tma" and q.dtype == torch.bfloat16 and d == 64 and page_size % 64 == 0
-            and max_q * (nh // nkv) <= 16):
-        code = 2                          # keep decode steps on the one-warp flash kernel
     _check(lib, lib.vapi_paged_attention(
         _p(q), ctypes.c_longlong(q_row_stride), _p(cache_layer), _dt(q), _p(block_table),
         block_table.stride(0), _p(cu_q), _p(seqlens_k), _p(out), _p(part_o), _p(part_ml), n, num_seqs,
