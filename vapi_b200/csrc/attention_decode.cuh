@@ -37,6 +37,9 @@ constexpr int FD_TILE_BYTES = FD_BK * FD_HD * 2;           // one K (or V) tile
 #define FD_STAGES_N 4
 #endif
 constexpr int FD_STAGES = FD_STAGES_N;
+#ifndef FD_MIN_BLOCKS_N
+#define FD_MIN_BLOCKS_N 3
+#endif
 constexpr size_t FD_SMEM = (size_t)FD_STAGES * 2 * FD_TILE_BYTES + 1024;     // + room to align to the swizzle's 1024 bytes
 static_assert(FD_STAGES * 2 * FD_TILE_BYTES >= (FD_CWARPS + 1) * FD_MAX_ROWS * FD_HD * 4, "the merge reuses the stages");
 
@@ -73,7 +76,7 @@ __device__ __forceinline__ float4 fd_peer_f32x4(unsigned addr) {
 // thread-block cluster; each leaves its partial result in its own shared memory and, after a
 // cluster barrier, they share out the rows' final sums among themselves (slice sp is rank sp).
 template <bool CLUSTER>
-__global__ void __launch_bounds__(FD_THREADS, 3)
+__global__ void __launch_bounds__(FD_THREADS, FD_MIN_BLOCKS_N)
 flash_decode_kernel(const __grid_constant__ CUtensorMap tm_kv, const FdParams p) {
     extern __shared__ unsigned char fd_smem_raw[];
     unsigned char* sKV = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fd_smem_raw) + 1023) & ~(uintptr_t)1023);

@@ -71,21 +71,41 @@ sample_rows_kernel(const float* __restrict__ logits, int vocab, long long row_st
     const int md = mode ? mode[row] : 1;
     if (md == 0) return;
     const float* l = logits + (size_t)row * row_stride;
-    const unsigned per = ((unsigned)vocab + slices - 1) / slices;
-    const unsigned lo = slice * per, hi = min((unsigned)vocab, lo + per);
+    // a slice is a multiple of 4 entries, so that an aligned row is read in 16-byte pieces
+    const unsigned per = ((((unsigned)vocab + slices - 1) / slices) + 3u) & ~3u;
+    const unsigned lo = min((unsigned)vocab, slice * per), hi = min((unsigned)vocab, lo + per);
     float bv = -INFINITY;
     unsigned bi = 0xffffffffu;
+    const bool vec = (reinterpret_cast<uintptr_t>(l) & 15) == 0;
+    const unsigned hi4 = vec ? lo + ((hi - lo) & ~3u) : lo;      // [lo, hi4) in pieces of 4, [hi4, hi) one by one
     if (md == 1) {
-        for (unsigned i = lo + threadIdx.x; i < hi; i += blockDim.x) arg_better(bv, bi, l[i], i);
+#pragma unroll 4
+        for (unsigned i = lo + 4 * threadIdx.x; i < hi4; i += 4 * blockDim.x) {
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(l + i));
+            arg_better(bv, bi, v.x, i);
+            arg_better(bv, bi, v.y, i + 1);
+            arg_better(bv, bi, v.z, i + 2);
+            arg_better(bv, bi, v.w, i + 3);
+        }
+        for (unsigned i = hi4 + threadIdx.x; i < hi; i += blockDim.x) arg_better(bv, bi, l[i], i);
     } else {
         const float it = inv_t[row];
         const unsigned long long key = mix64(seeds[row] ^ mix64(draws[row] + 0x9E3779B97F4A7C15ULL));
-        for (unsigned i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        auto noisy = [&](float x, unsigned i) {
             const unsigned long long h = mix64(key + (unsigned long long)i * 0xBF58476D1CE4E5B9ULL);
             const float u = ((float)(h >> 40) + 0.5f) * (1.0f / 16777216.0f);
             const float g = -logf(-logf(u));
-            arg_better(bv, bi, l[i] * it + g, i);
+            arg_better(bv, bi, x * it + g, i);
+        };
+#pragma unroll 2
+        for (unsigned i = lo + 4 * threadIdx.x; i < hi4; i += 4 * blockDim.x) {
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(l + i));
+            noisy(v.x, i);
+            noisy(v.y, i + 1);
+            noisy(v.z, i + 2);
+            noisy(v.w, i + 3);
         }
+        for (unsigned i = hi4 + threadIdx.x; i < hi; i += blockDim.x) noisy(l[i], i);
     }
     block_argmax(bv, bi, sv, si);
     if (slices == 1) {

@@ -703,8 +703,8 @@ def sample_rows(logits: torch.Tensor, mode: Optional[torch.Tensor] = None,
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     # few rows over a large vocabulary: cut each row into slices so that more than `rows` blocks work
     slices = 1
-    if rows < 148 and vocab >= 8192:
-        slices = max(1, min(32, 148 // rows, vocab // 4096))
+    if rows < 592 and vocab >= 8192:
+        slices = max(1, min(32, 592 // rows, vocab // 2048))
     part_v = part_i = counters = None
     if slices > 1:
         part_v, part_i, counters = _sample_scratch(logits.device, rows, slices)
