@@ -166,6 +166,31 @@ def test_python_entry_point(tiny_dirs, plain_kernels):
     assert out[0].finish_reason == "length" and out[0].prompt_tokens == 3
 
 
+def test_python_entry_point_raises_when_a_step_failed(tiny_dirs, plain_kernels):
+    from vapi_b200 import LLM
+    llm = LLM(tiny_dirs["A"], dtype="f32", device="cpu", num_blocks=16, page_size=16, max_concurrent_seqs=4,
+              max_batched_tokens=64, max_context=128, cuda_graphs=False)
+    real, calls = llm.engine.step_fn, {"n": 0}
+
+    def flaky(plan):
+        calls["n"] += 1
+        if calls["n"] == 2:
+            raise RuntimeError("injected")
+        return real(plan)
+
+    llm.engine.step_fn = flaky
+    prompts = _prompts(TINY_A, 5, [3, 12])
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    with pytest.raises(RuntimeError, match="2 of 2 requests ended in a failed step: RuntimeError: injected"):
+        llm.generate(prompts, sp)
+    # the engine goes on; a caller that wants the failed completions themselves can have them
+    plain = plain_lfm2.PlainLfm2(tiny_dirs["A"])
+    assert [c.tokens for c in llm.generate(prompts, sp)] == [plain.greedy(p, 5) for p in prompts]
+    calls["n"] = 0
+    out = llm.generate(prompts, sp, raise_on_error=False)
+    assert [c.finish_reason for c in out] == ["error", "error"]
+
+
 # ---- the sampler's host path -------------------------------------------------------------
 def test_host_sampler_truncations():
     logits = np.array([0.0, 3.0, 2.9, -50.0, 1.0], dtype=np.float32)

@@ -107,6 +107,27 @@ def test_temperature_sampling_is_seeded_and_batch_independent(tiny_dirs):
     assert one[0].tokens == greedy[0].tokens
 
 
+def test_the_collector_stays_out_of_graph_capture(tiny_dirs):
+    """Freeing another runner's graphs (garbage in reference cycles dies whenever the collector
+    happens to run) is not permitted while a stream captures and would lose the capture: the
+    collector runs before a capture and is off inside it."""
+    import gc
+    from vapi_b200 import LLM, SamplingParams
+    llm = LLM(tiny_dirs["B"], dtype="bf16", num_blocks=24, max_concurrent_seqs=4, max_batched_tokens=64, max_context=256)
+    real, seen = llm.runner.forward, []
+
+    def spy(ctx):
+        if torch.cuda.is_current_stream_capturing():
+            seen.append(gc.isenabled())
+        return real(ctx)
+
+    llm.runner.forward = spy
+    out = llm.generate(_prompts(TINY_B, 4, [5, 9]), SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    assert all(len(c.tokens) == 6 for c in out)
+    assert seen and not any(seen), "the decode graph was captured, with the collector off"
+    assert gc.isenabled()
+
+
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
 def test_running_one_step_ahead_changes_no_token(tiny_dirs, dtype):
     """The engine enqueues a step before it has read the tokens of the step before it.  With

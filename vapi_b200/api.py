@@ -75,12 +75,16 @@ class LLM:
 
     def generate(self, prompts: Sequence[Sequence[int]],
                  params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
-                 on_token=None) -> List[Completion]:
+                 on_token=None, raise_on_error: bool = True) -> List[Completion]:
         """Generate for every prompt (lists of token ids) with continuous batching; results
         come back in the order of ``prompts``.  With ``n`` above 1 a prompt gets that many
         completions, one after the other in the result (``Completion.index`` says which); each is
         a request of its own, seeded ``seed + index`` when a seed is given.  (The reference forks
-        them from one prefill through its prefix cache, which this engine does not have.)"""
+        them from one prefill through its prefix cache, which this engine does not have.)
+
+        A step that fails ends the requests in flight with the finish reason ``"error"`` and leaves
+        the engine usable, as in the reference; this call then raises with the step's message,
+        unless ``raise_on_error`` is false, in which case those completions come back as they are."""
         if params is None:
             params = SamplingParams()
         plist = [params] * len(prompts) if isinstance(params, SamplingParams) else list(params)
@@ -100,6 +104,9 @@ class LLM:
         for rid, i in ids:
             f = done[rid]
             out.append(Completion(rid, f.prompt_tokens, f.tokens, f.reason.value, f.preemptions, i, f.logprobs))
+        if raise_on_error and any(c.finish_reason == "error" for c in out):
+            failed = sum(c.finish_reason == "error" for c in out)
+            raise RuntimeError(f"{failed} of {len(out)} requests ended in a failed step: {self.engine.last_error}")
         return out
 
 

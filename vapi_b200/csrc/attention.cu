@@ -397,6 +397,8 @@ VAPI_EXPORT int vapi_paged_attention(const void* q, long long q_row_stride, cons
 // number of key slices that it combines inside the kernel.
 VAPI_EXPORT int vapi_decode_attention_slots() { return flash_decode_slots(); }
 VAPI_EXPORT int vapi_decode_attention_cluster() { return FD_MAX_CLUSTER; }
+// whether the decode kernel would combine the slices of such a step itself (1) or leave them to the combine kernel (0)
+VAPI_EXPORT int vapi_decode_attention_combines(int num_seqs, int nkv, int splits) { return flash_decode_combines(num_seqs, nkv, splits) ? 1 : 0; }
 
 // ---------------------------------------------------------------------------------------------
 // The same attention with its scratch inside the library (see attention_noalloc.h for who needs

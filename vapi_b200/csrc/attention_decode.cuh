@@ -402,7 +402,28 @@ static int flash_decode_slots() {
 // is resident at once.  With more blocks than that, clusters (which start together and leave
 // together) keep places occupied that single blocks would give up as they finish.
 static bool flash_decode_combines(int num_seqs, int nkv, int splits) {
-    return splits > 1 && splits <= FD_MAX_CLUSTER && (long long)num_seqs * nkv * splits <= flash_decode_slots();
+    if (splits <= 1 || splits > FD_MAX_CLUSTER || (long long)num_seqs * nkv * splits > flash_decode_slots()) return false;
+    // a cluster of this size must fit the device at all (asked once per size)
+    static int fits[FD_MAX_CLUSTER + 1] = {};              // 0 unknown, 1 yes, -1 no
+    if (fits[splits] == 0) {
+        cudaFuncSetAttribute(flash_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1, 1, (unsigned)splits);
+        cfg.blockDim = dim3(FD_THREADS);
+        cfg.dynamicSmemBytes = FD_SMEM;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = (unsigned)splits;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, flash_decode_kernel<true>, &cfg);
+        if (e != cudaSuccess) cudaGetLastError();
+        fits[splits] = (e == cudaSuccess && clusters > 0) ? 1 : -1;
+    }
+    return fits[splits] == 1;
 }
 
 static int launch_flash_decode(const void* q, long long q_row_stride, const void* cache, const int* block_table,

@@ -270,8 +270,19 @@ class ModelRunner:
         graph = torch.cuda.CUDAGraph()
         ctx.pos = {}
         before = ops.launch_count
-        with torch.cuda.graph(graph):
-            logits = self.forward(ctx)
+        # The collector must not run inside the capture: if it frees another runner's graphs there
+        # (objects in reference cycles die whenever it happens to run), releasing their memory is an
+        # operation that a capturing stream does not permit, and this capture is lost with it.
+        import gc
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                logits = self.forward(ctx)
+        finally:
+            if was_enabled:
+                gc.enable()
         return graph, logits, ops.launch_count - before
 
     def _decode_splits(self, B: int) -> int:

@@ -533,10 +533,12 @@ def decode_attention_applies(dtype: torch.dtype, d: int, page_size: int, rows: i
 
 
 def decode_attention_combines(num_seqs: int, nkv: int, splits: int) -> bool:
-    """Whether the decode kernel combines its slices itself (the library's own rule, restated):
-    at most a cluster's worth of slices, and the whole grid resident at once."""
-    slots, cluster = decode_attention_limits()
-    return 1 < splits <= cluster and num_seqs * nkv * splits <= slots
+    """Whether the decode kernel combines its slices itself (at most a cluster's worth of slices,
+    the whole grid resident at once, and a cluster of that size fits the device): the library's answer."""
+    if splits <= 1:
+        return False
+    decode_attention_limits()
+    return bool(_lib("attention").vapi_decode_attention_combines(num_seqs, nkv, splits))
 
 
 def attention_splits(num_seqs: int, max_q: int, max_k: int, nh: int, nkv: int, decode_kernel: bool = False) -> int:
