@@ -341,6 +341,84 @@ def test_decode_attention_ignores_garbage_beyond_the_sequence(ops):
         torch.testing.assert_close(got.cpu().float(), want.float(), atol=3e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("nh,nkv,page,splits", [(8, 2, 64, 1), (8, 2, 64, 3), (32, 8, 128, 5), (6, 2, 64, 2), (4, 4, 64, 1),
+                                                (16, 1, 256, 4), (8, 2, 64, 12)])
+@pytest.mark.parametrize("norm,rope,write", [(True, True, True), (False, True, True), (True, False, True), (True, True, False)])
+def test_decode_attention_fused_with_norm_rope_and_cache_write(ops, nh, nkv, page, splits, norm, rope, write):
+    """One kernel against the two it stands for, on the same inputs: the same output and the same cache, bit for
+    bit, and both close to the plain functions.  Sequences end at and around tile and page edges, some bring
+    several tokens (which may lie in two tiles, and so in two slices), the first token of a sequence included."""
+    torch.manual_seed(5)
+    d, n_rep = 64, nh // nkv
+    tokens = 16 // n_rep
+    lens = [(1, 1), (1, 64), (1, 65), (1, 128), (1, 129), (1, 700), (1, 1000), (1, 63)]
+    if tokens >= 2:
+        lens += [(2, 65), (tokens, 400), (tokens, tokens), (2, 129), (min(tokens, 3), 66)]
+    S, n = len(lens), sum(a for a, _ in lens)
+    need = [-(-k // page) for _, k in lens]
+    num_pages = sum(need) + 2
+    perm = torch.randperm(num_pages).tolist()
+    table = torch.zeros((S, max(need) + 1), dtype=torch.int32)
+    it = iter(perm)
+    for s_ in range(S):
+        for j in range(need[s_]):
+            table[s_, j] = next(it)
+    cache = torch.randn(num_pages, 2, nkv, page, d).to(torch.bfloat16)
+    qkv = torch.randn(n, (nh + 2 * nkv) * d).to(torch.bfloat16)
+    qw = (1 + 0.2 * torch.randn(d)) if norm else None
+    kw = (1 + 0.2 * torch.randn(d)) if norm else None
+    pos, slots = [], []
+    for s_, (a, b) in enumerate(lens):
+        for j in range(a):
+            p_ = b - a + j
+            pos.append(p_)
+            slots.append(int(table[s_, p_ // page]) * page + p_ % page)
+    cos = sin = None
+    if rope:
+        ang = torch.tensor(pos, dtype=torch.float32)[:, None] * (1e4 ** (-torch.arange(0, d, 2).float() / d))[None]
+        cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    cu = torch.tensor([0] + list(itertools.accumulate(a for a, _ in lens)), dtype=torch.int32)
+    kl = torch.tensor([b for _, b in lens], dtype=torch.int32)
+    sm = torch.tensor(slots, dtype=torch.int32)
+    max_q, max_k, scale = max(a for a, _ in lens), max(b for _, b in lens), 0.125
+    # the plain functions
+    p_qkv, p_cache = qkv.clone(), cache.clone()
+    plain_ops.qk_norm_rope_write(p_qkv, nh, nkv, d, qw, kw, 1e-5, cos, sin, d, p_cache if write else None, sm)
+    want = plain_ops.paged_attention(p_qkv, (nh + 2 * nkv) * d, p_cache, table, cu, kl, n, S, max_q, max_k, nh, nkv, d, scale)
+    # two kernels
+    g_qkv, g_cache = dev(qkv.clone()), dev(cache.clone())
+    ops.qk_norm_rope_write(g_qkv, nh, nkv, d, dev(qw), dev(kw), 1e-5, dev(cos), dev(sin), d, g_cache if write else None, dev(sm))
+    two = ops.paged_attention(g_qkv, (nh + 2 * nkv) * d, g_cache, dev(table), dev(cu), dev(kl), n, S, max_q, max_k,
+                              nh, nkv, d, scale, 0, splits, None, "decode")
+    # one kernel
+    f_qkv, f_cache = dev(qkv.clone()), dev(cache.clone())
+    before = ops.launch_count
+    one = ops.decode_attention_fused(f_qkv, nh, nkv, d, dev(qw), dev(kw), 1e-5, dev(cos), dev(sin), f_cache, write,
+                                     dev(table), dev(cu), dev(kl), n, S, max_q, max_k, scale, 0, splits)
+    assert ops.launch_count - before == (1 if splits == 1 or ops.decode_attention_combines(S, nkv, splits) else 2)
+    assert torch.equal(f_qkv.cpu(), qkv), "qkv is left as it was"
+    assert torch.equal(f_cache.cpu().view(torch.int16), g_cache.cpu().view(torch.int16)), "the same cache, bit for bit"
+    assert torch.equal(one.cpu().view(torch.int16), two.cpu().view(torch.int16)), "the same output, bit for bit"
+    torch.testing.assert_close(one.cpu().float(), want.float(), atol=3e-2, rtol=3e-2)
+    if write:
+        torch.testing.assert_close(f_cache.cpu().float(), p_cache.float(), atol=2e-2, rtol=2e-2)
+    else:
+        assert torch.equal(f_cache.cpu().view(torch.int16), cache.view(torch.int16)), "a reader leaves the cache alone"
+
+
+def test_decode_attention_fused_refuses_what_it_cannot_do(ops):
+    qkv = torch.zeros(1, (4 + 4) * 128, dtype=torch.bfloat16, device="cuda")
+    cache = torch.zeros(2, 2, 2, 64, 128, dtype=torch.bfloat16, device="cuda")
+    z = torch.zeros(1, 1, dtype=torch.int32, device="cuda")
+    cu = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+    kl = torch.tensor([1], dtype=torch.int32, device="cuda")
+    with pytest.raises(ops.KernelError, match="needs head_dim 64"):
+        ops.decode_attention_fused(qkv, 4, 2, 128, None, None, 0.0, None, None, cache, True, z, cu, kl, 1, 1, 1, 1, 0.1)
+    assert not ops.decode_attention_fused_applies(torch.bfloat16, 64, 64, 4, 32)      # a partial rotation
+    assert not ops.decode_attention_fused_applies(torch.bfloat16, 64, 64, 17, 64)
+    assert ops.decode_attention_fused_applies(torch.bfloat16, 64, 128, 16, None)
+
+
 def test_decode_attention_is_what_a_decode_step_gets_and_refuses_what_it_cannot_do(ops):
     before = ops.launch_count
     _attention_case(ops, dtype=torch.bfloat16, nh=32, nkv=8, d=64, page=64, lens=[(1, 500), (1, 64), (4, 95)], splits=1)

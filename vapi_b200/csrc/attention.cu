@@ -400,6 +400,47 @@ VAPI_EXPORT int vapi_decode_attention_cluster() { return FD_MAX_CLUSTER; }
 // whether the decode kernel would combine the slices of such a step itself (1) or leave them to the combine kernel (0)
 VAPI_EXPORT int vapi_decode_attention_combines(int num_seqs, int nkv, int splits) { return flash_decode_combines(num_seqs, nkv, splits) ? 1 : 0; }
 
+// A decode step's attention with what precedes it: qkv [n][(nh + 2 nkv) * 64] is the fused product as
+// it was left; the kernel applies the per-head RMSNorm (qw, kw: [64] or null) and rotate-half RoPE
+// (cosr, sinr: [n][32] or null) to q and to the new keys, writes the new keys and values into the
+// cache (write_kv; 0 for a layer that reads another layer's cache) and attends.  bfloat16, head_dim
+// 64, a page size that is a multiple of 64, at most 16 rows per sequence and kv head.  qkv is left
+// as it was.  splits > 1: scratch as for vapi_paged_attention.
+VAPI_EXPORT int vapi_decode_attention_fused(const void* qkv, const float* qw, const float* kw, float eps,
+                                            const float* cosr, const float* sinr, void* cache, int write_kv,
+                                            const int* block_table, int table_stride, const int* cu_q,
+                                            const int* seqlens_k, void* out, float* part_o, float* part_ml,
+                                            int n, int num_seqs, int max_q, int nh, int nkv, int d,
+                                            int page_size, int num_pages, float scale, int window, int splits,
+                                            int* status, cudaStream_t stream) {
+    if (n <= 0 || num_seqs <= 0 || max_q <= 0) return 0;
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0)
+        return fail(-1, "decode_attention_fused: %d heads are not a multiple of %d kv heads", nh, nkv);
+    if (d != FD_HD || page_size <= 0 || page_size % FD_BK != 0 || num_pages <= 0 || (long long)max_q * (nh / nkv) > FD_MAX_ROWS)
+        return fail(-3, "decode_attention_fused: needs head_dim 64, a page size that is a multiple of 64 and at most 16 rows "
+                        "per sequence and kv head (got head_dim %d, page size %d, %lld rows)", d, page_size,
+                    (long long)max_q * (nh / nkv));
+    if ((cosr == nullptr) != (sinr == nullptr)) return fail(-1, "decode_attention_fused: cos and sin come together");
+    if (splits < 1) splits = 1;
+    if (splits > 32) return fail(-1, "decode_attention_fused: %d splits are more than 32", splits);
+    if (splits > 1 && (!part_o || !part_ml)) return fail(-1, "decode_attention_fused: %d splits need scratch buffers", splits);
+    if (((uintptr_t)out & 15) != 0) return fail(-1, "decode_attention_fused: the output is not 16-byte aligned");
+    FdParams f = {};
+    f.write_kv = write_kv ? 1 : 0; f.qw = qw; f.kw = kw; f.eps = eps; f.cosr = cosr; f.sinr = sinr;
+    const long long stride = (long long)(nh + 2 * nkv) * d;
+    int rc = launch_flash_decode(qkv, stride, cache, block_table, table_stride, cu_q, seqlens_k, out, part_o, part_ml,
+                                 num_seqs, nh, nkv, page_size, num_pages, scale, window, splits, status, stream, true, &f);
+    if (rc != 0) return rc;
+    if (splits > 1 && !flash_decode_combines(num_seqs, nkv, splits)) {
+        const long long rows = (long long)n * nh;
+        const int wpb = 4;
+        const long long blocks = (rows + wpb - 1) / wpb;
+        return check_launch("attention_combine", launch(attention_combine_kernel<__nv_bfloat16>, (unsigned)blocks, wpb * 32, 0, stream,
+                                                        (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, rows, d, splits));
+    }
+    return 0;
+}
+
 // ---------------------------------------------------------------------------------------------
 // The same attention with its scratch inside the library (see attention_noalloc.h for who needs
 // this and what it costs).  In host code the name of a __device__ array is only a handle: the

@@ -51,7 +51,29 @@ struct FdParams {
     int nh, nkv, page_size, num_pages;
     float scale_log2e; int window, splits;
     int* status;
+    // fused mode (fused != 0): q points at this step's fused qkv rows [n][(nh + 2 nkv) * 64] as the product
+    // left them; the kernel norms and rotates q itself and, with write_kv, norms and rotates the new keys,
+    // writes them and the new values into the cache and into the tiles it has in shared memory
+    int fused, write_kv;
+    const float* qw; const float* kw; float eps;       // per-head RMSNorm weights [64] or null
+    const float* cosr; const float* sinr;              // [n][32] or null
+    __nv_bfloat16* cache;
 };
+
+// eight bfloat16 (16 bytes) to floats and back
+__device__ __forceinline__ void fd_load8(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ uint4 fd_pack8(const float (&v)[8]) {
+    return make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+}
 
 __device__ __forceinline__ void fd_cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -75,7 +97,8 @@ __device__ __forceinline__ float4 fd_peer_f32x4(unsigned addr) {
 // CLUSTER: the blocks of one (sequence, kv head) - its slices of the keys, at most 8 - form a
 // thread-block cluster; each leaves its partial result in its own shared memory and, after a
 // cluster barrier, they share out the rows' final sums among themselves (slice sp is rank sp).
-template <bool CLUSTER>
+// FUSED: q/k norm, RoPE and the cache write of the new tokens happen here too (FdParams::fused).
+template <bool CLUSTER, bool FUSED>
 __global__ void __launch_bounds__(FD_THREADS, FD_MIN_BLOCKS_N)
 flash_decode_kernel(const __grid_constant__ CUtensorMap tm_kv, const FdParams p) {
     extern __shared__ unsigned char fd_smem_raw[];
@@ -83,6 +106,9 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tm_kv, const FdParams p)
     __shared__ __align__(8) unsigned long long bars[2 * FD_STAGES];
     __shared__ float sM[FD_CWARPS][FD_MAX_ROWS], sL[FD_CWARPS][FD_MAX_ROWS];
     __shared__ float xM[FD_MAX_ROWS], xL[FD_MAX_ROWS];          // CLUSTER: this slice's result, read by its peers
+    // fused mode: the rows' queries and the new tokens' keys and values, normed and rotated
+    constexpr int FR = FUSED ? FD_MAX_ROWS : 1;
+    __shared__ __align__(16) __nv_bfloat16 sQ[FR][FD_HD], sKn[FR][FD_HD], sVn[FR][FD_HD];
     __shared__ int failed;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -140,9 +166,9 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tm_kv, const FdParams p)
         int pg_base = -(1 << 30), entry = 0;
         for (int it = 0; it < nt; ++it) {
             const int kt = kt_begin + it, k0 = kt * FD_BK, stage = it % FD_STAGES;
-            if (!waited && kt >= kt_old_end) {
+            if (!waited && kt >= kt_old_end && !(FUSED && p.write_kv)) {
                 pdl_wait();                                           // this step's keys are in the cache now
-                waited = true;
+                waited = true;                                        // (fused and writing: the consumers put them into the tile)
             }
             const int pg = k0 / p.page_size;
             if (pg - pg_base >= 32) {
@@ -171,7 +197,81 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tm_kv, const FdParams p)
         if (!waited) pdl_wait();
     } else {
         // ---- consumers ----
-        pdl_wait();                                                   // q was rotated by the kernel before this one
+        pdl_wait();                                                   // q (or qkv) comes from the kernel before this one
+        if (FUSED) {
+            // Four lanes per item, eight low and eight high elements each, as in the stand-alone kernel
+            // for this (rope.cu), sums in the same order: the rows' queries, then the keys and the values
+            // of the new tokens whose tile belongs to this block.
+            const int sub = threadIdx.x & 3, e = sub * 8;
+            for (int item = threadIdx.x >> 2; item < 3 * FD_MAX_ROWS; item += FD_CWARPS * 8) {
+                const int kind = item / FD_MAX_ROWS, idx = item - kind * FD_MAX_ROWS;     // 0 q, 1 k, 2 v
+                bool active;
+                int tok, col;
+                if (kind == 0) {
+                    active = idx < rows_total;
+                    tok = active ? idx / n_rep : 0;
+                    col = g * n_rep + (active ? idx - tok * n_rep : 0);
+                } else {
+                    const int kt_own = (base_pos + idx) / FD_BK;
+                    active = p.write_kv && idx < qlen && kt_own >= kt_begin && kt_own < kt_end;
+                    tok = active ? idx : 0;
+                    col = kind == 1 ? p.nh + g : p.nh + p.nkv + g;
+                }
+                const __nv_bfloat16* src = p.q + (size_t)(q0 + tok) * p.q_row_stride + (size_t)col * FD_HD;
+                float lo[8], hi[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) lo[i] = hi[i] = 0.f;
+                if (active) {
+                    fd_load8(src + e, lo);
+                    fd_load8(src + FD_HD / 2 + e, hi);
+                }
+                const float* w = kind == 0 ? p.qw : (kind == 1 ? p.kw : nullptr);
+                float inv = 1.f;
+                if (p.qw || p.kw) {                                   // (uniform: every lane takes part in the shuffles)
+                    float ss = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) ss += lo[i] * lo[i] + hi[i] * hi[i];
+                    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+                    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+                    inv = rsqrtf(ss / (float)FD_HD + p.eps);
+                }
+                if (!active) continue;
+                if (w) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        lo[i] = lo[i] * inv * w[e + i];
+                        hi[i] = hi[i] * inv * w[FD_HD / 2 + e + i];
+                    }
+                }
+                if (kind != 2 && p.cosr) {
+                    const float* c = p.cosr + (size_t)(q0 + tok) * (FD_HD / 2) + e;
+                    const float* sn = p.sinr + (size_t)(q0 + tok) * (FD_HD / 2) + e;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float a = lo[i], b = hi[i];
+                        lo[i] = a * c[i] - b * sn[i];
+                        hi[i] = b * c[i] + a * sn[i];
+                    }
+                }
+                const uint4 plo = fd_pack8(lo), phi = fd_pack8(hi);
+                __nv_bfloat16* dst = kind == 0 ? sQ[FUSED ? idx : 0] : (kind == 1 ? sKn[FUSED ? idx : 0] : sVn[FUSED ? idx : 0]);
+                *reinterpret_cast<uint4*>(dst + e) = plo;
+                *reinterpret_cast<uint4*>(dst + FD_HD / 2 + e) = phi;
+                if (kind != 0) {
+                    // the cache gets the new token too (later steps read it from there)
+                    const int pos = base_pos + idx;
+                    const int page = p.block_table[(size_t)s * p.table_stride + pos / p.page_size];
+                    if (page < 0 || page >= p.num_pages) {
+                        if (sub == 0 && p.status) atomicExch(p.status, 2);
+                    } else {
+                        __nv_bfloat16* cd = p.cache + ((((size_t)page * 2 + (kind == 1 ? 0 : 1)) * p.nkv + g) * p.page_size + pos % p.page_size) * FD_HD;
+                        *reinterpret_cast<uint4*>(cd + e) = plo;
+                        *reinterpret_cast<uint4*>(cd + FD_HD / 2 + e) = phi;
+                    }
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(FD_CWARPS * 32) : "memory");       // the consumers only
+        }
         unsigned qf[FD_HD / 16][4];
 #pragma unroll
         for (int kk = 0; kk < FD_HD / 16; ++kk) {
@@ -179,7 +279,8 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tm_kv, const FdParams p)
             for (int h = 0; h < 2; ++h) {
                 unsigned lo = 0u, hi = 0u;
                 if (row_ok[h]) {
-                    const __nv_bfloat16* src = p.q + (size_t)(q0 + row_tok[h]) * p.q_row_stride + (size_t)row_head[h] * FD_HD + kk * 16 + 2 * tq;
+                    const __nv_bfloat16* src = FUSED ? &sQ[FUSED ? gq + 8 * h : 0][kk * 16 + 2 * tq]
+                                                       : p.q + (size_t)(q0 + row_tok[h]) * p.q_row_stride + (size_t)row_head[h] * FD_HD + kk * 16 + 2 * tq;
                     lo = *reinterpret_cast<const unsigned*>(src);
                     hi = *reinterpret_cast<const unsigned*>(src + 8);
                 }
@@ -197,6 +298,23 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tm_kv, const FdParams p)
             if (!skip) {
                 const __nv_bfloat16* ks = reinterpret_cast<const __nv_bfloat16*>(sKV + (size_t)stage * 2 * FD_TILE_BYTES);
                 __nv_bfloat16* vs = reinterpret_cast<__nv_bfloat16*>(sKV + (size_t)stage * 2 * FD_TILE_BYTES + FD_TILE_BYTES);
+                if (FUSED && p.write_kv && k0 + FD_BK > base_pos) {
+                    // new tokens of this tile: their rows in the cache may be older than the copy, so the
+                    // warp that owns a row puts the key and the value in by hand (lanes 0..7 the key's
+                    // eight 16-byte pieces, lanes 8..15 the value's)
+                    const int j_end = min(qlen, k0 + FD_BK - base_pos);
+                    for (int j = max(0, k0 - base_pos); j < j_end; ++j) {
+                        const int r = base_pos + j - k0;
+                        if ((r >> 4) == warp && lane < 16) {
+                            const int c = lane & 7;
+                            const __nv_bfloat16* from = (lane < 8 ? sKn[FUSED ? j : 0] : sVn[FUSED ? j : 0]) + c * 8;
+                            __nv_bfloat16* to = (lane < 8 ? const_cast<__nv_bfloat16*>(ks) : vs) + r * FD_HD + ((c ^ (r & 7)) << 3);
+                            *reinterpret_cast<uint4*>(to) = *reinterpret_cast<const uint4*>(from);
+                        }
+                    }
+                    fence_proxy_async();                              // the stage's next writer is a TMA copy
+                    __syncwarp();
+                }
                 float sc[2][4];
 #pragma unroll
                 for (int i = 0; i < 2; ++i) { sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f; }
@@ -392,8 +510,8 @@ static int flash_decode_slots() {
     if (slots == 0) {
         int dev = 0, sms = 0, per_sm = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-        cudaFuncSetAttribute(flash_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, flash_decode_kernel<false>, FD_THREADS, FD_SMEM) != cudaSuccess) return 0;
+        cudaFuncSetAttribute(flash_decode_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, flash_decode_kernel<false, false>, FD_THREADS, FD_SMEM) != cudaSuccess) return 0;
         slots = sms * per_sm;
     }
     return slots;
@@ -406,7 +524,7 @@ static bool flash_decode_combines(int num_seqs, int nkv, int splits) {
     // a cluster of this size must fit the device at all (asked once per size)
     static int fits[FD_MAX_CLUSTER + 1] = {};              // 0 unknown, 1 yes, -1 no
     if (fits[splits] == 0) {
-        cudaFuncSetAttribute(flash_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
+        cudaFuncSetAttribute(flash_decode_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(1, 1, (unsigned)splits);
         cfg.blockDim = dim3(FD_THREADS);
@@ -419,7 +537,7 @@ static bool flash_decode_combines(int num_seqs, int nkv, int splits) {
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         int clusters = 0;
-        const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, flash_decode_kernel<true>, &cfg);
+        const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, flash_decode_kernel<true, false>, &cfg);
         if (e != cudaSuccess) cudaGetLastError();
         fits[splits] = (e == cudaSuccess && clusters > 0) ? 1 : -1;
     }
@@ -430,7 +548,7 @@ static int launch_flash_decode(const void* q, long long q_row_stride, const void
                                int table_stride, const int* cu_q, const int* seqlens_k, void* out, float* part_o,
                                float* part_ml, int num_seqs, int nh, int nkv, int page_size, int num_pages,
                                float scale, int window, int splits, int* status, cudaStream_t stream,
-                               bool may_combine = true) {
+                               bool may_combine = true, const FdParams* fused = nullptr) {
     if (nkv > 65535 || (long long)num_seqs * splits > 65535)
         return fail(-1, "paged_attention: %d kv heads or %d sequences x %d splits exceed the grid", nkv, num_seqs, splits);
     if (q_row_stride % 2 != 0 || ((uintptr_t)q & 3) != 0 || ((uintptr_t)out & 15) != 0)
@@ -440,8 +558,10 @@ static int launch_flash_decode(const void* q, long long q_row_stride, const void
     if (rc != 0) return rc;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_decode_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_decode_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_decode_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
         if (e != cudaSuccess) return fail(-101, "paged_attention: cannot reserve %zu bytes of shared memory: %s", FD_SMEM, cudaGetErrorString(e));
         attr_set = true;
     }
@@ -450,6 +570,13 @@ static int launch_flash_decode(const void* q, long long q_row_stride, const void
     p.cu_q = cu_q; p.seqlens_k = seqlens_k; p.out = (__nv_bfloat16*)out; p.part_o = part_o; p.part_ml = part_ml;
     p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.num_pages = num_pages; p.scale_log2e = scale * 1.4426950408889634f;
     p.window = window; p.splits = splits; p.status = status;
+    p.fused = 0; p.write_kv = 0; p.qw = p.kw = nullptr; p.eps = 0.f; p.cosr = p.sinr = nullptr; p.cache = nullptr;
+    if (fused) {
+        if (q_row_stride % 8 != 0 || ((uintptr_t)q & 15) != 0)
+            return fail(-1, "paged_attention: the fused decode kernel needs 16-byte aligned qkv rows");
+        p.fused = 1; p.write_kv = fused->write_kv; p.qw = fused->qw; p.kw = fused->kw; p.eps = fused->eps;
+        p.cosr = fused->cosr; p.sinr = fused->sinr; p.cache = (__nv_bfloat16*)const_cast<void*>(cache);
+    }
     dim3 grid(1, nkv, num_seqs * splits);
     if (may_combine && flash_decode_combines(num_seqs, nkv, splits)) {
         // the slices of one (sequence, kv head) are a cluster along z and combine among themselves
@@ -467,9 +594,13 @@ static int launch_flash_decode(const void* q, long long q_row_stride, const void
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = pdl_enabled() ? 2 : 1;
-        return check_launch("paged_attention (decode, cluster)", cudaLaunchKernelEx(&cfg, flash_decode_kernel<true>, map, p));
+        return check_launch("paged_attention (decode, cluster)",
+                            fused ? cudaLaunchKernelEx(&cfg, flash_decode_kernel<true, true>, map, p)
+                                  : cudaLaunchKernelEx(&cfg, flash_decode_kernel<true, false>, map, p));
     }
-    return check_launch("paged_attention (decode)", launch(flash_decode_kernel<false>, grid, FD_THREADS, FD_SMEM, stream, map, p));
+    return check_launch("paged_attention (decode)",
+                        fused ? launch(flash_decode_kernel<false, true>, grid, FD_THREADS, FD_SMEM, stream, map, p)
+                              : launch(flash_decode_kernel<false, false>, grid, FD_THREADS, FD_SMEM, stream, map, p));
 }
 
 }  // namespace vapi

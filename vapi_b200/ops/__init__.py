@@ -632,6 +632,75 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tenso
     return out
 
 
+#: whether decode steps run q/k norm, RoPE and the cache write inside the decode attention kernel.  Off
+#: unless asked for: it gives the same bits with one launch fewer per attention layer, but measured no
+#: faster (batch 8) to 1 % slower (batch 1 and 64) than the two kernels, whose first one hides behind
+#: the product before it.
+FUSED_DECODE_ROPE = os.environ.get("VAPI_FUSED_DECODE_ROPE", "0") == "1"
+
+
+def decode_attention_fused_applies(dtype: torch.dtype, d: int, page_size: int, rows: int, rot: Optional[int]) -> bool:
+    """Whether :func:`decode_attention_fused` takes a step of this shape (``rot``: the rotated width, or
+    None without a position encoding)."""
+    return decode_attention_applies(dtype, d, page_size, rows) and (rot is None or rot == d)
+
+
+def decode_attention_fused(qkv: torch.Tensor, nh: int, nkv: int, d: int,
+                           q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                           cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                           cache_layer: torch.Tensor, write_kv: bool, block_table: torch.Tensor,
+                           cu_q: torch.Tensor, seqlens_k: torch.Tensor, n: int, num_seqs: int, max_q: int,
+                           max_k: int, scale: float, window: int = 0, splits: Optional[int] = None,
+                           status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """:func:`qk_norm_rope_write` and :func:`paged_attention` of a decode step in one kernel: per-head
+    RMSNorm and rotate-half RoPE of q and of the new keys, the new keys and values written to
+    ``cache_layer`` (``write_kv``) at the places the block table gives for the sequences' last
+    ``q`` positions, and attention over the cache.  ``qkv`` [n, (nh+2nkv)*d] is left as it was.
+    bfloat16, head_dim 64, pages of 64n, at most 16 rows per sequence and kv head.  Gives exactly
+    what the two calls give."""
+    _cuda(qkv, q_weight, k_weight, cos, sin, cache_layer, block_table, cu_q, seqlens_k)
+    _contig(qkv, "qkv")
+    _contig(cache_layer, "cache layer")
+    _f32(q_weight, "q norm weight")
+    _f32(k_weight, "k norm weight")
+    _f32(cos, "cos")
+    _f32(sin, "sin")
+    _i32(block_table, "block table")
+    _i32(cu_q, "cu_q")
+    _i32(seqlens_k, "seqlens_k")
+    if qkv.dtype != torch.bfloat16 or cache_layer.dtype != torch.bfloat16:
+        raise KernelError("the fused decode attention is for bfloat16")
+    if qkv.shape[0] != n or qkv.shape[1] != (nh + 2 * nkv) * d:
+        raise KernelError(f"qkv is {tuple(qkv.shape)}, expected ({n}, {(nh + 2 * nkv) * d})")
+    if tuple(cache_layer.shape[1:3]) != (2, nkv) or cache_layer.shape[4] != d:
+        raise KernelError(f"cache layer {tuple(cache_layer.shape)} does not fit nkv={nkv} d={d}")
+    if block_table.dim() != 2 or block_table.stride(1) != 1:
+        raise KernelError("block table must be [S, width] with unit inner stride")
+    if cos is not None and (cos.shape != (n, d // 2) or sin is None or sin.shape != cos.shape or not cos.is_contiguous()
+                            or not sin.is_contiguous()):
+        raise KernelError("cos/sin must be contiguous [n, head_dim/2]")
+    for w, name in ((q_weight, "q"), (k_weight, "k")):
+        if w is not None and (w.numel() != d or not w.is_contiguous()):
+            raise KernelError(f"the {name} norm weight must be [head_dim]")
+    num_pages, page_size = cache_layer.shape[0], cache_layer.shape[3]
+    if splits is None:
+        splits = attention_splits(num_seqs, max_q, max_k, nh, nkv, True)
+    out = torch.empty((n, nh * d), dtype=qkv.dtype, device=qkv.device)
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty((n * nh * splits * d,), dtype=torch.float32, device=qkv.device)
+        part_ml = torch.empty((n * nh * splits * 2,), dtype=torch.float32, device=qkv.device)
+    lib = _lib("attention")
+    decode_attention_limits()
+    launches = 1 if splits == 1 or decode_attention_combines(num_seqs, nkv, splits) else 2
+    _check(lib, lib.vapi_decode_attention_fused(
+        _p(qkv), _p(q_weight), _p(k_weight), ctypes.c_float(eps), _p(cos), _p(sin), _p(cache_layer),
+        1 if write_kv else 0, _p(block_table), block_table.stride(0), _p(cu_q), _p(seqlens_k), _p(out),
+        _p(part_o), _p(part_ml), n, num_seqs, max_q, nh, nkv, d, page_size, num_pages, ctypes.c_float(scale),
+        window, splits, _p(status), _stream()), launches)
+    return out
+
+
 def shortconv(h3: torch.Tensor, in_bias: Optional[torch.Tensor], taps: torch.Tensor,
               conv_bias: Optional[torch.Tensor], state_layer: Optional[torch.Tensor],
               state_slots: torch.Tensor, tok_seq: torch.Tensor, cu_q: torch.Tensor,

@@ -94,6 +94,17 @@ class GQAttention(Mixer):
         if self.pos is not None:
             cos, sin = ctx.pos[self.pos]
         grp = cache.group
+        n_rep = nh // nkv
+        if (ops.FUSED_DECODE_ROPE and qkv.is_cuda and cache.tensor is not None
+                and ops.decode_attention_fused_applies(qkv.dtype, d, cache.tensor.shape[3], ctx.max_q * n_rep,
+                                                       self.rot_dim if cos is not None else None)
+                and (cos is None or (cos.is_contiguous() and sin.is_contiguous()))):
+            # a decode step: norm, rotation and the cache write ride in the attention kernel
+            return ops.decode_attention_fused(qkv, nh, nkv, d, self.q_w, self.k_w,
+                                              self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, cos, sin,
+                                              cache.tensor, cache.write, grp.block_table, ctx.cu_q, ctx.seqlens_k,
+                                              ctx.n, ctx.num_seqs, ctx.max_q, ctx.max_k, self.scale, self.window,
+                                              ctx.attention_splits, ctx.status)
         ops.qk_norm_rope_write(qkv, nh, nkv, d, self.q_w, self.k_w,
                                self.qk_norm_eps if self.qk_norm_eps is not None else 0.0,
                                cos, sin, self.rot_dim,
