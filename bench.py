@@ -133,7 +133,32 @@ def model_numbers(runner):
     return wbytes, mm_params
 
 
+def trace_table(events):
+    """Rows for the last whole step among the stamps: the step's kernels in the order in which their
+    dependency waits returned, each with how long it then took until the next kernel's wait returned
+    (its own dependent work, its drain and the hand-over)."""
+    rel = [e for e in events if e["kind"] == "released"]
+    ends = [i for i, e in enumerate(rel) if e["library"] == "sampling"]
+    if len(ends) < 2:
+        return []
+    step = rel[ends[-2] + 1:ends[-1] + 1]
+    start = {}
+    for e in events:
+        if e["kind"] == "start":
+            start.setdefault((e["library"], e["blocks"], e["threads"]), []).append(e["ns"])
+    rows = []
+    for a, b in zip(step, step[1:] + [None]):
+        key = (a["library"], a["blocks"], a["threads"])
+        began = max((t for t in start.get(key, []) if t <= a["ns"]), default=a["ns"])
+        rows.append({"library": a["library"], "blocks": a["blocks"], "threads": a["threads"],
+                     "waited_us": (a["ns"] - began) / 1e3, "at_us": (a["ns"] - step[0]["ns"]) / 1e3,
+                     "until_next_us": (b["ns"] - a["ns"]) / 1e3 if b else None})
+    return rows
+
+
 def run(args):
+    if args.only == "trace":          # a measuring build of every kernel library, named before the first import
+        os.environ["VAPI_NVCC_FLAGS"] = (os.environ.get("VAPI_NVCC_FLAGS", "") + " -DVAPI_TRACE").strip()
     import torch
     from vapi_b200 import ops
     from vapi_b200.engine.engine import Engine
@@ -217,6 +242,19 @@ def run(args):
 
     if args.only == "prefill":
         return prefill_only(args, runner, mm_params, pk, gen, vocab, dev)
+    if args.only == "trace":
+        # the decode step as it runs inside its captured graph, from the kernels' own time stamps
+        ops.trace_start()
+        steps = min(args.steps, 8)
+        ms, _, _, _ = decode_point(B, steps, min(args.warmup, 4))
+        rows = trace_table(ops.trace_read())
+        print(f"decode step, batch {B}, context {ctx_len}: {ms / steps:.4f} ms/step with the stamps on; one step's kernels in "
+              f"the order in which their dependency waits returned", flush=True)
+        print("   at us   library      blocks threads  waited us  until the next kernel's wait returns, us", flush=True)
+        for r in rows:
+            nxt = f"{r['until_next_us']:8.2f}" if r["until_next_us"] is not None else "       -"
+            print(f"{r['at_us']:8.2f}   {r['library']:12s} {r['blocks']:6d} {r['threads']:7d}  {r['waited_us']:9.2f}  {nxt}", flush=True)
+        return 0
     # ---- headline: decode at the given batch -----------------------------------------
     clocks = ClockSampler()
     ms, launches, clk, kv_bytes = decode_point(B, args.steps, args.warmup, clocks)
@@ -406,9 +444,11 @@ def main():
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0 = all)")
     ap.add_argument("--impl", default="vapi_b200", choices=["vapi_b200", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "serve"],
-                    help="run just the headline decode point, just the prefill, or (serve) continuous "
-                         "batching of --requests requests with random prompt lengths through the engine loop")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "serve", "trace"],
+                    help="run just the headline decode point, just the prefill, (serve) continuous "
+                         "batching of --requests requests with random prompt lengths through the engine loop, or "
+                         "(trace) a few decode steps of a measuring build whose kernels stamp the device clock, "
+                         "and print what one step's kernels did inside the captured graph")
     ap.add_argument("--sizes", default="1.2b", choices=["1.2b", "700m", "2.6b"], help="layer sizes of LFM2-<sizes>")
     ap.add_argument("--page-size", type=int, default=0, help="tokens per cache page (0: the engine's default)")
     ap.add_argument("--requests", type=int, default=64)

@@ -261,3 +261,30 @@ def test_row_logprobs_breaks_ties_by_the_lower_id():
     assert [t for t, _ in top] == [1, 2, 4, 0]
     assert abs(lse - float(torch.logsumexp(torch.tensor(row), 0))) < 1e-6
     assert row_logprobs(row, 0)[1] == []
+
+
+# ---- the bench's reading of the kernels' time stamps -----------------------------------------
+
+def test_trace_table_takes_the_last_whole_step():
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location("bench", os.path.join(os.path.dirname(__file__), "..", "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+
+    def ev(ns, kind, lib, blocks=4, threads=128):
+        return {"ns": ns, "kind": kind, "library": lib, "blocks": blocks, "threads": threads}
+
+    events = []
+    for step in range(3):
+        t = step * 1000
+        events += [ev(t + 10, "start", "elementwise"), ev(t + 20, "released", "elementwise"),
+                   ev(t + 15, "start", "gemv", 296, 256), ev(t + 120, "released", "gemv", 296, 256),
+                   ev(t + 100, "start", "sampling", 8), ev(t + 400, "released", "sampling", 8)]
+    events.sort(key=lambda e: e["ns"])
+    rows = bench.trace_table(events)
+    assert [r["library"] for r in rows] == ["elementwise", "gemv", "sampling"]
+    assert rows[0]["at_us"] == 0 and rows[0]["until_next_us"] == pytest.approx(0.1)
+    assert rows[1]["waited_us"] == pytest.approx(0.105) and rows[1]["until_next_us"] == pytest.approx(0.28)
+    assert rows[2]["until_next_us"] is None
+    assert bench.trace_table(events[:4]) == []

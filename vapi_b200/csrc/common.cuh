@@ -50,8 +50,34 @@ inline int check_launch(const char* what) {
 // completed and its writes are visible.  pdl_trigger() lets the following kernel be scheduled
 // as soon as all blocks of this one have started.  Both are no-ops for a kernel launched the
 // ordinary way.  Set VAPI_PDL=0 to launch everything the ordinary way.
+#ifndef VAPI_TRACE
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#else
+// A build with -DVAPI_TRACE (a measuring build, never the serving one) stamps the device's clock when
+// the first thread of a kernel's first block starts and when its dependency wait returns, into a
+// buffer that vapi_trace_set() names: what a step's kernels do inside a captured graph, where no
+// profiler looks.  Two words a stamp: nanoseconds, then kind | library << 4 | threads << 8 | blocks << 24.
+__device__ unsigned long long* g_trace_buf;
+__device__ unsigned* g_trace_count;
+__device__ unsigned g_trace_capacity;
+__device__ int g_trace_library;
+__device__ __forceinline__ void trace_stamp(int kind) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && g_trace_buf) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        const unsigned i = atomicAdd(g_trace_count, 1u);
+        if (i < g_trace_capacity) {
+            g_trace_buf[2 * (size_t)i] = t;
+            g_trace_buf[2 * (size_t)i + 1] = (unsigned long long)kind | ((unsigned long long)g_trace_library << 4) |
+                                             ((unsigned long long)blockDim.x << 8) |
+                                             ((unsigned long long)gridDim.x * gridDim.y * gridDim.z << 24);
+        }
+    }
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); trace_stamp(1); }
+__device__ __forceinline__ void pdl_trigger() { trace_stamp(0); asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 
 inline bool pdl_enabled() {
     static int v = -1;
@@ -127,3 +153,14 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 }  // namespace vapi
+
+#ifdef VAPI_TRACE
+// buffer of 2 * capacity 64-bit words and a 32-bit counter, both in device memory; null switches the stamps off
+VAPI_EXPORT int vapi_trace_set(unsigned long long* buf, unsigned* count, unsigned capacity, int library) {
+    cudaError_t e = cudaMemcpyToSymbol(vapi::g_trace_count, &count, sizeof(count));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(vapi::g_trace_capacity, &capacity, sizeof(capacity));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(vapi::g_trace_library, &library, sizeof(library));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(vapi::g_trace_buf, &buf, sizeof(buf));
+    return e == cudaSuccess ? 0 : vapi::fail(-100, "trace_set: %s", cudaGetErrorString(e));
+}
+#endif

@@ -44,7 +44,54 @@ def _lib(name: str) -> ctypes.CDLL:
             lib.vapi_last_error.restype = ctypes.c_char_p
             _libs[name] = lib
             loaded_libraries[name] = path
+            if _trace is not None:
+                _trace_attach(name, lib)
     return lib
+
+
+# ---- time stamps from inside captured graphs (a build with VAPI_NVCC_FLAGS=-DVAPI_TRACE) ----------
+_trace: Optional[Tuple[torch.Tensor, torch.Tensor, Dict[str, int]]] = None
+
+
+def _trace_attach(name: str, lib: ctypes.CDLL) -> None:
+    buf, count, ids = _trace
+    if not hasattr(lib, "vapi_trace_set"):
+        raise KernelError(f"lib{name} was built without -DVAPI_TRACE (set VAPI_NVCC_FLAGS before the first import)")
+    ids.setdefault(name, len(ids))
+    rc = lib.vapi_trace_set(ctypes.c_void_p(buf.data_ptr()), ctypes.c_void_p(count.data_ptr()), buf.numel() // 2, ids[name])
+    if rc != 0:
+        raise KernelError(lib.vapi_last_error().decode(errors="replace"))
+
+
+def trace_start(capacity: int = 1 << 16, device: str = "cuda") -> None:
+    """Start collecting the kernels' own time stamps (first block's start, return of its dependency
+    wait): every library loaded from now on, and those loaded already, writes into one buffer."""
+    global _trace
+    buf = torch.zeros(2 * capacity, dtype=torch.int64, device=device)
+    count = torch.zeros(1, dtype=torch.int32, device=device)
+    _trace = (buf, count, {})
+    for name, lib in list(_libs.items()):
+        if name != "host":
+            _trace_attach(name, lib)
+
+
+def trace_read() -> list:
+    """The stamps so far, in time order: dicts with ``ns``, ``kind`` ("start" | "released"), ``library``,
+    ``threads`` and ``blocks`` of the kernel that wrote them."""
+    if _trace is None:
+        raise KernelError("trace_start() was not called")
+    buf, count, ids = _trace
+    torch.cuda.synchronize()
+    n = min(int(count.item()), buf.numel() // 2)
+    raw = buf[:2 * n].cpu().tolist()
+    names = {v: k for k, v in ids.items()}
+    out = []
+    for i in range(n):
+        t, meta = raw[2 * i], raw[2 * i + 1]
+        out.append({"ns": t, "kind": "start" if (meta & 15) == 0 else "released", "library": names.get((meta >> 4) & 15, "?"),
+                    "threads": (meta >> 8) & 0xffff, "blocks": meta >> 24})
+    out.sort(key=lambda e: e["ns"])
+    return out
 
 
 #: how many of this package's own kernels have been launched (library products not counted)
