@@ -33,6 +33,10 @@
 using namespace vapi;
 
 constexpr int GV_WARPS = 8;
+// For 9..16 tokens the tokens' rows take 66 KB of a block's shared memory at K = 2048, so that two blocks
+// of eight warps have room for four stages each: too few bytes in flight.  One block of sixteen warps
+// shares one copy of the rows and has the room for a full queue per warp; it is used where it fits.
+constexpr int GV_WIDE_WARPS = 16;
 #ifndef GV_STAGES_N
 #define GV_STAGES_N 8
 #endif
@@ -49,7 +53,9 @@ constexpr int GV_STAGES_DEFAULT = GV_STAGES_N;   // depth of the per-lane copy q
 // (DEEP: a product with a long K and no more tiles than SMs has one block per SM anyway and takes
 // a deeper queue instead of a second block)
 // (16 stages of 3 slots for up to 8 tokens, 12 of 4 slots for up to 16: 196 KB either way)
-template <int EPI, bool DEEP = false, int NT = 1> __host__ __device__ constexpr int gv_stages() {
+template <int EPI, bool DEEP = false, int NT = 1, int PRO = 1, int WARPS = GV_WARPS> __host__ __device__ constexpr int gv_stages() {
+    if (WARPS == GV_WIDE_WARPS)      // one block per SM: 8 stages beside the staged rows, 6 when the rows travel in the queue, 5 with three weight rows
+        return EPI == 4 ? 5 : (PRO == 0 ? 6 : 8);
     return DEEP ? (NT == 1 ? GV_DEEP_STAGES : (GV_DEEP_STAGES * 3) / 4)
                 : (NT == 2 ? GV_NT2_STAGES : (EPI == 4 ? (GV_STAGES_DEFAULT < 6 ? GV_STAGES_DEFAULT : 6) : GV_STAGES_DEFAULT));
 }
@@ -100,37 +106,37 @@ template <int N> __device__ __forceinline__ void gv_wait() { asm volatile("cp.as
 template <int NT, int PRO, int EPI>
 __host__ __device__ constexpr int gv_slots() { return (EPI == GV_EPI_CONV ? 3 : 2) + (PRO == GV_PRO_ACT ? NT : 0); }
 
-template <int NT, int PRO, int EPI, bool DEEP>
+template <int NT, int PRO, int EPI, bool DEEP, int WARPS = GV_WARPS>
 static size_t gv_smem_bytes(int K) {
-    size_t b = (size_t)GV_WARPS * gv_stages<EPI, DEEP, NT>() * gv_slots<NT, PRO, EPI>() * 32 * sizeof(uint4);
+    size_t b = (size_t)WARPS * gv_stages<EPI, DEEP, NT, PRO, WARPS>() * gv_slots<NT, PRO, EPI>() * 32 * sizeof(uint4);
     if (PRO == GV_PRO_NORM) b += (size_t)8 * NT * (K + 32) * sizeof(__nv_bfloat16);
     return b;
 }
 
-template <int NT, int PRO, int EPI, bool DEEP = false>
-__global__ void __launch_bounds__(GV_WARPS * 32)
+template <int NT, int PRO, int EPI, bool DEEP = false, int WARPS = GV_WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 skinny_linear_kernel(const GvParams p) {
     constexpr int SLOTS = gv_slots<NT, PRO, EPI>();
-    constexpr int GV_STAGES = gv_stages<EPI, DEEP, NT>();
+    constexpr int GV_STAGES = gv_stages<EPI, DEEP, NT, PRO, WARPS>();
     constexpr int WS = EPI == GV_EPI_CONV ? 3 : 2;     // weight rows a lane streams per chunk
     constexpr int COLS = 8 * NT;
     extern __shared__ __align__(16) unsigned char gv_smem[];
-    __shared__ float red[GV_WARPS][16][COLS + 1];
-    __shared__ float red_x[EPI == GV_EPI_CONV ? GV_WARPS : 1][8][COLS + 1];
+    __shared__ float red[WARPS][16][COLS + 1];
+    __shared__ float red_x[EPI == GV_EPI_CONV ? WARPS : 1][8][COLS + 1];
     __shared__ float inv_s[COLS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int R = p.rows_per_cta;
     uint4* fifo = reinterpret_cast<uint4*>(gv_smem) + (size_t)warp * (GV_STAGES * SLOTS * 32);
     __nv_bfloat16* act_s = reinterpret_cast<__nv_bfloat16*>(
-        reinterpret_cast<uint4*>(gv_smem) + (size_t)GV_WARPS * GV_STAGES * SLOTS * 32);   // PRO_NORM only
+        reinterpret_cast<uint4*>(gv_smem) + (size_t)WARPS * GV_STAGES * SLOTS * 32);   // PRO_NORM only
     const int pitch = p.K + 32;
 
     // A block works through tiles blockIdx.x, blockIdx.x + gridDim.x, ...; a warp owns the
     // same slice of K in every tile, so its copy queue runs on across tile boundaries.
     const int my_tiles = (int)blockIdx.x < p.num_tiles ? (p.num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
     const int nchunks = p.K >> 5;
-    const int cpw = (nchunks + GV_WARPS - 1) / GV_WARPS;
+    const int cpw = (nchunks + WARPS - 1) / WARPS;
     const int c_begin = min(nchunks, warp * cpw), c_end = min(nchunks, c_begin + cpw);
     const int len = c_end - c_begin;
 
@@ -202,14 +208,14 @@ skinny_linear_kernel(const GvParams p) {
         // every token's row (already multiplied by the norm's weight) into shared memory, by
         // asynchronous copies that overlap the weights already on their way
         const int k8 = p.K >> 3;
-        for (int idx = threadIdx.x; idx < COLS * k8; idx += GV_WARPS * 32) {
+        for (int idx = threadIdx.x; idx < COLS * k8; idx += WARPS * 32) {
             const int m = idx / k8, k = (idx - m * k8) << 3;
             const bool ok = m < p.M;
             gv_cp16(act_s + (size_t)m * pitch + k, p.xw + (size_t)(ok ? m : 0) * p.K + k, ok ? 16 : 0);
         }
         gv_commit();
         // the token's factor rsqrt(mean x^2 + eps) from the producer's partial sums, in a fixed order
-        for (int m = warp; m < p.M; m += GV_WARPS) {
+        for (int m = warp; m < p.M; m += WARPS) {
             float s = 0.f;
             for (int i = lane; i < p.ss_parts; i += 32) s += p.ss_in[(size_t)i * p.M + m];
             s = warp_sum(s);
@@ -284,16 +290,16 @@ skinny_linear_kernel(const GvParams p) {
         float y = 0.f, y2 = 0.f;
         if (i < 16) {
 #pragma unroll
-            for (int w = 0; w < GV_WARPS; ++w) y += red[w][i][m];
+            for (int w = 0; w < WARPS; ++w) y += red[w][i][m];
             if ((EPI == GV_EPI_SWIGLU || EPI == GV_EPI_CONV) && i < 8) {
 #pragma unroll
-                for (int w = 0; w < GV_WARPS; ++w) y2 += red[w][i + 8][m];
+                for (int w = 0; w < WARPS; ++w) y2 += red[w][i + 8][m];
             }
         }
         float y3 = 0.f;
         if (EPI == GV_EPI_CONV && i < 8) {
 #pragma unroll
-            for (int w = 0; w < GV_WARPS; ++w) y3 += red_x[w][i][m];
+            for (int w = 0; w < WARPS; ++w) y3 += red_x[w][i][m];
         }
         if (PRO == GV_PRO_NORM && m < p.M) {
             y *= inv_s[m];
@@ -374,29 +380,46 @@ skinny_linear_kernel(const GvParams p) {
     gv_wait<0>();
 }
 
-template <int NT, int PRO, int EPI, bool DEEP = false>
-static int launch_gv(const GvParams& p, int blocks, cudaStream_t stream) {
-    const size_t smem = gv_smem_bytes<NT, PRO, EPI, DEEP>(p.K);
-    auto kern = skinny_linear_kernel<NT, PRO, EPI, DEEP>;
-    if (smem > 200 * 1024) return fail(-1, "skinny_linear: K=%d needs %zu bytes of shared memory", p.K, smem);
-    if (smem + 16 * 1024 > 48 * 1024) {      // (static shared memory, up to about 10 KB, counts toward the default limit)
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return fail(-101, "skinny_linear: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    }
+static int gv_sm_count() {
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     }
+    return sms;
+}
+
+template <int NT, int PRO, int EPI, bool DEEP, int WARPS>
+static int launch_gv_as(const GvParams& p, int blocks, int blocks_per_sm, cudaStream_t stream) {
+    const size_t smem = gv_smem_bytes<NT, PRO, EPI, DEEP, WARPS>(p.K);
+    auto kern = skinny_linear_kernel<NT, PRO, EPI, DEEP, WARPS>;
+    if (smem > 200 * 1024) return fail(-1, "skinny_linear: K=%d needs %zu bytes of shared memory", p.K, smem);
+    if (smem + 28 * 1024 > 48 * 1024) {      // (static shared memory, up to about 26 KB, counts toward the default limit)
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(-101, "skinny_linear: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    }
     // a fixed number of blocks per SM, each walking its share of the tiles
-    static int per_sm = -1;
+    const int cap = blocks_per_sm > 0 ? gv_sm_count() * blocks_per_sm : blocks;
+    return check_launch("skinny_linear", launch(kern, blocks < cap ? blocks : cap, WARPS * 32, smem, stream, p));
+}
+
+template <int NT, int PRO, int EPI, bool DEEP = false>
+static int launch_gv(const GvParams& p, int blocks, cudaStream_t stream) {
+    static int per_sm = -1, wide = -1;
     if (per_sm < 0) {
         const char* e = getenv("VAPI_GV_BLOCKS_PER_SM");
         per_sm = e ? atoi(e) : 2;
+        const char* w = getenv("VAPI_GV_WIDE");
+        wide = (w && w[0] == '0') ? 0 : 1;
     }
-    const int cap = per_sm > 0 ? sms * per_sm : blocks;
-    return check_launch("skinny_linear", launch(kern, blocks < cap ? blocks : cap, GV_WARPS * 32, smem, stream, p));
+    if (NT == 2 && wide) {
+        // sixteen warps, one block per SM, where the queue and the tokens' rows fit (with the static arrays beside them)
+        constexpr int W = GV_WIDE_WARPS;
+        if (gv_smem_bytes<NT, PRO, EPI, false, W>(p.K) <= 198 * 1024)
+            return launch_gv_as<NT, PRO, EPI, false, (NT == 2 ? W : GV_WARPS)>(p, blocks, 1, stream);
+    }
+    return launch_gv_as<NT, PRO, EPI, DEEP, GV_WARPS>(p, blocks, per_sm, stream);
 }
 
 // Number of blocks (and so of partial sums a residual epilogue leaves) for a given shape.
