@@ -667,6 +667,37 @@ def test_skinny_linear_fusions(ops, M):
     torch.testing.assert_close(lg.cpu(), (xw.float() @ wv.float().t()) * inv, atol=2e-3, rtol=1e-3)
 
 
+@pytest.mark.parametrize("M", [8, 11, 16])
+def test_skinny_linear_fusions_with_more_tiles_than_blocks(ops, M):
+    """The same fusions where a product has more tiles than the device has SMs: with 9..16 rows a block's
+    sixteen warps then walk the tiles as two groups of eight, each with its own sums and barriers."""
+    torch.manual_seed(23)
+    H, F, eps = 2432, 1304, 1e-5                      # 152 tiles of 16 rows, 163 tiles of 8 gate/up pairs
+    x = torch.randn(M, H)
+    nw = 1 + 0.1 * torch.randn(H)
+    w13 = (torch.randn(2 * F, H) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(H, 1312) * 0.05).to(torch.bfloat16)
+    parts = torch.stack([(x[:, i::7] ** 2).sum(1) for i in range(7)]).contiguous()
+    xw = (x * nw).to(torch.bfloat16)
+    inv = torch.rsqrt((x ** 2).mean(1, keepdim=True) + eps)
+    s_ = ops.skinny_linear(dev(w13), xw=dev(xw), ss_in=dev(parts), eps=eps, epilogue="swiglu")
+    gu = (xw.float() @ w13.float().t()) * inv
+    want_s = (gu[:, :F] / (1 + torch.exp(-gu[:, :F]))) * gu[:, F:]
+    torch.testing.assert_close(s_.cpu().float(), want_s, atol=3e-2, rtol=3e-2)
+    s2 = torch.randn(M, 1312).to(torch.bfloat16)
+    nw2 = 1 + 0.1 * torch.randn(H)
+    xr = dev(x.clone())
+    ss, xw2 = ops.skinny_linear(dev(w2), act=dev(s2), epilogue="resid", resid=xr, next_weight=dev(nw2))
+    want_x = x + s2.float() @ w2.float().t()
+    torch.testing.assert_close(xr.cpu(), want_x, atol=3e-3, rtol=1e-3)
+    assert ss.shape == (152, M)
+    torch.testing.assert_close(ss.sum(0).cpu(), (want_x ** 2).sum(1), atol=5e-2, rtol=1e-3)
+    torch.testing.assert_close(xw2.cpu().float(), (want_x * nw2).to(torch.bfloat16).float(), atol=4e-2, rtol=2e-2)
+    lg = ops.skinny_linear(dev(w13), xw=dev(xw), ss_in=dev(parts), eps=eps, epilogue="f32")
+    torch.testing.assert_close(lg.cpu(), gu, atol=5e-3, rtol=2e-3)
+    assert torch.equal(ops.skinny_linear(dev(w13), xw=dev(xw), ss_in=dev(parts), eps=eps, epilogue="swiglu"), s_)
+
+
 def test_embed_and_residual_add_prepare_the_next_norm(ops):
     torch.manual_seed(22)
     table = torch.randn(50, 72).to(torch.bfloat16)
@@ -686,7 +717,7 @@ def test_embed_and_residual_add_prepare_the_next_norm(ops):
 
 
 @pytest.mark.parametrize("M,H,K,L,bias", [(8, 2048, 2048, 3, False), (1, 72, 96, 4, True), (11, 200, 160, 2, True),
-                                          (16, 64, 64, 5, False), (3, 40, 32, 1, False)])
+                                          (16, 64, 64, 5, False), (3, 40, 32, 1, False), (12, 1280, 128, 3, True)])
 def test_skinny_shortconv_is_in_proj_then_the_conv_kernel(ops, M, H, K, L, bias):
     """The decode form of the short-conv mixer in one launch, against the two steps it replaces
     (in_proj rounded to bfloat16, then the conv kernel's plain restatement), over two steps on the

@@ -125,6 +125,18 @@ skinny_linear_kernel(const GvParams p) {
     __shared__ float red_x[EPI == GV_EPI_CONV ? WARPS : 1][8][COLS + 1];
     __shared__ float inv_s[COLS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // Sixteen warps are two groups of eight that walk tiles of their own (their epilogues then fall at
+    // different times, so that one group streams while the other adds up) when the product has more
+    // tiles than blocks, and one group that splits K sixteen ways when it has not.
+    const int groups = (WARPS == GV_WIDE_WARPS && p.num_tiles > (int)gridDim.x) ? 2 : 1;
+    const int gw = WARPS / groups;                                 // warps of a group
+    const int grp = warp / gw, wig = warp - grp * gw;              // group, warp in the group
+    const int tig = (int)threadIdx.x - grp * gw * 32;              // thread in the group
+    const int vblock = (int)blockIdx.x * groups + grp, vgrid = (int)gridDim.x * groups;
+    auto group_sync = [&]() {
+        if (WARPS == GV_WIDE_WARPS && groups == 2) asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(gw * 32) : "memory");
+        else __syncthreads();
+    };
     const int g = lane >> 2, t = lane & 3;
     const int R = p.rows_per_cta;
     uint4* fifo = reinterpret_cast<uint4*>(gv_smem) + (size_t)warp * (GV_STAGES * SLOTS * 32);
@@ -134,10 +146,10 @@ skinny_linear_kernel(const GvParams p) {
 
     // A block works through tiles blockIdx.x, blockIdx.x + gridDim.x, ...; a warp owns the
     // same slice of K in every tile, so its copy queue runs on across tile boundaries.
-    const int my_tiles = (int)blockIdx.x < p.num_tiles ? (p.num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int my_tiles = vblock < p.num_tiles ? (p.num_tiles - vblock + vgrid - 1) / vgrid : 0;
     const int nchunks = p.K >> 5;
-    const int cpw = (nchunks + WARPS - 1) / WARPS;
-    const int c_begin = min(nchunks, warp * cpw), c_end = min(nchunks, c_begin + cpw);
+    const int cpw = (nchunks + gw - 1) / gw;
+    const int c_begin = min(nchunks, wig * cpw), c_end = min(nchunks, c_begin + cpw);
     const int len = c_end - c_begin;
 
     // the two weight rows (MMA rows g and g + 8) this lane streams in a given tile
@@ -161,7 +173,7 @@ skinny_linear_kernel(const GvParams p) {
         if (q_tile < my_tiles) {
             long long row_lo, row_hi;
             bool ok_lo, ok_hi;
-            rows_of((int)blockIdx.x + q_tile * (int)gridDim.x, row_lo, row_hi, ok_lo, ok_hi);
+            rows_of(vblock + q_tile * vgrid, row_lo, row_hi, ok_lo, ok_hi);
             q_lo = p.W + (size_t)(ok_lo ? row_lo : 0) * p.K + 8 * t;
             q_hi = p.W + (size_t)(ok_hi ? row_hi : 0) * p.K + 8 * t;
             if (EPI == GV_EPI_CONV) q_x = p.W + (size_t)(ok_lo ? 2 * (long long)p.ff + row_lo : 0) * p.K + 8 * t;
@@ -239,7 +251,7 @@ skinny_linear_kernel(const GvParams p) {
     bool first = true;
     int stage = 0;
     for (int ti = 0; ti < my_tiles; ++ti) {
-        const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+        const int tile = vblock + ti * vgrid;
         float acc[NT][4];
         float acc_x[EPI == GV_EPI_CONV ? NT : 1][4];
 #pragma unroll
@@ -285,21 +297,22 @@ skinny_linear_kernel(const GvParams p) {
                 red_x[warp][g][nt * 8 + 2 * t + 1] = acc_x[nt][1];
             }
         }
-        __syncthreads();
-        const int i = threadIdx.x / COLS, m = threadIdx.x - i * COLS;      // MMA row, token
+        group_sync();
+        const int i = tig / COLS, m = tig - i * COLS;                      // MMA row, token
+        const int w0 = grp * gw;                                           // the group's first warp
         float y = 0.f, y2 = 0.f;
         if (i < 16) {
 #pragma unroll
-            for (int w = 0; w < WARPS; ++w) y += red[w][i][m];
+            for (int w = 0; w < WARPS; ++w) if (w < gw) y += red[w0 + w][i][m];
             if ((EPI == GV_EPI_SWIGLU || EPI == GV_EPI_CONV) && i < 8) {
 #pragma unroll
-                for (int w = 0; w < WARPS; ++w) y2 += red[w][i + 8][m];
+                for (int w = 0; w < WARPS; ++w) if (w < gw) y2 += red[w0 + w][i + 8][m];
             }
         }
         float y3 = 0.f;
         if (EPI == GV_EPI_CONV && i < 8) {
 #pragma unroll
-            for (int w = 0; w < WARPS; ++w) y3 += red_x[w][i][m];
+            for (int w = 0; w < WARPS; ++w) if (w < gw) y3 += red_x[w0 + w][i][m];
         }
         if (PRO == GV_PRO_NORM && m < p.M) {
             y *= inv_s[m];
@@ -363,19 +376,19 @@ skinny_linear_kernel(const GvParams p) {
                     if (p.xw_out) p.xw_out[(size_t)m * p.N + n] = __float2bfloat16_rn(v * p.next_w[n]);
                 }
                 if (p.ss_out) {
-                    __syncthreads();                     // everyone has read its sums out of red[]
-                    if (i < 16) red[0][i][m] = v * v;
-                    __syncthreads();
-                    if (threadIdx.x < COLS && threadIdx.x < p.M) {
+                    group_sync();                        // everyone has read its sums out of red[]
+                    if (i < 16) red[w0][i][m] = v * v;
+                    group_sync();
+                    if (tig < COLS && tig < p.M) {
                         float sq = 0.f;
 #pragma unroll
-                        for (int r = 0; r < 16; ++r) sq += red[0][r][threadIdx.x];
-                        p.ss_out[(size_t)tile * p.M + threadIdx.x] = sq;
+                        for (int r = 0; r < 16; ++r) sq += red[w0][r][tig];
+                        p.ss_out[(size_t)tile * p.M + tig] = sq;
                     }
                 }
             }
         }
-        __syncthreads();                                 // red[] is free for the next tile
+        group_sync();                                    // red[] is free for the next tile
     }
     gv_wait<0>();
 }
