@@ -66,6 +66,17 @@ TINY_D = {
     "tie_word_embeddings": True, "max_position_embeddings": 512, "eos_token_id": 2,
 }
 
+# A fifth: head size 128 (the other head size of the bfloat16 flash kernel), an attention layer
+# first, one kv head, a conv of two taps with bias
+TINY_E = {
+    "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2",
+    "vocab_size": 777, "hidden_size": 192, "intermediate_size": 448, "block_auto_adjust_ff_dim": False,
+    "num_hidden_layers": 3, "layer_types": ["full_attention", "conv", "full_attention"],
+    "num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 128,
+    "conv_L_cache": 2, "conv_bias": True, "rope_theta": 10000.0, "norm_eps": 1e-6,
+    "tie_word_embeddings": True, "max_position_embeddings": 512, "eos_token_id": 3,
+}
+
 
 @pytest.fixture(scope="session")
 def tiny_dirs(tmp_path_factory):
@@ -73,11 +84,12 @@ def tiny_dirs(tmp_path_factory):
     dropped norm weight shows)."""
     from vapi_b200.weights import write_random_model
     out = {}
-    for name, cfg, seed in (("A", TINY_A, 0), ("B", TINY_B, 2), ("C", TINY_C, 4), ("D", TINY_D, 6)):
+    for name, cfg, seed in (("A", TINY_A, 0), ("B", TINY_B, 2), ("C", TINY_C, 4), ("D", TINY_D, 6),
+                            ("E", TINY_E, 8)):
         d = tmp_path_factory.mktemp(f"tiny{name}")
         # std 0.2 / perturbed norms as the reference's golden generator uses
         # (tools/gen_lfm2_goldens.py:27-49): activations large enough that faults show.
-        write_random_model(str(d), cfg, seed, std={"A": 0.02, "D": 0.1}.get(name, 0.2),
+        write_random_model(str(d), cfg, seed, std={"A": 0.02, "D": 0.1, "E": 0.1}.get(name, 0.2),
                            norm_init="perturbed" if name != "A" else "ones", dtype=torch.float32)
         out[name] = str(d)
     return out

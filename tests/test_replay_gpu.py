@@ -7,11 +7,11 @@ import torch
 
 import plain_lfm2
 import replay_util as ru
-from conftest import TINY_A, TINY_B, TINY_C, TINY_D
+from conftest import TINY_A, TINY_B, TINY_C, TINY_D, TINY_E
 
 pytestmark = pytest.mark.gpu
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def _requests(cfg, seed, lengths):
@@ -24,9 +24,9 @@ def bf16_dirs(tmp_path_factory):
     """The tiny models with weights stored in bfloat16 (what a served checkpoint looks like)."""
     from vapi_b200.weights import write_random_model
     out = {}
-    for name, seed in (("A", 10), ("B", 12), ("C", 14), ("D", 16)):
+    for name, seed in (("A", 10), ("B", 12), ("C", 14), ("D", 16), ("E", 18)):
         d = tmp_path_factory.mktemp(f"tiny{name}bf16")
-        write_random_model(str(d), CONFIGS[name], seed, std=0.1 if name == "D" else 0.2, norm_init="perturbed",
+        write_random_model(str(d), CONFIGS[name], seed, std=0.1 if name in "DE" else 0.2, norm_init="perturbed",
                            dtype=torch.bfloat16)
         out[name] = str(d)
     return out
@@ -55,7 +55,7 @@ def _full_trace(cfg, seed):
     return tr, ref_tokens
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_every_way_of_cutting(name, dtype, tiny_dirs, bf16_dirs, tmp_path):
     model_dir = tiny_dirs[name] if dtype == "float32" else bf16_dirs[name]
