@@ -12,7 +12,8 @@
 //    several chunks are always in flight whatever the arithmetic is doing, and there is no
 //    barrier in the loop.
 //  * the 8 warps of a block split K and add their partial tiles in a fixed order through shared
-//    memory (deterministic: no atomics), then one thread per output applies the epilogue.
+//    memory (deterministic: no atomics), then one thread per output applies the epilogue.  (For
+//    9..16 tokens a block has 16 warps, as one group or as two groups of 8: see GV_WIDE_WARPS.)
 //  * prologue (what the token operand is): bfloat16 activations, or the residual stream seen
 //    through an RMSNorm that was not applied yet.  RMSNorm is x * w * rsqrt(mean x^2 + eps): the
 //    last factor is one number per token, so the product runs on bfloat16(x * w), which the
@@ -285,7 +286,7 @@ skinny_linear_kernel(const GvParams p) {
             stage = stage == GV_STAGES - 1 ? 0 : stage + 1;
         }
 
-        // partial tiles of the 8 warps, added in warp order
+        // partial tiles of the group's warps, added in warp order
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             red[warp][g][nt * 8 + 2 * t] = acc[nt][0];
