@@ -31,7 +31,10 @@ constexpr int FD_HD = 64;
 constexpr int FD_CWARPS = 4;                               // consumer warps: 16 keys of every tile each
 constexpr int FD_THREADS = (FD_CWARPS + 1) * 32;
 constexpr int FD_MAX_ROWS = 16;
-constexpr int FD_MAX_CLUSTER = 8;                          // slices of the keys that combine inside the kernel
+#ifndef FD_MAX_CLUSTER_N
+#define FD_MAX_CLUSTER_N 16
+#endif
+constexpr int FD_MAX_CLUSTER = FD_MAX_CLUSTER_N;           // slices of the keys that combine inside the kernel (above 8: a cluster size the device must allow)
 constexpr int FD_TILE_BYTES = FD_BK * FD_HD * 2;           // one K (or V) tile
 #ifndef FD_STAGES_N
 #define FD_STAGES_N 4
@@ -94,7 +97,7 @@ __device__ __forceinline__ float4 fd_peer_f32x4(unsigned addr) {
     return v;
 }
 
-// CLUSTER: the blocks of one (sequence, kv head) - its slices of the keys, at most 8 - form a
+// CLUSTER: the blocks of one (sequence, kv head) - its slices of the keys, at most 16 (above 8 a cluster size that the device has to allow; asked once) - form a
 // thread-block cluster; each leaves its partial result in its own shared memory and, after a
 // cluster barrier, they share out the rows' final sums among themselves (slice sp is rank sp).
 // FUSED: q/k norm, RoPE and the cache write of the new tokens happen here too (FdParams::fused).
@@ -525,6 +528,10 @@ static bool flash_decode_combines(int num_seqs, int nkv, int splits) {
     static int fits[FD_MAX_CLUSTER + 1] = {};              // 0 unknown, 1 yes, -1 no
     if (fits[splits] == 0) {
         cudaFuncSetAttribute(flash_decode_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FD_SMEM);
+        if (FD_MAX_CLUSTER > 8) {
+            cudaFuncSetAttribute(flash_decode_kernel<true, false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            cudaFuncSetAttribute(flash_decode_kernel<true, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        }
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(1, 1, (unsigned)splits);
         cfg.blockDim = dim3(FD_THREADS);
