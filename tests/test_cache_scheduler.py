@@ -279,6 +279,24 @@ def test_watermark_is_kept_at_admission():
     assert [s.seqs[i].request_id for i in p.started] == ["a"]
 
 
+def test_a_page_set_aside_for_padding_is_not_counted_as_room():
+    """A page that was taken out of circulation (for the padding rows of fixed-shape decode steps)
+    never comes back: a prompt that needs every page of the pool is refused at admission, and one
+    that was admitted before the page was set aside ends with ``length`` instead of waiting for
+    room that cannot appear."""
+    s = sched(num_pages=4, page=16, max_requests=4, max_context=400)
+    s.admit("early", list(range(60)), SamplingParams(max_tokens=1, temperature=0.0))    # 61 positions: all 4 pages
+    assert s.cache.set_aside_pages() is not None
+    with pytest.raises(AdmitError, match="whole cache"):
+        s.admit("late", list(range(60)), SamplingParams(max_tokens=1, temperature=0.0))
+    s.admit("fits", list(range(40)), SamplingParams(max_tokens=1, temperature=0.0))     # 3 pages
+    Script(s, {"early": [1], "fits": [2]}).run()
+    done = {q.request_id: q for q in s.drain_finished()}
+    assert done["early"].finish_reason == FinishReason.LENGTH and done["early"].generated == []
+    assert done["fits"].generated == [2]
+    s.cache.check_invariants()
+
+
 def test_cancel_and_fail_all_free_everything():
     s = sched(max_context=256)
     a = s.admit("a", list(range(30)), SamplingParams(max_tokens=5))

@@ -125,6 +125,63 @@ def test_a_failed_step_fails_requests_in_flight_and_the_engine_goes_on(tiny_dirs
     assert c.tokens == plain.greedy(p[0], 4)
 
 
+def test_a_status_left_by_a_kernel_fails_the_step(tiny_dirs, plain_kernels):
+    """A kernel that refuses an index or gives up a bounded wait records a status word and leaves
+    its output unwritten.  The engine reads the word with the step's tokens: the step then counts
+    as failed (requests in flight end with ``error``, everything goes back), the word is cleared,
+    and the engine serves the next request.  The word is injected on the host here."""
+    from vapi_b200.engine.runner import KernelRefusal, STATUS_NAMES
+    plain = plain_lfm2.PlainLfm2(tiny_dirs["A"])
+    eng = _engine(tiny_dirs["A"], max_context=128)
+    p = _prompts(TINY_A, 3, [5, 6])
+    eng.admit("a", p[0], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    eng.admit("b", p[1], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    eng.step()
+    eng.runner.status[0] = 16
+    done = {f.request_id: f for f in eng.run()}
+    assert done["a"].reason == FinishReason.ERROR and done["b"].reason == FinishReason.ERROR
+    assert eng.stats.failed_steps == 1 and "wait" in eng.last_error and 16 in STATUS_NAMES
+    assert int(eng.runner.status[0]) == 0
+    eng.runner.cache.check_invariants()
+    assert eng.runner.cache.slots.num_free == 4 and eng.runner.cache.paged[0].pool.num_free == 16
+    eng.admit("c", p[0], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    (c,) = eng.run()
+    assert c.tokens == plain.greedy(p[0], 4) and c.reason == FinishReason.LENGTH
+    eng.runner.status[0] = 4
+    with pytest.raises(KernelRefusal, match="page id"):
+        eng.runner.check_status()
+    assert int(eng.runner.status[0]) == 0
+
+
+def test_the_status_word_travels_with_the_sampled_tokens():
+    """The sampler's pending result carries the word that stood in front of the tokens."""
+    from vapi_b200.sampling.sampler import PendingSample, Sampler
+    host = torch.tensor([16, 7, 8, 9], dtype=torch.int32)
+
+    class Done:
+        def synchronize(self):
+            pass
+
+    pending = PendingSample(3, host, Done(), with_status=True)
+    assert Sampler("cpu").finish(pending) == [7, 8, 9] and pending.status == 16
+    pending = PendingSample(3, host[1:], Done())
+    assert Sampler("cpu").finish(pending) == [7, 8, 9] and pending.status == 0
+
+
+def test_decode_buckets_stay_within_the_packers_capacity(tiny_dirs):
+    """A request limit that is no power of two: the largest bucket is the limit itself, so the
+    padded step of 40 live requests still fits the packer (48 sequences) instead of asking for 64."""
+    r = ModelRunner.from_dir(tiny_dirs["A"], dtype="float32", device="cpu", page_size=16, num_pages=64,
+                             max_requests=48, max_batched_tokens=64)
+    assert r.graph_max_batch == 48
+    assert [r._bucket(s) for s in (1, 3, 4, 17, 33, 40, 48)] == [1, 4, 4, 32, 48, 48, 48]
+    r.packer.set_pad_pages(r.cache.set_aside_pages())
+    for s in (3, 40):
+        B = r._bucket(s)
+        ctx = r.packer.pack([], r.dtype, n_cap=B, s_cap=B, width=r.packer.max_width)
+        assert ctx.n == B and ctx.num_seqs == B
+
+
 def test_failures_in_a_row_are_passed_on(tiny_dirs, plain_kernels):
     eng = _engine(tiny_dirs["A"], max_context=128)
     eng.max_step_failures = 2

@@ -107,6 +107,30 @@ def test_temperature_sampling_is_seeded_and_batch_independent(tiny_dirs):
     assert one[0].tokens == greedy[0].tokens
 
 
+@pytest.mark.parametrize("ahead", [True, False])
+def test_a_status_word_on_the_device_fails_the_step_and_is_cleared(tiny_dirs, ahead):
+    """The status word reaches the host in the copy that brings the sampled tokens; a non-zero word
+    fails the step like a step function that raised.  The word is written from the host here (a
+    kernel writes it when it refuses an index or gives up a bounded wait): nothing on the device
+    is made to go wrong."""
+    from vapi_b200 import LLM, SamplingParams
+    plain = plain_lfm2.PlainLfm2(tiny_dirs["B"])
+    prompts = _prompts(TINY_B, 6, [5, 23])
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    llm = LLM(tiny_dirs["B"], dtype="f32", num_blocks=24, max_concurrent_seqs=4, max_batched_tokens=64, max_context=256,
+              run_ahead=ahead)
+    llm.runner.status.fill_(16)
+    out = llm.generate(prompts, sp, raise_on_error=False)
+    assert [c.finish_reason for c in out] == ["error", "error"]
+    assert "wait" in llm.engine.last_error and llm.engine.stats.failed_steps == 1
+    assert int(llm.runner.status.item()) == 0
+    llm.runner.cache.check_invariants()
+    out = llm.generate(prompts, sp)
+    for p, c in zip(prompts, out):
+        want = plain.greedy(p, 6)
+        assert c.tokens == want or _agrees_up_to_a_near_tie(plain, p, c.tokens, want, gap=1e-3)
+
+
 def test_the_collector_stays_out_of_graph_capture(tiny_dirs):
     """Freeing another runner's graphs (garbage in reference cycles dies whenever the collector
     happens to run) is not permitted while a stream captures and would lose the capture: the

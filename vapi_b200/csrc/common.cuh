@@ -43,6 +43,20 @@ inline int check_launch(const char* what) {
     return 0;
 }
 
+// Multiprocessors of the current device, asked of the device once per device (host).
+inline int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 // ---- programmatic dependent launch --------------------------------------------------
 // Kernels of a step are launched so that the next one may begin while the one before it
 // drains: a kernel first does what does not depend on its predecessor (index arithmetic,

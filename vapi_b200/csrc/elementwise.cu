@@ -277,7 +277,7 @@ VAPI_EXPORT int vapi_add_residual(float* x, const void* delta, int dtype, long l
     if (total <= 0) return 0;
     const int threads = 256;
     long long blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > sm_count() * 16) blocks = sm_count() * 16;
     cudaError_t e;
     if (dtype == VAPI_F32)
         e = launch(add_residual_kernel<float>, (int)blocks, threads, 0, stream, x, (const float*)delta, (size_t)total);
@@ -355,7 +355,7 @@ VAPI_EXPORT int vapi_swiglu(const void* g, void* out, int dtype, int rows, int f
     const int threads = 256;
     long long total = (long long)rows * ff;
     long long blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (blocks > sm_count() * 32) blocks = sm_count() * 32;
     cudaError_t e;
     if (dtype == VAPI_BF16 && ff % 8 == 0 && rows <= 65535) {
         const int th = 128;
@@ -365,7 +365,7 @@ VAPI_EXPORT int vapi_swiglu(const void* g, void* out, int dtype, int rows, int f
     }
     if (ff % 4 == 0 && (dtype == VAPI_F32 || dtype == VAPI_BF16)) {
         long long vb = (total / 4 + threads - 1) / threads;
-        if (vb > 148 * 16) vb = 148 * 16;
+        if (vb > sm_count() * 16) vb = sm_count() * 16;
         if (dtype == VAPI_F32) e = launch(swiglu_vec_kernel<float>, (int)vb, threads, 0, stream, (const float*)g, (float*)out, rows, ff);
         else e = launch(swiglu_vec_kernel<__nv_bfloat16>, (int)vb, threads, 0, stream, (const __nv_bfloat16*)g, (__nv_bfloat16*)out, rows, ff);
         return check_launch("swiglu", e);

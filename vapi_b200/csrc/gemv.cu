@@ -394,15 +394,7 @@ skinny_linear_kernel(const GvParams p) {
     gv_wait<0>();
 }
 
-static int gv_sm_count() {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
-    return sms;
-}
+static int gv_sm_count() { return sm_count(); }
 
 template <int NT, int PRO, int EPI, bool DEEP, int WARPS>
 static int launch_gv_as(const GvParams& p, int blocks, int blocks_per_sm, cudaStream_t stream) {
@@ -481,7 +473,7 @@ VAPI_EXPORT int vapi_skinny_linear(const void* W, int N, int K, int M, int pro, 
         const char* e = getenv("VAPI_GV_DEEP_K");
         deep_k = e ? atoi(e) : 4096;
     }
-    if (pro == GV_PRO_ACT && epi == GV_EPI_RESID && deep_k > 0 && K >= deep_k && blocks <= 148) {
+    if (pro == GV_PRO_ACT && epi == GV_EPI_RESID && deep_k > 0 && K >= deep_k && blocks <= gv_sm_count()) {
         if (M <= 8) return launch_gv<1, GV_PRO_ACT, GV_EPI_RESID, true>(p, blocks, stream);
         return launch_gv<2, GV_PRO_ACT, GV_EPI_RESID, true>(p, blocks, stream);
     }

@@ -397,9 +397,11 @@ struct Sched {
     }
     static void erase(std::vector<int>& v, int x) { v.erase(std::remove(v.begin(), v.end(), x), v.end()); }
 
+    // Pages of the smallest group that requests can ever hold (pages set aside for the padding
+    // rows of fixed-shape decode steps never come back).
     int min_pool_pages() const {
         int m = INT32_MAX;
-        for (const Group& g : cache->groups) m = std::min(m, g.pool.n);
+        for (const Group& g : cache->groups) m = std::min(m, g.pool.n - (int)g.set_aside.size());
         return m;
     }
     int admit(const int* prompt, int n, int max_tokens, bool ignore_eos, const int* stop, int nstop) {
@@ -465,7 +467,7 @@ struct Sched {
     bool can_ever_fit(const Seq& s) const {
         int need = cache->pages_for(s.prefill_target + 1);
         for (const Group& g : cache->groups)
-            if (need + g.pool.watermark > g.pool.n) return false;
+            if (need + g.pool.watermark > g.pool.n - (int)g.set_aside.size()) return false;
         return true;
     }
     bool try_start(Seq& s) {

@@ -8,7 +8,7 @@
 // are the narrow operand (MMA N = BN = 32 .. 256 tokens, rows beyond M zero-filled by TMA), so
 // a small batch does not waste the tensor core's fixed M and every weight byte is read once.
 // A block owns one tile of 128 weight rows (for SwiGLU: 64 gate rows and the 64 matching up
-// rows) and a slice of K.  When N is small there are too few tiles for 148 SMs, so K is cut
+// rows) and a slice of K.  When N is small there are too few tiles for the device's multiprocessors, so K is cut
 // into up to 8 slices whose blocks form a thread-block cluster: each block leaves its partial
 // tile in its own shared memory, and after a cluster barrier every block sums, for its share
 // of the tokens, the partials of all blocks through distributed shared memory in rank order
@@ -381,8 +381,9 @@ VAPI_EXPORT int vapi_linear_tc_plan(int N, int K, int M, int epi, int* tiles, in
     while (b < M) b *= 2;
     const int num_kb = (K + TC_BK - 1) / TC_BK;
     int s = 1;
-    if (t < 100 && b <= 128) {                       // too few tiles for 148 SMs: cut K (partials must fit the stages)
-        s = 148 / t;
+    const int sms = sm_count();
+    if (3 * t <= 2 * sms && b <= 128) {               // too few tiles for the multiprocessors: cut K (partials must fit the stages)
+        s = sms / t;
         if (s > 8) s = 8;                            // portable cluster size
         const int max_s = num_kb / 2 > 0 ? num_kb / 2 : 1;      // at least 2 k-blocks a slice
         if (s > max_s) s = max_s;

@@ -125,8 +125,12 @@ class Engine:
         return self.run_ahead and not self._needs_host and self.scheduler.can_run_ahead()
 
     def _resolve(self, plan: StepPlan, pending: PendingSample, out: StepOutput) -> None:
-        """Read a step's sampled tokens, hand them to the scheduler and report them."""
+        """Read a step's sampled tokens, hand them to the scheduler and report them.  The
+        kernels' status word comes with the tokens: if a kernel of the step (or of any step
+        since the word was last read) refused an index or gave up a wait, the tokens are not
+        trusted and the step counts as failed."""
         toks = self.sampler.finish(pending)
+        self._check_status(pending.status)
         took = self.scheduler.resolve(plan, toks)
         for sid, tok, ok in zip(plan.sampled_seqs, toks, took):
             if not ok:
@@ -139,6 +143,18 @@ class Engine:
                 out.new_tokens[seq.request_id] = tok
         self.stats.tokens_out += sum(took)
 
+    def _check_status(self, code: int) -> None:
+        """Raise for a non-zero status word.  On a CUDA device the word is the one that came to
+        the host with the sampled tokens; a device whose memory the host can read is asked
+        directly."""
+        status = getattr(self.runner, "status", None)
+        if status is None:
+            return
+        if not status.is_cuda:
+            code = int(status[0])
+        if code:
+            self.runner.raise_on_status(code)
+
     def _settle(self, out: StepOutput) -> None:
         """Resolve the step in flight, if there is one."""
         if self._inflight is not None:
@@ -146,8 +162,28 @@ class Engine:
             self._inflight = None
             self._resolve(plan, pending, out)
 
+    def _fail(self, exc: Exception, out: StepOutput) -> StepOutput:
+        """A step failed (the step function raised, or a kernel left a status): every request in
+        flight ends with ``error`` and gives back what it holds; the engine goes on serving.
+        After ``max_step_failures`` failures in a row the error is passed on."""
+        self.last_error = f"{type(exc).__name__}: {exc}"
+        self.stats.failed_steps += 1
+        self._failures_in_a_row += 1
+        self._inflight = None
+        self.scheduler.fail_all()
+        out.finished = self._drain()
+        if self._failures_in_a_row >= self.max_step_failures:
+            raise exc
+        return out
+
     def step(self) -> StepOutput:
         out = StepOutput()
+        try:
+            return self._step(out)
+        except Exception as exc:
+            return self._fail(exc, out)
+
+    def _step(self, out: StepOutput) -> StepOutput:
         t0 = time.perf_counter()
         if self._inflight is not None and not self._can_run_ahead():
             self._settle(out)
@@ -162,35 +198,27 @@ class Engine:
             return out
         out.did_work = True
         out.num_tokens = plan.num_tokens
-        try:
-            logits = self.step_fn(plan)
-            t2 = time.perf_counter()
-            rows = [(self.scheduler.seqs[s].params, self.states[s]) for s in plan.sampled_seqs]
-            ahead = (self.run_ahead and not self._needs_host and logits is not None and logits.is_cuda
-                     and bool(rows))
-            if not rows:
-                pending = PendingSample(0, tokens=[])
-            elif ahead:
-                pending = self.sampler.launch(logits, rows, self.runner.sampled)
-            else:
-                self._settle(out)        # the host needs this step's logits: nothing may be ahead of it
-                pending = PendingSample(len(rows), tokens=self.sampler.sample(logits, rows))
-                for sid, lp in zip(plan.sampled_seqs, self.sampler.last_logprobs):
-                    if lp is not None and sid in self._logprobs:
-                        self._logprobs[sid].append(lp)
-            self.scheduler.advance(plan)
-            t3 = time.perf_counter()
-        except Exception as exc:
-            self.last_error = f"{type(exc).__name__}: {exc}"
-            self.stats.failed_steps += 1
-            self._failures_in_a_row += 1
-            self._inflight = None
-            self.scheduler.fail_all()
-            out.finished = self._drain()
-            if self._failures_in_a_row >= self.max_step_failures:
-                raise
-            return out
-        self._failures_in_a_row = 0
+        logits = self.step_fn(plan)
+        t2 = time.perf_counter()
+        rows = [(self.scheduler.seqs[s].params, self.states[s]) for s in plan.sampled_seqs]
+        ahead = (self.run_ahead and not self._needs_host and logits is not None and logits.is_cuda
+                 and bool(rows))
+        block = getattr(self.runner, "status_and_sampled", None)
+        if not rows:
+            pending = PendingSample(0, tokens=[])
+        elif ahead:
+            pending = self.sampler.launch(logits, rows, self.runner.sampled, block)
+        else:
+            self._settle(out)        # the host needs this step's logits: nothing may be ahead of it
+            on_device = logits is not None and logits.is_cuda and block is not None
+            toks = self.sampler.sample(logits, rows, self.runner.sampled if on_device else None,
+                                       block if on_device else None)
+            pending = PendingSample(len(rows), tokens=toks, status=self.sampler.last_status if on_device else 0)
+            for sid, lp in zip(plan.sampled_seqs, self.sampler.last_logprobs):
+                if lp is not None and sid in self._logprobs:
+                    self._logprobs[sid].append(lp)
+        self.scheduler.advance(plan)
+        t3 = time.perf_counter()
         if self._inflight is not None:
             self.stats.ahead_steps += 1
         self._settle(out)
@@ -198,6 +226,7 @@ class Engine:
             self._inflight = (plan, pending)
         else:
             self._resolve(plan, pending, out)
+        self._failures_in_a_row = 0
         t4 = time.perf_counter()
         st = self.stats
         st.steps += 1

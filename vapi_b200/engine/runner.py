@@ -69,10 +69,14 @@ class ModelRunner:
         width = -(-width // 4) * 4
         self.packer = StepPacker(self.cache, self.device, self.max_batched_tokens,
                                  max(max_requests, 1) , width)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # The kernels' status word and the sampled tokens share one buffer, word first, so that the
+        # word travels to the host in the same copy as a step's tokens.
+        self.status_and_sampled = torch.zeros(1 + max(256, max_requests), dtype=torch.int32, device=self.device)
+        #: non-zero once a kernel refused an index or gave up a bounded wait (see :data:`STATUS_NAMES`)
+        self.status = self.status_and_sampled[:1]
         #: the tokens the last step sampled on the device, one per wanted row.  A step that is
         #: enqueued before the host has read them takes its input tokens from here.
-        self.sampled = torch.zeros(max(256, max_requests), dtype=torch.int32, device=self.device)
+        self.sampled = self.status_and_sampled[1:]
         # one CacheView skeleton per run-order entry
         self._site_of: List[Optional[int]] = []
         for i, call in enumerate(plan.order):
@@ -237,10 +241,12 @@ class ModelRunner:
 
     # ---- captured decode steps --------------------------------------------------------
     def _bucket(self, S: int) -> int:
+        """The fixed shape a decode step of S sequences is padded to: the next power of two, but
+        never more than the packer and the scratch buffers were sized for."""
         b = 1
         while b < S:
             b *= 2
-        return b
+        return min(b, self.graph_max_batch)
 
     def _capture(self, B: int):
         """Capture the device work of a pure decode step of B sequences into a CUDA graph
@@ -251,7 +257,7 @@ class ModelRunner:
         if self.packer._pad_pages is None:
             pages = self.cache.set_aside_pages()
             if pages is None:
-                return None
+                raise RuntimeError("no page can be set aside for the padding rows")
             self.packer.set_pad_pages(pages)
         width = self.packer.max_width
         ctx = self.packer.pack([], self.dtype, n_cap=B, s_cap=B, width=width, status=self.status)
@@ -314,17 +320,23 @@ class ModelRunner:
                           self.max_context)
         B = self._bucket(S)
         if B not in self._graphs:
+            if self.packer._pad_pages is None and self.cache.paged:
+                pages = self.cache.set_aside_pages()
+                if pages is None:         # no page to spare for padding rows: no bucket can be captured
+                    self._graphs_off = True
+                    return None
+                self.packer.set_pad_pages(pages)
             try:
                 self._graphs[B] = self._capture(B)
-            except Exception as exc:      # capture failed: run eagerly from now on
+            except Exception as exc:      # this bucket decodes eagerly; the others keep their graphs
                 import warnings
-                warnings.warn(f"CUDA graph capture failed ({exc}); decoding eagerly")
-                self._graphs_off = True
-                torch.cuda.synchronize()
-                return None
-            if self._graphs[B] is None:
-                self._graphs_off = True
-                return None
+                warnings.warn(f"CUDA graph capture of a decode step of {B} sequences failed ({exc}); "
+                              f"steps of that size run eagerly")
+                self._graphs[B] = None
+                if self.device.type == "cuda":
+                    torch.cuda.synchronize()
+        if self._graphs[B] is None:
+            return None
         graph, logits, kernels = self._graphs[B]
         self.packer.pack(entries, self.dtype, n_cap=B, s_cap=B, width=self.packer.max_width, status=self.status,
                          plan=plan)
@@ -336,10 +348,27 @@ class ModelRunner:
 
     def check_status(self) -> None:
         """Raise if a kernel met an index it refused to follow (a bad token id, slot or
-        page): the host validation should have caught it first."""
-        code = int(self.status.item())
+        page: the host validation should have caught it first) or gave up a bounded wait."""
+        self.raise_on_status(int(self.status.item()))
+
+    def raise_on_status(self, code: int) -> None:
+        """Turn a status word that was read from the device into a :class:`KernelRefusal` and
+        clear the word on the device.  The engine loop calls this with the word that came to the
+        host beside a step's sampled tokens, so generation costs no copy or wait of its own."""
         if code:
             self.status.zero_()
-            names = {1: "token id outside the vocabulary", 2: "cache slot outside the pool",
-                     3: "state slot outside the pool", 4: "page id outside the pool"}
-            raise RuntimeError(f"a kernel refused an index: {names.get(code, code)}")
+            raise KernelRefusal(code)
+
+
+#: what the kernels write into the status word
+STATUS_NAMES = {1: "token id outside the vocabulary", 2: "cache slot outside the pool",
+                3: "state slot outside the pool", 4: "page id outside the pool",
+                16: "a bounded wait inside a kernel ran out, and the kernel left its output unwritten"}
+
+
+class KernelRefusal(RuntimeError):
+    """A kernel of the step recorded a status: what the step produced cannot be trusted."""
+
+    def __init__(self, code: int):
+        self.code = int(code)
+        super().__init__(f"a kernel refused to go on: {STATUS_NAMES.get(self.code, f'status {self.code}')}")

@@ -141,6 +141,20 @@ def _f32(t: Optional[torch.Tensor], what: str) -> None:
         raise KernelError(f"{what} must be contiguous float32")
 
 
+_sm_counts: Dict[int, int] = {}
+
+
+def sm_count() -> int:
+    """Multiprocessors of the current CUDA device, asked of the device (once per device)."""
+    if not torch.cuda.is_available():
+        raise KernelError("vapi_b200 kernels need a CUDA device; there is no CPU fallback")
+    dev = torch.cuda.current_device()
+    n = _sm_counts.get(dev)
+    if n is None:
+        n = _sm_counts[dev] = int(torch.cuda.get_device_properties(dev).multi_processor_count)
+    return n
+
+
 # ---------------------------------------------------------------------------------------
 def embed(table: torch.Tensor, tokens: torch.Tensor, status: Optional[torch.Tensor] = None,
           next_weight: Optional[torch.Tensor] = None):
@@ -568,7 +582,7 @@ def decode_attention_limits() -> Tuple[int, int]:
     if _decode_limits is None:
         lib = _lib("attention")
         lib.vapi_attention_use_decode_kernel(1 if DECODE_ATTENTION == "tma" else 0)
-        _decode_limits = (int(lib.vapi_decode_attention_slots()) or 148 * 3, int(lib.vapi_decode_attention_cluster()))
+        _decode_limits = (int(lib.vapi_decode_attention_slots()) or sm_count() * 3, int(lib.vapi_decode_attention_cluster()))
     return _decode_limits
 
 
@@ -591,8 +605,8 @@ def decode_attention_combines(num_seqs: int, nkv: int, splits: int) -> bool:
 def attention_splits(num_seqs: int, max_q: int, max_k: int, nh: int, nkv: int, decode_kernel: bool = False) -> int:
     """How many blocks share the keys of one row tile: 1 unless the step is so small that
     the device would sit idle (decode of few sequences over long contexts).  A block of the
-    one-warp flash kernel has 48 KB of shared memory, so 4 fit on an SM: aim at one full wave of
-    148 x 4 blocks, each with at least 128 keys.
+    one-warp flash kernel has 48 KB of shared memory, so 4 fit on a multiprocessor: aim at one
+    full wave of 4 blocks on each, every block with at least 128 keys.
 
     The decode kernel (measured at head size 64, 8 kv heads, context 4096 and 32768): while the
     (sequence, kv head) pairs are fewer than two blocks per SM, slices up to that many blocks, and
@@ -614,9 +628,10 @@ def attention_splits(num_seqs: int, max_q: int, max_k: int, nh: int, nkv: int, d
         if want > cluster and (key_tiles <= 32 * cluster or 3 * blocks * cluster >= slots):
             want = cluster
         return max(1, min(want, by_len, 32))
-    if rows > 16 and blocks >= 148:
+    sms = sm_count()
+    if rows > 16 and blocks >= sms:
         return 1
-    want = max(1, 592 // blocks)
+    want = max(1, 4 * sms // blocks)
     by_len = max(1, max_k // 128)
     return max(1, min(want, by_len, 32))
 
@@ -821,8 +836,9 @@ def sample_rows(logits: torch.Tensor, mode: Optional[torch.Tensor] = None,
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     # few rows over a large vocabulary: cut each row into slices so that more than `rows` blocks work
     slices = 1
-    if rows < 592 and vocab >= 8192:
-        slices = max(1, min(32, 592 // rows, vocab // 2048))
+    wave = 4 * sm_count()
+    if rows < wave and vocab >= 8192:
+        slices = max(1, min(32, wave // rows, vocab // 2048))
     part_v = part_i = counters = None
     if slices > 1:
         part_v, part_i, counters = _sample_scratch(logits.device, rows, slices)

@@ -122,6 +122,8 @@ class PendingSample:
     host: Optional[torch.Tensor] = None         # pinned int32 buffer the copy lands in
     event: Optional["torch.cuda.Event"] = None
     tokens: Optional[List[int]] = None          # set when the tokens are already on the host
+    with_status: bool = False                   # the copy starts with the kernels' status word
+    status: int = 0                             # that word, once :meth:`Sampler.finish` has read it
 
 
 class Sampler:
@@ -137,6 +139,8 @@ class Sampler:
         self._next = 0
         #: per row of the last :meth:`sample` call: None, or the :class:`TokenLogprobs` it asked for
         self.last_logprobs: List[Optional[TokenLogprobs]] = []
+        #: the kernels' status word as the last :meth:`sample` call read it (0 without a status block)
+        self.last_status = 0
         self._out: Optional[torch.Tensor] = None
 
     @staticmethod
@@ -150,7 +154,7 @@ class Sampler:
         """The next set of pinned staging buffers (results, per-row sampling data) with the event
         that says the copies of their last use are done."""
         if not self._ring:
-            cap = max(self.max_rows, out.numel())
+            cap = max(self.max_rows, out.numel()) + 1
             for _ in range(3):
                 self._ring.append([torch.zeros(cap, dtype=torch.int32, pin_memory=True),
                                    torch.zeros(cap * self._META_BYTES, dtype=torch.uint8, pin_memory=True),
@@ -166,11 +170,18 @@ class Sampler:
     _META_BYTES = 36
 
     def launch(self, logits: torch.Tensor, rows: Sequence[Tuple[SamplingParams, SamplerState]],
-               out: torch.Tensor) -> PendingSample:
+               out: torch.Tensor, status_block: Optional[torch.Tensor] = None) -> PendingSample:
         """Decide every row on the device into ``out`` (penalties, if any, must already have been
-        applied to ``logits``) and start the copy to the host without waiting for it."""
+        applied to ``logits``) and start the copy to the host without waiting for it.
+
+        ``status_block`` is a buffer whose first word is the kernels' status word and whose rest is
+        ``out``: the word then comes to the host in the same copy as the tokens, so whoever reads
+        the tokens learns at no cost whether a kernel of the step refused to go on."""
         R = len(rows)
         assert logits.shape[0] >= R
+        if status_block is not None and (status_block.dtype != torch.int32
+                                         or status_block.data_ptr() + 4 != out.data_ptr()):
+            raise ValueError("the status block must be the int32 word right before the output tokens")
         entry = self._ring_entry(out)
         host, meta_host, event = entry[0], entry[1], entry[2]
         self.h2d_bytes_last = 0
@@ -209,24 +220,33 @@ class Sampler:
                 ops.sample_rows(logits[:R], d32i[0], d32f[0], d64[0], d64[1], out=out[:R])
             if cut:
                 ops.sample_truncated(logits[:R], d32f[0], d32i[1], d32f[1], d32f[2], d64[0], d64[1], out=out[:R])
-        host[:R].copy_(out[:R], non_blocking=True)
+        if status_block is not None:
+            host[:R + 1].copy_(status_block[:R + 1], non_blocking=True)
+        else:
+            host[:R].copy_(out[:R], non_blocking=True)
         event.record(torch.cuda.current_stream())
         entry[3] = True
-        self.d2h_bytes_last = 4 * R
-        return PendingSample(R, host, event)
+        self.d2h_bytes_last = 4 * (R + (status_block is not None))
+        return PendingSample(R, host, event, with_status=status_block is not None)
 
     def finish(self, pending: PendingSample) -> List[int]:
         """Wait for a launched sample and return its tokens."""
         if pending.tokens is not None:
             return pending.tokens
         pending.event.synchronize()
-        pending.tokens = pending.host[:pending.rows].tolist()
+        if pending.with_status:
+            words = pending.host[:pending.rows + 1].tolist()
+            pending.status, pending.tokens = words[0], words[1:]
+        else:
+            pending.tokens = pending.host[:pending.rows].tolist()
         return pending.tokens
 
-    def sample(self, logits: torch.Tensor, rows: Sequence[Tuple[SamplingParams, SamplerState]]) -> List[int]:
+    def sample(self, logits: torch.Tensor, rows: Sequence[Tuple[SamplingParams, SamplerState]],
+               out: Optional[torch.Tensor] = None, status_block: Optional[torch.Tensor] = None) -> List[int]:
         """Tokens for the rows of a step, waiting for them: raw rows are read back for requests
         that report logprobs, penalties are applied on the device, and every row is then decided
-        as :meth:`launch` decides it (logits on the host: by the host restatement)."""
+        as :meth:`launch` decides it (logits on the host: by the host restatement).  ``out`` and
+        ``status_block`` as for :meth:`launch`; the status word read is left in ``last_status``."""
         R = len(rows)
         assert logits.shape[0] >= R
         dev = logits.device
@@ -239,9 +259,13 @@ class Sampler:
                 raw[r] = (lse, top, row)
         extra_h2d = self._penalise(logits, rows, dev)
         if logits.is_cuda:
-            if self._out is None or self._out.numel() < R or self._out.device != dev:
-                self._out = torch.zeros(max(self.max_rows, R), dtype=torch.int32, device=dev)
-            toks = self.finish(self.launch(logits, rows, self._out))
+            if out is None or out.numel() < R:
+                if self._out is None or self._out.numel() < R or self._out.device != dev:
+                    self._out = torch.zeros(max(self.max_rows, R), dtype=torch.int32, device=dev)
+                out, status_block = self._out, None
+            pending = self.launch(logits, rows, out, status_block)
+            toks = self.finish(pending)
+            self.last_status = pending.status
             self.h2d_bytes_last += extra_h2d
         else:
             toks = self._choose_on_host(logits, rows)
