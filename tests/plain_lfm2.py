@@ -84,9 +84,9 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1)
 
 
-def attention(a: torch.Tensor, w: Dict[str, torch.Tensor], pre: str, c: dict, pos0: int = 0) -> torch.Tensor:
-    """Whole-sequence causal GQA with per-head q/k RMSNorm and RoPE
-    (lfm2.rs:343-406; masking and softmax as attention.rs:90-163)."""
+def attention_heads(a: torch.Tensor, w: Dict[str, torch.Tensor], pre: str, c: dict, pos0: int = 0):
+    """q, k, v of a whole sequence as [T, heads, d], q and k normed per head and rotated
+    (lfm2.rs:343-376)."""
     T = a.shape[0]
     nh, nkv, d = c["heads"], c["kv_heads"], c["head_dim"]
     q = (a @ w[pre + "q_proj.weight"].T).view(T, nh, d)
@@ -95,17 +95,32 @@ def attention(a: torch.Tensor, w: Dict[str, torch.Tensor], pre: str, c: dict, po
     q = rmsnorm(q, w[pre + "q_layernorm.weight"], c["eps"])                             # :364
     k = rmsnorm(k, w[pre + "k_layernorm.weight"], c["eps"])                             # :365
     cos, sin = rope_tables(torch.arange(pos0, pos0 + T), d, c["theta"], a.dtype)
-    q, k = rope(q, cos, sin), rope(k, cos, sin)
-    rep = nh // nkv
+    return rope(q, cos, sin), rope(k, cos, sin), v
+
+
+def attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int = 0) -> torch.Tensor:
+    """Causal softmax attention of q [T, nh, d] over k, v [T, nkv, d]; query head h reads kv head
+    h // (nh / nkv); with a window only the last ``window`` keys up to the query's own position are
+    seen (attention.rs:87-163)."""
+    T, nh, d = q.shape
+    rep = nh // k.shape[1]
     k = k.repeat_interleave(rep, dim=1)                                                 # head h -> kv head h // rep
     v = v.repeat_interleave(rep, dim=1)
-    scale = 1.0 / math.sqrt(d)                                                          # :377
+    scale = 1.0 / math.sqrt(d)                                                          # lfm2.rs:377
     s = torch.einsum("thd,shd->hts", q, k) * scale
     mask = torch.ones(T, T, dtype=torch.bool).tril()                                    # key i <= query position
+    if window > 0:
+        mask &= ~torch.ones(T, T, dtype=torch.bool).tril(-window)                      # and i > position - window
     s = s.masked_fill(~mask[None], float("-inf"))
     p = torch.softmax(s, dim=-1)
-    y = torch.einsum("hts,shd->thd", p, v).reshape(T, nh * d)
-    return y @ w[pre + "out_proj.weight"].T
+    return torch.einsum("hts,shd->thd", p, v).reshape(T, nh * d)
+
+
+def attention(a: torch.Tensor, w: Dict[str, torch.Tensor], pre: str, c: dict, pos0: int = 0) -> torch.Tensor:
+    """Whole-sequence causal GQA with per-head q/k RMSNorm and RoPE
+    (lfm2.rs:343-406; masking and softmax as attention.rs:90-163)."""
+    q, k, v = attention_heads(a, w, pre, c, pos0)
+    return attend(q, k, v) @ w[pre + "out_proj.weight"].T
 
 
 def shortconv(a: torch.Tensor, w: Dict[str, torch.Tensor], pre: str, c: dict) -> torch.Tensor:
@@ -179,6 +194,19 @@ class PlainLfm2:
         out = []
         for _ in range(steps):
             nxt = int(torch.argmax(self.logits(toks)[-1]).item())   # first index wins ties (sampler.rs:285-295)
+            out.append(nxt)
+            toks.append(nxt)
+        return out
+
+    def sample(self, prompt: Sequence[int], steps: int, temperature: float, seed: int) -> List[int]:
+        """Temperature sampling by the Gumbel-max rule with the reference's noise: the k-th generated
+        token is argmax(logits / T + g(seed, k)) (crates/vapi-backend-candle/src/fused.rs:236-293)."""
+        from plain_ops import gumbel_noise
+        toks, out = list(prompt), []
+        for k in range(steps):
+            row = self.logits(toks)[-1]
+            g = gumbel_noise(seed & ((1 << 64) - 1), k, row.numel())
+            nxt = int(torch.argmax(row.double() * float(torch.tensor(1.0 / temperature, dtype=torch.float32)) + g))
             out.append(nxt)
             toks.append(nxt)
         return out

@@ -140,7 +140,13 @@ def compare(tr: Trace, got: Dict[int, np.ndarray], ref: Dict[str, torch.Tensor],
             if d > worst[0]:
                 worst = (d, (step, rid, pos))
     limit = limit_for(dtype, span)
-    return worst[0] <= limit, f"worst |diff| {worst[0]:.3e} at (step, request, position) {worst[1]}; limit {limit:.3e}, logit range {span:.2f}"
+    msg = (f"worst |diff| {worst[0]:.3e} ({worst[0] / span:.2e} of the logit range) at (step, request, position) "
+           f"{worst[1]}; limit {limit:.3e}, logit range {span:.2f}")
+    report = os.environ.get("VAPI_TEST_REPORT")
+    if report:                   # a table of the deviations that the runs really had
+        with open(report, "a") as f:
+            f.write(f"{os.environ.get('PYTEST_CURRENT_TEST', '?').split(' ')[0]}\t{dtype}\t{worst[0] / span:.3e}\t{worst[0]:.3e}\t{span:.2f}\n")
+    return worst[0] <= limit, msg
 
 
 def limit_for(dtype: str, span: float) -> float:

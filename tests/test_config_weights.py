@@ -6,7 +6,8 @@ import pytest
 import torch
 
 from conftest import TINY_A, TINY_B
-from vapi_b200.config import (ConfigError, Lfm2Config, registered_architectures, resolve_architecture)
+from vapi_b200.config import ConfigError, registered_architectures, resolve_architecture
+from vapi_b200.models.lfm2 import Lfm2Config
 from vapi_b200.config.runtime import RuntimeConfig, RuntimeConfigError
 from vapi_b200.weights import WeightError, load_tensors, write_random_model
 

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import plain_lfm2
-from conftest import TINY_A, TINY_B
+from conftest import TINY_A, TINY_A0, TINY_B, TINY_B0
 from vapi_b200.engine.engine import Engine
 from vapi_b200.engine.runner import ModelRunner
 from vapi_b200.engine.scheduler import SchedulerConfig
@@ -81,6 +81,28 @@ def test_greedy_generation_matches_the_plain_model(tiny_dirs, plain_kernels):
         assert done[i].reason == FinishReason.LENGTH
     eng.runner.cache.check_invariants()
     assert eng.runner.cache.slots.num_free == 4
+
+
+def test_the_two_described_tiny_workloads(tiny_dirs, plain_kernels):
+    """The tiny configurations as the benchmark description words them, with its workloads: A with
+    prompts of 1, 7 and 33 tokens (seed 1) and 16 greedy steps; B (one kv head of 16, vocabulary 512,
+    256 positions, an untied head) with three requests of 5, 40 and 97 tokens as a mixed batch,
+    prompts cut into portions of 16, sampled at temperature 0.8 with seed 3."""
+    plain = plain_lfm2.PlainLfm2(tiny_dirs["A0"])
+    eng = _engine(tiny_dirs["A0"], prefill_chunk_tokens=16, max_context=128)
+    prompts = _prompts(TINY_A0, 1, [1, 7, 33])
+    for i, p in enumerate(prompts):
+        eng.admit(i, p, SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True))
+    done = {f.request_id: f for f in eng.run()}
+    assert [done[i].tokens for i in range(3)] == [plain.greedy(p, 16) for p in prompts]
+    plain = plain_lfm2.PlainLfm2(tiny_dirs["B0"])
+    eng = _engine(tiny_dirs["B0"], num_pages=24, prefill_chunk_tokens=16, max_context=256)
+    prompts = _prompts(TINY_B0, 3, [5, 40, 97])
+    for i, p in enumerate(prompts):
+        eng.admit(i, p, SamplingParams(temperature=0.8, seed=3, max_tokens=6, ignore_eos=True))
+    done = {f.request_id: f for f in eng.run()}
+    assert [done[i].tokens for i in range(3)] == [plain.sample(p, 6, 0.8, 3) for p in prompts]
+    assert eng.stats.steps > 7, "prompts were cut into portions and decoded beside one another"
 
 
 def test_preemption_recomputes_to_the_same_tokens(tiny_dirs, plain_kernels):

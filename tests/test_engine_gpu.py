@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import plain_lfm2
-from conftest import TINY_A, TINY_B, TINY_C, TINY_D
+from conftest import TINY_A, TINY_A0, TINY_B, TINY_B0, TINY_C, TINY_D
 
 pytestmark = pytest.mark.gpu
 
@@ -42,6 +42,37 @@ def test_greedy_generation_float32(name, cfg, tiny_dirs):
         llm.runner.cache.check_invariants()
         if graphs:
             assert llm.runner._graphs, "pure decode steps must have gone through a captured graph"
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_the_two_described_tiny_workloads(tiny_dirs, dtype):
+    """The tiny configurations as the benchmark description words them, with its workloads, through
+    the entry point: A (prompts of 1, 7, 33 tokens, 16 greedy steps) and B (three requests of 5, 40
+    and 97 tokens as a mixed batch, portions of 16, temperature 0.8 with seed 3).  In float32 the
+    tokens are the plain model's; in bfloat16 (float32 checkpoint, bfloat16 activations and cache)
+    they may part only at a near-tie of the plain model."""
+    from vapi_b200 import LLM, SamplingParams
+    plain = plain_lfm2.PlainLfm2(tiny_dirs["A0"])
+    prompts = _prompts(TINY_A0, 1, [1, 7, 33])
+    llm = LLM(tiny_dirs["A0"], dtype=dtype, num_blocks=8, max_concurrent_seqs=4, max_batched_tokens=64, max_context=128,
+              prefill_chunk_tokens=16)
+    out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True))
+    llm.runner.check_status()
+    for p, c in zip(prompts, out):
+        want = plain.greedy(p, 16)
+        assert c.tokens == want or _agrees_up_to_a_near_tie(plain, p, c.tokens, want, gap=1e-3 if dtype == "f32" else 0.5)
+    plain = plain_lfm2.PlainLfm2(tiny_dirs["B0"])
+    prompts = _prompts(TINY_B0, 3, [5, 40, 97])
+    llm = LLM(tiny_dirs["B0"], dtype=dtype, num_blocks=8, max_concurrent_seqs=4, max_batched_tokens=64, max_context=256,
+              prefill_chunk_tokens=16)
+    out = llm.generate(prompts, SamplingParams(temperature=0.8, seed=3, max_tokens=10, ignore_eos=True))
+    llm.runner.check_status()
+    if dtype == "f32":
+        assert [c.tokens for c in out] == [plain.sample(p, 10, 0.8, 3) for p in prompts]
+    else:
+        assert all(len(c.tokens) == 10 for c in out)
+        again = llm.generate(prompts, SamplingParams(temperature=0.8, seed=3, max_tokens=10, ignore_eos=True))
+        assert [c.tokens for c in again] == [c.tokens for c in out]
 
 
 def test_greedy_generation_bfloat16(tiny_dirs, tmp_path):
@@ -219,6 +250,166 @@ def test_one_step_ahead_and_graphs_with_the_serving_kernels(tmp_path):
         assert _agrees_up_to_a_near_tie(plain, p, got, plain.greedy(p, len(got))), got
 
 
+@pytest.mark.parametrize("sizes", ["1.2b", "700m"])
+def test_captured_decode_at_serving_widths(sizes, tmp_path):
+    """Three layers of the serving models' widths in bfloat16 through the engine with captured
+    graphs, 12 and then 24 live requests: the buckets of 16 and 32 sequences (the sixteen-warp
+    weight-streaming product, the tcgen05 product, decode attention cut for the whole context,
+    padding rows).  Tokens follow the plain model up to near-ties, and the logits of a captured
+    step are those of an eager step within bfloat16 rounding."""
+    from conftest import serving_width_config
+    from vapi_b200 import LLM, SamplingParams
+    from vapi_b200.engine.runner import ModelRunner
+    from vapi_b200.engine.step import StepEntry
+    from vapi_b200.weights import write_random_model
+    cfg = serving_width_config(sizes)
+    d = write_random_model(str(tmp_path / "m"), cfg, 7, std=0.02, norm_init="perturbed", dtype=torch.bfloat16)
+    plain = plain_lfm2.PlainLfm2(d)
+    lens = [9, 33, 64, 17, 5, 40, 65, 12, 3, 28, 50, 21] * 2
+    prompts = _prompts(cfg, 11, lens)
+    span = float(plain.logits(prompts[1]).max() - plain.logits(prompts[1]).min())
+    for live in (12, 24):
+        llm = LLM(d, dtype="bf16", num_blocks=80, max_concurrent_seqs=32, max_batched_tokens=2048, max_context=256,
+                  prefill_chunk_tokens=512, cuda_graphs=True)
+        out = llm.generate(prompts[:live], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+        llm.runner.check_status()
+        bucket = 16 if live == 12 else 32
+        assert llm.runner._graphs.get(bucket) is not None, f"decode steps of {live} requests run as a graph of {bucket}"
+        for p, c in zip(prompts, out):
+            assert _agrees_up_to_a_near_tie(plain, p, c.tokens, plain.greedy(p, 4), gap=0.03 * span), c.tokens
+    # one decode step of 12 requests: captured against eager against the plain model
+    rows = {}
+    for graphs in (True, False):
+        r = ModelRunner.from_dir(d, dtype="bfloat16", num_pages=40, max_requests=16, max_batched_tokens=1024, max_context=256)
+        rcs = []
+        for i, p in enumerate(prompts[:12]):
+            rc = r.cache.open(i)
+            assert r.cache.reserve(rc, len(p) + 1)
+            rcs.append(rc)
+        r.step([StepEntry(rc, p, []) for rc, p in zip(rcs, prompts[:12])])
+        entries = [StepEntry(rc, [100 + i], [0]) for i, rc in enumerate(rcs)]
+        lg = r.step_decode_graph(entries) if graphs else r.step(entries)
+        assert lg is not None
+        rows[graphs] = lg.float().cpu().clone()
+        r.check_status()
+    want = torch.stack([plain.logits(p + [100 + i])[-1] for i, p in enumerate(prompts[:12])])
+    assert float((rows[True] - rows[False]).abs().max()) < 0.01 * span
+    assert float((rows[True] - want).abs().max()) < 0.02 * span
+
+
+def test_the_cache_is_sized_from_free_memory(tiny_dirs):
+    """Without a page count the runner takes a fraction of the free device memory, less the state
+    slots (crates/vapi-backend-candle/src/backend.rs:385-400), and never more pages than every
+    request at full context could use."""
+    from vapi_b200 import LLM, SamplingParams
+    from vapi_b200.engine.runner import ModelRunner
+    plain = plain_lfm2.PlainLfm2(tiny_dirs["D"])
+    free, _ = torch.cuda.mem_get_info()
+    fraction = 24e6 / free                                     # a budget of about 24 MB
+    r = ModelRunner.from_dir(tiny_dirs["D"], dtype="bfloat16", max_requests=64, max_batched_tokens=256, max_context=512,
+                             num_pages=None, kv_cache_fraction=fraction)
+    pages = r.cache.paged[0].pool.num_pages
+    page_bytes = r.cache.bytes_per_token() * r.cache.page_size
+    state_bytes = r.cache.state_bytes_per_request() * (64 + 1)
+    assert 0 < pages < 64 * 8, "the budget, not the cap, decided"
+    assert pages * page_bytes + state_bytes <= 24e6 * 1.01 and (pages + 1) * page_bytes + state_bytes > 24e6 * 0.95
+    assert r.cache.paged[0].tensor.numel() * r.cache.paged[0].tensor.element_size() == pages * page_bytes
+    # a generous fraction is capped by what the requests could ever use
+    r2 = ModelRunner.from_dir(tiny_dirs["D"], dtype="bfloat16", max_requests=4, max_batched_tokens=256, max_context=512,
+                              num_pages=None, kv_cache_fraction=0.5)
+    assert r2.cache.paged[0].pool.num_pages == 4 * 8
+    llm = LLM(tiny_dirs["D"], dtype="f32", max_concurrent_seqs=4, max_batched_tokens=256, max_context=256,
+              kv_cache_fraction=fraction)
+    p = _prompts(TINY_D, 3, [30, 9])
+    out = llm.generate(p, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    for q, c in zip(p, out):
+        want = plain.greedy(q, 6)
+        assert c.tokens == want or _agrees_up_to_a_near_tie(plain, q, c.tokens, want, gap=1e-3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_windowed_group_and_a_layer_that_reads_another_layers_cache(tmp_path, dtype):
+    """A plan from the package's own parts that LFM2 does not use: an attention layer with a
+    window of 40 keys (a cache group of its own, whose pages are given back as the window passes
+    them), and a run-order entry that reads the cache another entry owns (its own keys and values
+    are computed and dropped).  Whole, in portions, token by token, beside another request, with
+    so few pages that released pages are used again, against a plain restatement."""
+    from vapi_b200.config import Architecture, register_architecture, unregister_architecture
+    from vapi_b200.engine.runner import ModelRunner
+    from vapi_b200.engine.step import StepEntry
+    from vapi_b200.models.plan import LayerCall, ModelPlan
+    from vapi_b200.parts import (GQAttention, OutputHead, PreNormBlock, RMSNorm, RotaryEncoding, SwiGLU, TokenEmbedding)
+    from vapi_b200.weights import write_random_model
+    H, nh, nkv, hd, F, V, W, eps, theta = 64, 4, 2, 16, 96, 120, 40, 1e-5, 10000.0
+    sub = {"mixer_norm": "n1.", "mixer": "att.", "ffn_norm": "n2.", "ffn": "ffn."}
+
+    def plan(cfg):
+        emb = TokenEmbedding(V, H, "emb.weight")
+        att = lambda window: GQAttention(H, nh, nkv, hd, qk_norm_eps=eps, pos="rope", window=window)
+        layers = [PreNormBlock(RMSNorm(H, eps), att(w), RMSNorm(H, eps), SwiGLU(H, F, {"gate": "w1", "up": "w3", "down": "w2"}), sub)
+                  for w in (0, W, 0)]
+        # entry 2 reads the cache that entry 0 owns
+        return ModelPlan("ToyWindowForCausalLM", V, H, 512, emb, layers, ["l0.", "l1.", "l2."],
+                         [LayerCall(0), LayerCall(1), LayerCall(2, cache_of=0)], RMSNorm(H, eps), "final.",
+                         OutputHead(V, H, True, emb), position_encodings=[RotaryEncoding(hd, theta, 512, "rope")])
+
+    def plain_logits(w, toks):
+        c = dict(heads=nh, kv_heads=nkv, head_dim=hd, eps=eps, theta=theta)
+        x = w["emb.weight"][torch.tensor(toks)]
+        kv0 = None
+        for l, window in enumerate((0, W, 0)):
+            pre = f"l{l}."
+            a = plain_lfm2.rmsnorm(x, w[pre + "n1.weight"], eps)
+            q, k, v = plain_lfm2.attention_heads(a, w, pre + "att.", c)
+            if l == 0:
+                kv0 = (k, v)
+            if l == 2:
+                k, v = kv0
+            x = x + plain_lfm2.attend(q, k, v, window) @ w[pre + "att.out_proj.weight"].T
+            x = x + plain_lfm2.feed_forward(plain_lfm2.rmsnorm(x, w[pre + "n2.weight"], eps), w, pre + "ffn.")
+        return plain_lfm2.rmsnorm(x, w["final.weight"], eps) @ w["emb.weight"].T
+
+    register_architecture(Architecture("ToyWindowForCausalLM", ("toy_window",), lambda v: v, plan), replace=True)
+    try:
+        d = write_random_model(str(tmp_path / "toy"), {"architectures": ["ToyWindowForCausalLM"]}, 3, std=0.2,
+                               norm_init="perturbed", dtype=torch.float32 if dtype == "float32" else torch.bfloat16)
+        w = plain_lfm2.read_weights(d)
+        # 10 pages of 16 a group: the request of 150 tokens needs 10 in the group that keeps everything,
+        # and the windowed group serves it and its neighbour out of pages that keep coming back
+        r = ModelRunner.from_dir(d, dtype=dtype, num_pages=12, page_size=16, max_requests=3, max_batched_tokens=256,
+                                 max_context=256)
+        assert [g.spec.window for g in r.cache.paged] == [0, W] and [len(g.sites) for g in r.cache.paged] == [1, 1]
+        toks = torch.randint(0, V, (150,), generator=torch.Generator().manual_seed(5)).tolist()
+        want = plain_logits(w, toks)
+        span = float(want.max() - want.min())
+        tol = 1e-4 * max(1.0, span / 10) if dtype == "float32" else 0.04 * span
+        a = r.cache.open("whole")
+        assert r.cache.reserve(a, len(toks))
+        got = r.step([StepEntry(a, toks, list(range(len(toks))))]).cpu()
+        assert float((got - want).abs().max()) < tol
+        assert r.cache.paged[1].pool.num_free > r.cache.paged[0].pool.num_free, "the window released pages"
+        r.cache.close(a)
+        b, other = r.cache.open("cut"), r.cache.open("other")
+        rows, pos = [], 0
+        sizes = [2, 47, 1, 16, 33, 3] + [1] * 48
+        for q in sizes:
+            entries = [StepEntry(b, toks[pos:pos + q], list(range(q)))]
+            assert r.cache.reserve(b, pos + q)
+            if other.num_tokens < 30 and r.cache.reserve(other, other.num_tokens + 2):
+                entries.insert(0, StepEntry(other, [3, 4], []))
+            rows.append(r.step(entries).cpu())
+            pos += q
+        assert pos == len(toks)
+        assert float((torch.cat(rows) - want).abs().max()) < tol
+        r.check_status()
+        r.cache.close(b)
+        r.cache.close(other)
+        r.cache.check_invariants()
+        assert all(g.pool.num_free == g.pool.num_pages for g in r.cache.paged)
+    finally:
+        unregister_architecture("ToyWindowForCausalLM")
+
+
 def test_several_completions_per_prompt_and_logprobs(tiny_dirs):
     from vapi_b200 import LLM, SamplingParams
     prompts = _prompts(TINY_B, 8, [12, 30])
@@ -275,14 +466,39 @@ def test_randomized_serving_gives_the_same_tokens_however_it_is_scheduled(tiny_d
         assert not bad, (key, bad[:5])
 
 
-def test_penalties_change_what_is_generated(tiny_dirs):
+def test_penalties_give_the_tokens_of_the_plain_model_with_the_rule_applied_on_the_host(tiny_dirs):
+    """Repetition, frequency and presence penalties over the prompt's and the generated tokens
+    (crates/vapi-engine/src/sampler.rs:249-283): greedy generation with them must give exactly
+    the tokens of the plain model whose logits get the rule applied on the host."""
+    import plain_ops
     from vapi_b200 import LLM, SamplingParams
-    p = _prompts(TINY_A, 6, [12])
-    llm = LLM(tiny_dirs["A"], dtype="f32", num_blocks=8, max_concurrent_seqs=2, max_batched_tokens=64, max_context=128)
-    base = llm.generate(p, SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True))[0].tokens
-    pen = llm.generate(p, SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True, presence_penalty=2.0,
-                                         frequency_penalty=1.0))[0].tokens
-    assert len(set(pen)) >= len(set(base)) and pen != base
+    plain = plain_lfm2.PlainLfm2(tiny_dirs["B"])
+    prompts = _prompts(TINY_B, 6, [12, 30])
+    prompts[0] = prompts[0][:6] * 2                            # repeated tokens in the prompt count too
+    llm = LLM(tiny_dirs["B"], dtype="f32", num_blocks=8, max_concurrent_seqs=2, max_batched_tokens=64, max_context=128)
+    base = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True))
+    changed = 0
+    for rep, freq, pres in ((1.0, 1.0, 2.0), (1.7, 0.0, 0.0), (0.8, 0.3, 0.5)):
+        sp = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True, repetition_penalty=rep,
+                            frequency_penalty=freq, presence_penalty=pres)
+        out = llm.generate(prompts, sp)
+        for p, c, b0 in zip(prompts, out, base):
+            text, counts, want = list(p), {}, []
+            for t in p:
+                counts[t] = counts.get(t, 0) + 1
+            for _ in range(24):
+                row = plain.logits(text)[-1:].clone()
+                toks = sorted(counts)
+                plain_ops.apply_penalties(row, torch.zeros(len(toks), dtype=torch.int32), torch.tensor(toks, dtype=torch.int32),
+                                          torch.tensor([float(counts[t]) for t in toks]), torch.tensor([rep]),
+                                          torch.tensor([freq]), torch.tensor([pres]))
+                nxt = int(torch.argmax(row[0]))
+                want.append(nxt)
+                text.append(nxt)
+                counts[nxt] = counts.get(nxt, 0) + 1
+            assert c.tokens == want or _agrees_up_to_a_near_tie(plain, p, c.tokens, want, gap=1e-3), (rep, freq, pres)
+            changed += c.tokens != b0.tokens
+    assert changed >= 4, "the penalties must change what is generated"
 
 
 # ---- each part alone -----------------------------------------------------------------------
@@ -363,15 +579,56 @@ def test_parts_alone(dtype):
 
 
 # ---- a toy mixer with state of its own --------------------------------------------------------
-def test_a_toy_mixer_with_its_own_state_can_be_registered_built_and_stepped(tmp_path):
+def _whole_cut_and_token_by_token(r, toks, vocab, limit, graphs):
+    """One request whole in one step (more rows than the few-row route takes), then the same
+    tokens in portions beside another request, the last ones one by one (through captured decode
+    steps when ``graphs``); returns the worst difference between the two, which must stay below
+    ``limit`` times the logit range."""
+    from vapi_b200.engine.step import StepEntry
+    n = len(toks)
+    a = r.cache.open("whole")
+    assert r.cache.reserve(a, n)
+    whole = r.step([StepEntry(a, toks, list(range(n)))]).cpu()
+    r.cache.close(a)
+    b, other = r.cache.open("cut"), r.cache.open("other")       # `cut` lands in the slot `whole` used
+    rows, pos = [], 0
+    for q in (2, 1, 9, 1, 1, 16, 3):
+        assert r.cache.reserve(b, pos + q) and r.cache.reserve(other, other.num_tokens + 2)
+        out = r.step([StepEntry(other, [5, 6], []), StepEntry(b, toks[pos:pos + q], list(range(q)))])
+        rows.append(out.cpu())
+        pos += q
+    used_graph = 0
+    while pos < n:                                             # the rest token by token, two requests a step
+        assert r.cache.reserve(b, pos + 1) and r.cache.reserve(other, other.num_tokens + 1)
+        entries = [StepEntry(other, [7], [0]), StepEntry(b, toks[pos:pos + 1], [0])]
+        out = r.step_decode_graph(entries) if graphs else None
+        used_graph += out is not None
+        if out is None:
+            out = r.step(entries)
+        rows.append(out[1:2].clone().cpu())
+        pos += 1
+    if graphs:
+        assert used_graph > 0, "decode steps must have gone through a captured graph"
+    r.check_status()
+    span = float(whole.max() - whole.min())
+    worst = float((torch.cat(rows) - whole).abs().max())
+    assert worst < limit * max(span, 1.0), (worst, span)
+    return whole
+
+
+@pytest.mark.parametrize("dtype,hidden", [("float32", 48), ("bfloat16", 64)])
+def test_a_toy_mixer_with_its_own_state_can_be_registered_built_and_stepped(tmp_path, dtype, hidden):
     """A running-mean mixer defined here: state = (sum of inputs so far) per request.  It gets
     a state slot from the cache manager, a registry entry, an architecture of its own, and
     runs through the package's step function, portions and decode tokens alike; the
     package's files are not touched.  Its math is plain torch on the device, which is the
-    toy's own business; everything around it is the engine."""
+    toy's own business; everything around it is the engine.
+
+    In bfloat16 (widths that the package's own decode products take) steps of few rows run the
+    blocks in their stream form: the toy mixer has none, so it is run the ordinary way between the
+    package's feed-forwards, which add into the stream themselves; captured decode steps too."""
     from vapi_b200.config import Architecture, register_architecture, unregister_architecture
     from vapi_b200.engine.runner import ModelRunner
-    from vapi_b200.engine.step import StepEntry
     from vapi_b200.models.plan import LayerCall, ModelPlan
     from vapi_b200.parts import (Mixer, OutputHead, PreNormBlock, RMSNorm, StateSpec, SwiGLU, TensorSpec,
                                  TokenEmbedding, register_mixer, make_part, MIXERS)
@@ -391,6 +648,11 @@ def test_a_toy_mixer_with_its_own_state_can_be_registered_built_and_stepped(tmp_
             self.gain = tensors[prefix + "gain"]
 
         def forward(self, a, ctx, cache):
+            if ctx.max_q == 1:               # one token a sequence: no host round trip, so a graph can hold it
+                slots, first = ctx.state_slots.long(), (ctx.positions == 0)[:, None]
+                run = torch.where(first, torch.zeros_like(a, dtype=torch.float32), cache.tensor[slots]) + a.float()
+                cache.tensor.index_copy_(0, slots, run)
+                return (run / (ctx.positions + 1)[:, None] * self.gain).to(a.dtype)
             out = torch.empty_like(a)
             cu, pos, slots = ctx.cu_q.tolist(), ctx.positions.tolist(), ctx.state_slots.tolist()
             for s in range(ctx.num_seqs):
@@ -418,38 +680,41 @@ def test_a_toy_mixer_with_its_own_state_can_be_registered_built_and_stepped(tmp_
 
     register_architecture(Architecture("ToyForCausalLM", ("toy",), lambda v: v, plan), replace=True)
     try:
-        cfg = {"architectures": ["ToyForCausalLM"], "vocab_size": 100, "hidden_size": 48, "ff": 64}
-        d = write_random_model(str(tmp_path / "toy"), cfg, 0, std=0.3, norm_init="perturbed")
-        r = ModelRunner.from_dir(d, dtype="float32", num_pages=4, max_requests=3, max_batched_tokens=64, max_context=128)
-        assert len(r.cache.state) == 1 and r.cache.state[0].tensor.shape == (4, 3, 48) and not r.cache.paged
-        toks = torch.randint(0, 100, (30,), generator=torch.Generator().manual_seed(0)).tolist()
-        a = r.cache.open("whole")
-        whole = r.step([StepEntry(a, toks, list(range(30)))]).cpu()
-        r.cache.close(a)
-        b, c2 = r.cache.open("cut"), r.cache.open("other")     # `cut` lands in the slot `whole` used
-        rows, pos = [], 0
-        for q in (2, 1, 9, 1, 1, 16):
-            other = StepEntry(c2, [5] * 3, [])                 # another request alongside, in its own slot
-            out = r.step([other, StepEntry(b, toks[pos:pos + q], list(range(q)))])
-            rows.append(out.cpu())
-            pos += q
-        assert (torch.cat(rows) - whole).abs().max() < 1e-4
+        cfg = {"architectures": ["ToyForCausalLM"], "vocab_size": 100, "hidden_size": hidden, "ff": 64}
+        d = write_random_model(str(tmp_path / "toy"), cfg, 0, std=0.3, norm_init="perturbed",
+                               dtype=torch.float32 if dtype == "float32" else torch.bfloat16)
+        toks = torch.randint(0, 100, (45,), generator=torch.Generator().manual_seed(0)).tolist()
+        r = ModelRunner.from_dir(d, dtype=dtype, num_pages=4, max_requests=3, max_batched_tokens=64, max_context=128)
+        assert len(r.cache.state) == 1 and r.cache.state[0].tensor.shape == (4, 3, hidden) and not r.cache.paged
+        if dtype == "float32":
+            _whole_cut_and_token_by_token(r, toks, 100, 1e-5, graphs=False)
+        else:
+            from vapi_b200 import ops
+            assert ops.few_rows_applies(2, r.plan.layers[0].ffn.w_gate_up), "the package's own product takes the feed-forward"
+            got = _whole_cut_and_token_by_token(r, toks, 100, 0.03, graphs=True)
+            # and the bfloat16 run stays near the same model in float32
+            r32 = ModelRunner.from_dir(d, dtype="float32", num_pages=4, max_requests=3, max_batched_tokens=64, max_context=128)
+            want = _whole_cut_and_token_by_token(r32, toks, 100, 1e-5, graphs=True)
+            assert float((got - want).abs().max()) < 0.04 * float(want.max() - want.min())
     finally:
         unregister_architecture("ToyForCausalLM")
         MIXERS.pop("toy_running_mean", None)
 
 
 # ---- a toy feed-forward with routing and a toy position encoding -----------------------------
-def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_can_be_registered_built_and_stepped(tmp_path):
+@pytest.mark.parametrize("dtype,hidden", [("float32", 48), ("bfloat16", 64)])
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_can_be_registered_built_and_stepped(tmp_path, dtype, hidden):
     """Two more kinds of part defined here, neither of them a model of anyone's: a feed-forward
     that routes each token to one of several small experts (router logits and softmax in
     float32), and a position encoding that hands mixers a table of sines which a toy mixer adds to
     its input.  They sit in one plan beside the package's own attention (with its rotary
     encoding: two position encodings in one model), in layers of different kinds, and are stepped
-    whole, in portions and token by token through the package's step function."""
+    whole, in portions and token by token through the package's step function.
+
+    In bfloat16 the attention layer runs in its stream form beside a feed-forward that has none,
+    and the toy mixer beside the package's SwiGLU, in eager and in captured decode steps."""
     from vapi_b200.config import Architecture, register_architecture, unregister_architecture
     from vapi_b200.engine.runner import ModelRunner
-    from vapi_b200.engine.step import StepEntry
     from vapi_b200.models.plan import LayerCall, ModelPlan
     from vapi_b200.parts import (FEED_FORWARDS, MIXERS, POSITION_ENCODINGS, FeedForward, GQAttention, Mixer, OutputHead,
                                  PositionEncoding, PreNormBlock, RMSNorm, RotaryEncoding, SwiGLU, TensorSpec,
@@ -475,11 +740,10 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_can_be_registered
             prob = torch.softmax(f.float() @ self.router.t(), dim=-1)              # routing in float32
             top_p, top_e = prob.max(dim=-1)
             out = torch.zeros_like(f)
-            for e in range(self.experts):
-                rows = (top_e == e).nonzero().flatten()
-                if rows.numel():
-                    h = torch.relu(f[rows] @ self.up[e].t())
-                    out[rows] = ((h @ self.down[e].t()).float() * top_p[rows, None]).to(f.dtype)
+            for e in range(self.experts):          # (every expert on every token, then masked: a toy may be wasteful)
+                h = torch.relu(f @ self.up[e].t())
+                y = ((h @ self.down[e].t()).float() * top_p[:, None]).to(f.dtype)
+                out = torch.where((top_e == e)[:, None], y, out)
             return out
 
     class SineTable(PositionEncoding):
@@ -520,10 +784,10 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_can_be_registered
         layers = [
             PreNormBlock(RMSNorm(H, 1e-5), make_part(MIXERS, "toy_add_positions", hidden=H, pos="sines"), RMSNorm(H, 1e-5),
                          make_part(FEED_FORWARDS, "toy_top_one_experts", hidden=H, width=40, experts=E), sub),
-            PreNormBlock(RMSNorm(H, 1e-6), GQAttention(H, 3, 1, 16, qk_norm_eps=1e-6, pos="rope"), RMSNorm(H, 1e-6),
-                         SwiGLU(H, 80), sub),
-            PreNormBlock(RMSNorm(H, 1e-5), make_part(MIXERS, "toy_add_positions", hidden=H, pos="sines"), RMSNorm(H, 1e-5),
+            PreNormBlock(RMSNorm(H, 1e-6), GQAttention(H, 4, 1, 16, qk_norm_eps=1e-6, pos="rope"), RMSNorm(H, 1e-6),
                          make_part(FEED_FORWARDS, "toy_top_one_experts", hidden=H, width=40, experts=E), sub),
+            PreNormBlock(RMSNorm(H, 1e-5), make_part(MIXERS, "toy_add_positions", hidden=H, pos="sines"), RMSNorm(H, 1e-5),
+                         SwiGLU(H, 96), sub),
         ]
         return ModelPlan("ToyRoutedForCausalLM", V, H, 512, emb, layers, ["l0.", "l1.", "l2."],
                          [LayerCall(0), LayerCall(1), LayerCall(2)], RMSNorm(H, 1e-5), "final.",
@@ -533,31 +797,29 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_can_be_registered
 
     register_architecture(Architecture("ToyRoutedForCausalLM", ("toy_routed",), lambda v: v, plan), replace=True)
     try:
-        cfg = {"architectures": ["ToyRoutedForCausalLM"], "vocab_size": 90, "hidden_size": 48, "experts": 3}
-        d = write_random_model(str(tmp_path / "toy"), cfg, 1, std=0.3, norm_init="perturbed")
-        r = ModelRunner.from_dir(d, dtype="float32", num_pages=6, page_size=16, max_requests=3, max_batched_tokens=64,
-                                 max_context=128)
+        cfg = {"architectures": ["ToyRoutedForCausalLM"], "vocab_size": 90, "hidden_size": hidden, "experts": 3}
+        d = write_random_model(str(tmp_path / "toy"), cfg, 1, std=0.3, norm_init="perturbed",
+                               dtype=torch.float32 if dtype == "float32" else torch.bfloat16)
+        kw = dict(num_pages=8, page_size=16, max_requests=3, max_batched_tokens=64, max_context=128)
+        r = ModelRunner.from_dir(d, dtype=dtype, **kw)
         assert len(r.cache.paged) == 1 and not r.cache.state            # only the attention layer owns a cache
-        toks = torch.randint(0, 90, (37,), generator=torch.Generator().manual_seed(2)).tolist()
-        a = r.cache.open("whole")
-        assert r.cache.reserve(a, len(toks))
-        whole = r.step([StepEntry(a, toks, list(range(len(toks))))]).cpu()
-        r.cache.close(a)
+        toks = torch.randint(0, 90, (45,), generator=torch.Generator().manual_seed(2)).tolist()
         # the routed feed-forward really routes: more than one expert is in use on these tokens
         ffn = r.plan.layers[0].ffn
         x = r.plan.embedding.forward(type("C", (), {"tokens": torch.tensor(toks, dtype=torch.int32, device="cuda"),
                                                      "status": None})())
         used = torch.softmax(x.float() @ ffn.router.t(), -1).argmax(-1).unique().numel()
         assert used >= 2
-        b, other = r.cache.open("cut"), r.cache.open("other")
-        rows, pos = [], 0
-        for q in (2, 1, 9, 1, 1, 16, 7):
-            assert r.cache.reserve(b, pos + q) and r.cache.reserve(other, other.num_tokens + 2)
-            out = r.step([StepEntry(other, [5, 6], []), StepEntry(b, toks[pos:pos + q], list(range(q)))])
-            rows.append(out.cpu())
-            pos += q
-        assert (torch.cat(rows) - whole).abs().max() < 2e-4
-        r.check_status()
+        if dtype == "float32":
+            _whole_cut_and_token_by_token(r, toks, 90, 2e-5, graphs=False)
+        else:
+            got = _whole_cut_and_token_by_token(r, toks, 90, 0.03, graphs=True)
+            r32 = ModelRunner.from_dir(d, dtype="float32", **kw)
+            want = _whole_cut_and_token_by_token(r32, toks, 90, 2e-5, graphs=True)
+            # (a token whose two best experts are nearly tied may be routed differently in bfloat16:
+            # compare the bulk, not the worst row)
+            close = ((got - want).abs().amax(dim=1) < 0.04 * float(want.max() - want.min())).float().mean()
+            assert float(close) > 0.9, float(close)
     finally:
         unregister_architecture("ToyRoutedForCausalLM")
         MIXERS.pop("toy_add_positions", None)

@@ -157,10 +157,13 @@ def _attention_case(ops, dtype, nh, nkv, d, page, lens, window=0, splits=None, p
     max_q, max_k = max(a for a, _ in lens), max(b for _, b in lens)
     scale = 1.0 / math.sqrt(d)
     want = plain_ops.paged_attention(q, nh * d, cache, table, cu_q, kl, n, S, max_q, max_k, nh, nkv, d, scale, window)
+    before = ops.launch_count
     got = ops.paged_attention(dev(q), nh * d, dev(cache), dev(table), dev(cu_q), dev(kl), n, S, max_q, max_k,
                               nh, nkv, d, scale, window, splits, None, impl)
+    launches = ops.launch_count - before
     t = dict(atol=3e-5, rtol=3e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
     torch.testing.assert_close(got.cpu().float(), want.float(), **t)
+    return launches
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -309,10 +312,32 @@ def test_decode_attention_mixed_lengths(ops, nh, nkv, page, splits):
     _attention_case(ops, nh=nh, nkv=nkv, d=64, page=page, lens=lens, splits=splits, **DEC)
 
 
-@pytest.mark.parametrize("splits", [1, 2, 5, 32])
+def _decode_launches(ops, num_seqs, nkv, splits):
+    """One launch while the slices of a (sequence, kv head) combine among themselves as a
+    thread-block cluster, two (the kernel, then the combine kernel) otherwise."""
+    return 1 if splits == 1 or ops.decode_attention_combines(num_seqs, nkv, splits) else 2
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 9, 12, 16, 32])
 def test_decode_attention_far_key_and_many_slices(ops, splits):
-    _attention_case(ops, nh=8, nkv=2, d=64, page=64, lens=[(1, 2500), (1, 640), (1, 65), (2, 3000)], planted=True,
-                    splits=splits, **DEC)
+    # (1, 65) is two tiles of keys: with more slices than that, most of its slices are empty
+    lens = [(1, 2500), (1, 640), (1, 65), (2, 3000)]
+    launches = _attention_case(ops, nh=8, nkv=2, d=64, page=64, lens=lens, planted=True, splits=splits, **DEC)
+    assert launches == _decode_launches(ops, len(lens), 2, splits)
+    _, cluster = ops.decode_attention_limits()
+    if 1 < splits <= cluster:
+        assert launches == 1, "a resident grid of at most a cluster's worth of slices combines inside the kernel"
+    if splits > cluster:
+        assert launches == 2
+
+
+@pytest.mark.parametrize("splits", [9, 12, 16])
+@pytest.mark.parametrize("lens", [[(1, 4096)], [(1, 700), (1, 8000)], [(1, 200)]])
+def test_decode_attention_large_clusters_few_sequences(ops, splits, lens):
+    """One or two sequences over long and short contexts (decode at batch 1 or 2): slices above the
+    portable cluster size, slices that get no tile at all, and the planted far key in the first."""
+    launches = _attention_case(ops, nh=32, nkv=8, d=64, page=64, lens=lens, planted=True, splits=splits, **DEC)
+    assert launches == _decode_launches(ops, len(lens), 8, splits)
 
 
 @pytest.mark.parametrize("window", [1, 5, 64, 100, 1000])
@@ -320,6 +345,10 @@ def test_decode_attention_window(ops, window):
     _attention_case(ops, nh=8, nkv=2, d=64, page=64, lens=[(1, 90), (1, 300), (1, 64), (3, 500), (1, 129), (1, 1)],
                     window=window, **DEC)
     _attention_case(ops, nh=8, nkv=2, d=64, page=128, lens=[(1, 900), (2, 300)], window=window, splits=4, **DEC)
+    for splits in (9, 12, 16):
+        launches = _attention_case(ops, nh=8, nkv=2, d=64, page=64, lens=[(1, 2000), (2, 1300)], window=window,
+                                   planted=True, splits=splits, **DEC)
+        assert launches == _decode_launches(ops, 2, 2, splits)
 
 
 def test_decode_attention_ignores_garbage_beyond_the_sequence(ops):

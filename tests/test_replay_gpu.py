@@ -7,11 +7,11 @@ import torch
 
 import plain_lfm2
 import replay_util as ru
-from conftest import TINY_A, TINY_B, TINY_C, TINY_D, TINY_E
+from conftest import TINY_A, TINY_A0, TINY_B, TINY_B0, TINY_C, TINY_D, TINY_E
 
 pytestmark = pytest.mark.gpu
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "A0": TINY_A0, "B0": TINY_B0}
 
 
 def _requests(cfg, seed, lengths):
@@ -24,7 +24,7 @@ def bf16_dirs(tmp_path_factory):
     """The tiny models with weights stored in bfloat16 (what a served checkpoint looks like)."""
     from vapi_b200.weights import write_random_model
     out = {}
-    for name, seed in (("A", 10), ("B", 12), ("C", 14), ("D", 16), ("E", 18)):
+    for name, seed in (("A", 10), ("B", 12), ("C", 14), ("D", 16), ("E", 18), ("A0", 20), ("B0", 22)):
         d = tmp_path_factory.mktemp(f"tiny{name}bf16")
         write_random_model(str(d), CONFIGS[name], seed, std=0.1 if name in "DE" else 0.2, norm_init="perturbed",
                            dtype=torch.bfloat16)
@@ -34,7 +34,10 @@ def bf16_dirs(tmp_path_factory):
 
 def _full_trace(cfg, seed):
     """All the ways of cutting, one after the other, in a single run."""
-    reqs = _requests(cfg, seed, [1, 7, 33, 150, 97, 200, 64, 129, 70, 45])
+    lengths = [1, 7, 33, 150, 97, 200, 64, 129, 70, 45]
+    if cfg["max_position_embeddings"] < 200:                   # (the configuration with 128 positions)
+        lengths = [1, 7, 33, 110, 97, 128, 64, 127, 70, 45]
+    reqs = _requests(cfg, seed, lengths)
     tr = ru.Trace()
     ref_tokens = {}
 
@@ -55,12 +58,12 @@ def _full_trace(cfg, seed):
     return tr, ref_tokens
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "A0", "B0"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_every_way_of_cutting(name, dtype, tiny_dirs, bf16_dirs, tmp_path):
     model_dir = tiny_dirs[name] if dtype == "float32" else bf16_dirs[name]
     plain = plain_lfm2.PlainLfm2(model_dir)
-    tr, ref_tokens = _full_trace(CONFIGS[name], seed=100 + ord(name))
+    tr, ref_tokens = _full_trace(CONFIGS[name], seed=100 + sum(map(ord, name)))
     ref = {k: plain.logits(v) for k, v in ref_tokens.items()}
     # the pool is exactly what the trace needs at its fullest, so pages are used again and again
     got = ru.run_trace(model_dir, dtype, tr, str(tmp_path / "out"))
@@ -103,22 +106,19 @@ def test_out_of_pages_is_an_error_not_a_wrong_result(tiny_dirs, tmp_path):
 
 
 @pytest.mark.parametrize("sizes", ["1.2b", "700m"])
-def test_layers_of_serving_size_in_bfloat16(sizes, tmp_path):
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_layers_of_serving_size(sizes, dtype, tmp_path):
     """Three layers with the sizes of the 1.2B model (hidden 2048, 32 heads over 8 kv heads of 64,
     feed-forward 8192) and of the 700M model (hidden 1536, 24 heads, feed-forward 6912: three query
-    heads per kv head, widths that are no power of two), conv - attention - conv, bfloat16 weights:
-    the shapes the serving kernels are tuned for, whole, in portions, token by token and mixed,
-    against the plain model."""
+    heads per kv head, widths that are no power of two), conv - attention - conv: the shapes the
+    serving kernels are tuned for, whole, in portions, token by token and mixed, against the plain
+    model; with bfloat16 weights on the serving kernels, and with float32 weights on the true
+    32-bit path, where the float32 limit holds at these widths too."""
+    from conftest import serving_width_config
     from vapi_b200.weights import write_random_model
-    hidden, heads, inter = {"1.2b": (2048, 32, 12288), "700m": (1536, 24, 10240)}[sizes]
-    cfg = {
-        "architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2", "vocab_size": 4096, "hidden_size": hidden,
-        "intermediate_size": inter, "block_auto_adjust_ff_dim": True, "block_ffn_dim_multiplier": 1.0,
-        "block_multiple_of": 256, "num_hidden_layers": 3, "layer_types": ["conv", "full_attention", "conv"],
-        "num_attention_heads": heads, "num_key_value_heads": 8, "head_dim": 64, "conv_L_cache": 3, "conv_bias": False,
-        "rope_theta": 1000000.0, "norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 1024,
-    }
-    d = write_random_model(str(tmp_path / "m"), cfg, 3, std=0.02, norm_init="perturbed", dtype=torch.bfloat16)
+    cfg = serving_width_config(sizes)
+    d = write_random_model(str(tmp_path / "m"), cfg, 3, std=0.02, norm_init="perturbed",
+                           dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32)
     plain = plain_lfm2.PlainLfm2(d)
     reqs = _requests(cfg, 8, [300, 40, 150, 20, 9, 25, 33, 12, 70, 3, 16, 48])
     tr = ru.Trace()
@@ -129,6 +129,6 @@ def test_layers_of_serving_size_in_bfloat16(sizes, tmp_path):
     ru.mixed(tr, mix, seed=4, max_live=12, decode_tail=8)      # up to 12 live: decode steps of 9..16 rows too
     ref_tokens = {"whole-r0": reqs["r0"], "tail-r2": reqs["r2"], "cut-r0": reqs["r0"], **mix}
     ref = {k: plain.logits(v) for k, v in ref_tokens.items()}
-    got = ru.run_trace(d, "bfloat16", tr, str(tmp_path / "out"), extra_args=["--max-requests", "16"])
-    ok, msg = ru.compare(tr, got, ref, "bfloat16")
+    got = ru.run_trace(d, dtype, tr, str(tmp_path / "out"), extra_args=["--max-requests", "16"])
+    ok, msg = ru.compare(tr, got, ref, dtype)
     assert ok, msg

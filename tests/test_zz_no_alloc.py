@@ -6,9 +6,12 @@ latency-critical loop that must stay out of the allocator, a program with a fixe
 a plug-in whose host owns all device memory.  The ordinary entry point asks such a caller for two
 scratch buffers; this one keeps its scratch in a fixed 8 MiB array inside the library.
 
-The test runs the same inputs through both entry points, twice in a row with different data (the
-built-in array keeps the first call's leftovers, which must not show), and checks the refusal of a
-call that would not fit the array.  This file is collected last on purpose."""
+The test runs the same inputs through both entry points, twice in a row with different data, the
+larger call first (the built-in array keeps the first call's leftovers, which must not show in
+the second), in the forms that really go through the array (bfloat16 on the one-warp flash kernel
+and with more slices than the decode kernel combines by itself; float32 on the general kernel),
+compares with the plain restatement of attention as well, and checks the refusal of a call that
+would not fit the array.  This file is collected last on purpose."""
 import ctypes
 import math
 
@@ -18,9 +21,9 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _case(seed, dtype, n_seqs=5, nh=8, nkv=2, d=64, page=64):
+def _case(seed, dtype, n_seqs=5, nh=8, nkv=2, d=64, page=64, longest=600):
     g = torch.Generator().manual_seed(seed)
-    lens = [int(x) for x in torch.randint(1, 600, (n_seqs,), generator=g)]
+    lens = [int(x) for x in torch.randint(1, longest, (n_seqs,), generator=g)]
     need = [-(-k // page) for k in lens]
     pages = sum(need) + 2
     perm = torch.randperm(pages, generator=g).tolist()
@@ -50,25 +53,42 @@ def _noalloc(lib, c, splits, impl=0):
     return rc, out
 
 
-@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_attention_without_allocation_matches_the_ordinary_entry_point(dtype):
+_IMPL = {"auto": 0, "general": 1, "tensor_core": 2, "decode": 4}
+
+
+# (dtype, kernel, slices): every case but the first writes its partial results to the built-in array
+# and reads them back in the combine kernel; in the first the decode kernel's slices combine among
+# themselves as a thread-block cluster, and the array stays untouched
+@pytest.mark.parametrize("dtype,impl,splits", [(torch.bfloat16, "auto", 4), (torch.bfloat16, "tensor_core", 4),
+                                               (torch.bfloat16, "auto", 32), (torch.float32, "auto", 4),
+                                               (torch.float32, "general", 7)])
+def test_attention_without_allocation_matches_the_ordinary_entry_point(dtype, impl, splits):
+    import plain_ops
     from vapi_b200 import ops
     lib = ops._lib("attention")
     assert hasattr(lib, "vapi_paged_attention_noalloc")
     tol = dict(atol=3e-2, rtol=3e-2) if dtype == torch.bfloat16 else dict(atol=3e-5, rtol=3e-5)
-    for call, seed in enumerate((40, 41)):                 # two calls in a row share the built-in array
-        c = _case(seed, dtype)
+    if dtype == torch.bfloat16 and impl == "auto":
+        assert ops.decode_attention_combines(5, 2, splits) == (splits == 4)
+    # two calls in a row share the built-in array; the first is the larger one (more sequences and
+    # longer contexts), so the second runs over what the first left behind
+    for call, (seed, n_seqs, longest) in enumerate(((40, 9, 3000), (41, 5, 600))):
+        c = _case(seed, dtype, n_seqs=n_seqs, longest=longest)
+        scale = 1.0 / math.sqrt(c["d"])
         want = ops.paged_attention(c["q"], c["nh"] * c["d"], c["cache"], c["table"], c["cu"], c["kl"], c["n"], c["n"],
-                                   1, c["max_k"], c["nh"], c["nkv"], c["d"], 1.0 / math.sqrt(c["d"]), 0, 4)
+                                   1, c["max_k"], c["nh"], c["nkv"], c["d"], scale, 0, splits, None, impl)
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
-        rc, got = _noalloc(lib, c, splits=4)
+        rc, got = _noalloc(lib, c, splits=splits, impl=_IMPL[impl])
         torch.cuda.synchronize()
         assert rc == 0, lib.vapi_last_error().decode()
         grown = torch.cuda.memory_allocated() - before
         assert grown <= got.numel() * got.element_size() + 1024, "only the output was allocated (by the test itself)"
         torch.testing.assert_close(got.float().cpu(), want.float().cpu(), **tol)
         assert torch.isfinite(got.float()).all(), f"call {call}"
+        plain = plain_ops.paged_attention(c["q"].cpu(), c["nh"] * c["d"], c["cache"].cpu(), c["table"].cpu(), c["cu"].cpu(),
+                                          c["kl"].cpu(), c["n"], c["n"], 1, c["max_k"], c["nh"], c["nkv"], c["d"], scale, 0)
+        torch.testing.assert_close(got.float().cpu(), plain.float(), **tol)
 
 
 def test_attention_without_allocation_refuses_what_does_not_fit():

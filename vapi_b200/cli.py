@@ -108,7 +108,13 @@ def main(argv: Optional[List[str]] = None) -> int:
         presence_penalty=args.presence_penalty, max_tokens=args.max_tokens, seed=args.seed, n=args.n,
         logprobs=args.logprobs,
         stop_token_ids=tuple(int(t) for t in args.stop_token_ids.split(",") if t.strip()))
-    for c in llm.generate(prompts, params):
+    from .engine.scheduler import AdmitError
+    try:
+        completions = llm.generate(prompts, params)
+    except (AdmitError, ValueError) as e:       # a prompt or a sampling parameter that cannot be served
+        print(f"vapi_b200: {e}", file=sys.stderr)
+        return 2
+    for c in completions:
         rec = {"request": c.request_id, "prompt_tokens": c.prompt_tokens, "tokens": c.tokens,
                "finish_reason": c.finish_reason}
         if params.n > 1:

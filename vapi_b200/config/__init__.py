@@ -1,8 +1,7 @@
-"""Model configuration (from config.json) and run-time configuration (TOML / flags)."""
-from .model import (Architecture, ConfigError, Lfm2Config, eos_token_ids, load_config_json,
-                    register_architecture, registered_architectures, resolve_architecture,
-                    unregister_architecture)
+"""The architecture registry (config.json -> model) and run-time configuration (TOML / flags)."""
+from .model import (Architecture, ConfigError, eos_token_ids, load_config_json, register_architecture,
+                    registered_architectures, resolve_architecture, unregister_architecture)
 
-__all__ = ["Architecture", "ConfigError", "Lfm2Config", "eos_token_ids", "load_config_json",
+__all__ = ["Architecture", "ConfigError", "eos_token_ids", "load_config_json",
            "register_architecture", "registered_architectures", "resolve_architecture",
            "unregister_architecture"]

@@ -464,7 +464,7 @@ VAPI_EXPORT int vapi_paged_attention_noalloc(const void* q, long long q_row_stri
     if (splits > 1 && n > 0) {
         const long long rows = (long long)n * nh * splits;
         const long long need = rows * ((long long)d + 2);
-        if (n < 0 || nh <= 0 || d <= 0 || need > VAPI_ATTN_NOALLOC_MAX_FLOATS)
+        if (nh <= 0 || d <= 0 || need > VAPI_ATTN_NOALLOC_MAX_FLOATS)
             return fail(-4, "paged_attention_noalloc: %d tokens x %d heads x %d splits x (head size %d + 2) = %lld floats "
                             "of scratch, the built-in array holds %d", n, nh, splits, d, need, VAPI_ATTN_NOALLOC_MAX_FLOATS);
         int dev = -1;

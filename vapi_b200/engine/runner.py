@@ -263,7 +263,8 @@ class ModelRunner:
         ctx = self.packer.pack([], self.dtype, n_cap=B, s_cap=B, width=width, status=self.status)
         ctx.max_k = self.max_context
         ctx.unknown_tokens = True       # the captured step always looks: token_src says where
-        ctx.attention_splits = self._decode_splits(B)
+        for gi, splits in enumerate(self._decode_splits(B)):
+            ctx.groups[gi].splits, ctx.groups[gi].max_k = splits, self.max_context
         cur = torch.cuda.current_stream()
         side = torch.cuda.Stream()
         side.wait_stream(cur)
@@ -291,14 +292,18 @@ class ModelRunner:
                 gc.enable()
         return graph, logits, ops.launch_count - before
 
-    def _decode_splits(self, B: int) -> int:
-        from ..parts.attention import GQAttention
-        best = 1
-        for blk in self.plan.layers:
-            m = getattr(blk, "mixer", None)
-            if isinstance(m, GQAttention):
-                dec = ops.decode_attention_applies(self.dtype, m.d, self.cache.page_size, m.nh // m.nkv)
-                best = max(best, ops.attention_splits(B, 1, self.max_context, m.nh, m.nkv, dec))
+    def _decode_splits(self, B: int) -> List[int]:
+        """Per paged cache group: into how many slices a captured decode step of B sequences cuts
+        a sequence's keys, the most that any mixer of the group asks for."""
+        best = [1] * len(self.cache.paged)
+        for i, call in enumerate(self.plan.order):
+            site = self._site_of[i]
+            if site is None:
+                continue
+            kind, gi = self.cache.site_kind(site)
+            mixer = getattr(self.plan.layers[call.layer], "mixer", None)
+            if kind == "paged" and mixer is not None:
+                best[gi] = max(best[gi], int(mixer.decode_splits(B, self.max_context, self.cache.page_size, self.dtype)))
         return best
 
     def step_decode_graph(self, entries: Optional[Sequence[StepEntry]], plan=None) -> Optional[torch.Tensor]:

@@ -38,8 +38,14 @@ class StepEntry:
 
 @dataclass
 class GroupMeta:
+    """What a step holds for one paged cache group.  ``splits`` and ``max_k`` are set for steps
+    of a fixed shape (captured decode steps), where they cannot follow the batch: into how many
+    slices the group's mixers cut a sequence's keys, and the most keys a sequence of the group can
+    have.  None leaves the choice to the mixer and to the step's own ``max_k``."""
     slot_mapping: torch.Tensor      # [n] int32: page * page_size + offset of each token
     block_table: torch.Tensor       # [S, width] int32
+    splits: Optional[int] = None
+    max_k: Optional[int] = None
 
 
 @dataclass

@@ -75,6 +75,11 @@ class GQAttention(Mixer):
             self.q_w = tensors[f"{prefix}{n['q_norm']}.weight"].contiguous()
             self.k_w = tensors[f"{prefix}{n['k_norm']}.weight"].contiguous()
 
+    def decode_splits(self, batch: int, max_context: int, page_size: int, dtype: torch.dtype) -> int:
+        keys = min(max_context, self.window) if self.window > 0 else max_context
+        dec = ops.decode_attention_applies(dtype, self.d, page_size, self.nh // self.nkv)
+        return ops.attention_splits(batch, 1, keys, self.nh, self.nkv, dec)
+
     def forward(self, a: torch.Tensor, ctx: Any, cache: CacheView) -> torch.Tensor:
         qkv = ops.linear(a, self.w_qkv, self.b_qkv)
         return ops.linear(self._attend(qkv, ctx, cache), self.w_o, self.b_o)
@@ -95,6 +100,10 @@ class GQAttention(Mixer):
             cos, sin = ctx.pos[self.pos]
         grp = cache.group
         n_rep = nh // nkv
+        splits = grp.splits if getattr(grp, "splits", None) is not None else ctx.attention_splits
+        max_k = getattr(grp, "max_k", None) or ctx.max_k
+        if self.window > 0:
+            max_k = min(max_k, self.window + ctx.max_q - 1)      # a query reads at most `window` keys
         if (ops.FUSED_DECODE_ROPE and qkv.is_cuda and cache.tensor is not None
                 and ops.decode_attention_fused_applies(qkv.dtype, d, cache.tensor.shape[3], ctx.max_q * n_rep,
                                                        self.rot_dim if cos is not None else None)
@@ -103,15 +112,15 @@ class GQAttention(Mixer):
             return ops.decode_attention_fused(qkv, nh, nkv, d, self.q_w, self.k_w,
                                               self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, cos, sin,
                                               cache.tensor, cache.write, grp.block_table, ctx.cu_q, ctx.seqlens_k,
-                                              ctx.n, ctx.num_seqs, ctx.max_q, ctx.max_k, self.scale, self.window,
-                                              ctx.attention_splits, ctx.status)
+                                              ctx.n, ctx.num_seqs, ctx.max_q, max_k, self.scale, self.window,
+                                              splits, ctx.status)
         ops.qk_norm_rope_write(qkv, nh, nkv, d, self.q_w, self.k_w,
                                self.qk_norm_eps if self.qk_norm_eps is not None else 0.0,
                                cos, sin, self.rot_dim,
                                cache.tensor if cache.write else None, grp.slot_mapping, ctx.status)
         y = ops.paged_attention(qkv, qkv.stride(0), cache.tensor, grp.block_table, ctx.cu_q,
-                                ctx.seqlens_k, ctx.n, ctx.num_seqs, ctx.max_q, ctx.max_k, nh, nkv, d,
-                                self.scale, self.window, ctx.attention_splits, ctx.status)
+                                ctx.seqlens_k, ctx.n, ctx.num_seqs, ctx.max_q, max_k, nh, nkv, d,
+                                self.scale, self.window, splits, ctx.status)
         return y
 
 

@@ -172,6 +172,13 @@ class Mixer(Part):
         contribution to the residual stream, [n, H] in the activation dtype."""
         raise NotImplementedError
 
+    def decode_splits(self, batch: int, max_context: int, page_size: int, dtype: torch.dtype) -> int:
+        """Into how many slices this mixer wants a sequence's cached tokens cut in a decode step of
+        ``batch`` single-token sequences whose contexts may reach ``max_context``.  Asked once per
+        fixed-shape (captured) decode step, whose kernels cannot follow the batch's real lengths;
+        the answer comes back to the mixer as ``cache.group.splits``.  1: no cutting."""
+        return 1
+
     def forward_stream(self, a: NormedStream, ctx: "Any", cache: CacheView, x: torch.Tensor,
                        next_weight: torch.Tensor):
         """Optional fast form for steps of a few rows: take the normed input lazily, add the
