@@ -128,7 +128,7 @@ def run_trace(model_dir: str, dtype: str, tr: Trace, out_dir: str, max_tokens: i
     return out
 
 
-def compare(tr: Trace, got: Dict[int, np.ndarray], ref: Dict[str, torch.Tensor], dtype: str):
+def compare(tr: Trace, got: Dict[int, np.ndarray], ref: Dict[str, torch.Tensor], dtype: str, bf16_frac: float = 0.04):
     """Worst difference over all wanted rows, with where it is.  Returns (ok, message)."""
     worst = (0.0, None)
     span = max(float(r.max() - r.min()) for r in ref.values())
@@ -139,7 +139,7 @@ def compare(tr: Trace, got: Dict[int, np.ndarray], ref: Dict[str, torch.Tensor],
                 return False, f"step {step} row {i} ({rid} @ {pos}) is not finite"
             if d > worst[0]:
                 worst = (d, (step, rid, pos))
-    limit = limit_for(dtype, span)
+    limit = limit_for(dtype, span, bf16_frac)
     msg = (f"worst |diff| {worst[0]:.3e} ({worst[0] / span:.2e} of the logit range) at (step, request, position) "
            f"{worst[1]}; limit {limit:.3e}, logit range {span:.2f}")
     report = os.environ.get("VAPI_TEST_REPORT")
@@ -149,8 +149,12 @@ def compare(tr: Trace, got: Dict[int, np.ndarray], ref: Dict[str, torch.Tensor],
     return worst[0] <= limit, msg
 
 
-def limit_for(dtype: str, span: float) -> float:
+def limit_for(dtype: str, span: float, bf16_frac: float = 0.04) -> float:
     """float32: 1e-4 absolute on logits of order 10 (the reference's model tests use 1e-4,
-    crates/vapi-backend-candle/src/models/lfm2.rs:924-953); bfloat16: 5 % of the logit range
-    (lfm2.rs:1017-1024)."""
-    return 1e-4 * max(1.0, span / 10.0) if dtype == "float32" else 0.05 * span
+    crates/vapi-backend-candle/src/models/lfm2.rs:924-953).  bfloat16: a fraction of the logit
+    range.  The reference allows 5 % (lfm2.rs:1017-1024); the plain model here holds the same
+    bfloat16-rounded weights, so the honest error is smaller, and the limits follow what the runs
+    really show (the worst row of every case is listed in profiles/bf16_deviation_of_replay_cases.txt):
+    at most 2.1 % for the tiny models, whose narrow layers with weights of N(0, 0.2) are noisy (limit
+    4 %), and 0.6 % at the serving models' widths (limit 2 %, given by those tests)."""
+    return 1e-4 * max(1.0, span / 10.0) if dtype == "float32" else bf16_frac * span
