@@ -125,7 +125,8 @@ def part_tensors(plan):
             if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
                 seen.add(v.data_ptr())
                 yield f"{type(part).__name__}.{name}", v
-            elif isinstance(v, Part):
+        for v in vars(part).values():
+            if isinstance(v, Part):
                 yield from of_part(v)
 
     for call in plan.order:
@@ -139,10 +140,9 @@ def model_numbers(runner):
     """Bytes of every weight a decode step reads once (the embedding table counts once: a step
     gathers a few rows of it and the tied head reads all of it), and matrix-product parameters."""
     wbytes, mm_params = 0, 0
-    tied = runner.plan.head.weight.data_ptr() == runner.plan.embedding.table.data_ptr()
     for label, t in part_tensors(runner.plan):
-        if label == "TokenEmbedding.table" and not tied:
-            continue                      # an untied table is gathered from, not streamed
+        if label == "TokenEmbedding.table":
+            continue                      # (reached only when untied) a table is gathered from, not streamed
         wbytes += t.numel() * t.element_size()
         if t.dim() == 2 and t.shape[0] > 8:
             mm_params += t.numel()
@@ -171,6 +171,9 @@ def trace_table(events):
                      "until_next_us": (b["ns"] - a["ns"]) / 1e3 if b else None})
     return rows
 
+
+#: the calls that are matrix products (time against the tensor peak); the rest move bytes
+PRODUCTS = ("linear", "skinny_linear", "linear_tc", "skinny_shortconv")
 
 #: the package's kernels as the parts call them, with the library each lives in
 OPS = {"embed": "elementwise", "add_residual_ss": "elementwise", "resolve_tokens": "elementwise",
@@ -223,7 +226,12 @@ class OpLog:
                     ev[1].record()
                 outs = [t for t in (out if isinstance(out, tuple) else (out,)) if isinstance(t, torch.Tensor)]
                 rows = max([t.shape[0] for t in outs if t.dim() >= 1] or [0])
-                moved = sum(t.numel() * t.element_size() for t in tensors + outs if weight is None or t is not weight[1])
+                # what an elementwise call moves: its activations in and out (not the caches and states it
+                # touches a few rows of, not the plan's own tensors)
+                moved = sum(t.numel() * t.element_size() for t in tensors + outs
+                            if t.dim() <= 2 and t.data_ptr() not in self.labels)
+                if name == "embed":
+                    moved *= 2            # the rows gathered from the table, and the stream written
                 self.calls.append({"op": name, "weight": weight[0] if weight else None,
                                    "weight_shape": tuple(weight[1].shape) if weight else None,
                                    "weight_bytes": weight[1].numel() * weight[1].element_size() if weight else 0,
@@ -235,9 +243,10 @@ class OpLog:
 
 
 def family_of(call):
-    """The name under which a noted call is summed up."""
-    if call["weight"]:
-        return call["weight"]
+    """The name under which a noted call is summed up: a product by the matrix it streams, any
+    other kernel by its own name."""
+    if call["op"] in PRODUCTS and call["weight"]:
+        return call["weight"] + ("+conv" if call["op"] == "skinny_shortconv" else "")
     return call["op"]
 
 
@@ -526,15 +535,18 @@ def trace_pass(args, runner, fill, decode_steps, ops, ctx_len, B):
     log = OpLog(ops, runner.plan)
     real_forward = runner.forward
 
+    graph_calls = []
+
     def forward(ctx):               # the last forward pass before the steps is the one the graph holds
         log.calls.clear()
-        return real_forward(ctx)
+        out = real_forward(ctx)
+        graph_calls[:] = list(log.calls)
+        return out
 
     runner.forward = forward
     with log:
         decode_steps(runner, rcs, warm, False)
     runner.forward = real_forward
-    graph_calls = list(log.calls)
     ms = decode_steps(runner, rcs, steps, True)
     rows = trace_table(ops.trace_read())
     kv_per_site = sum(rc.num_tokens for rc in rcs) * runner.cache.bytes_per_token() / \
@@ -552,7 +564,7 @@ def trace_pass(args, runner, fill, decode_steps, ops, ctx_len, B):
     expect = []
     for c in graph_calls:
         for k in range(c["launches"]):
-            nbytes = c["weight_bytes"] if k == 0 else 0
+            nbytes = (c["weight_bytes"] if c["op"] in PRODUCTS else c["moved_bytes"]) if k == 0 else 0
             if c["op"] in ("paged_attention", "decode_attention_fused") and k == 0:
                 nbytes = int(kv_per_site)
             if c["op"] == "skinny_shortconv" and k == 0:
@@ -684,7 +696,7 @@ def measure_prefill(runner, ops, mm_params, pk, peak_tflops, gen, vocab, dev, wa
             f = fam.setdefault(family_of(c), {"ms": 0.0, "flops": 0.0, "bytes": 0, "calls": 0})
             f["ms"] += c["events"][0].elapsed_time(c["events"][1])
             f["calls"] += 1
-            if c["weight_shape"]:
+            if c["op"] in PRODUCTS and c["weight_shape"]:
                 f["flops"] += 2.0 * c["rows"] * c["weight_shape"][0] * c["weight_shape"][1]
             elif c["op"] in ("paged_attention", "decode_attention_fused"):
                 f["flops"] += attn_flops / max(1, len(n_attn_sites))
