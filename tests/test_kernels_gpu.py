@@ -632,8 +632,9 @@ def test_linear_is_not_reduced_precision(ops, dtype):
 
 # ---- the weight-streaming product of decode steps ---------------------------------------------
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("N,K", [(72, 96), (2048, 2048), (1000, 320), (6144, 1536)])
+@pytest.mark.parametrize("N,K", [(72, 96), (2048, 2048), (1000, 320), (6144, 1536), (520, 4096), (300, 2560), (48, 2080)])
 def test_skinny_linear_plain_products(ops, M, N, K):
+    # (inner sizes up to 2048: the tokens' rows live in registers; above: in the copy queue)
     torch.manual_seed(20)
     w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
     a = torch.randn(M, K).to(torch.bfloat16)
@@ -725,6 +726,27 @@ def test_skinny_linear_fusions_with_more_tiles_than_blocks(ops, M):
     lg = ops.skinny_linear(dev(w13), xw=dev(xw), ss_in=dev(parts), eps=eps, epilogue="f32")
     torch.testing.assert_close(lg.cpu(), gu, atol=5e-3, rtol=2e-3)
     assert torch.equal(ops.skinny_linear(dev(w13), xw=dev(xw), ss_in=dev(parts), eps=eps, epilogue="swiglu"), s_)
+
+
+@pytest.mark.parametrize("M", [2, 8, 14])
+@pytest.mark.parametrize("N,K", [(2048, 8192), (1536, 6912), (256, 4096), (2048, 2048)])
+def test_skinny_linear_residual_epilogue_over_a_long_inner_size(ops, M, N, K):
+    """The down projection's shapes: a long inner size with no more tiles than SMs takes the deeper
+    copy queue; the residual stream is read early and must still be this call's own element."""
+    torch.manual_seed(24)
+    w = (torch.randn(N, K) * 0.02).to(torch.bfloat16)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    x = torch.randn(M, N)
+    nw = 1 + 0.1 * torch.randn(N)
+    xr = dev(x.clone())
+    ss, xw = ops.skinny_linear(dev(w), act=dev(a), epilogue="resid", resid=xr, next_weight=dev(nw))
+    want = x + a.float() @ w.float().t()
+    torch.testing.assert_close(xr.cpu(), want, atol=3e-3, rtol=1e-3)
+    torch.testing.assert_close(ss.sum(0).cpu(), (want ** 2).sum(1), atol=5e-2, rtol=1e-3)
+    torch.testing.assert_close(xw.cpu().float(), (want * nw).to(torch.bfloat16).float(), atol=4e-2, rtol=2e-2)
+    # twice in a row on the same stream: the second call adds to what the first left
+    ops.skinny_linear(dev(w), act=dev(a), epilogue="resid", resid=xr)
+    torch.testing.assert_close(xr.cpu(), want + a.float() @ w.float().t(), atol=6e-3, rtol=1e-3)
 
 
 def test_embed_and_residual_add_prepare_the_next_norm(ops):

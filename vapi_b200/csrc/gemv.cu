@@ -54,7 +54,15 @@ constexpr int GV_STAGES_DEFAULT = GV_STAGES_N;   // depth of the per-lane copy q
 // (DEEP: a product with a long K and no more tiles than SMs has one block per SM anyway and takes
 // a deeper queue instead of a second block)
 // (16 stages of 3 slots for up to 8 tokens, 12 of 4 slots for up to 16: 196 KB either way)
-template <int EPI, bool DEEP = false, int NT = 1, int PRO = 1, int WARPS = GV_WARPS> __host__ __device__ constexpr int gv_stages() {
+#ifndef GV_REGB_STAGES_N
+#define GV_REGB_STAGES_N 12
+#endif
+// REGB: the tokens' operand is kept in registers (see the kernel), so the queue holds weights only and the
+// room that the staged rows took goes to more stages: 12 of two weight rows (96 KB a block, two blocks on
+// an SM), 8 of three for the conv epilogue; one block of sixteen warps: 11 and 7.
+template <int EPI, bool DEEP = false, int NT = 1, int PRO = 1, int WARPS = GV_WARPS, bool REGB = false> __host__ __device__ constexpr int gv_stages() {
+    if (REGB)
+        return WARPS == GV_WIDE_WARPS ? (EPI == 4 ? 7 : 11) : (EPI == 4 ? (GV_REGB_STAGES_N * 2) / 3 : GV_REGB_STAGES_N);
     if (WARPS == GV_WIDE_WARPS)      // one block per SM: 8 stages beside the staged rows, 6 when the rows travel in the queue, 5 with three weight rows
         return EPI == 4 ? 5 : (PRO == 0 ? 6 : 8);
     return DEEP ? (NT == 1 ? GV_DEEP_STAGES : (GV_DEEP_STAGES * 3) / 4)
@@ -104,21 +112,31 @@ __device__ __forceinline__ void gv_cp16(void* smem_dst, const void* gsrc, int by
 __device__ __forceinline__ void gv_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void gv_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-template <int NT, int PRO, int EPI>
-__host__ __device__ constexpr int gv_slots() { return (EPI == GV_EPI_CONV ? 3 : 2) + (PRO == GV_PRO_ACT ? NT : 0); }
+template <int NT, int PRO, int EPI, bool REGB = false>
+__host__ __device__ constexpr int gv_slots() { return (EPI == GV_EPI_CONV ? 3 : 2) + ((PRO == GV_PRO_ACT && !REGB) ? NT : 0); }
 
-template <int NT, int PRO, int EPI, bool DEEP, int WARPS = GV_WARPS>
+// chunks of 32 k that a warp keeps of every token's row in registers (REGB): K up to 8 * 32 * 8 = 2048
+constexpr int GV_REGB_CHUNKS = 8;
+
+template <int NT, int PRO, int EPI, bool DEEP, int WARPS = GV_WARPS, bool REGB = false>
 static size_t gv_smem_bytes(int K) {
-    size_t b = (size_t)WARPS * gv_stages<EPI, DEEP, NT, PRO, WARPS>() * gv_slots<NT, PRO, EPI>() * 32 * sizeof(uint4);
-    if (PRO == GV_PRO_NORM) b += (size_t)8 * NT * (K + 32) * sizeof(__nv_bfloat16);
+    size_t b = (size_t)WARPS * gv_stages<EPI, DEEP, NT, PRO, WARPS, REGB>() * gv_slots<NT, PRO, EPI, REGB>() * 32 * sizeof(uint4);
+    if (PRO == GV_PRO_NORM && !REGB) b += (size_t)8 * NT * (K + 32) * sizeof(__nv_bfloat16);
     return b;
 }
 
-template <int NT, int PRO, int EPI, bool DEEP = false, int WARPS = GV_WARPS>
-__global__ void __launch_bounds__(WARPS * 32)
+// REGB (products with K of at most 2048): a warp owns the same slice of K in every tile, so it reads
+// its slice of the tokens' rows once, straight from global memory into the registers that the MMAs take
+// them from, as soon as the dependency wait has returned: no staging in shared memory, no barrier
+// between the wait and the first MMA, and the queue's room all goes to weights.
+template <int NT, int PRO, int EPI, bool DEEP = false, int WARPS = GV_WARPS, bool REGB = false>
+#ifndef GV_REGB_MIN_BLOCKS
+#define GV_REGB_MIN_BLOCKS 1
+#endif
+__global__ void __launch_bounds__(WARPS * 32, (REGB && NT == 1 && WARPS == GV_WARPS) ? GV_REGB_MIN_BLOCKS : 1)
 skinny_linear_kernel(const GvParams p) {
-    constexpr int SLOTS = gv_slots<NT, PRO, EPI>();
-    constexpr int GV_STAGES = gv_stages<EPI, DEEP, NT, PRO, WARPS>();
+    constexpr int SLOTS = gv_slots<NT, PRO, EPI, REGB>();
+    constexpr int GV_STAGES = gv_stages<EPI, DEEP, NT, PRO, WARPS, REGB>();
     constexpr int WS = EPI == GV_EPI_CONV ? 3 : 2;     // weight rows a lane streams per chunk
     constexpr int COLS = 8 * NT;
     extern __shared__ __align__(16) unsigned char gv_smem[];
@@ -217,7 +235,28 @@ skinny_linear_kernel(const GvParams p) {
     }
     pdl_wait();
 
-    if (PRO == GV_PRO_NORM) {
+    uint4 breg[REGB ? NT : 1][REGB ? GV_REGB_CHUNKS : 1];
+    if (REGB) {
+        const __nv_bfloat16* tok = PRO == GV_PRO_NORM ? p.xw : p.act;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const int m = nt * 8 + g;
+#pragma unroll
+            for (int j = 0; j < GV_REGB_CHUNKS; ++j)
+                breg[nt][j] = (j < len && m < p.M)
+                    ? __ldcg(reinterpret_cast<const uint4*>(tok + (size_t)m * p.K + ((size_t)(c_begin + j) << 5) + 8 * t))
+                    : make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (PRO == GV_PRO_NORM) {
+            for (int m = warp; m < p.M; m += WARPS) {
+                float s = 0.f;
+                for (int i = lane; i < p.ss_parts; i += 32) s += p.ss_in[(size_t)i * p.M + m];
+                s = warp_sum(s);
+                if (lane == 0) inv_s[m] = rsqrtf(s / (float)p.K + p.eps);
+            }
+            __syncthreads();
+        }
+    } else if (PRO == GV_PRO_NORM) {
         // every token's row (already multiplied by the norm's weight) into shared memory, by
         // asynchronous copies that overlap the weights already on their way
         const int k8 = p.K >> 3;
@@ -260,6 +299,71 @@ skinny_linear_kernel(const GvParams p) {
 #pragma unroll
         for (int i = 0; i < (EPI == GV_EPI_CONV ? NT : 1); ++i) acc_x[i][0] = acc_x[i][1] = acc_x[i][2] = acc_x[i][3] = 0.f;
 
+        // what the residual epilogue adds to: asked for now, so that it is here when the sums are
+        const int ei = tig / COLS, em = tig - ei * COLS;                   // MMA row, token of this thread's output
+        float r_old = 0.f, r_nw = 0.f;
+        if (EPI == GV_EPI_RESID) {
+            const long long n = (long long)tile * R + ei;
+            if (ei < R && n < p.N && em < p.M) {
+                r_old = __ldcg(&p.resid[(size_t)em * p.N + n]);
+                if (p.xw_out) r_nw = p.next_w[n];
+            }
+        }
+        // the short convolution's state, taps and biases: none of them is written by a kernel of this
+        // step before this one, so they are asked for before the sums exist
+        float hist[EPI == GV_EPI_CONV ? GV_CONV_LMAX : 1], tapv[EPI == GV_EPI_CONV ? GV_CONV_LMAX : 1];
+        float cbias = 0.f, bB = 0.f, bC = 0.f, bX = 0.f;
+        bool slot_ok = true;
+        __nv_bfloat16* st_ptr = nullptr;
+        if (EPI == GV_EPI_CONV) {
+            const long long c = (long long)tile * 8 + ei;
+            const int L = p.L;
+#pragma unroll
+            for (int j = 0; j < GV_CONV_LMAX; ++j) hist[j] = tapv[j] = 0.f;
+            if (ei < 8 && em < p.M && c < p.ff) {
+#pragma unroll
+                for (int j = 0; j < GV_CONV_LMAX; ++j)
+                    if (j < L) tapv[j] = p.taps[(size_t)j * p.ff + c];
+                if (p.conv_bias) cbias = p.conv_bias[c];
+                if (p.bias) { bB = p.bias[c]; bC = p.bias[p.ff + c]; bX = p.bias[2 * (long long)p.ff + c]; }
+                if (L > 1) {
+                    const int slot = p.state_slots[em], p0 = p.positions[em];
+                    slot_ok = slot >= 0 && slot < p.num_slots;
+                    if (slot_ok) {
+                        st_ptr = p.state + (size_t)slot * p.slot_stride + c;
+#pragma unroll
+                        for (int j = 0; j < GV_CONV_LMAX; ++j)      // rows for positions before 0 count as zero
+                            if (j < L - 1 && p0 - (L - 1) + j >= 0) hist[j] = __bfloat162float(st_ptr[(size_t)j * p.ff]);
+                    }
+                }
+            }
+        }
+        if (REGB) {
+#pragma unroll
+            for (int j = 0; j < GV_REGB_CHUNKS; ++j) {
+                if (j < len) {
+                    const int nstage = stage == 0 ? GV_STAGES - 1 : stage - 1;
+                    queue_next(nstage, false);
+                    gv_commit();
+                    gv_wait<GV_STAGES - 1>();
+                    const uint4 wl = fifo[(stage * SLOTS + 0) * 32 + lane];
+                    const uint4 wh = fifo[(stage * SLOTS + 1) * 32 + lane];
+                    uint4 wx = make_uint4(0u, 0u, 0u, 0u);
+                    if (EPI == GV_EPI_CONV) wx = fifo[(stage * SLOTS + 2) * 32 + lane];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const uint4 av = breg[nt][j];
+                        mma16816(acc[nt], wl.x, wh.x, wl.y, wh.y, av.x, av.y);
+                        mma16816(acc[nt], wl.z, wh.z, wl.w, wh.w, av.z, av.w);
+                        if (EPI == GV_EPI_CONV) {
+                            mma16816(acc_x[nt], wx.x, 0u, wx.y, 0u, av.x, av.y);
+                            mma16816(acc_x[nt], wx.z, 0u, wx.w, 0u, av.z, av.w);
+                        }
+                    }
+                    stage = stage == GV_STAGES - 1 ? 0 : stage + 1;
+                }
+            }
+        } else
         for (int c = c_begin; c < c_end; ++c) {
             const int nstage = stage == 0 ? GV_STAGES - 1 : stage - 1;      // (stage + STAGES - 1) % STAGES
             queue_next(nstage, true);
@@ -299,7 +403,7 @@ skinny_linear_kernel(const GvParams p) {
             }
         }
         group_sync();
-        const int i = tig / COLS, m = tig - i * COLS;                      // MMA row, token
+        const int i = ei, m = em;
         const int w0 = grp * gw;                                           // the group's first warp
         float y = 0.f, y2 = 0.f;
         if (i < 16) {
@@ -328,31 +432,28 @@ skinny_linear_kernel(const GvParams p) {
                 float B = __bfloat162float(__float2bfloat16_rn(y));
                 float C = __bfloat162float(__float2bfloat16_rn(y2));
                 float X = __bfloat162float(__float2bfloat16_rn(y3));
-                if (p.bias) { B += p.bias[c]; C += p.bias[p.ff + c]; X += p.bias[2 * (long long)p.ff + c]; }
+                if (p.bias) { B += bB; C += bC; X += bX; }
                 const float gate = __bfloat162float(__float2bfloat16_rn(B * X));
                 const int L = p.L;
-                float conv = p.taps[(size_t)(L - 1) * p.ff + c] * gate;
+                float conv = 0.f;
+#pragma unroll
+                for (int j = 0; j < GV_CONV_LMAX; ++j)
+                    if (j == L - 1) conv = tapv[j] * gate;
                 if (L > 1) {
-                    const int slot = p.state_slots[m], p0 = p.positions[m];
-                    if (slot < 0 || slot >= p.num_slots) {
+                    if (!slot_ok) {
                         if (p.status) atomicExch(p.status, 3);
                     } else {
-                        __nv_bfloat16* st = p.state + (size_t)slot * p.slot_stride + c;
-                        float hist[GV_CONV_LMAX];
-#pragma unroll
-                        for (int j = 0; j < GV_CONV_LMAX; ++j)      // rows for positions before 0 count as zero
-                            hist[j] = (j < L - 1 && p0 - (L - 1) + j >= 0) ? __bfloat162float(st[(size_t)j * p.ff]) : 0.f;
                         float acc_c = 0.f;
 #pragma unroll
                         for (int j = 0; j < GV_CONV_LMAX; ++j)
-                            if (j < L - 1) acc_c += p.taps[(size_t)j * p.ff + c] * hist[j];
+                            if (j < L - 1) acc_c += tapv[j] * hist[j];
                         conv += acc_c;
 #pragma unroll
                         for (int j = 0; j < GV_CONV_LMAX; ++j)
-                            if (j < L - 1) st[(size_t)j * p.ff] = __float2bfloat16_rn(j + 1 < L - 1 ? hist[j + 1 < GV_CONV_LMAX ? j + 1 : 0] : gate);
+                            if (j < L - 1) st_ptr[(size_t)j * p.ff] = __float2bfloat16_rn(j + 1 < L - 1 ? hist[j + 1 < GV_CONV_LMAX ? j + 1 : 0] : gate);
                     }
                 }
-                if (p.conv_bias) conv += p.conv_bias[c];
+                conv += cbias;
                 p.out_bf16[(size_t)m * p.out_stride + c] = __float2bfloat16_rn(C * conv);
             }
         } else if (EPI == GV_EPI_SWIGLU) {
@@ -372,9 +473,9 @@ skinny_linear_kernel(const GvParams p) {
             } else {   // GV_EPI_RESID
                 float v = 0.f;
                 if (valid) {
-                    v = p.resid[(size_t)m * p.N + n] + y;
+                    v = r_old + y;
                     p.resid[(size_t)m * p.N + n] = v;
-                    if (p.xw_out) p.xw_out[(size_t)m * p.N + n] = __float2bfloat16_rn(v * p.next_w[n]);
+                    if (p.xw_out) p.xw_out[(size_t)m * p.N + n] = __float2bfloat16_rn(v * r_nw);
                 }
                 if (p.ss_out) {
                     group_sync();                        // everyone has read its sums out of red[]
@@ -396,10 +497,10 @@ skinny_linear_kernel(const GvParams p) {
 
 static int gv_sm_count() { return sm_count(); }
 
-template <int NT, int PRO, int EPI, bool DEEP, int WARPS>
+template <int NT, int PRO, int EPI, bool DEEP, int WARPS, bool REGB = false>
 static int launch_gv_as(const GvParams& p, int blocks, int blocks_per_sm, cudaStream_t stream) {
-    const size_t smem = gv_smem_bytes<NT, PRO, EPI, DEEP, WARPS>(p.K);
-    auto kern = skinny_linear_kernel<NT, PRO, EPI, DEEP, WARPS>;
+    const size_t smem = gv_smem_bytes<NT, PRO, EPI, DEEP, WARPS, REGB>(p.K);
+    auto kern = skinny_linear_kernel<NT, PRO, EPI, DEEP, WARPS, REGB>;
     if (smem > 200 * 1024) return fail(-1, "skinny_linear: K=%d needs %zu bytes of shared memory", p.K, smem);
     if (smem + 28 * 1024 > 48 * 1024) {      // (static shared memory, up to about 26 KB, counts toward the default limit)
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -412,19 +513,26 @@ static int launch_gv_as(const GvParams& p, int blocks, int blocks_per_sm, cudaSt
 
 template <int NT, int PRO, int EPI, bool DEEP = false>
 static int launch_gv(const GvParams& p, int blocks, cudaStream_t stream) {
-    static int per_sm = -1, wide = -1;
+    static int per_sm = -1, wide = -1, regb = -1;
     if (per_sm < 0) {
         const char* e = getenv("VAPI_GV_BLOCKS_PER_SM");
         per_sm = e ? atoi(e) : 2;
         const char* w = getenv("VAPI_GV_WIDE");
         wide = (w && w[0] == '0') ? 0 : 1;
+        const char* r = getenv("VAPI_GV_REGB");     // bits: 1 norm prologue, 2 plain activations, 4 nine to sixteen tokens
+        regb = r ? atoi(r) : 1;
     }
+    // the tokens' rows in registers where a warp's slice of K is at most GV_REGB_CHUNKS chunks
+    const bool in_regs = (regb & (PRO == GV_PRO_NORM ? 1 : 2)) && (NT == 1 || (regb & 4)) && !DEEP &&
+                         (p.K >> 5) <= GV_REGB_CHUNKS * GV_WARPS;
     if (NT == 2 && wide) {
         // sixteen warps, one block per SM, where the queue and the tokens' rows fit (with the static arrays beside them)
-        constexpr int W = GV_WIDE_WARPS;
+        constexpr int W = NT == 2 ? GV_WIDE_WARPS : GV_WARPS;
+        if (in_regs) return launch_gv_as<NT, PRO, EPI, false, W, !DEEP>(p, blocks, 1, stream);
         if (gv_smem_bytes<NT, PRO, EPI, false, W>(p.K) <= 198 * 1024)
-            return launch_gv_as<NT, PRO, EPI, false, (NT == 2 ? W : GV_WARPS)>(p, blocks, 1, stream);
+            return launch_gv_as<NT, PRO, EPI, false, W>(p, blocks, 1, stream);
     }
+    if (in_regs) return launch_gv_as<NT, PRO, EPI, false, GV_WARPS, !DEEP>(p, blocks, per_sm, stream);
     return launch_gv_as<NT, PRO, EPI, DEEP, GV_WARPS>(p, blocks, per_sm, stream);
 }
 
