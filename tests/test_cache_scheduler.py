@@ -14,8 +14,8 @@ from vapi_b200.sampling.params import FinishReason, SamplingParams
 
 
 def make_cache(num_pages=8, page=16, max_requests=4, window=0, watermark=0.0, extra=()):
-    sites = [(0, StateSpec("shortconv", (2, 8))), (1, PagedSpec(2, 16, window)), (2, StateSpec("shortconv", (2, 8))),
-             (3, PagedSpec(2, 16, window))] + list(extra)
+    sites = [(0, StateSpec("shortconv", (2, 8))), (1, PagedSpec.kv(2, 16, window)), (2, StateSpec("shortconv", (2, 8))),
+             (3, PagedSpec.kv(2, 16, window))] + list(extra)
     return CacheManager(sites, page_size=page, num_pages=num_pages, max_requests=max_requests,
                         dtype=torch.float32, device="cpu", watermark=watermark)
 
@@ -40,13 +40,45 @@ def test_pool_refuses_double_free_and_exhaustion():
 
 
 def test_groups_and_tensors():
-    c = make_cache(extra=[(4, PagedSpec(1, 32, 0))])
+    c = make_cache(extra=[(4, PagedSpec.kv(1, 32, 0))])
     assert len(c.paged) == 2 and len(c.state) == 1
-    assert c.paged[0].tensor.shape == (2, 8, 2, 2, 16, 16) and c.paged[1].tensor.shape == (1, 8, 2, 1, 16, 32)
+    # pages are flat: [sites, pages, page_size * elements per token]; the buffers are views into them
+    assert c.paged[0].tensor.shape == (2, 8, 16 * 2 * 2 * 16) and c.paged[1].tensor.shape == (1, 8, 16 * 2 * 32)
     assert c.state[0].tensor.shape == (5, 2, 2, 8)          # 4 slots + the scratch slot
-    assert c.site_tensor(3).shape == (8, 2, 2, 16, 16) and c.site_tensor(2).shape == (5, 2, 8)
+    assert c.site_tensor(3).shape == (8, 16 * 64) and c.site_tensor(2).shape == (5, 2, 8)
     assert c.site_tensor(3).data_ptr() == c.paged[0].tensor[1].data_ptr()
     assert c.bytes_per_token() == (2 * 2 * 2 * 16 + 1 * 2 * 32) * 4
+    bufs = c.site_buffers(3)
+    assert sorted(bufs) == ["k", "v"] and bufs["k"].shape == (8, 2, 16, 16)
+    assert bufs["v"].data_ptr() - bufs["k"].data_ptr() == 2 * 16 * 16 * 4      # values follow the keys inside a page
+    c.site_tensor(3).zero_()
+    bufs["v"][5, 1, 3, 7] = 2.0
+    from vapi_b200.parts.base import CacheView
+    kv = CacheView("paged", c.site_tensor(3), None, True, bufs, c.site_spec(3)).stacked()
+    assert kv.shape == (8, 2, 2, 16, 16) and float(kv[5, 1, 1, 3, 7]) == 2.0 and float(kv.sum()) == 2.0
+
+
+def test_buffers_of_unlike_shapes_share_a_page():
+    """A spec whose buffers differ (a wide row and a narrow one per token): the page holds them one
+    after the other, and each is reachable as its own view."""
+    from vapi_b200.parts.base import CacheView, PagedBuffer
+    spec = PagedSpec((PagedBuffer("latent", 1, 24), PagedBuffer("rope_key", 2, 8)), 0)
+    assert spec.elems_per_token() == 40 and not spec.uniform()
+    c = CacheManager([(0, spec), (1, PagedSpec.rows(24))], page_size=16, num_pages=4, max_requests=2, dtype=torch.float32,
+                     device="cpu")
+    assert len(c.paged) == 2 and c.paged[0].tensor.shape == (1, 4, 16 * 40)
+    bufs = c.site_buffers(0)
+    assert bufs["latent"].shape == (4, 1, 16, 24) and bufs["rope_key"].shape == (4, 2, 16, 8)
+    c.site_tensor(0).zero_()
+    bufs["latent"][2, 0, 15, 23] = 1.0
+    bufs["rope_key"][2, 1, 0, 0] = 3.0
+    flat = c.site_tensor(0)
+    assert float(flat[2, 16 * 24 - 1]) == 1.0 and float(flat[2, 16 * 24 + 16 * 8]) == 3.0 and float(flat.sum()) == 4.0
+    with pytest.raises(ValueError, match="equal shape"):
+        CacheView("paged", flat, None, True, bufs, spec).stacked()
+    # one row per token: the pages read as one long table of rows, indexed by page * page_size + offset
+    rows = c.site_buffers(1)["row"]
+    assert rows.shape == (4, 1, 16, 24) and rows.reshape(64, 24).data_ptr() == rows.data_ptr()
 
 
 def test_reserve_is_all_or_nothing_and_close_gives_everything_back():

@@ -701,6 +701,91 @@ def test_a_toy_mixer_with_its_own_state_can_be_registered_built_and_stepped(tmp_
         MIXERS.pop("toy_running_mean", None)
 
 
+# ---- a toy mixer that pages one row per token ---------------------------------------------------
+def test_a_toy_mixer_that_pages_one_row_per_token_through_the_pools(tmp_path):
+    """A causal convolution that keeps its input rows in the paged cache instead of a state slot
+    (the reference's own layout for its conv layers, ``LayerLayout::Rows``,
+    crates/vapi-backend-candle/src/cache.rs:22-45): one buffer of one row of the hidden width per
+    token, with a window so that pages come back.  The cache manager lays the pages out from the
+    description alone; the mixer reads earlier rows through the block table.  Defined here,
+    registered, built and stepped (whole, portions, captured decode steps) without a change to
+    the package."""
+    from vapi_b200.config import Architecture, register_architecture, unregister_architecture
+    from vapi_b200.engine.runner import ModelRunner
+    from vapi_b200.models.plan import LayerCall, ModelPlan
+    from vapi_b200.parts import (MIXERS, CacheView, Mixer, OutputHead, PagedSpec, PreNormBlock, RMSNorm, SwiGLU, TensorSpec,
+                                 TokenEmbedding, make_part, register_mixer)
+    from vapi_b200.weights import write_random_model
+    L = 4
+
+    class PagedRowsConv(Mixer):
+        def __init__(self, hidden, taps):
+            self.hidden, self.L = hidden, taps
+
+        def cache_spec(self):
+            return PagedSpec.rows(self.hidden, window=self.L)
+
+        def tensor_specs(self, prefix):
+            return [TensorSpec(prefix + "taps", (self.L, self.hidden), role="vector")]
+
+        def bind(self, tensors, prefix, dtype):
+            self.taps = tensors[prefix + "taps"]
+
+        def forward(self, a, ctx, cache):
+            rows = cache.buffers["row"]                              # [pages, 1, page_size, hidden]
+            page = rows.shape[2]
+            table = rows.view(-1, self.hidden)                       # row of (page, offset) at page * page_size + offset
+            if cache.write:
+                table.index_copy_(0, cache.group.slot_mapping.long(), a)
+            pos, seq = ctx.positions.long(), ctx.tok_seq.long()
+            out = self.taps[self.L - 1] * a.float()
+            for k in range(1, self.L):                               # the row k positions back, through the block table
+                q = (pos - k).clamp(min=0)
+                slot = cache.group.block_table[seq, q // page].long() * page + q % page
+                out = out + torch.where((pos - k >= 0)[:, None], self.taps[self.L - 1 - k] * table[slot].float(), 0.0)
+            return out.to(a.dtype)
+
+    register_mixer("toy_paged_rows_conv", PagedRowsConv, replace=True)
+
+    def plan(cfg):
+        H, V = cfg["hidden_size"], cfg["vocab_size"]
+        emb = TokenEmbedding(V, H, "emb.weight")
+        layers = [PreNormBlock(RMSNorm(H, 1e-5), make_part(MIXERS, "toy_paged_rows_conv", hidden=H, taps=L), RMSNorm(H, 1e-5),
+                               SwiGLU(H, 64), {"mixer_norm": "n1.", "mixer": "mix.", "ffn_norm": "n2.", "ffn": "ffn."})
+                  for _ in range(2)]
+        return ModelPlan("ToyRowsForCausalLM", V, H, 512, emb, layers, ["l0.", "l1."], [LayerCall(0), LayerCall(1)],
+                         RMSNorm(H, 1e-5), "final.", OutputHead(V, H, True, emb))
+
+    register_architecture(Architecture("ToyRowsForCausalLM", ("toy_rows",), lambda v: v, plan), replace=True)
+    try:
+        cfg = {"architectures": ["ToyRowsForCausalLM"], "vocab_size": 100, "hidden_size": 48}
+        d = write_random_model(str(tmp_path / "toy"), cfg, 0, std=0.3, norm_init="perturbed")
+        # the mixer alone against the convolution written out
+        r = ModelRunner.from_dir(d, dtype="float32", num_pages=6, page_size=16, max_requests=3, max_batched_tokens=64,
+                                 max_context=128)
+        assert len(r.cache.paged) == 1 and r.cache.paged[0].spec.window == L
+        assert r.cache.paged[0].tensor.shape == (2, 6, 16 * 48), "two call sites, pages of 16 rows of 48"
+        mixer = r.plan.layers[0].mixer
+        T = 21
+        a = torch.randn(T, 48, device="cuda")
+        ctx = _ctx_for(T, 1, [0, T], [T], list(range(T)), page_table=[[3, 1]], slots=[[3, 1][p // 16] * 16 + p % 16 for p in range(T)])
+        got = mixer.forward(a, ctx, CacheView("paged", r.cache.site_tensor(0), ctx.groups[0], True, r.cache.site_buffers(0),
+                                              r.cache.site_spec(0)))
+        want = torch.zeros_like(a)
+        for t in range(T):
+            for k in range(L):
+                if t - k >= 0:
+                    want[t] += mixer.taps[L - 1 - k] * a[t - k]
+        assert float((got - want).abs().max()) < 1e-5
+        # the model through the step function: 45 tokens need 3 pages at once only if nothing came back
+        toks = torch.randint(0, 100, (45,), generator=torch.Generator().manual_seed(0)).tolist()
+        _whole_cut_and_token_by_token(r, toks, 100, 1e-5, graphs=True)
+        r.cache.check_invariants()
+    finally:
+        unregister_architecture("ToyRowsForCausalLM")
+        MIXERS.pop("toy_paged_rows_conv", None)
+
+
 # ---- a toy feed-forward with routing and a toy position encoding -----------------------------
 @pytest.mark.parametrize("dtype,hidden", [("float32", 48), ("bfloat16", 64)])
 def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_can_be_registered_built_and_stepped(tmp_path, dtype, hidden):

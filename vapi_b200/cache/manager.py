@@ -2,10 +2,13 @@
 
 Call sites of the model's run order that own a cache are grouped by what they need:
 
-* a **paged group** per distinct :class:`~vapi_b200.parts.base.PagedSpec` (kv heads, head
-  size, window).  Each group has pages of its own: one pool, one device tensor
-  ``[sites, pages, 2, n_kv, page_size, head_dim]`` and one block table per request.  A group
-  with a window gives pages back as soon as the window has passed them.
+* a **paged group** per distinct :class:`~vapi_b200.parts.base.PagedSpec` (the buffers a mixer
+  keeps per token, and its window).  Each group has pages of its own: one pool, one device
+  tensor ``[sites, pages, page_size * elements per token]`` and one block table per request.
+  Inside a page the spec's buffers follow one another, each as ``[rows, page_size, width]``, so
+  keys and values of ``n_kv`` heads lie as ``[2, n_kv, page_size, head_dim]``; the manager
+  itself only knows sizes.  A group with a window gives pages back as soon as the window has
+  passed them.
 * a **state group** per distinct :class:`~vapi_b200.parts.base.StateSpec`: one device tensor
   ``[slots + 1, sites, *shape]``.  All state groups share one slot pool, so a request holds a
   single slot index that is valid in every state tensor.  The extra last slot is a scratch
@@ -39,7 +42,7 @@ class PagedGroup:
     spec: PagedSpec
     sites: List[int]
     pool: PagePool
-    tensor: torch.Tensor            # [sites, pages, 2, n_kv, page_size, head_dim]
+    tensor: torch.Tensor            # [sites, pages, page_size * elements per token]
 
     def bytes_per_token(self) -> int:
         return len(self.sites) * self.spec.elems_per_token() * self.tensor.element_size()
@@ -122,7 +125,7 @@ class CacheManager:
         if not self._h:
             raise ValueError(hostlib.last_error())
         for gi, (spec, ss) in enumerate(by_paged.items()):
-            t = torch.empty((len(ss), sizes[gi][0], 2, spec.n_kv, self.page_size, spec.head_dim),
+            t = torch.empty((len(ss), sizes[gi][0], self.page_size * spec.elems_per_token()),
                             dtype=dtype, device=self.device)
             pool = PagePool(borrowed=self._lib.vh_cache_group_pool(self._h, gi), owner=self)
             self.paged.append(PagedGroup(spec, list(ss), pool, t))
@@ -167,13 +170,35 @@ class CacheManager:
         return kind, gi
 
     def site_tensor(self, site: int) -> Optional[torch.Tensor]:
-        """This call site's part of the cache: [pages, 2, n_kv, page, d] or [slots+1, *shape]."""
+        """This call site's part of the cache: its pages, flat [pages, page_size * elements per
+        token], or its states [slots+1, *shape]."""
         if site not in self._site:
             return None
         kind, gi, j = self._site[site]
         if kind == "paged":
             return self.paged[gi].tensor[j]
         return self.state[gi].tensor[:, j]
+
+    def site_buffers(self, site: int) -> Optional[Dict[str, torch.Tensor]]:
+        """A paged call site's pages seen buffer by buffer: name -> [pages, rows, page_size, width]
+        (views of the same memory; the stride between pages is the whole page)."""
+        if site not in self._site or self._site[site][0] != "paged":
+            return None
+        _, gi, j = self._site[site]
+        spec, flat = self.paged[gi].spec, self.paged[gi].tensor[j]
+        out, off = {}, 0
+        for b in spec.buffers:
+            out[b.name] = flat.as_strided((flat.shape[0], b.rows, self.page_size, b.width),
+                                          (flat.stride(0), self.page_size * b.width, b.width, 1), flat.storage_offset() + off)
+            off += b.rows * self.page_size * b.width
+        return out
+
+    def site_spec(self, site: int):
+        """The spec of the group that the call site's cache belongs to."""
+        if site not in self._site:
+            return None
+        kind, gi, _ = self._site[site]
+        return self.paged[gi].spec if kind == "paged" else self.state[gi].spec
 
     def set_aside_pages(self) -> Optional[List[int]]:
         """Take one page per paged group out of circulation (for the padding rows of a

@@ -82,6 +82,7 @@ class ModelRunner:
         for i, call in enumerate(plan.order):
             owner = call.cache_of if call.cache_of is not None else i
             self._site_of.append(owner if self.cache.site_tensor(owner) is not None else None)
+        self._site_buffers = {s: self.cache.site_buffers(s) for s in set(self._site_of) if s is not None}
         self.steps_run = 0
         self.graph_max_batch = min(64, max_requests)
         self._graphs: Dict[int, Any] = {}
@@ -149,7 +150,9 @@ class ModelRunner:
             kind, gi = self.cache.site_kind(site)
             out.append(CacheView(kind, self.cache.site_tensor(site),
                                  ctx.groups[gi] if kind == "paged" else None,
-                                 write=call.cache_of is None))
+                                 write=call.cache_of is None,
+                                 buffers=self._site_buffers[site] if kind == "paged" else None,
+                                 spec=self.cache.site_spec(site)))
         return out
 
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:

@@ -1,5 +1,5 @@
 """Parts a model is assembled from: mixers, feed-forwards, norms, position encodings, blocks."""
-from .base import (CacheView, FeedForward, Mixer, Norm, NormedStream, PagedSpec, StreamState, Part, PositionEncoding, StateSpec,
+from .base import (CacheView, FeedForward, Mixer, Norm, NormedStream, PagedBuffer, PagedSpec, StreamState, Part, PositionEncoding, StateSpec,
                    TensorSpec, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, make_part,
                    register_feed_forward, register_mixer, register_norm, register_position_encoding)
 from .norm import RMSNorm
@@ -11,7 +11,7 @@ from .embedding import OutputHead, TokenEmbedding
 from .block import BLOCKS, PreNormBlock, register_block
 
 __all__ = [
-    "CacheView", "FeedForward", "Mixer", "Norm", "NormedStream", "PagedSpec", "StreamState", "Part", "PositionEncoding", "StateSpec",
+    "CacheView", "FeedForward", "Mixer", "Norm", "NormedStream", "PagedBuffer", "PagedSpec", "StreamState", "Part", "PositionEncoding", "StateSpec",
     "TensorSpec", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "BLOCKS", "make_part",
     "register_feed_forward", "register_mixer", "register_norm", "register_position_encoding",
     "register_block", "RMSNorm", "RotaryEncoding", "GQAttention", "ShortConv", "SwiGLU", "OutputHead",

@@ -44,7 +44,7 @@ class GQAttention(Mixer):
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_w = self.k_w = None
 
     def cache_spec(self):
-        return PagedSpec(self.nkv, self.d, self.window)
+        return PagedSpec.kv(self.nkv, self.d, self.window)
 
     def tensor_specs(self, prefix: str) -> List[TensorSpec]:
         n, (h, nh, nkv, d) = self.names, (self.hidden, self.nh, self.nkv, self.d)
@@ -100,25 +100,26 @@ class GQAttention(Mixer):
             cos, sin = ctx.pos[self.pos]
         grp = cache.group
         n_rep = nh // nkv
+        kv = cache.stacked() if cache.tensor is not None else None      # [pages, 2, n_kv, page_size, head_dim]
         splits = grp.splits if getattr(grp, "splits", None) is not None else ctx.attention_splits
         max_k = getattr(grp, "max_k", None) or ctx.max_k
         if self.window > 0:
             max_k = min(max_k, self.window + ctx.max_q - 1)      # a query reads at most `window` keys
-        if (ops.FUSED_DECODE_ROPE and qkv.is_cuda and cache.tensor is not None
-                and ops.decode_attention_fused_applies(qkv.dtype, d, cache.tensor.shape[3], ctx.max_q * n_rep,
+        if (ops.FUSED_DECODE_ROPE and qkv.is_cuda and kv is not None
+                and ops.decode_attention_fused_applies(qkv.dtype, d, kv.shape[3], ctx.max_q * n_rep,
                                                        self.rot_dim if cos is not None else None)
                 and (cos is None or (cos.is_contiguous() and sin.is_contiguous()))):
             # a decode step: norm, rotation and the cache write ride in the attention kernel
             return ops.decode_attention_fused(qkv, nh, nkv, d, self.q_w, self.k_w,
                                               self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, cos, sin,
-                                              cache.tensor, cache.write, grp.block_table, ctx.cu_q, ctx.seqlens_k,
+                                              kv, cache.write, grp.block_table, ctx.cu_q, ctx.seqlens_k,
                                               ctx.n, ctx.num_seqs, ctx.max_q, max_k, self.scale, self.window,
                                               splits, ctx.status)
         ops.qk_norm_rope_write(qkv, nh, nkv, d, self.q_w, self.k_w,
                                self.qk_norm_eps if self.qk_norm_eps is not None else 0.0,
                                cos, sin, self.rot_dim,
-                               cache.tensor if cache.write else None, grp.slot_mapping, ctx.status)
-        y = ops.paged_attention(qkv, qkv.stride(0), cache.tensor, grp.block_table, ctx.cu_q,
+                               kv if cache.write else None, grp.slot_mapping, ctx.status)
+        y = ops.paged_attention(qkv, qkv.stride(0), kv, grp.block_table, ctx.cu_q,
                                 ctx.seqlens_k, ctx.n, ctx.num_seqs, ctx.max_q, max_k, nh, nkv, d,
                                 self.scale, self.window, splits, ctx.status)
         return y

@@ -46,20 +46,52 @@ class TensorSpec:
 
 
 @dataclass(frozen=True)
+class PagedBuffer:
+    """One thing a mixer keeps for every token of a request: ``rows`` rows of ``width`` elements
+    (keys: one row of ``head_dim`` per kv head; a latent or a conv input: one row of its width)."""
+
+    name: str
+    rows: int
+    width: int
+
+
+@dataclass(frozen=True)
 class PagedSpec:
-    """Per-token cache in pages: keys and values of ``n_kv`` heads of ``head_dim``.
+    """Per-token cache in pages, described so that the cache manager can lay it out without
+    knowing what the mixer is: a tuple of :class:`PagedBuffer`, each holding some rows of some
+    width for every token (the reference's ``LayerLayout::{Kv, Rows}``,
+    crates/vapi-backend-candle/src/cache.rs:22-45).  Keys and values of grouped-query attention
+    are the special case of two buffers of ``n_kv`` rows of ``head_dim`` (:meth:`kv`).
+
+    A page holds ``page_size`` tokens; inside a page the buffers follow one another, each as
+    ``[rows, page_size, width]``.  Buffers of equal shape therefore lie as
+    ``[n_buffers, rows, page_size, width]`` (:meth:`CacheView.stacked`), which is what the
+    attention kernels read.
 
     ``window`` = 0 keeps every position; ``window`` = W > 0 means positions more than W
     behind the newest are never read again, so the manager may give their pages back.
     Layers with equal specs share one group: one pool of pages, one block table a request.
     """
 
-    n_kv: int
-    head_dim: int
+    buffers: Tuple[PagedBuffer, ...]
     window: int = 0
 
+    @classmethod
+    def kv(cls, n_kv: int, head_dim: int, window: int = 0) -> "PagedSpec":
+        """Keys and values of ``n_kv`` heads of ``head_dim``."""
+        return cls((PagedBuffer("k", int(n_kv), int(head_dim)), PagedBuffer("v", int(n_kv), int(head_dim))), int(window))
+
+    @classmethod
+    def rows(cls, width: int, name: str = "row", window: int = 0) -> "PagedSpec":
+        """One row of ``width`` elements per token."""
+        return cls((PagedBuffer(name, 1, int(width)),), int(window))
+
     def elems_per_token(self) -> int:
-        return 2 * self.n_kv * self.head_dim
+        return sum(b.rows * b.width for b in self.buffers)
+
+    def uniform(self) -> bool:
+        """Whether all buffers have one shape (so that they can be read as one stacked tensor)."""
+        return len({(b.rows, b.width) for b in self.buffers}) == 1
 
 
 @dataclass(frozen=True)
@@ -80,16 +112,34 @@ class StateSpec:
 class CacheView:
     """What a mixer sees of the cache at one call site of one step.
 
-    ``paged``: ``tensor`` is this layer's [pages, 2, n_kv, page_size, head_dim]; ``group`` has
-    the step's ``slot_mapping`` [n] and ``block_table`` [S, width] for the layer's group.
-    ``state``: ``tensor`` is this layer's view [slots, *shape]; ``ctx.state_slots`` [S] names
-    each sequence's slot.  ``write`` False: the call site reads a cache another layer owns.
+    ``paged``: ``tensor`` is this call site's pages, flat: [pages, page_size * elements per token];
+    ``buffers`` names a view ``[pages, rows, page_size, width]`` of it for each
+    :class:`PagedBuffer` of the mixer's spec, and :meth:`stacked` gives buffers of equal shape as
+    one ``[pages, n_buffers, rows, page_size, width]`` (keys and values:
+    ``[pages, 2, n_kv, page_size, head_dim]``); ``group`` has the step's ``slot_mapping`` [n]
+    (page * page_size + offset of each new token) and ``block_table`` [S, width] for the layer's
+    group.  ``state``: ``tensor`` is this call site's view [slots, *shape]; ``ctx.state_slots``
+    [S] names each sequence's slot.  ``write`` False: the call site reads a cache another layer
+    owns.
     """
 
     kind: str                 # "paged" | "state" | "none"
     tensor: Optional[torch.Tensor] = None
     group: Any = None
     write: bool = True
+    buffers: Optional[Dict[str, torch.Tensor]] = None
+    spec: Any = None
+
+    def stacked(self) -> torch.Tensor:
+        """Buffers of one shape as a single tensor [pages, n_buffers, rows, page_size, width]."""
+        if self.kind == "paged" and self.tensor is not None and self.tensor.dim() == 5:
+            return self.tensor               # handed over in that shape already
+        if self.kind != "paged" or self.spec is None or not self.spec.uniform():
+            raise ValueError("only paged buffers of equal shape can be read as one stacked tensor")
+        b = self.spec.buffers[0]
+        pages = self.tensor.shape[0]
+        page_size = self.tensor.shape[1] // self.spec.elems_per_token()
+        return self.tensor.view(pages, len(self.spec.buffers), b.rows, page_size, b.width)
 
 
 @dataclass
