@@ -749,6 +749,28 @@ def test_skinny_linear_residual_epilogue_over_a_long_inner_size(ops, M, N, K):
     torch.testing.assert_close(xr.cpu(), want + a.float() @ w.float().t(), atol=6e-3, rtol=1e-3)
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 11, 16])
+@pytest.mark.parametrize("N,K", [(70, 96), (2048, 2048), (1003, 324), (515, 8192), (6, 4)])
+def test_skinny_linear_float32_is_plain_float_arithmetic(ops, M, N, K):
+    """The decode product of the 32-bit path: float weights, FMA only.  Against a float64 product
+    the error must be that of float32 sums (a product rounded to 19 or 10 bits of mantissa, as the
+    tensor cores' reduced modes would give, is a hundred times off), a token's result must not
+    depend on what else is in the batch, and `linear` must send decode-sized float products there."""
+    torch.manual_seed(30)
+    w = torch.randn(N, K)
+    a = torch.randn(M, K)
+    b = torch.randn(N)
+    want = (a.double() @ w.double().t() + b.double())
+    got = ops.skinny_linear_f32(dev(w), dev(a), dev(b))
+    err = (got.cpu().double() - want).abs().max().item()
+    assert err < 3e-7 * K ** 0.5 * max(1.0, want.abs().max().item()) + 1e-6, err
+    alone = ops.skinny_linear_f32(dev(w), dev(a[M - 1:]), dev(b))
+    assert torch.equal(alone[0], got[M - 1]), "a token's row must not depend on the batch"
+    before = ops.launch_count
+    via = ops.linear(dev(a), dev(w), dev(b))
+    assert ops.launch_count == before + 1 and torch.equal(via, got)
+
+
 def test_embed_and_residual_add_prepare_the_next_norm(ops):
     torch.manual_seed(22)
     table = torch.randn(50, 72).to(torch.bfloat16)

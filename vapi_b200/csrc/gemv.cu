@@ -623,4 +623,117 @@ VAPI_EXPORT int vapi_skinny_linear_conv(const void* W, int H, int K, int M, cons
     return launch_gv<2, GV_PRO_NORM, GV_EPI_CONV>(p, blocks, stream);
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same product on the true 32-bit path: float weights, float tokens, float FMA and nothing
+// else (no tensor cores, no reduced-precision mode), for the decode steps of that path.  A warp
+// owns a few weight rows and walks K in 16-byte pieces, a chunk of K at a time; the tokens' pieces
+// of a chunk are used for all rows of all warps of the block.  The sum over K is formed per (token, row) in an order that depends on K alone:
+// lane-strided partial sums, then a butterfly over the lanes, so a token's result does not
+// depend on what else is in the batch.
+constexpr int F32_WARPS = 8;
+// rows of the weight a warp owns, and 16-byte pieces of each row that a lane asks for together
+// (fewer of both for nine to sixteen tokens, whose sums take the registers)
+__host__ __device__ constexpr int f32_rows(int mt) { return mt <= 8 ? 4 : 2; }
+__host__ __device__ constexpr int f32_depth(int mt) { return mt <= 8 ? 4 : 2; }
+
+// The tokens' rows travel through shared memory, a chunk of K at a time (two buffers, filled by
+// asynchronous copies one chunk ahead), so that they are read from L2 once per block, not once per warp.
+template <int MT>
+__global__ void __launch_bounds__(F32_WARPS * 32)
+skinny_linear_f32_kernel(const float* __restrict__ W, const float* __restrict__ act, const float* __restrict__ bias,
+                         float* __restrict__ out, int N, int K, int M, long long out_stride) {
+    constexpr int F32_ROWS = f32_rows(MT), F32_DEPTH = f32_depth(MT);
+    constexpr int F32_CHUNK = 32 * F32_DEPTH;             // pieces of K in a chunk
+    __shared__ float4 abuf[2][MT][F32_CHUNK];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long n0 = ((long long)blockIdx.x * F32_WARPS + warp) * F32_ROWS;
+    pdl_trigger();
+    float acc[F32_ROWS][MT];
+#pragma unroll
+    for (int r = 0; r < F32_ROWS; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
+    const int k4 = K >> 2;
+    const int chunks = (k4 + F32_CHUNK - 1) / F32_CHUNK;
+    const float4* wrow[F32_ROWS];
+#pragma unroll
+    for (int r = 0; r < F32_ROWS; ++r) wrow[r] = reinterpret_cast<const float4*>(W + (size_t)(n0 + r < N ? n0 + r : 0) * K);
+    float4 w[F32_DEPTH][F32_ROWS];
+    auto fetch = [&](int c0) {          // this lane's pieces of a chunk of its rows
+#pragma unroll
+        for (int u = 0; u < F32_DEPTH; ++u)
+#pragma unroll
+            for (int r = 0; r < F32_ROWS; ++r)
+                w[u][r] = (c0 + 32 * u < k4 && n0 < N) ? __ldcs(wrow[r] + c0 + 32 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    auto stage = [&](int chunk, int buf) {     // the tokens' pieces of a chunk, by the whole block
+        for (int idx = threadIdx.x; idx < MT * F32_CHUNK; idx += F32_WARPS * 32) {
+            const int m = idx / F32_CHUNK, c = idx - m * F32_CHUNK, cg = chunk * F32_CHUNK + c;
+            const bool ok = m < M && cg < k4;
+            gv_cp16(&abuf[buf][m][c], reinterpret_cast<const float4*>(act + (size_t)(ok ? m : 0) * K) + (ok ? cg : 0), ok ? 16 : 0);
+        }
+        gv_commit();
+    };
+    fetch(lane);                         // the weights do not depend on the kernel before this one
+    pdl_wait();
+    stage(0, 0);
+    for (int ch = 0; ch < chunks; ++ch) {
+        if (ch + 1 < chunks) stage(ch + 1, (ch + 1) & 1);
+        else gv_commit();
+        gv_wait<1>();
+        __syncthreads();                 // chunk ch of the tokens is in place for every warp
+        if (ch > 0) fetch(ch * F32_CHUNK + lane);
+#pragma unroll
+        for (int u = 0; u < F32_DEPTH; ++u) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                const float4 a = abuf[ch & 1][m][lane + 32 * u];
+#pragma unroll
+                for (int r = 0; r < F32_ROWS; ++r) {
+                    acc[r][m] = fmaf(w[u][r].x, a.x, acc[r][m]);
+                    acc[r][m] = fmaf(w[u][r].y, a.y, acc[r][m]);
+                    acc[r][m] = fmaf(w[u][r].z, a.z, acc[r][m]);
+                    acc[r][m] = fmaf(w[u][r].w, a.w, acc[r][m]);
+                }
+            }
+        }
+        __syncthreads();                 // everyone is done with this buffer before it is filled again
+    }
+    gv_wait<0>();
+    if (n0 >= N) return;
+#pragma unroll
+    for (int r = 0; r < F32_ROWS; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[r][m] = warp_sum(acc[r][m]);
+    if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < F32_ROWS; ++r) {
+            if (n0 + r < N) {
+                const float b = bias ? bias[n0 + r] : 0.f;
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+                    if (m < M) out[(size_t)m * out_stride + n0 + r] = acc[r][m] + b;
+            }
+        }
+    }
+}
+
+// y[m][n] = sum_k act[m][k] * W[n][k] (+ bias[n]) in float, M <= 16, K a multiple of 4.
+VAPI_EXPORT int vapi_skinny_linear_f32(const float* W, int N, int K, int M, const float* act, const float* bias,
+                                       float* out, long long out_stride, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (M > 16) return fail(-1, "skinny_linear_f32: %d rows are more than 16", M);
+    if (N <= 0 || K <= 0 || K % 4 != 0) return fail(-1, "skinny_linear_f32: K=%d must be a positive multiple of 4 (N=%d)", K, N);
+    if (!W || !act || !out) return fail(-1, "skinny_linear_f32: missing array");
+    if ((((uintptr_t)W | (uintptr_t)act) & 15) != 0) return fail(-1, "skinny_linear_f32: operands must be 16-byte aligned");
+    const int mt = M <= 1 ? 1 : (M <= 4 ? 4 : (M <= 8 ? 8 : 16));
+    const int blocks = (N + F32_WARPS * f32_rows(mt) - 1) / (F32_WARPS * f32_rows(mt));
+    cudaError_t e;
+    if (M <= 1) e = launch(skinny_linear_f32_kernel<1>, blocks, F32_WARPS * 32, 0, stream, W, act, bias, out, N, K, M, out_stride);
+    else if (M <= 4) e = launch(skinny_linear_f32_kernel<4>, blocks, F32_WARPS * 32, 0, stream, W, act, bias, out, N, K, M, out_stride);
+    else if (M <= 8) e = launch(skinny_linear_f32_kernel<8>, blocks, F32_WARPS * 32, 0, stream, W, act, bias, out, N, K, M, out_stride);
+    else e = launch(skinny_linear_f32_kernel<16>, blocks, F32_WARPS * 32, 0, stream, W, act, bias, out, N, K, M, out_stride);
+    return check_launch("skinny_linear_f32", e);
+}
+
 VAPI_EXPORT const char* vapi_last_error() { return error_buffer(); }

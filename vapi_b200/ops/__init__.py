@@ -478,6 +478,30 @@ def few_rows_linear(weight: torch.Tensor, **kw):
     return linear_tc(weight, **kw)
 
 
+def skinny_f32_applies(rows: int, weight: torch.Tensor) -> bool:
+    """Whether the float32 weight-streaming kernel takes this product: float32 weight, at most 16
+    rows, inner size a multiple of 4."""
+    return (use_skinny and weight.is_cuda and weight.dtype == torch.float32 and 0 < rows <= SKINNY_MAX_ROWS
+            and weight.dim() == 2 and weight.shape[1] % 4 == 0 and weight.is_contiguous() and weight.data_ptr() % 16 == 0)
+
+
+def skinny_linear_f32(weight: torch.Tensor, act: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``act @ weight.T (+ bias)`` for at most 16 rows in true float32 (FMA only): the decode
+    product of the 32-bit path, bound by reading the weight once."""
+    _cuda(weight, act, bias)
+    N, K = weight.shape
+    M = act.shape[0]
+    if weight.dtype != torch.float32 or not weight.is_contiguous():
+        raise KernelError("skinny_linear_f32 needs a contiguous float32 weight")
+    if act.dtype != torch.float32 or tuple(act.shape) != (M, K) or not act.is_contiguous():
+        raise KernelError(f"skinny_linear_f32: token operand {tuple(act.shape)} / {act.dtype} does not fit a weight of {N}x{K}")
+    _f32(bias, "bias")
+    out = torch.empty((M, N), dtype=torch.float32, device=weight.device)
+    lib = _lib("gemv")
+    _check(lib, lib.vapi_skinny_linear_f32(_p(weight), N, K, M, _p(act), _p(bias), _p(out), ctypes.c_longlong(N), _stream()))
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """``x @ weight.T (+ bias)``.  The library matrix product, except for decode-sized
@@ -497,6 +521,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
             return linear_tc(weight, act=x, epilogue="bf16", bias=bias)
         if out_dtype == torch.float32:
             return linear_tc(weight, act=x, epilogue="f32", bias=bias)
+    if (x.dtype == torch.float32 and out_dtype in (None, torch.float32) and skinny_f32_applies(x.shape[0], weight)
+            and x.is_contiguous() and x.data_ptr() % 16 == 0):
+        return skinny_linear_f32(weight, x, bias)
     if weight.dtype != x.dtype:
         y = torch.mm(x.to(torch.float32), weight.to(torch.float32).t())
         if bias is not None:
