@@ -728,6 +728,50 @@ def test_skinny_linear_fusions_with_more_tiles_than_blocks(ops, M):
     assert torch.equal(ops.skinny_linear(dev(w13), xw=dev(xw), ss_in=dev(parts), eps=eps, epilogue="swiglu"), s_)
 
 
+@pytest.fixture()
+def tma_weights(ops):
+    """The decode product in its second form: weights by TMA into mbarrier rings."""
+    was = ops.skinny_use_tma(True)
+    yield
+    ops.skinny_use_tma(was)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("N,K", [(72, 96), (2048, 2048), (1000, 320), (6144, 1536), (48, 2016), (4100, 64)])
+def test_skinny_linear_with_weights_by_tma(ops, tma_weights, M, N, K):
+    """Every prologue and epilogue of the decode product in the form whose weights come by TMA:
+    bit for bit what the form with per-lane copies gives (the sums are formed in the same order)."""
+    torch.manual_seed(26)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    b = torch.randn(N)
+    x = torch.randn(M, K) * 2
+    nw = 1 + 0.1 * torch.randn(K)
+    parts = torch.stack([(x[:, i::5] ** 2).sum(1) for i in range(5)]).contiguous()
+    xw = (x * nw).to(torch.bfloat16)
+    nw2 = 1 + 0.1 * torch.randn(N)
+
+    def run():
+        out = [ops.skinny_linear(dev(w), act=dev(a), epilogue="f32"),
+               ops.skinny_linear(dev(w), act=dev(a), epilogue="bf16", bias=dev(b)),
+               ops.skinny_linear(dev(w), xw=dev(xw), ss_in=dev(parts), eps=1e-5, epilogue="f32"),
+               ops.skinny_linear(dev(w), xw=dev(xw), ss_in=dev(parts), eps=1e-5, epilogue="bf16")]
+        if N % 2 == 0:
+            out.append(ops.skinny_linear(dev(w), xw=dev(xw), ss_in=dev(parts), eps=1e-5, epilogue="swiglu"))
+            out.append(ops.skinny_linear(dev(w), act=dev(a), epilogue="swiglu"))
+        r = dev(torch.arange(M * N, dtype=torch.float32).reshape(M, N) / 100)
+        ss, xw2 = ops.skinny_linear(dev(w), act=dev(a), epilogue="resid", resid=r, bias=dev(b), next_weight=dev(nw2))
+        return out + [r, ss, xw2]
+
+    got = run()
+    ops.skinny_use_tma(False)
+    want = run()
+    ops.skinny_use_tma(True)
+    torch.testing.assert_close(got[0].cpu(), a.float() @ w.float().t(), atol=2e-3, rtol=1e-3)
+    for i, (g_, w_) in enumerate(zip(got, want)):
+        assert torch.equal(g_, w_), f"output {i} differs between the two forms"
+
+
 @pytest.mark.parametrize("M", [2, 8, 14])
 @pytest.mark.parametrize("N,K", [(2048, 8192), (1536, 6912), (256, 4096), (2048, 2048)])
 def test_skinny_linear_residual_epilogue_over_a_long_inner_size(ops, M, N, K):
@@ -787,6 +831,34 @@ def test_embed_and_residual_add_prepare_the_next_norm(ops):
     torch.testing.assert_close(x.cpu(), want2, atol=1e-6, rtol=1e-6)
     torch.testing.assert_close(ss2.cpu(), (want2 ** 2).sum(1)[None], atol=1e-4, rtol=1e-5)
     torch.testing.assert_close(xw2.cpu().float(), (want2 * nw).to(torch.bfloat16).float(), atol=2e-2, rtol=1e-2)
+
+
+def test_skinny_shortconv_with_weights_by_tma(ops, tma_weights):
+    """The conv epilogue in the TMA form against the form with per-lane copies, state included."""
+    torch.manual_seed(27)
+    for M, H, K, L, bias in ((8, 2048, 2048, 3, False), (3, 72, 96, 4, True), (5, 200, 160, 2, True)):
+        w = (torch.randn(3 * H, K) * 0.05).to(torch.bfloat16)
+        x = torch.randn(M, K)
+        nw = 1 + 0.1 * torch.randn(K)
+        parts = torch.stack([(x[:, i::3] ** 2).sum(1) for i in range(3)]).contiguous()
+        xw = (x * nw).to(torch.bfloat16)
+        taps, cb, ib = torch.randn(L, H) * 0.5, torch.randn(H) * 0.1, torch.randn(3 * H) * 0.1
+        state0 = torch.randn(M + 2, max(L - 1, 1), H).to(torch.bfloat16)
+        slots = torch.randperm(M + 2)[:M].to(torch.int32)
+        pos = torch.tensor([0, 1, 5, 2, 9, 1, 0, 3][:M], dtype=torch.int32)
+
+        def run():
+            st = dev(state0.clone())
+            y = ops.skinny_shortconv(dev(w), xw=dev(xw), ss_in=dev(parts), eps=1e-5, in_bias=dev(ib) if bias else None,
+                                     taps=dev(taps), conv_bias=dev(cb) if bias else None, state_layer=st if L > 1 else None,
+                                     state_slots=dev(slots), positions=dev(pos))
+            return y, st
+
+        got = run()
+        ops.skinny_use_tma(False)
+        want = run()
+        ops.skinny_use_tma(True)
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1]), (M, H, K, L)
 
 
 @pytest.mark.parametrize("M,H,K,L,bias", [(8, 2048, 2048, 3, False), (1, 72, 96, 4, True), (11, 200, 160, 2, True),

@@ -29,7 +29,8 @@
 //
 // The reference does these products with cuBLAS and separate norm / SwiGLU / add kernels
 // (crates/vapi-backend-candle/src/models/lfm2.rs:519-534, 591-593, 645-647).
-#include "common.cuh"
+#include "tcgen05.cuh"
+#include <unordered_map>
 
 using namespace vapi;
 
@@ -125,15 +126,173 @@ static size_t gv_smem_bytes(int K) {
     return b;
 }
 
+// What a tile's epilogue needs beside the sums and does not depend on them: asked for at the top
+// of the tile, so that it is here when the sums are.  The residual epilogue: the stream's old
+// value and the next norm's weight.  The conv epilogue: the request's state, the taps and the
+// biases (none of them is written by a kernel of this step before this one).
+template <int EPI> struct GvTilePre {
+    float r_old = 0.f, r_nw = 0.f;
+    float hist[EPI == GV_EPI_CONV ? GV_CONV_LMAX : 1], tapv[EPI == GV_EPI_CONV ? GV_CONV_LMAX : 1];
+    float cbias = 0.f, bB = 0.f, bC = 0.f, bX = 0.f;
+    bool slot_ok = true;
+    __nv_bfloat16* st_ptr = nullptr;
+};
+
+template <int EPI>
+__device__ __forceinline__ GvTilePre<EPI> gv_tile_prefetch(const GvParams& p, int tile, int R, int ei, int em) {
+    GvTilePre<EPI> q;
+    q.hist[0] = q.tapv[0] = 0.f;
+    if (EPI == GV_EPI_RESID) {
+        const long long n = (long long)tile * R + ei;
+        if (ei < R && n < p.N && em < p.M) {
+            q.r_old = __ldcg(&p.resid[(size_t)em * p.N + n]);
+            if (p.xw_out) q.r_nw = p.next_w[n];
+        }
+    }
+    if (EPI == GV_EPI_CONV) {
+        const long long c = (long long)tile * 8 + ei;
+        const int L = p.L;
+#pragma unroll
+        for (int j = 0; j < (EPI == GV_EPI_CONV ? GV_CONV_LMAX : 1); ++j) q.hist[j] = q.tapv[j] = 0.f;
+        if (ei < 8 && em < p.M && c < p.ff) {
+#pragma unroll
+            for (int j = 0; j < (EPI == GV_EPI_CONV ? GV_CONV_LMAX : 1); ++j)
+                if (j < L) q.tapv[j] = p.taps[(size_t)j * p.ff + c];
+            if (p.conv_bias) q.cbias = p.conv_bias[c];
+            if (p.bias) { q.bB = p.bias[c]; q.bC = p.bias[p.ff + c]; q.bX = p.bias[2 * (long long)p.ff + c]; }
+            if (L > 1) {
+                const int slot = p.state_slots[em], p0 = p.positions[em];
+                q.slot_ok = slot >= 0 && slot < p.num_slots;
+                if (q.slot_ok) {
+                    q.st_ptr = p.state + (size_t)slot * p.slot_stride + c;
+#pragma unroll
+                    for (int j = 0; j < (EPI == GV_EPI_CONV ? GV_CONV_LMAX : 1); ++j)      // rows for positions before 0 count as zero
+                        if (j < L - 1 && p0 - (L - 1) + j >= 0) q.hist[j] = __bfloat162float(q.st_ptr[(size_t)j * p.ff]);
+                }
+            }
+        }
+    }
+    return q;
+}
+
+// The end of a tile: the warps' partial sums are added in warp order through shared memory, then
+// one thread per output applies the epilogue.  `sync` is the barrier of the warps that share the
+// tile (`gw` warps from warp `w0` on).
+template <int NT, int PRO, int EPI, int WARPS, typename Sync>
+__device__ __forceinline__ void gv_tile_finish(const GvParams& p, int tile, int R, float (&acc)[NT][4],
+                                               float (&acc_x)[EPI == GV_EPI_CONV ? NT : 1][4], const GvTilePre<EPI>& pre,
+                                               float (&red)[WARPS][16][8 * NT + 1],
+                                               float (&red_x)[EPI == GV_EPI_CONV ? WARPS : 1][8][8 * NT + 1],
+                                               const float* inv_s, int warp, int g, int t, int tig, int ei, int em,
+                                               int w0, int gw, Sync sync) {
+    constexpr int COLS = 8 * NT;
+    // partial tiles of the group's warps, added in warp order
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        red[warp][g][nt * 8 + 2 * t] = acc[nt][0];
+        red[warp][g][nt * 8 + 2 * t + 1] = acc[nt][1];
+        red[warp][g + 8][nt * 8 + 2 * t] = acc[nt][2];
+        red[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
+        if (EPI == GV_EPI_CONV) {
+            red_x[warp][g][nt * 8 + 2 * t] = acc_x[nt][0];
+            red_x[warp][g][nt * 8 + 2 * t + 1] = acc_x[nt][1];
+        }
+    }
+    sync();
+    const int i = ei, m = em;
+    float y = 0.f, y2 = 0.f;
+    if (i < 16) {
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) if (w < gw) y += red[w0 + w][i][m];
+        if ((EPI == GV_EPI_SWIGLU || EPI == GV_EPI_CONV) && i < 8) {
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) if (w < gw) y2 += red[w0 + w][i + 8][m];
+        }
+    }
+    float y3 = 0.f;
+    if (EPI == GV_EPI_CONV && i < 8) {
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) if (w < gw) y3 += red_x[w0 + w][i][m];
+    }
+    if (PRO == GV_PRO_NORM && m < p.M) {
+        y *= inv_s[m];
+        y2 *= inv_s[m];
+        y3 *= inv_s[m];
+    }
+    if (EPI == GV_EPI_CONV) {
+        // y, y2, y3 = B, C, x of channel c for token m, which is a sequence of its own.  The
+        // values are rounded where the unfused path stores them (in_proj's output, then g).
+        const long long c = (long long)tile * 8 + i;
+        if (i < 8 && m < p.M && c < p.ff) {
+            float B = __bfloat162float(__float2bfloat16_rn(y));
+            float C = __bfloat162float(__float2bfloat16_rn(y2));
+            float X = __bfloat162float(__float2bfloat16_rn(y3));
+            if (p.bias) { B += pre.bB; C += pre.bC; X += pre.bX; }
+            const float gate = __bfloat162float(__float2bfloat16_rn(B * X));
+            const int L = p.L;
+            float conv = 0.f;
+#pragma unroll
+            for (int j = 0; j < GV_CONV_LMAX; ++j)
+                if (j == L - 1) conv = pre.tapv[j] * gate;
+            if (L > 1) {
+                if (!pre.slot_ok) {
+                    if (p.status) atomicExch(p.status, 3);
+                } else {
+                    float acc_c = 0.f;
+#pragma unroll
+                    for (int j = 0; j < GV_CONV_LMAX; ++j)
+                        if (j < L - 1) acc_c += pre.tapv[j] * pre.hist[j];
+                    conv += acc_c;
+#pragma unroll
+                    for (int j = 0; j < GV_CONV_LMAX; ++j)
+                        if (j < L - 1) pre.st_ptr[(size_t)j * p.ff] = __float2bfloat16_rn(j + 1 < L - 1 ? pre.hist[j + 1 < GV_CONV_LMAX ? j + 1 : 0] : gate);
+                }
+            }
+            conv += pre.cbias;
+            p.out_bf16[(size_t)m * p.out_stride + c] = __float2bfloat16_rn(C * conv);
+        }
+    } else if (EPI == GV_EPI_SWIGLU) {
+        const long long col = (long long)tile * 8 + i;
+        if (i < 8 && m < p.M && col < p.ff) {
+            const float sg = y / (1.f + expf(-y));
+            p.out_bf16[(size_t)m * p.out_stride + col] = __float2bfloat16_rn(sg * y2);
+        }
+    } else {
+        const long long n = (long long)tile * R + i;
+        const bool valid = i < R && n < p.N && m < p.M;
+        if (valid && p.bias) y += p.bias[n];
+        if (EPI == GV_EPI_BF16) {
+            if (valid) p.out_bf16[(size_t)m * p.out_stride + n] = __float2bfloat16_rn(y);
+        } else if (EPI == GV_EPI_F32) {
+            if (valid) p.out_f32[(size_t)m * p.out_stride + n] = y;
+        } else {   // GV_EPI_RESID
+            float v = 0.f;
+            if (valid) {
+                v = pre.r_old + y;
+                p.resid[(size_t)m * p.N + n] = v;
+                if (p.xw_out) p.xw_out[(size_t)m * p.N + n] = __float2bfloat16_rn(v * pre.r_nw);
+            }
+            if (p.ss_out) {
+                sync();                        // everyone has read its sums out of red[]
+                if (i < 16) red[w0][i][m] = v * v;
+                sync();
+                if (tig < COLS && tig < p.M) {
+                    float sq = 0.f;
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) sq += red[w0][r][tig];
+                    p.ss_out[(size_t)tile * p.M + tig] = sq;
+                }
+            }
+        }
+    }
+}
+
 // REGB (products with K of at most 2048): a warp owns the same slice of K in every tile, so it reads
 // its slice of the tokens' rows once, straight from global memory into the registers that the MMAs take
 // them from, as soon as the dependency wait has returned: no staging in shared memory, no barrier
 // between the wait and the first MMA, and the queue's room all goes to weights.
 template <int NT, int PRO, int EPI, bool DEEP = false, int WARPS = GV_WARPS, bool REGB = false>
-#ifndef GV_REGB_MIN_BLOCKS
-#define GV_REGB_MIN_BLOCKS 1
-#endif
-__global__ void __launch_bounds__(WARPS * 32, (REGB && NT == 1 && WARPS == GV_WARPS) ? GV_REGB_MIN_BLOCKS : 1)
+__global__ void __launch_bounds__(WARPS * 32)
 skinny_linear_kernel(const GvParams p) {
     constexpr int SLOTS = gv_slots<NT, PRO, EPI, REGB>();
     constexpr int GV_STAGES = gv_stages<EPI, DEEP, NT, PRO, WARPS, REGB>();
@@ -299,45 +458,8 @@ skinny_linear_kernel(const GvParams p) {
 #pragma unroll
         for (int i = 0; i < (EPI == GV_EPI_CONV ? NT : 1); ++i) acc_x[i][0] = acc_x[i][1] = acc_x[i][2] = acc_x[i][3] = 0.f;
 
-        // what the residual epilogue adds to: asked for now, so that it is here when the sums are
         const int ei = tig / COLS, em = tig - ei * COLS;                   // MMA row, token of this thread's output
-        float r_old = 0.f, r_nw = 0.f;
-        if (EPI == GV_EPI_RESID) {
-            const long long n = (long long)tile * R + ei;
-            if (ei < R && n < p.N && em < p.M) {
-                r_old = __ldcg(&p.resid[(size_t)em * p.N + n]);
-                if (p.xw_out) r_nw = p.next_w[n];
-            }
-        }
-        // the short convolution's state, taps and biases: none of them is written by a kernel of this
-        // step before this one, so they are asked for before the sums exist
-        float hist[EPI == GV_EPI_CONV ? GV_CONV_LMAX : 1], tapv[EPI == GV_EPI_CONV ? GV_CONV_LMAX : 1];
-        float cbias = 0.f, bB = 0.f, bC = 0.f, bX = 0.f;
-        bool slot_ok = true;
-        __nv_bfloat16* st_ptr = nullptr;
-        if (EPI == GV_EPI_CONV) {
-            const long long c = (long long)tile * 8 + ei;
-            const int L = p.L;
-#pragma unroll
-            for (int j = 0; j < GV_CONV_LMAX; ++j) hist[j] = tapv[j] = 0.f;
-            if (ei < 8 && em < p.M && c < p.ff) {
-#pragma unroll
-                for (int j = 0; j < GV_CONV_LMAX; ++j)
-                    if (j < L) tapv[j] = p.taps[(size_t)j * p.ff + c];
-                if (p.conv_bias) cbias = p.conv_bias[c];
-                if (p.bias) { bB = p.bias[c]; bC = p.bias[p.ff + c]; bX = p.bias[2 * (long long)p.ff + c]; }
-                if (L > 1) {
-                    const int slot = p.state_slots[em], p0 = p.positions[em];
-                    slot_ok = slot >= 0 && slot < p.num_slots;
-                    if (slot_ok) {
-                        st_ptr = p.state + (size_t)slot * p.slot_stride + c;
-#pragma unroll
-                        for (int j = 0; j < GV_CONV_LMAX; ++j)      // rows for positions before 0 count as zero
-                            if (j < L - 1 && p0 - (L - 1) + j >= 0) hist[j] = __bfloat162float(st_ptr[(size_t)j * p.ff]);
-                    }
-                }
-            }
-        }
+        const GvTilePre<EPI> pre = gv_tile_prefetch<EPI>(p, tile, R, ei, em);
         if (REGB) {
 #pragma unroll
             for (int j = 0; j < GV_REGB_CHUNKS; ++j) {
@@ -390,112 +512,229 @@ skinny_linear_kernel(const GvParams p) {
             stage = stage == GV_STAGES - 1 ? 0 : stage + 1;
         }
 
-        // partial tiles of the group's warps, added in warp order
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            red[warp][g][nt * 8 + 2 * t] = acc[nt][0];
-            red[warp][g][nt * 8 + 2 * t + 1] = acc[nt][1];
-            red[warp][g + 8][nt * 8 + 2 * t] = acc[nt][2];
-            red[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
-            if (EPI == GV_EPI_CONV) {
-                red_x[warp][g][nt * 8 + 2 * t] = acc_x[nt][0];
-                red_x[warp][g][nt * 8 + 2 * t + 1] = acc_x[nt][1];
-            }
-        }
-        group_sync();
-        const int i = ei, m = em;
-        const int w0 = grp * gw;                                           // the group's first warp
-        float y = 0.f, y2 = 0.f;
-        if (i < 16) {
-#pragma unroll
-            for (int w = 0; w < WARPS; ++w) if (w < gw) y += red[w0 + w][i][m];
-            if ((EPI == GV_EPI_SWIGLU || EPI == GV_EPI_CONV) && i < 8) {
-#pragma unroll
-                for (int w = 0; w < WARPS; ++w) if (w < gw) y2 += red[w0 + w][i + 8][m];
-            }
-        }
-        float y3 = 0.f;
-        if (EPI == GV_EPI_CONV && i < 8) {
-#pragma unroll
-            for (int w = 0; w < WARPS; ++w) if (w < gw) y3 += red_x[w0 + w][i][m];
-        }
-        if (PRO == GV_PRO_NORM && m < p.M) {
-            y *= inv_s[m];
-            y2 *= inv_s[m];
-            y3 *= inv_s[m];
-        }
-        if (EPI == GV_EPI_CONV) {
-            // y, y2, y3 = B, C, x of channel c for token m, which is a sequence of its own.  The
-            // values are rounded where the unfused path stores them (in_proj's output, then g).
-            const long long c = (long long)tile * 8 + i;
-            if (i < 8 && m < p.M && c < p.ff) {
-                float B = __bfloat162float(__float2bfloat16_rn(y));
-                float C = __bfloat162float(__float2bfloat16_rn(y2));
-                float X = __bfloat162float(__float2bfloat16_rn(y3));
-                if (p.bias) { B += bB; C += bC; X += bX; }
-                const float gate = __bfloat162float(__float2bfloat16_rn(B * X));
-                const int L = p.L;
-                float conv = 0.f;
-#pragma unroll
-                for (int j = 0; j < GV_CONV_LMAX; ++j)
-                    if (j == L - 1) conv = tapv[j] * gate;
-                if (L > 1) {
-                    if (!slot_ok) {
-                        if (p.status) atomicExch(p.status, 3);
-                    } else {
-                        float acc_c = 0.f;
-#pragma unroll
-                        for (int j = 0; j < GV_CONV_LMAX; ++j)
-                            if (j < L - 1) acc_c += tapv[j] * hist[j];
-                        conv += acc_c;
-#pragma unroll
-                        for (int j = 0; j < GV_CONV_LMAX; ++j)
-                            if (j < L - 1) st_ptr[(size_t)j * p.ff] = __float2bfloat16_rn(j + 1 < L - 1 ? hist[j + 1 < GV_CONV_LMAX ? j + 1 : 0] : gate);
-                    }
-                }
-                conv += cbias;
-                p.out_bf16[(size_t)m * p.out_stride + c] = __float2bfloat16_rn(C * conv);
-            }
-        } else if (EPI == GV_EPI_SWIGLU) {
-            const long long col = (long long)tile * 8 + i;
-            if (i < 8 && m < p.M && col < p.ff) {
-                const float sg = y / (1.f + expf(-y));
-                p.out_bf16[(size_t)m * p.out_stride + col] = __float2bfloat16_rn(sg * y2);
-            }
-        } else {
-            const long long n = (long long)tile * R + i;
-            const bool valid = i < R && n < p.N && m < p.M;
-            if (valid && p.bias) y += p.bias[n];
-            if (EPI == GV_EPI_BF16) {
-                if (valid) p.out_bf16[(size_t)m * p.out_stride + n] = __float2bfloat16_rn(y);
-            } else if (EPI == GV_EPI_F32) {
-                if (valid) p.out_f32[(size_t)m * p.out_stride + n] = y;
-            } else {   // GV_EPI_RESID
-                float v = 0.f;
-                if (valid) {
-                    v = r_old + y;
-                    p.resid[(size_t)m * p.N + n] = v;
-                    if (p.xw_out) p.xw_out[(size_t)m * p.N + n] = __float2bfloat16_rn(v * r_nw);
-                }
-                if (p.ss_out) {
-                    group_sync();                        // everyone has read its sums out of red[]
-                    if (i < 16) red[w0][i][m] = v * v;
-                    group_sync();
-                    if (tig < COLS && tig < p.M) {
-                        float sq = 0.f;
-#pragma unroll
-                        for (int r = 0; r < 16; ++r) sq += red[w0][r][tig];
-                        p.ss_out[(size_t)tile * p.M + tig] = sq;
-                    }
-                }
-            }
-        }
+        gv_tile_finish<NT, PRO, EPI, WARPS>(p, tile, R, acc, acc_x, pre, red, red_x, inv_s, warp, g, t, tig, ei, em,
+                                            grp * gw, gw, group_sync);
         group_sync();                                    // red[] is free for the next tile
     }
     gv_wait<0>();
 }
 
 static int gv_sm_count() { return sm_count(); }
+
+// ---------------------------------------------------------------------------------------------
+// The same product with the weight stream moved by the tensor memory accelerator: a second form of
+// the kernel above for steps of at most 8 tokens and K of at most 2048 (the tokens' rows in
+// registers), chosen with VAPI_GV_TMA.  A ninth warp's first lane is the producer: it brings the
+// weights in with cp.async.bulk.tensor, one box per half-tile of 8 rows and GT_SUB chunks of 32 k,
+// into per-warp rings of shared-memory stages guarded by full / empty mbarriers (the tensor map
+// sees the weight as [K/32 chunks][rows][32 k], so a box lands as [chunk][8 rows][64 bytes]: the
+// layout in which a quarter-warp's 16-byte reads touch every bank once).  The eight consumer
+// warps do what they do above: each owns a slice of K, multiplies with mma.sync out of shared
+// memory and hands its stage back; the tiles' ends are the same code.  Nothing is requested by the
+// consumers' lanes, so their issue slots are free and a block holds its whole ring in flight from
+// its first cycle, before the dependency wait.  Every mbarrier wait is bounded; when one runs out
+// the block records status 16, stops waiting and runs to its end (its output is then not valid).
+constexpr int GT_SUB = 4;                                   // chunks of 32 k in a stage
+template <int EPI> __host__ __device__ constexpr int gt_halves() { return EPI == GV_EPI_CONV ? 3 : 2; }
+template <int EPI> __host__ __device__ constexpr int gt_stage_bytes() { return gt_halves<EPI>() * GT_SUB * 512; }
+#ifndef GT_RING_KB
+#define GT_RING_KB 96
+#endif
+template <int EPI> __host__ __device__ constexpr int gt_depth() { return (GT_RING_KB * 1024) / (GV_WARPS * gt_stage_bytes<EPI>()); }
+
+__device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map, unsigned bar, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
+template <int PRO, int EPI>
+__global__ void __launch_bounds__((GV_WARPS + 1) * 32, 2)
+skinny_linear_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const GvParams p) {
+    constexpr int NT = 1, COLS = 8, WARPS = GV_WARPS;
+    constexpr int HALVES = gt_halves<EPI>(), SB = gt_stage_bytes<EPI>(), DW = gt_depth<EPI>();
+    extern __shared__ __align__(128) unsigned char gt_smem[];      // [warp][DW][HALVES][GT_SUB][8 rows][32 k]
+    __shared__ float red[WARPS][16][COLS + 1];
+    __shared__ float red_x[EPI == GV_EPI_CONV ? WARPS : 1][8][COLS + 1];
+    __shared__ float inv_s[COLS];
+    __shared__ unsigned long long bars[2 * WARPS * DW];             // full[warp][slot], then empty[warp][slot]
+    __shared__ int gave_up;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int R = p.rows_per_cta;
+    const int vblock = (int)blockIdx.x, vgrid = (int)gridDim.x;
+    const int my_tiles = vblock < p.num_tiles ? (p.num_tiles - vblock + vgrid - 1) / vgrid : 0;
+    const int nchunks = p.K >> 5;
+    const int cpw = (nchunks + WARPS - 1) / WARPS;
+    const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + WARPS * DW);
+    auto consumer_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"r"(WARPS * 32) : "memory"); };
+
+    pdl_trigger();
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2 * WARPS * DW; ++i) mbar_init(full0 + 8 * i, 1);
+        gave_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == WARPS) {
+        // ---- producer: nothing it moves depends on the kernel before this one ----
+        if (lane == 0) {
+            bool ok = true;
+            const int nsub_max = (cpw + GT_SUB - 1) / GT_SUB;
+            for (int ti = 0; ti < my_tiles && ok; ++ti) {
+                const int tile = vblock + ti * vgrid;
+                int row[3];
+                if (EPI == GV_EPI_SWIGLU || EPI == GV_EPI_CONV) { row[0] = tile * 8; row[1] = p.ff + tile * 8; row[2] = 2 * p.ff + tile * 8; }
+                else { row[0] = tile * 16; row[1] = tile * 16 + 8; row[2] = 0; }
+                for (int sub = 0; sub < nsub_max && ok; ++sub) {
+                    for (int w = 0; w < WARPS; ++w) {
+                        const int cb = min(nchunks, w * cpw), len = min(nchunks, cb + cpw) - cb;
+                        if (sub * GT_SUB >= len) continue;
+                        const int nsub = (len + GT_SUB - 1) / GT_SUB;
+                        const int q = ti * nsub + sub, slot = q % DW;
+                        if (q >= DW && !mbar_wait(empty0 + 8 * (w * DW + slot), ((q / DW) - 1) & 1)) { ok = false; break; }
+                        const unsigned bar = full0 + 8 * (w * DW + slot);
+                        const unsigned dst = smem_u32(gt_smem + (size_t)(w * DW + slot) * SB);
+                        mbar_expect_tx(bar, SB);
+#pragma unroll
+                        for (int h = 0; h < HALVES; ++h)
+                            tma_load_3d(dst + h * GT_SUB * 512, &tm_w, bar, 0, row[h], cb + sub * GT_SUB);
+                    }
+                }
+            }
+            if (!ok) { gave_up = 1; if (p.status) atomicExch(p.status, 16); }
+        }
+        return;
+    }
+
+    // ---- consumers ----
+    const int c_begin = min(nchunks, warp * cpw), c_end = min(nchunks, c_begin + cpw);
+    const int len = c_end - c_begin;
+    const int nsub = (len + GT_SUB - 1) / GT_SUB;
+    pdl_wait();
+    uint4 breg[GV_REGB_CHUNKS];
+    {
+        const __nv_bfloat16* tok = PRO == GV_PRO_NORM ? p.xw : p.act;
+#pragma unroll
+        for (int j = 0; j < GV_REGB_CHUNKS; ++j)
+            breg[j] = (j < len && g < p.M)
+                ? __ldcg(reinterpret_cast<const uint4*>(tok + (size_t)g * p.K + ((size_t)(c_begin + j) << 5) + 8 * t))
+                : make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (PRO == GV_PRO_NORM) {
+        for (int m = warp; m < p.M; m += WARPS) {
+            float s = 0.f;
+            for (int i = lane; i < p.ss_parts; i += 32) s += p.ss_in[(size_t)i * p.M + m];
+            s = warp_sum(s);
+            if (lane == 0) inv_s[m] = rsqrtf(s / (float)p.K + p.eps);
+        }
+        consumer_sync();
+    }
+    const int tig = (int)threadIdx.x;
+    bool ok = true;
+    int q = 0;
+    for (int ti = 0; ti < my_tiles; ++ti) {
+        const int tile = vblock + ti * vgrid;
+        float acc[NT][4] = {{0.f, 0.f, 0.f, 0.f}};
+        float acc_x[EPI == GV_EPI_CONV ? NT : 1][4] = {{0.f, 0.f, 0.f, 0.f}};
+        const int ei = tig / COLS, em = tig - ei * COLS;
+        const GvTilePre<EPI> pre = gv_tile_prefetch<EPI>(p, tile, R, ei, em);
+#pragma unroll
+        for (int sub = 0; sub < GV_REGB_CHUNKS / GT_SUB; ++sub) {
+            if (sub < nsub) {
+                const int slot = q % DW;
+                ok = ok && mbar_wait(full0 + 8 * (warp * DW + slot), (q / DW) & 1);
+                const unsigned char* base = gt_smem + (size_t)(warp * DW + slot) * SB + g * 64 + t * 16;
+#pragma unroll
+                for (int j = 0; j < GT_SUB; ++j) {
+                    if (sub * GT_SUB + j < len) {
+                        const uint4 wl = *reinterpret_cast<const uint4*>(base + (0 * GT_SUB + j) * 512);
+                        const uint4 wh = *reinterpret_cast<const uint4*>(base + (1 * GT_SUB + j) * 512);
+                        const uint4 av = breg[sub * GT_SUB + j];
+                        mma16816(acc[0], wl.x, wh.x, wl.y, wh.y, av.x, av.y);
+                        mma16816(acc[0], wl.z, wh.z, wl.w, wh.w, av.z, av.w);
+                        if (EPI == GV_EPI_CONV) {
+                            const uint4 wx = *reinterpret_cast<const uint4*>(base + (2 * GT_SUB + j) * 512);
+                            mma16816(acc_x[0], wx.x, 0u, wx.y, 0u, av.x, av.y);
+                            mma16816(acc_x[0], wx.z, 0u, wx.w, 0u, av.z, av.w);
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty0 + 8 * (warp * DW + slot));
+                ++q;
+            }
+        }
+        gv_tile_finish<NT, PRO, EPI, WARPS>(p, tile, R, acc, acc_x, pre, red, red_x, inv_s, warp, g, t, tig, ei, em,
+                                            0, WARPS, consumer_sync);
+        consumer_sync();                                    // red[] is free for the next tile
+    }
+    if (!ok && lane == 0) { gave_up = 1; if (p.status) atomicExch(p.status, 16); }
+}
+
+// the weight [rows][K] seen as [K/32 chunks][rows][32 k], in boxes of GT_SUB chunks x 8 rows; one map
+// per weight is kept (a map holds nothing but the address and the shape)
+static int gt_weight_map(CUtensorMap* out, const void* W, long long rows, long long K) {
+    struct Key { const void* w; long long rows, K; bool operator==(const Key& o) const { return w == o.w && rows == o.rows && K == o.K; } };
+    struct Hash { size_t operator()(const Key& k) const { return (size_t)k.w ^ ((size_t)k.rows << 20) ^ (size_t)k.K; } };
+    static thread_local std::unordered_map<Key, CUtensorMap, Hash> cache;
+    const Key key{W, rows, K};
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(-102, "skinny_linear: cuTensorMapEncodeTiled is not available from the driver");
+    if (((uintptr_t)W & 15) != 0 || K % 32 != 0) return fail(-1, "skinny_linear: the weight is not 16-byte aligned or K=%lld is no multiple of 32", K);
+    cuuint64_t dims[3] = {32, (cuuint64_t)rows, (cuuint64_t)(K / 32)};
+    cuuint64_t strides[2] = {(cuuint64_t)K * 2, 64};
+    cuuint32_t box[3] = {32, 8, (cuuint32_t)GT_SUB};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(W), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(-103, "skinny_linear: cuTensorMapEncodeTiled failed with %d", (int)r);
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = *out;
+    return 0;
+}
+
+static int g_gt_enabled = -1;          // -1: not asked yet (then VAPI_GV_TMA decides)
+static bool gt_enabled() {
+    if (g_gt_enabled < 0) {
+        const char* e = getenv("VAPI_GV_TMA");
+        g_gt_enabled = (e && e[0] == '1') ? 1 : 0;
+    }
+    return g_gt_enabled == 1;
+}
+// 1: steps of at most 8 tokens take the form whose weights come by TMA where it applies; 0: never
+VAPI_EXPORT int vapi_skinny_linear_use_tma(int on) {
+    const int was = gt_enabled() ? 1 : 0;
+    g_gt_enabled = on ? 1 : 0;
+    return was;
+}
+// whether the form above takes a call: at most 8 tokens, tiles of 16 rows, a warp's slice of K in registers
+static bool gt_applies(const GvParams& p) {
+    return gt_enabled() && p.M <= 8 && p.rows_per_cta == 16 && (p.K >> 5) <= GV_REGB_CHUNKS * GV_WARPS && p.K % 32 == 0 &&
+           ((uintptr_t)p.W & 15) == 0;
+}
+
+template <int PRO, int EPI>
+static int launch_gt(const GvParams& p, int blocks, cudaStream_t stream) {
+    CUtensorMap map;
+    int rc = gt_weight_map(&map, p.W, p.N, p.K);
+    if (rc) return rc;
+    constexpr size_t smem = (size_t)GV_WARPS * gt_depth<EPI>() * gt_stage_bytes<EPI>();
+    auto kern = skinny_linear_tma_kernel<PRO, EPI>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(-101, "skinny_linear: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        attr_done = true;
+    }
+    const int cap = gv_sm_count() * 2;
+    return check_launch("skinny_linear (tma)", launch(kern, blocks < cap ? blocks : cap, (GV_WARPS + 1) * 32, smem, stream, map, p));
+}
+
+
 
 template <int NT, int PRO, int EPI, bool DEEP, int WARPS, bool REGB = false>
 static int launch_gv_as(const GvParams& p, int blocks, int blocks_per_sm, cudaStream_t stream) {
@@ -576,6 +815,23 @@ VAPI_EXPORT int vapi_skinny_linear(const void* W, int N, int K, int M, int pro, 
         case GV_EPI_F32: GV_GO(NT, PRO, GV_EPI_F32);          \
         default: return fail(-2, "skinny_linear: unknown epilogue %d", epi); \
     }
+    if (gt_applies(p)) {
+        if (pro == GV_PRO_ACT) {
+            switch (epi) {
+                case GV_EPI_BF16: return launch_gt<GV_PRO_ACT, GV_EPI_BF16>(p, blocks, stream);
+                case GV_EPI_SWIGLU: return launch_gt<GV_PRO_ACT, GV_EPI_SWIGLU>(p, blocks, stream);
+                case GV_EPI_RESID: return launch_gt<GV_PRO_ACT, GV_EPI_RESID>(p, blocks, stream);
+                case GV_EPI_F32: return launch_gt<GV_PRO_ACT, GV_EPI_F32>(p, blocks, stream);
+            }
+        } else if (pro == GV_PRO_NORM) {
+            switch (epi) {
+                case GV_EPI_BF16: return launch_gt<GV_PRO_NORM, GV_EPI_BF16>(p, blocks, stream);
+                case GV_EPI_SWIGLU: return launch_gt<GV_PRO_NORM, GV_EPI_SWIGLU>(p, blocks, stream);
+                case GV_EPI_RESID: return launch_gt<GV_PRO_NORM, GV_EPI_RESID>(p, blocks, stream);
+                case GV_EPI_F32: return launch_gt<GV_PRO_NORM, GV_EPI_F32>(p, blocks, stream);
+            }
+        }
+    }
     static int deep_k = -1;
     if (deep_k < 0) {
         const char* e = getenv("VAPI_GV_DEEP_K");
@@ -619,6 +875,7 @@ VAPI_EXPORT int vapi_skinny_linear_conv(const void* W, int H, int K, int M, cons
     p.state_slots = state_slots; p.positions = positions; p.L = L; p.num_slots = num_slots; p.status = status;
     const int blocks = (H + 7) / 8;
     p.num_tiles = blocks;
+    if (gt_applies(p)) return launch_gt<GV_PRO_NORM, GV_EPI_CONV>(p, blocks, stream);
     if (M <= 8) return launch_gv<1, GV_PRO_NORM, GV_EPI_CONV>(p, blocks, stream);
     return launch_gv<2, GV_PRO_NORM, GV_EPI_CONV>(p, blocks, stream);
 }

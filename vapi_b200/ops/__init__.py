@@ -272,6 +272,13 @@ def skinny_applies(rows: int, weight: torch.Tensor) -> bool:
             and weight.dim() == 2 and weight.shape[1] % 32 == 0 and weight.is_contiguous())
 
 
+def skinny_use_tma(on: bool) -> bool:
+    """Choose the form of the decode product whose weight stream is moved by TMA into mbarrier
+    rings (steps of at most 8 tokens, inner size up to 2048) instead of per-lane asynchronous
+    copies; returns what was chosen before.  ``VAPI_GV_TMA=1`` chooses it from the start."""
+    return bool(_lib("gemv").vapi_skinny_linear_use_tma(1 if on else 0))
+
+
 def skinny_blocks(n_out: int, epilogue: str, rows_per_block: int = 16) -> int:
     if epilogue == "swiglu":
         return (n_out // 2 + 7) // 8
