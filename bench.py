@@ -430,19 +430,22 @@ def run(args):
     n_attn = len(runner.cache.paged[0].sites) if runner.cache.paged else 0
 
     # ---- end to end through the engine loop ----------------------------------------
-    reps = max(3, min(int(MIN_TIMED_S * 1e3 / max(ms, 1e-3)) + 1, max(3, 1500 // args.steps)))
+    # regions of `steps` engine steps, one after the other (the contexts grow): as many as 0.3 s needs, and no
+    # more than keep every request below the context limit with the middle region near the context length
+    warm_e2e = max(8, args.warmup)
+    reps = max(1, min(int(MIN_TIMED_S * 1e3 / max(ms, 1e-3)) + 1, (512 + args.steps - 40 - warm_e2e) // args.steps))
     eng = Engine(runner, SchedulerConfig(max_concurrent_seqs=max_b, max_batched_tokens=8192,
                                          prefill_chunk_tokens=4096, max_context=ctx_len + 256), use_graphs=True)
     # the middle region ends near the context length; requests finish their prompts at different
     # steps, so leave room for the early ones
-    start_len = max(16, ctx_len - args.warmup - (reps * args.steps) // 2 - args.steps // 2 - 2)
+    start_len = max(16, ctx_len - warm_e2e - (reps * args.steps) // 2 - args.steps // 2 - 2)
     for i in range(B):
         prompt = torch.randint(0, vocab, (start_len,), generator=gen).tolist()
-        eng.admit(("e2e", i), prompt, SamplingParams(temperature=0.0, max_tokens=args.warmup + reps * args.steps + 128,
+        eng.admit(("e2e", i), prompt, SamplingParams(temperature=0.0, max_tokens=warm_e2e + reps * args.steps + 128,
                                                      ignore_eos=True))
     while any(s.needs_prefill() for s in eng.scheduler.seqs.values()) or eng.scheduler.num_waiting:
         eng.step()
-    for _ in range(max(8, args.warmup)):
+    for _ in range(warm_e2e):
         eng.step()
     torch.cuda.synchronize()
     st0 = dict(eng.stats.__dict__)
