@@ -398,9 +398,9 @@ def run(args):
     fp32_peak = measure_fp32_peak(dev) if (dtype == "float32" or args.only == "all") else None
     peak_tflops = fp32_peak if dtype == "float32" else pk["bf16_tflops"]
     if args.only == "prefill":
-        p, _ = measure_prefill(runner, ops, mm_params, pk, peak_tflops, gen, vocab, dev, warm=max(1, min(args.warmup, 3)),
-                               iters=max(1, min(args.steps, 5)))
-        print(json.dumps({"only": "prefill", "dtype": dtype, "prefill": p}), flush=True)
+        p, fam = measure_prefill(runner, ops, mm_params, pk, peak_tflops, gen, vocab, dev, warm=max(1, min(args.warmup, 3)),
+                                 iters=max(1, min(args.steps, 5)))
+        print(json.dumps({"only": "prefill", "dtype": dtype, "prefill": p, "kernels": fam}), flush=True)
         return 0
     # ---- headline: decode at the given batch -----------------------------------------
     clocks = ClockSampler()
