@@ -308,13 +308,12 @@ def run(args):
     torch.cuda.set_device(dev)
     max_b = max(B, 64)
     page = args.page_size or ModelRunner.default_page_size
-    pages = max_b * (-(-ctx_len // page)) + 8
     gen = torch.Generator().manual_seed(1)
     vocab = cfg["vocab_size"]
     MIN_TIMED_S = 0.3
 
     def make_runner(dtype, most_requests=max_b):
-        n_pages = most_requests * (-(-ctx_len // page)) + 8
+        n_pages = most_requests * (-(-(ctx_len + 256) // page)) + 8      # (the engine-loop run lets contexts grow past ctx_len)
         return ModelRunner.from_random(cfg, seed=0, dtype=dtype, device="cuda:0", num_pages=n_pages, page_size=page,
                                        max_requests=most_requests, max_batched_tokens=8192, max_context=ctx_len + 256,
                                        watermark=0.0, validate=False)
