@@ -557,7 +557,6 @@ skinny_linear_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const GvParam
     __shared__ float red_x[EPI == GV_EPI_CONV ? WARPS : 1][8][COLS + 1];
     __shared__ float inv_s[COLS];
     __shared__ unsigned long long bars[2 * WARPS * DW];             // full[warp][slot], then empty[warp][slot]
-    __shared__ int gave_up;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int R = p.rows_per_cta;
@@ -571,7 +570,6 @@ skinny_linear_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const GvParam
     pdl_trigger();
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2 * WARPS * DW; ++i) mbar_init(full0 + 8 * i, 1);
-        gave_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -602,7 +600,7 @@ skinny_linear_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const GvParam
                     }
                 }
             }
-            if (!ok) { gave_up = 1; if (p.status) atomicExch(p.status, 16); }
+            if (!ok && p.status) atomicExch(p.status, 16);
         }
         return;
     }
@@ -669,7 +667,7 @@ skinny_linear_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const GvParam
                                             0, WARPS, consumer_sync);
         consumer_sync();                                    // red[] is free for the next tile
     }
-    if (!ok && lane == 0) { gave_up = 1; if (p.status) atomicExch(p.status, 16); }
+    if (!ok && lane == 0 && p.status) atomicExch(p.status, 16);
 }
 
 // the weight [rows][K] seen as [K/32 chunks][rows][32 k], in boxes of GT_SUB chunks x 8 rows; one map
