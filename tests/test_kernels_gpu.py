@@ -1031,3 +1031,61 @@ def test_linear_tc_fusions(ops, M):
     lg = ops.linear_tc(dev(w13), xw=dev(xw), ss_in=dev(parts), eps=eps, epilogue="f32", status=st)
     torch.testing.assert_close(lg.cpu(), (xw.float() @ w13.float().t()) * inv, atol=3e-3, rtol=1e-3)
     assert int(st.item()) == 0
+
+
+# ---- the persistent tcgen05 / TMA product of prompt-sized steps ------------------------------
+@pytest.fixture(params=[(256, 2), (128, 2), (256, 1), (128, 1), (0, 0)], ids=["256x2", "128x2", "256x1", "128x1", "planned"])
+def prompt_tiles(ops, request):
+    """Every tile shape of the kernel (features a tile x blocks a tile), and the kernel's own choice."""
+    ops.prompt_force(*request.param)
+    yield request.param
+    ops.prompt_force(0, 0)
+
+
+@pytest.mark.parametrize("M", [33, 128, 300, 1031])
+@pytest.mark.parametrize("N,K", [(200, 96), (2048, 2048), (1000, 328), (384, 8192)])
+def test_prompt_linear_plain_products(ops, prompt_tiles, M, N, K):
+    """Tiles that are not full along the features (N no multiple of 128) or the tokens, K that is no
+    multiple of 64, fewer tiles than blocks and many tiles a block (the ring of stages and the two
+    accumulators wrap around)."""
+    torch.manual_seed(32)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    b = torch.randn(N)
+    want = a.float() @ w.float().t()
+    st = torch.zeros(1, dtype=torch.int32).cuda()
+    got = ops.prompt_linear(dev(w), act=dev(a), epilogue="f32", status=st)
+    assert int(st.item()) == 0, "a bounded wait ran out"
+    torch.testing.assert_close(got.cpu(), want, atol=3e-3 * math.sqrt(K / 96), rtol=1e-3)
+    got = ops.prompt_linear(dev(w), act=dev(a), epilogue="bf16", bias=dev(b), status=st)
+    torch.testing.assert_close(got.cpu().float(), (want + b).to(torch.bfloat16).float(), atol=3e-2 * math.sqrt(K / 96), rtol=2e-2)
+    assert int(st.item()) == 0
+
+
+@pytest.mark.parametrize("M", [40, 130, 700])
+def test_prompt_linear_fusions(ops, prompt_tiles, M):
+    torch.manual_seed(33)
+    H, F, eps = 264, 328, 1e-6
+    x = torch.randn(M, H) * 2
+    nw = 1 + 0.1 * torch.randn(H)
+    w13 = (torch.randn(2 * F, H) * 0.1).to(torch.bfloat16)
+    w2 = (torch.randn(H, F) * 0.1).to(torch.bfloat16)
+    parts = torch.stack([(x[:, i * 66:(i + 1) * 66] ** 2).sum(1) for i in range(4)]).contiguous()
+    xw = (x * nw).to(torch.bfloat16)
+    st = torch.zeros(1, dtype=torch.int32).cuda()
+    s = ops.prompt_linear(dev(w13), xw=dev(xw), ss_in=dev(parts), eps=eps, epilogue="swiglu", status=st)
+    inv = torch.rsqrt((x ** 2).mean(1, keepdim=True) + eps)
+    gu = (xw.float() @ w13.float().t()) * inv
+    want_s = (gu[:, :F] / (1 + torch.exp(-gu[:, :F]))) * gu[:, F:]
+    torch.testing.assert_close(s.cpu().float(), want_s.to(torch.bfloat16).float(), atol=4e-2, rtol=3e-2)
+    s2 = torch.randn(M, F).to(torch.bfloat16)
+    bias, nw2 = torch.randn(H), 1 + 0.1 * torch.randn(H)
+    xr = dev(x.clone())
+    ss, xw2 = ops.prompt_linear(dev(w2), act=dev(s2), epilogue="resid", resid=xr, bias=dev(bias), next_weight=dev(nw2), status=st)
+    want_x = x + s2.float() @ w2.float().t() + bias
+    torch.testing.assert_close(xr.cpu(), want_x, atol=3e-3, rtol=1e-3)
+    torch.testing.assert_close(ss.sum(0).cpu(), (want_x ** 2).sum(1), atol=2e-2, rtol=1e-3)
+    torch.testing.assert_close(xw2.cpu().float(), (want_x * nw2).to(torch.bfloat16).float(), atol=3e-2, rtol=2e-2)
+    lg = ops.prompt_linear(dev(w13), xw=dev(xw), ss_in=dev(parts), eps=eps, epilogue="f32", status=st)
+    torch.testing.assert_close(lg.cpu(), (xw.float() @ w13.float().t()) * inv, atol=3e-3, rtol=1e-3)
+    assert int(st.item()) == 0

@@ -165,7 +165,8 @@ class ModelRunner:
             ctx.pos[pe.name] = pe.prepare(ctx)
         views = self.views(ctx)
         ctx.fused = (self.device.type == "cuda" and self.dtype == torch.bfloat16 and ops.use_skinny
-                     and ctx.n <= (ops.TC_MAX_ROWS if ops.use_tc else ops.SKINNY_MAX_ROWS))
+                     and (ctx.n <= (ops.TC_MAX_ROWS if ops.use_tc else ops.SKINNY_MAX_ROWS)
+                          or 0 < ops.PROMPT_MIN_ROWS <= ctx.n))
         if ctx.fused:
             return self._forward_few_rows(ctx, views)
         x = plan.embedding.forward(ctx)

@@ -419,30 +419,35 @@ def _tc_plan(N: int, K: int, M: int, epi: int):
     return t.value, s.value, b.value
 
 
-def linear_tc(weight: torch.Tensor, *, act: Optional[torch.Tensor] = None, xw: Optional[torch.Tensor] = None,
-              ss_in: Optional[torch.Tensor] = None, eps: float = 0.0, epilogue: str = "bf16",
-              bias: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
-              next_weight: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None):
-    """The tcgen05 / TMA product for 17..256 rows; same operands, epilogues and results as
-    :func:`skinny_linear`."""
+def _fused_product(which: str, weight: torch.Tensor, act, xw, ss_in, eps: float, epilogue: str, bias, resid,
+                   next_weight, status):
+    """Operand checks, outputs and the call shared by :func:`linear_tc` and :func:`prompt_linear`."""
     _cuda(weight, act, xw, ss_in, bias, resid, next_weight)
     N, K = weight.shape
     pro = "act" if act is not None else "norm"
     src = act if act is not None else xw
     if src is None:
-        raise KernelError("linear_tc needs a token operand (act or xw)")
+        raise KernelError(f"{which} needs a token operand (act or xw)")
     M = src.shape[0]
     if weight.dtype != torch.bfloat16 or not weight.is_contiguous():
-        raise KernelError("linear_tc needs a contiguous bfloat16 weight")
+        raise KernelError(f"{which} needs a contiguous bfloat16 weight")
     if src.shape[1] != K or not src.is_contiguous() or src.dtype != torch.bfloat16:
-        raise KernelError(f"linear_tc: token operand {tuple(src.shape)} / {src.dtype} does not fit a weight of {N}x{K}")
+        raise KernelError(f"{which}: token operand {tuple(src.shape)} / {src.dtype} does not fit a weight of {N}x{K}")
     if pro == "norm":
         _f32(ss_in, "partial sums")
         if ss_in is None or ss_in.dim() != 2 or ss_in.shape[1] != M:
             raise KernelError("partial sums must be [parts, M]")
     _f32(bias, "bias")
     _f32(next_weight, "norm weight")
-    tiles, splits, bn = _tc_plan(N, K, M, _EPI[epilogue])
+    if epilogue not in _EPI:
+        raise KernelError(f"unknown epilogue {epilogue}")
+    lib = _lib(which)
+    if which == "linear_tc":
+        parts = _tc_plan(N, K, M, _EPI[epilogue])[0]
+        fn = lib.vapi_linear_tc
+    else:
+        parts = _prompt_plan(N, K, M, _EPI[epilogue])[2]
+        fn = lib.vapi_prompt_linear
     out_bf16 = out_f32 = sso = xwo = None
     out_stride = N
     if epilogue == "bf16":
@@ -452,17 +457,14 @@ def linear_tc(weight: torch.Tensor, *, act: Optional[torch.Tensor] = None, xw: O
     elif epilogue == "swiglu":
         out_stride = N // 2
         out_bf16 = torch.empty((M, N // 2), dtype=torch.bfloat16, device=weight.device)
-    elif epilogue == "resid":
-        _f32(resid, "residual stream")
-        if resid is None or tuple(resid.shape) != (M, N):
-            raise KernelError("the residual stream must be [M, N]")
-        if next_weight is not None:
-            sso = torch.empty((tiles, M), dtype=torch.float32, device=weight.device)
-            xwo = torch.empty((M, N), dtype=torch.bfloat16, device=weight.device)
     else:
-        raise KernelError(f"unknown epilogue {epilogue}")
-    lib = _lib("linear_tc")
-    _check(lib, lib.vapi_linear_tc(
+        _f32(resid, "residual stream")
+        if resid is None or tuple(resid.shape) != (M, N) or not resid.is_contiguous():
+            raise KernelError("the residual stream must be a contiguous [M, N]")
+        if next_weight is not None:
+            sso = torch.empty((parts, M), dtype=torch.float32, device=weight.device)
+            xwo = torch.empty((M, N), dtype=torch.bfloat16, device=weight.device)
+    _check(lib, fn(
         _p(weight), N, K, M, _PRO[pro], _p(src), _p(ss_in), 0 if ss_in is None else ss_in.shape[0], ctypes.c_float(eps),
         _EPI[epilogue], _p(out_bf16), _p(out_f32), ctypes.c_longlong(out_stride), _p(bias), _p(resid), _p(sso),
         _p(next_weight), _p(xwo), _p(status), _stream()))
@@ -471,18 +473,66 @@ def linear_tc(weight: torch.Tensor, *, act: Optional[torch.Tensor] = None, xw: O
     return out_bf16 if out_bf16 is not None else out_f32
 
 
+def linear_tc(weight: torch.Tensor, *, act: Optional[torch.Tensor] = None, xw: Optional[torch.Tensor] = None,
+              ss_in: Optional[torch.Tensor] = None, eps: float = 0.0, epilogue: str = "bf16",
+              bias: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
+              next_weight: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None):
+    """The tcgen05 / TMA product for 17..256 rows; same operands, epilogues and results as
+    :func:`skinny_linear`."""
+    return _fused_product("linear_tc", weight, act, xw, ss_in, eps, epilogue, bias, resid, next_weight, status)
+
+
+#: steps of more rows than TC_MAX_ROWS go to the persistent tcgen05 product of csrc/linear_prompt.cu
+#: (with its fused prologue and epilogues) from this many rows on; 0 keeps them on the library's
+#: product with separate norm / SwiGLU / add kernels
+PROMPT_MIN_ROWS = int(os.environ.get("VAPI_PROMPT_MIN_ROWS", "0"))
+
+
+def prompt_applies(rows: int, weight: torch.Tensor) -> bool:
+    """Whether the persistent tcgen05 product takes this product: bfloat16 weight, at least
+    PROMPT_MIN_ROWS rows, inner size a multiple of 8 (16-byte rows for TMA)."""
+    return (PROMPT_MIN_ROWS > 0 and rows >= PROMPT_MIN_ROWS and rows > TC_MAX_ROWS and weight.is_cuda
+            and weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.shape[1] % 8 == 0
+            and weight.shape[0] % 8 == 0 and weight.is_contiguous())
+
+
+def _prompt_plan(N: int, K: int, M: int, epi: int):
+    lib = _lib("linear_prompt")
+    b, pr, parts = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    lib.vapi_prompt_linear_plan(N, K, M, epi, ctypes.byref(b), ctypes.byref(pr), ctypes.byref(parts))
+    return b.value, pr.value, parts.value
+
+
+def prompt_force(bn: int = 0, pair: int = 0) -> None:
+    """Fix the tile (128 | 256 features) and the blocks working on a tile (1 | 2) of
+    :func:`prompt_linear` for the calls that follow; 0 gives the choice back to the kernel's plan."""
+    lib = _lib("linear_prompt")
+    _check(lib, lib.vapi_prompt_linear_force(bn, pair), launches=0)
+
+
+def prompt_linear(weight: torch.Tensor, *, act: Optional[torch.Tensor] = None, xw: Optional[torch.Tensor] = None,
+                  ss_in: Optional[torch.Tensor] = None, eps: float = 0.0, epilogue: str = "bf16",
+                  bias: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
+                  next_weight: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None):
+    """The persistent tcgen05 / TMA product for prompt-sized steps; same operands, epilogues and
+    results as :func:`skinny_linear`."""
+    return _fused_product("linear_prompt", weight, act, xw, ss_in, eps, epilogue, bias, resid, next_weight, status)
+
+
 def few_rows_applies(rows: int, weight: torch.Tensor) -> bool:
     """Whether one of this package's own products (with their fused prologues and epilogues)
     takes a step of ``rows`` rows against ``weight``."""
-    return skinny_applies(rows, weight) or tc_applies(rows, weight)
+    return skinny_applies(rows, weight) or tc_applies(rows, weight) or prompt_applies(rows, weight)
 
 
 def few_rows_linear(weight: torch.Tensor, **kw):
-    """:func:`skinny_linear` up to 16 rows, :func:`linear_tc` above."""
+    """:func:`skinny_linear` up to 16 rows, :func:`linear_tc` up to TC_MAX_ROWS, :func:`prompt_linear` above."""
     src = kw.get("act") if kw.get("act") is not None else kw.get("xw")
     if src.shape[0] <= SKINNY_MAX_ROWS:
         return skinny_linear(weight, **kw)
-    return linear_tc(weight, **kw)
+    if src.shape[0] <= TC_MAX_ROWS:
+        return linear_tc(weight, **kw)
+    return prompt_linear(weight, **kw)
 
 
 def skinny_f32_applies(rows: int, weight: torch.Tensor) -> bool:
