@@ -173,12 +173,13 @@ def trace_table(events):
 
 
 #: the calls that are matrix products (time against the tensor peak); the rest move bytes
-PRODUCTS = ("linear", "skinny_linear", "linear_tc", "skinny_shortconv")
+PRODUCTS = ("linear", "skinny_linear", "linear_tc", "prompt_linear", "skinny_shortconv")
 
 #: the package's kernels as the parts call them, with the library each lives in
 OPS = {"embed": "elementwise", "add_residual_ss": "elementwise", "resolve_tokens": "elementwise",
        "add_rmsnorm": "elementwise", "add_residual": "elementwise", "swiglu": "elementwise",
-       "skinny_linear": "gemv", "skinny_shortconv": "gemv", "linear_tc": "linear_tc", "rope_cos_sin": "rope",
+       "skinny_linear": "gemv", "skinny_shortconv": "gemv", "linear_tc": "linear_tc", "prompt_linear": "linear_prompt",
+       "rope_cos_sin": "rope",
        "qk_norm_rope_write": "rope", "paged_attention": "attention", "decode_attention_fused": "attention",
        "shortconv": "shortconv", "sample_rows": "sampling", "sample_truncated": "sampling", "linear": "library"}
 

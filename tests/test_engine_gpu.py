@@ -297,6 +297,45 @@ def test_captured_decode_at_serving_widths(sizes, tmp_path):
     assert float((rows[True] - want).abs().max()) < 0.02 * span
 
 
+@pytest.mark.parametrize("route", ["stream", "swiglu"])
+def test_prompt_sized_steps_on_the_persistent_product(tmp_path, monkeypatch, route):
+    """Prompt portions of 33 rows and more on csrc/linear_prompt.cu: every product of the step with
+    its fused prologue and epilogue (the stream form: deferred norms, residual adds, SwiGLU), or the
+    library's products with only the gate|up product and its SwiGLU on the own kernel (what prompts
+    run on unless told otherwise).  Whole, cut into portions, and beside decode tokens of others."""
+    from conftest import serving_width_config
+    from vapi_b200 import ops
+    from vapi_b200.engine.runner import ModelRunner
+    from vapi_b200.engine.step import StepEntry
+    from vapi_b200.weights import write_random_model
+    cfg = serving_width_config("700m")
+    d = write_random_model(str(tmp_path / "m"), cfg, 9, std=0.02, norm_init="perturbed", dtype=torch.bfloat16)
+    plain = plain_lfm2.PlainLfm2(d)
+    monkeypatch.setattr(ops, "PROMPT_MIN_ROWS", 33 if route == "stream" else 0)
+    monkeypatch.setattr(ops, "PROMPT_SWIGLU_MIN_ROWS", 33)
+    a, b, c = _prompts(cfg, 12, [300, 77, 140])
+    want_a, want_b, want_c = plain.logits(a), plain.logits(b), plain.logits(c)
+    span = float(want_a.max() - want_a.min())
+    r = ModelRunner.from_dir(d, dtype="bfloat16", num_pages=24, max_requests=4, max_batched_tokens=1024, max_context=512)
+    before = ops.launch_count
+    ra, rb, rc = r.cache.open("a"), r.cache.open("b"), r.cache.open("c")
+    assert r.cache.reserve(ra, 300) and r.cache.reserve(rb, 77) and r.cache.reserve(rc, 140)
+    # a whole, with logits everywhere; then b cut 40 + 36 + 1 with c's portions beside it
+    got = r.step([StepEntry(ra, a, list(range(300)))])
+    assert float((got.float().cpu() - want_a).abs().max()) < 0.03 * span
+    assert r.step([StepEntry(rb, b[:40], []), StepEntry(rc, c[:100], [])]) is None
+    got = r.step([StepEntry(rb, b[40:76], [35]), StepEntry(rc, c[100:], [39])])
+    assert float((got[0].float().cpu() - want_b[75]).abs().max()) < 0.03 * span
+    assert float((got[1].float().cpu() - want_c[139]).abs().max()) < 0.03 * span
+    got = r.step([StepEntry(rb, b[76:], [0])])
+    assert float((got[0].float().cpu() - want_b[76]).abs().max()) < 0.03 * span
+    r.check_status()
+    assert "linear_prompt" in ops.loaded_libraries and ops.launch_count > before
+    for x in (ra, rb, rc):
+        r.cache.close(x)
+    r.cache.check_invariants()
+
+
 def test_the_cache_is_sized_from_free_memory(tiny_dirs):
     """Without a page count the runner takes a fraction of the free device memory, less the state
     slots (crates/vapi-backend-candle/src/backend.rs:385-400), and never more pages than every

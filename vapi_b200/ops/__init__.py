@@ -503,6 +503,22 @@ def _prompt_plan(N: int, K: int, M: int, epi: int):
     return b.value, pr.value, parts.value
 
 
+#: a feed-forward's gate|up product with SwiGLU as its epilogue goes to the persistent tcgen05 product
+#: from this many rows on, also where the other products stay on the library (0: never)
+PROMPT_SWIGLU_MIN_ROWS = int(os.environ.get("VAPI_PROMPT_SWIGLU_MIN_ROWS", "256"))
+
+
+def linear_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``silu(x @ Wg.T) * (x @ Wu.T)`` for ``weight = [Wg; Wu]``: one kernel with SwiGLU as the
+    product's epilogue for prompt-sized bfloat16 steps, else the product followed by :func:`swiglu`."""
+    rows = x.shape[0]
+    if (x.dtype == torch.bfloat16 and 0 < PROMPT_SWIGLU_MIN_ROWS <= rows and rows > TC_MAX_ROWS and weight.is_cuda
+            and weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.shape[1] % 8 == 0 and weight.shape[0] % 16 == 0
+            and weight.is_contiguous() and x.is_contiguous()):
+        return prompt_linear(weight, act=x, epilogue="swiglu")
+    return swiglu(linear(x, weight))
+
+
 def prompt_force(bn: int = 0, pair: int = 0) -> None:
     """Fix the tile (128 | 256 features) and the blocks working on a tile (1 | 2) of
     :func:`prompt_linear` for the calls that follow; 0 gives the choice back to the kernel's plan."""

@@ -36,8 +36,7 @@ class SwiGLU(FeedForward):
         self.w_down = tensors[f"{prefix}{n['down']}.weight"].contiguous()
 
     def forward(self, f: torch.Tensor, ctx: Any) -> torch.Tensor:
-        g = ops.linear(f, self.w_gate_up)
-        return ops.linear(ops.swiglu(g), self.w_down)
+        return ops.linear(ops.linear_swiglu(f, self.w_gate_up), self.w_down)
 
     def forward_stream(self, f, ctx, x, next_weight):
         n = x.shape[0]
