@@ -1062,6 +1062,33 @@ def test_prompt_linear_plain_products(ops, prompt_tiles, M, N, K):
     assert int(st.item()) == 0
 
 
+@pytest.mark.parametrize("M", [35, 260])
+def test_prompt_linear_rows_that_are_not_16_byte_aligned(ops, prompt_tiles, M):
+    """Output rows whose pitch is no multiple of 8 elements take the value-by-value ends of the
+    epilogues: 100 SwiGLU features, a residual stream and plain outputs of 204 features."""
+    torch.manual_seed(34)
+    K, F, N = 96, 100, 204
+    a = torch.randn(M, K).to(torch.bfloat16)
+    w13 = (torch.randn(2 * F, K) * 0.1).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.1).to(torch.bfloat16)
+    st = torch.zeros(1, dtype=torch.int32).cuda()
+    gu = a.float() @ w13.float().t()
+    want_s = (gu[:, :F] / (1 + torch.exp(-gu[:, :F]))) * gu[:, F:]
+    s = ops.prompt_linear(dev(w13), act=dev(a), epilogue="swiglu", status=st)
+    torch.testing.assert_close(s.cpu().float(), want_s.to(torch.bfloat16).float(), atol=4e-2, rtol=3e-2)
+    y = a.float() @ w.float().t()
+    torch.testing.assert_close(ops.prompt_linear(dev(w), act=dev(a), epilogue="f32", status=st).cpu(), y, atol=3e-3, rtol=1e-3)
+    torch.testing.assert_close(ops.prompt_linear(dev(w), act=dev(a), epilogue="bf16", status=st).cpu().float(),
+                               y.to(torch.bfloat16).float(), atol=3e-2, rtol=2e-2)
+    x, nw = torch.randn(M, N), 1 + 0.1 * torch.randn(N)
+    xr = dev(x.clone())
+    ss, xw = ops.prompt_linear(dev(w), act=dev(a), epilogue="resid", resid=xr, next_weight=dev(nw), status=st)
+    torch.testing.assert_close(xr.cpu(), x + y, atol=3e-3, rtol=1e-3)
+    torch.testing.assert_close(ss.sum(0).cpu(), ((x + y) ** 2).sum(1), atol=2e-2, rtol=1e-3)
+    torch.testing.assert_close(xw.cpu().float(), ((x + y) * nw).to(torch.bfloat16).float(), atol=3e-2, rtol=2e-2)
+    assert int(st.item()) == 0
+
+
 @pytest.mark.parametrize("M", [40, 130, 700])
 def test_prompt_linear_fusions(ops, prompt_tiles, M):
     torch.manual_seed(33)
