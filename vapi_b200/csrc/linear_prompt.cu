@@ -17,14 +17,15 @@
 // each block holds (and finishes) the accumulator of its own 128 tokens.  Every operand byte then
 // crosses from L2 into a multiprocessor half as often.
 //
-// Roles (64 + 32 x epilogue warps threads).  Warp 0, one lane: TMA producer.  Warp 1: tensor-memory allocation, and one
-// lane of the even block: the MMA issue loop; tcgen05.commit hands a stage back to the producers
-// of both blocks and a finished accumulator to the epilogue warps of both.  Warps 2..: epilogue,
-// one token (and, with eight warps, one half of the tile's features) per thread: bfloat16 out | float out | SwiGLU (a tile's columns are BN/2 gate
-// features followed by the BN/2 matching up features) | add into the float residual stream with
-// what the next norm needs (bfloat16(stream * next norm weight), one partial sum of squares per
-// token and tile column).  The token operand may be the residual stream seen through a deferred
-// RMSNorm (see gemv.cu): then the epilogue scales every token's row by rsqrt(mean x^2 + eps).
+// Roles (64 threads and the epilogue warps).  Warp 0, one lane: TMA producer.  Warp 1: tensor-memory
+// allocation, and one lane of the even block: the MMA issue loop; tcgen05.commit hands a stage back
+// to the producers of both blocks and a finished accumulator to the epilogue warps of both.
+// Warps 2..: epilogue, a warp for 32 tokens of the tile, one token per thread while the sums come
+// out of tensor memory: bfloat16 out | float out | SwiGLU (a tile's columns are BN/2 gate features
+// followed by the BN/2 matching up features) | add into the float residual stream with what the
+// next norm needs (bfloat16(stream * next norm weight), one partial sum of squares per token and
+// tile column).  The token operand may be the residual stream seen through a deferred RMSNorm (see
+// gemv.cu): then the epilogue scales every token's row by rsqrt(mean x^2 + eps).
 //
 // Every mbarrier wait is bounded: after the limit a role records that it gave up, every role of the
 // block leaves its loop at its next wait, status 16 is recorded and the block drains to its end
