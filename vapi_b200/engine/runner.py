@@ -158,6 +158,12 @@ class ModelRunner:
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
         """Device work of a step for a prepared context; returns float32 logits [rows, vocab]
         or None when no logits are wanted (the caches are written either way)."""
+        if self.device.type == "cuda":
+            with ops.one_stream():
+                return self._forward(ctx)
+        return self._forward(ctx)
+
+    def _forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
         plan = self.plan
         if ctx.unknown_tokens:
             ops.resolve_tokens(ctx.tokens, ctx.token_src, self.sampled, self.status)

@@ -122,8 +122,27 @@ def _p(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+_held_stream = threading.local()
+
+
 def _stream() -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    h = getattr(_held_stream, "handle", None)
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream if h is None else h)
+
+
+class one_stream:
+    """Within the block every kernel of this module launches on the stream that is current at its
+    entry, looked up once instead of once per kernel (a step launches a few hundred).  The caller
+    must not switch streams inside the block."""
+
+    def __enter__(self):
+        self.before = getattr(_held_stream, "handle", None)
+        _held_stream.handle = torch.cuda.current_stream().cuda_stream if torch.cuda.is_available() else None
+        return self
+
+    def __exit__(self, *exc):
+        _held_stream.handle = self.before
+        return False
 
 
 def _contig(t: torch.Tensor, what: str) -> None:
