@@ -336,6 +336,38 @@ def test_prompt_sized_steps_on_the_persistent_product(tmp_path, monkeypatch, rou
     r.cache.check_invariants()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_step_runs_on_the_callers_stream(tiny_dirs, dtype):
+    """The kernels of a step launch on the stream that is current when the step begins (looked up
+    once per step): a step made under another stream than the default one gives the same logits,
+    and work queued on that stream before the step is waited for."""
+    from vapi_b200.engine.runner import ModelRunner
+    from vapi_b200.engine.step import StepEntry
+    (prompt,) = _prompts(TINY_D, 41, [37])
+    outs = []
+    for side in (False, True):
+        r = ModelRunner.from_dir(tiny_dirs["D"], dtype=dtype, num_pages=8, max_requests=2, max_batched_tokens=64, max_context=128)
+        rc = r.cache.open("a")
+        assert r.cache.reserve(rc, len(prompt) + 1)
+        if side:
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                torch.cuda._sleep(20_000_000)                       # the step must queue behind this, on s
+                r.step([StepEntry(rc, prompt[:30], [])])
+                lg = r.step([StepEntry(rc, prompt[30:], [6])])
+                tail = r.step([StepEntry(rc, [9], [0])])
+            torch.cuda.current_stream().wait_stream(s)
+        else:
+            r.step([StepEntry(rc, prompt[:30], [])])
+            lg = r.step([StepEntry(rc, prompt[30:], [6])])
+            tail = r.step([StepEntry(rc, [9], [0])])
+        torch.cuda.synchronize()
+        r.check_status()
+        outs.append((lg.float().cpu(), tail.float().cpu()))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
 def test_the_cache_is_sized_from_free_memory(tiny_dirs):
     """Without a page count the runner takes a fraction of the free device memory, less the state
     slots (crates/vapi-backend-candle/src/backend.rs:385-400), and never more pages than every
